@@ -1,0 +1,133 @@
+// Shared host/device helpers of the B200 NVFP4 path.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp4.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdint>
+
+#include "flashrt_b200.h"
+
+namespace frt {
+
+extern std::atomic<int64_t> g_launches;     // kernels launched by this library
+extern int g_opt_quant_encoder;             // FRT_OPT_QUANT_ENCODER
+extern int g_opt_gemm_config;               // FRT_OPT_GEMM_CONFIG
+
+// Status word written by kernels whose bounded waits ran out (one per device
+// context, lives in device global memory of this library).
+unsigned* device_status_word();
+
+inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
+
+inline int launch_result() {
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError() == cudaSuccess ? FRT_OK : FRT_E_LAUNCH;
+}
+
+inline bool aligned(const void* p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+
+// Byte offset of the UE4M3 scale of (row, 16-element block kb) in the swizzled
+// buffer of a tensor with `sf_cols` = ceil(dim/64) 512-byte tiles per 128 rows.
+__host__ __device__ __forceinline__ int64_t sf_offset(int row, int kb, int sf_cols) {
+  return (static_cast<int64_t>(row >> 7) * sf_cols + (kb >> 2)) * 512 +
+         (row & 31) * 16 + ((row >> 5) & 3) * 4 + (kb & 3);
+}
+
+#ifdef __CUDACC__
+// ---- NVFP4 block quantiser -------------------------------------------------
+
+// UE4M3 byte -> fp32 (exact).
+__device__ __forceinline__ float ue4m3_to_float(uint8_t b) {
+  return __half2float(__half(__nv_cvt_fp8_to_halfraw(b, __NV_E4M3)));
+}
+
+// max(amax/6, 1e-12) -> UE4M3 byte (round to nearest even, saturating).
+__device__ __forceinline__ uint8_t block_scale_byte(float amax) {
+  float d = __fdiv_rn(amax, 6.f);
+  if (d < 1e-12f) d = 1e-12f;
+  return static_cast<uint8_t>(__nv_cvt_float_to_fp8(d, __NV_SATFINITE, __NV_E4M3));
+}
+
+// Rule A (thresholds, ties toward the smaller magnitude) by a compare chain.
+// `!(a <= t)` keeps the NaN behaviour of an if/else-if chain of `<=`.
+__device__ __forceinline__ uint32_t e2m1_rule_a_chain(float q) {
+  const float a = fabsf(q);
+  uint32_t m = 0;
+  m += !(a <= 0.25f);
+  m += !(a <= 0.75f);
+  m += !(a <= 1.25f);
+  m += !(a <= 1.75f);
+  m += !(a <= 2.5f);
+  m += !(a <= 3.5f);
+  m += !(a <= 5.0f);
+  return m | (q < 0.f ? 8u : 0u);
+}
+
+// Rule A through the hardware e2m1 conversion.  The conversion rounds to
+// nearest even; replacing |q| by the float just below it with its lowest
+// mantissa bit set puts the value strictly on the rule-A side of every
+// threshold (thresholds have a clear low bit), so no tie is ever seen and the
+// hardware result equals the compare chain.  `q + 0` turns -0 into +0, whose
+// sign bit the chain would not set.
+__device__ __forceinline__ float rule_a_nudge(float q) {
+  const uint32_t u = __float_as_uint(__fadd_rn(q, 0.f));
+  const uint32_t mag = u & 0x7fffffffu;
+  const uint32_t nudged = ((mag == 0u ? 1u : mag) - 1u) | 1u;
+  return __uint_as_float((u & 0x80000000u) | nudged);
+}
+
+__device__ __forceinline__ uint32_t e2m1x2_rule_a_hw(float q_lo, float q_hi) {
+  return __nv_cvt_float2_to_fp4x2(make_float2(rule_a_nudge(q_lo), rule_a_nudge(q_hi)),
+                                  __NV_E2M1, cudaRoundNearest);
+}
+
+// Hardware round-to-nearest-even e2m1 pair ("rule B").
+__device__ __forceinline__ uint32_t e2m1x2_rne_hw(float q_lo, float q_hi) {
+  return __nv_cvt_float2_to_fp4x2(make_float2(q_lo, q_hi), __NV_E2M1, cudaRoundNearest);
+}
+
+enum : int { kEncHw = 0, kEncChain = 1, kEncRne = 2 };
+
+// Quantise 16 fp32 values: returns 8 packed bytes in a uint2 and the scale byte.
+template <int ENC>
+__device__ __forceinline__ uint2 quantize_block16(const float (&v)[16], uint8_t& sf_byte) {
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+  sf_byte = block_scale_byte(amax);
+  const float inv = __fdiv_rn(1.f, ue4m3_to_float(sf_byte));
+  uint32_t w[2] = {0u, 0u};
+#pragma unroll
+  for (int p = 0; p < 8; ++p) {
+    const float q0 = __fmul_rn(v[2 * p], inv);
+    const float q1 = __fmul_rn(v[2 * p + 1], inv);
+    uint32_t byte;
+    if (ENC == kEncHw) byte = e2m1x2_rule_a_hw(q0, q1);
+    else if (ENC == kEncRne) byte = e2m1x2_rne_hw(q0, q1);
+    else byte = e2m1_rule_a_chain(q0) | (e2m1_rule_a_chain(q1) << 4);
+    w[p >> 2] |= (byte & 0xffu) << (8 * (p & 3));
+  }
+  return make_uint2(w[0], w[1]);
+}
+
+__device__ __forceinline__ void unpack_bf16x8(const uint4& raw, float* out) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    out[2 * i] = __uint_as_float(w[i] << 16);
+    out[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+#endif  // __CUDACC__
+
+}  // namespace frt

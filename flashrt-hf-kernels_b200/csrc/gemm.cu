@@ -1,0 +1,458 @@
+// NVFP4 A4W4 block-scaled GEMM with bf16 output for sm_100a.
+//
+//   D[p, q] = alpha * sum_k P[p,k] * SFP[p,k/16] * Q[q,k] * SFQ[q,k/16]  (+ bias) (+ beta*C)
+//
+// P is the operand on the 128-lane (UMMA M) axis, Q the operand on the UMMA N
+// axis.  For prefill shapes P = activations and Q = weights; for small token
+// counts the host swaps them (P = weights, so every CTA streams 128 distinct
+// weight rows and the tokens sit on a narrow N axis) and the epilogue writes
+// the transposed tile.
+//
+// One persistent CTA per SM, 6 warps:
+//   warp 0      TMA producer: 128B-swizzled operand tiles (cp.async.bulk.tensor)
+//               and the swizzled scale-factor chunks (cp.async.bulk) into a
+//               STAGES-deep shared-memory ring, mbarrier complete_tx.
+//   warp 1      MMA issuer: tcgen05.cp of the scale chunks shared -> TMEM, then
+//               tcgen05.mma kind::mxf4nvf4 (K = 64 per instruction, 4 per stage)
+//               into one of ACC accumulator stages in TMEM; tcgen05.commit frees
+//               the smem stage / publishes the accumulator.
+//   warps 2..5  epilogue: tcgen05.ld the accumulator (one 32-lane TMEM quarter
+//               per warp), alpha / bias / residual in fp32, bf16 pack, 16-byte
+//               global stores; overlaps the next tile's mainloop when ACC == 2.
+//
+// Every wait on an mbarrier is bounded; a wait that runs out sets a bit in the
+// device status word and the CTA drains and returns.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include <mutex>
+
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace frt {
+
+namespace {
+
+__device__ unsigned g_status_word = 0;
+
+constexpr int BM = 128;            // UMMA M, rows of P per tile
+constexpr int BK = 256;            // elements of K per smem stage (128 bytes per row)
+constexpr int KT_PER_STAGE = 4;    // UMMA K = 64 elements
+constexpr int SF_TILE = 512;       // bytes of scales for 128 rows x 64 elements
+constexpr long long WAIT_LIMIT = 1ll << 31;   // SM clocks (~1 s) before a wait gives up
+
+struct GemmParams {
+  int P, Q, K;              // extents on the M axis, N axis, reduction
+  int p_tiles, q_tiles;     // tile counts
+  int k_tiles;              // ceil(K / 64)
+  int sf_cols;              // ceil(K / 64): 512-byte scale tiles per 128-row group
+  const uint8_t* sfp;       // swizzled scales of P
+  const uint8_t* sfq;       // swizzled scales of Q
+  int sfq_row_blocks;       // 128-row groups present in sfq
+  __nv_bfloat16* d;
+  const __nv_bfloat16* c;       // or null
+  const __nv_bfloat16* bias;    // or null
+  int ldd;                  // row stride of d and c, in elements
+  float alpha, beta;
+  int group_m;              // raster: tiles walk GROUP_M p-tiles before the next q-tile
+};
+
+template <int BN, int STAGES>
+struct SmemLayout {
+  static constexpr int A_BYTES = BM * 128;
+  static constexpr int B_BYTES = BN * 128;
+  static constexpr int SFQ_BLOCKS = BN <= 128 ? 1 : 2;   // 128-row scale groups a Q tile can touch
+  static constexpr int SFP_BYTES = KT_PER_STAGE * SF_TILE;
+  static constexpr int SFQ_BYTES = SFQ_BLOCKS * KT_PER_STAGE * SF_TILE;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFP_BYTES + SFQ_BYTES;
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+};
+
+__device__ __forceinline__ void tile_coords(int t, const GemmParams& p, int& pt, int& qt) {
+  const int per_group = p.group_m * p.q_tiles;
+  const int group = t / per_group;
+  const int first = group * p.group_m;
+  const int gsize = min(p.p_tiles - first, p.group_m);
+  const int r = t - group * per_group;
+  pt = first + r % gsize;
+  qt = r / gsize;
+}
+
+template <int BN, int STAGES, int ACC, bool SWAP>
+__global__ void __launch_bounds__(192, 1)
+nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
+                  const GemmParams p) {
+  using L = SmemLayout<BN, STAGES>;
+  constexpr int SFQ_COLS_PER_KT = L::SFQ_BLOCKS * 4;               // TMEM columns of Q scales per k-tile
+  constexpr int SF_COLS = KT_PER_STAGE * (4 + SFQ_COLS_PER_KT);    // per SF buffer
+  constexpr int ACC_COLS = ACC * BN;
+  static_assert(ACC_COLS + 2 * SF_COLS <= 512, "TMEM budget");
+  constexpr uint32_t IDESC = ptx::idesc_nvf4(BM, BN);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * L::STAGE_BYTES);
+  uint64_t* full = bars;                    // [STAGES] TMA -> MMA
+  uint64_t* empty = bars + STAGES;          // [STAGES] MMA -> TMA
+  uint64_t* acc_full = bars + 2 * STAGES;   // [ACC]    MMA -> epilogue
+  uint64_t* acc_empty = acc_full + ACC;     // [ACC]    epilogue -> MMA
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + ACC);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int total_tiles = p.p_tiles * p.q_tiles;
+  const int k_stages = (p.k_tiles + KT_PER_STAGE - 1) / KT_PER_STAGE;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < STAGES; ++i) { ptx::mbar_init(&full[i], 1); ptx::mbar_init(&empty[i], 1); }
+    for (int i = 0; i < ACC; ++i) { ptx::mbar_init(&acc_full[i], 1); ptx::mbar_init(&acc_empty[i], 4); }
+    *abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::prefetch_tensormap(&map_p);
+    ptx::prefetch_tensormap(&map_q);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(tmem_slot, 512);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ===================== TMA producer =====================
+    if (ptx::elect_one()) {
+      int it = 0;
+      for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
+        int pt, qt;
+        tile_coords(t, p, pt, qt);
+        const int q0 = qt * BN;
+        const int qblk0 = q0 >> 7;
+        for (int ks = 0; ks < k_stages; ++ks, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!ptx::mbar_wait_bounded(&empty[s], ph ^ 1, WAIT_LIMIT)) {
+            atomicOr(&g_status_word, 1u); *abort_flag = 1; break;
+          }
+          uint8_t* st = smem + s * L::STAGE_BYTES;
+          const int kts = min(KT_PER_STAGE, p.k_tiles - ks * KT_PER_STAGE);
+          int nblk = 0;
+          for (int b = 0; b < L::SFQ_BLOCKS; ++b) nblk += (qblk0 + b < p.sfq_row_blocks) ? 1 : 0;
+          const uint32_t bytes = L::A_BYTES + L::B_BYTES + kts * SF_TILE * (1 + nblk);
+          ptx::mbar_expect_tx(&full[s], bytes);
+          ptx::tma_load_2d(st, &map_p, &full[s], ks * 128, pt * BM);
+          ptx::tma_load_2d(st + L::A_BYTES, &map_q, &full[s], ks * 128, q0);
+          ptx::bulk_load(st + L::A_BYTES + L::B_BYTES,
+                         p.sfp + (static_cast<int64_t>(pt) * p.sf_cols + ks * KT_PER_STAGE) * SF_TILE,
+                         kts * SF_TILE, &full[s]);
+          for (int b = 0; b < nblk; ++b)
+            ptx::bulk_load(st + L::A_BYTES + L::B_BYTES + L::SFP_BYTES + b * KT_PER_STAGE * SF_TILE,
+                           p.sfq + (static_cast<int64_t>(qblk0 + b) * p.sf_cols + ks * KT_PER_STAGE) * SF_TILE,
+                           kts * SF_TILE, &full[s]);
+        }
+      }
+      // drain: wait until the MMA side has released every stage this thread armed,
+      // so no bulk copy is in flight when the CTA exits
+      if (!*abort_flag) {
+        for (int i = 0; i < STAGES && i < it; ++i) {
+          const int j = it - 1 - i;
+          if (!ptx::mbar_wait_bounded(&empty[j % STAGES], (j / STAGES) & 1, WAIT_LIMIT)) {
+            atomicOr(&g_status_word, 2u); break;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ===================== MMA issuer =====================
+    if (ptx::elect_one()) {
+      int it = 0, tl = 0;
+      for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x, ++tl) {
+        int pt, qt;
+        tile_coords(t, p, pt, qt);
+        const int a = tl % ACC;
+        const uint32_t aph = (tl / ACC) & 1;
+        if (!ptx::mbar_wait_bounded(&acc_empty[a], aph ^ 1, WAIT_LIMIT)) {
+          atomicOr(&g_status_word, 4u); *abort_flag = 1; break;
+        }
+        ptx::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + a * BN;
+        const int q_col_off = ((qt * BN) & 127) >> 5;       // tile start inside its first 128-row scale group
+        for (int ks = 0; ks < k_stages; ++ks, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!ptx::mbar_wait_bounded(&full[s], ph, WAIT_LIMIT)) {
+            atomicOr(&g_status_word, 8u); *abort_flag = 1; break;
+          }
+          ptx::tc_fence_after();
+          const uint32_t st = ptx::smem_u32(smem + s * L::STAGE_BYTES);
+          const uint32_t sf_tmem = tmem_base + ACC_COLS + (it & 1) * SF_COLS;
+          const uint64_t a_desc = ptx::desc_sw128_kmajor(st);
+          const uint64_t b_desc = ptx::desc_sw128_kmajor(st + L::A_BYTES);
+          const int kts = min(KT_PER_STAGE, p.k_tiles - ks * KT_PER_STAGE);
+          for (int kt = 0; kt < kts; ++kt) {
+            const uint32_t sfp_t = sf_tmem + kt * 4;
+            const uint32_t sfq_t = sf_tmem + KT_PER_STAGE * 4 + kt * SFQ_COLS_PER_KT;
+            ptx::tc_cp_32x128b_warpx4(sfp_t, ptx::desc_sf_32x16(st + L::A_BYTES + L::B_BYTES + kt * SF_TILE));
+#pragma unroll
+            for (int b = 0; b < L::SFQ_BLOCKS; ++b)
+              ptx::tc_cp_32x128b_warpx4(
+                  sfq_t + 4 * b,
+                  ptx::desc_sf_32x16(st + L::A_BYTES + L::B_BYTES + L::SFP_BYTES +
+                                     (b * KT_PER_STAGE + kt) * SF_TILE));
+            // +2 per k-tile: 32 bytes (64 e2m1) along K inside the 128-byte swizzle span
+            ptx::tc_mma_nvf4(d_tmem, a_desc + 2 * kt, b_desc + 2 * kt, IDESC, sfp_t, sfq_t + q_col_off,
+                             (ks | kt) != 0);
+          }
+          ptx::tc_commit(&empty[s]);
+        }
+        if (*abort_flag) break;
+        ptx::tc_commit(&acc_full[a]);
+      }
+    }
+  } else {
+    // ===================== epilogue (warps 2..5) =====================
+    const int quarter = warp & 3;      // TMEM lanes [32*quarter, +32)
+    int tl = 0;
+    for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x, ++tl) {
+      int pt, qt;
+      tile_coords(t, p, pt, qt);
+      const int a = tl % ACC;
+      const uint32_t aph = (tl / ACC) & 1;
+      if (!ptx::mbar_wait_bounded(&acc_full[a], aph, WAIT_LIMIT)) {
+        if (lane == 0) { atomicOr(&g_status_word, 16u); *abort_flag = 1; }
+        break;
+      }
+      ptx::tc_fence_after();
+      const int prow = pt * BM + quarter * 32 + lane;          // index on the P axis
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + a * BN;
+#pragma unroll 1
+      for (int cchunk = 0; cchunk < BN / 32 || (BN % 32 && cchunk * 32 < BN); ++cchunk) {
+        const int q_base = qt * BN + cchunk * 32;                // index on the Q axis
+        if (q_base >= p.Q) break;                                // warp-uniform
+        uint32_t r[32];
+        if (BN % 32 == 0 || cchunk * 32 + 32 <= BN) {
+          ptx::tc_ld_32x32b_x32(taddr + cchunk * 32, r);
+        } else {
+          uint32_t r16[16];
+          ptx::tc_ld_32x32b_x16(taddr + cchunk * 32, r16);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) { r[j] = r16[j]; r[16 + j] = 0; }
+        }
+        ptx::tc_wait_ld();
+        if (!SWAP) {
+          // thread = output row prow, 32 consecutive output columns from q_base
+          if (prow < p.P) {
+            const int64_t off = static_cast<int64_t>(prow) * p.ldd + q_base;
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              const int col = q_base + 8 * g;
+              if (col >= p.Q) break;
+              float v[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[8 * g + j]) * p.alpha;
+              if (p.bias != nullptr) {
+                float b[8];
+                unpack_bf16x8(__ldg(reinterpret_cast<const uint4*>(p.bias + col)), b);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] += b[j];
+              }
+              if (p.c != nullptr) {
+                float cc[8];
+                unpack_bf16x8(*reinterpret_cast<const uint4*>(p.c + off + 8 * g), cc);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] += p.beta * cc[j];
+              }
+              uint4 o;
+              o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
+              o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
+              *reinterpret_cast<uint4*>(p.d + off + 8 * g) = o;
+            }
+          }
+        } else {
+          // thread = output column prow (a weight row), columns of the tile = tokens
+          const float bias = (p.bias != nullptr && prow < p.P) ? __bfloat162float(p.bias[prow]) : 0.f;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int tok = q_base + j;
+            if (tok < p.Q && prow < p.P) {
+              const int64_t off = static_cast<int64_t>(tok) * p.ldd + prow;
+              float v = __uint_as_float(r[j]) * p.alpha + bias;
+              if (p.c != nullptr) v += p.beta * __bfloat162float(p.c[off]);
+              p.d[off] = __float2bfloat16_rn(v);
+            }
+          }
+        }
+      }
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&acc_empty[a]);
+    }
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) ptx::tmem_dealloc(tmem_base, 512);
+}
+
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+PFN_cuTensorMapEncodeTiled_v12000 get_encode() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
+  });
+  return fn;
+}
+
+// packed e2m1 [rows, K/2] bytes, row-major; box = 128 bytes x box_rows, 128B swizzle
+int make_operand_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
+  auto enc = get_encode();
+  if (!enc) return FRT_E_DRIVER;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K / 2), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K / 2)};
+  const cuuint32_t box[2] = {128, static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? FRT_OK : FRT_E_DRIVER;
+}
+
+struct DeviceInfo { int sms = 0; int cc_major = 0; bool ok = false; };
+DeviceInfo device_info() {
+  // per-device cache (index by current device)
+  static DeviceInfo cache[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return DeviceInfo{};
+  if (!cache[dev].ok) {
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) return DeviceInfo{};
+    cache[dev].sms = prop.multiProcessorCount;
+    cache[dev].cc_major = prop.major;
+    cache[dev].ok = true;
+  }
+  return cache[dev];
+}
+
+template <int BN, int STAGES, int ACC, bool SWAP>
+int launch_gemm(const CUtensorMap& mp, const CUtensorMap& mq, GemmParams& p, int sms, cudaStream_t st) {
+  using L = SmemLayout<BN, STAGES>;
+  auto kern = nvfp4_gemm_kernel<BN, STAGES, ACC, SWAP>;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_set[dev & 63]) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL) != cudaSuccess)
+      return FRT_E_LAUNCH;
+    attr_set[dev & 63] = true;
+  }
+  p.q_tiles = (p.Q + BN - 1) / BN;
+  p.p_tiles = (p.P + BM - 1) / BM;
+  const int tiles = p.p_tiles * p.q_tiles;
+  const int grid = tiles < sms ? tiles : sms;
+  kern<<<grid, 192, L::TOTAL, st>>>(mp, mq, p);
+  return launch_result();
+}
+
+}  // namespace
+
+unsigned* device_status_word() {
+  unsigned* ptr = nullptr;
+  cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_status_word);
+  return ptr;
+}
+
+// Shared by the dense and the small-M entry: P/Q already in kernel orientation.
+int run_gemm(const void* p_packed, const void* sfp, int P, const void* q_packed, const void* sfq, int Q, int K,
+             const void* bias, const void* c, void* d, int ldd, float alpha, float beta, bool swap,
+             int config, cudaStream_t st) {
+  const DeviceInfo di = device_info();
+  if (!di.ok || di.cc_major != 10) return FRT_E_DEVICE;
+  GemmParams p{};
+  p.P = P; p.Q = Q; p.K = K;
+  p.k_tiles = (K + 63) / 64;
+  p.sf_cols = p.k_tiles;
+  p.sfp = static_cast<const uint8_t*>(sfp);
+  p.sfq = static_cast<const uint8_t*>(sfq);
+  p.sfq_row_blocks = (Q + 127) / 128;
+  p.d = static_cast<__nv_bfloat16*>(d);
+  p.c = static_cast<const __nv_bfloat16*>(c);
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.ldd = ldd;
+  p.alpha = alpha; p.beta = beta;
+  p.group_m = 16;
+
+  // configuration: 1 = 128x128 (2 acc), 2 = 128x256 (1 acc), 3 = 128x192 (2 acc);
+  // swapped: 11 = N16, 12 = N32, 13 = N64, 14 = N128
+  int cfg = config;
+  if (cfg == 0) {
+    if (swap) cfg = Q <= 16 ? 11 : Q <= 32 ? 12 : Q <= 64 ? 13 : 14;
+    else cfg = 2;
+  }
+  int bn = 0;
+  switch (cfg) {
+    case 1: bn = 128; break; case 2: bn = 256; break; case 3: bn = 192; break;
+    case 11: bn = 16; break; case 12: bn = 32; break; case 13: bn = 64; break; case 14: bn = 128; break;
+    default: return FRT_E_UNSUPPORTED;
+  }
+  if ((cfg >= 11) != swap) return FRT_E_UNSUPPORTED;
+  if (bn < 32 && Q > bn) return FRT_E_UNSUPPORTED;   // a 16-row tile must start a 32-row scale group
+  CUtensorMap mp, mq;
+  if (int rc = make_operand_map(&mp, p_packed, P, K, BM)) return rc;
+  if (int rc = make_operand_map(&mq, q_packed, Q, K, bn)) return rc;
+  switch (cfg) {
+    case 1: return launch_gemm<128, 6, 2, false>(mp, mq, p, di.sms, st);
+    case 2: return launch_gemm<256, 4, 1, false>(mp, mq, p, di.sms, st);
+    case 3: return launch_gemm<192, 4, 2, false>(mp, mq, p, di.sms, st);
+    case 11: return launch_gemm<16, 8, 2, true>(mp, mq, p, di.sms, st);
+    case 12: return launch_gemm<32, 8, 2, true>(mp, mq, p, di.sms, st);
+    case 13: return launch_gemm<64, 8, 2, true>(mp, mq, p, di.sms, st);
+    case 14: return launch_gemm<128, 6, 2, true>(mp, mq, p, di.sms, st);
+  }
+  return FRT_E_UNSUPPORTED;
+}
+
+}  // namespace frt
+
+using namespace frt;
+
+extern "C" {
+
+int frt_nvfp4_gemm_bf16(const void* a, const void* sfa, const void* b, const void* sfb, const void* bias,
+                        const void* c, void* d, int M, int N, int K, float alpha, float beta, void* stream) {
+  if (!a || !sfa || !b || !sfb || !d) return FRT_E_NULL;
+  if (M <= 0 || N <= 0 || K <= 0 || K % 32 != 0 || N % 8 != 0) return FRT_E_SHAPE;
+  if (!aligned(a, 16) || !aligned(b, 16) || !aligned(d, 16) || !aligned(c, 16) || !aligned(bias, 16) ||
+      !aligned(sfa, 16) || !aligned(sfb, 16))
+    return FRT_E_ALIGN;
+  if (beta != 0.f && c == nullptr) return FRT_E_NULL;
+  const void* cc = beta != 0.f ? c : nullptr;
+  const int cfg = g_opt_gemm_config;
+  const bool swap = cfg ? cfg >= 11 : (M <= 64);
+  if (swap) return run_gemm(b, sfb, N, a, sfa, M, K, bias, cc, d, N, alpha, beta, true, cfg, as_stream(stream));
+  return run_gemm(a, sfa, M, b, sfb, N, K, bias, cc, d, N, alpha, beta, false, cfg, as_stream(stream));
+}
+
+int frt_device_status(void* stream, unsigned* status_out) {
+  if (!status_out) return FRT_E_NULL;
+  unsigned* w = device_status_word();
+  if (!w) return FRT_E_LAUNCH;
+  cudaStream_t st = as_stream(stream);
+  unsigned v = 0;
+  if (cudaMemcpyAsync(&v, w, sizeof(v), cudaMemcpyDeviceToHost, st) != cudaSuccess) return FRT_E_LAUNCH;
+  if (cudaStreamSynchronize(st) != cudaSuccess) return FRT_E_LAUNCH;
+  *status_out = v;
+  if (v != 0 && cudaMemsetAsync(w, 0, sizeof(v), st) != cudaSuccess) return FRT_E_LAUNCH;
+  return FRT_OK;
+}
+
+}  // extern "C"

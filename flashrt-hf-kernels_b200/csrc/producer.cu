@@ -1,0 +1,427 @@
+// HBM-bound kernels of the NVFP4 path: scale-factor layout, stand-alone
+// quantiser / dequantiser, and the fused (residual-add +) RMSNorm -> NVFP4
+// producer.  Hand-written for sm_100a; every kernel touches each byte of its
+// operands exactly once, with 128-bit loads.
+#include "common.cuh"
+
+namespace frt {
+
+std::atomic<int64_t> g_launches{0};
+int g_opt_quant_encoder = 0;
+int g_opt_gemm_config = 0;
+
+namespace {
+
+// ---------------------------------------------------------------------------
+// linear [rows, nb] -> swizzled.  One thread moves the 4 scale bytes of one
+// (row, 64-element group): a 4-byte read (or byte reads at a ragged edge) and
+// one aligned 4-byte write.
+// ---------------------------------------------------------------------------
+__global__ void sf_linear_to_swizzled_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst,
+                                             int rows, int nb, int sf_cols, bool vec_ok) {
+  const int g = blockIdx.x * blockDim.x + threadIdx.x;   // 4-block group in the row
+  const int row = blockIdx.y;
+  if (g >= sf_cols) return;
+  const uint8_t* s = src + static_cast<int64_t>(row) * nb + 4 * g;
+  uint8_t* d = dst + sf_offset(row, 4 * g, sf_cols);
+  if (vec_ok && 4 * g + 4 <= nb) {
+    *reinterpret_cast<uint32_t*>(d) = *reinterpret_cast<const uint32_t*>(s);
+  } else {
+    for (int j = 0; j < 4 && 4 * g + j < nb; ++j) d[j] = s[j];
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Stand-alone quantiser: one thread per 16-element block (two 16-byte loads,
+// one 8-byte store); a warp covers 1 KiB of one row.
+// ---------------------------------------------------------------------------
+template <int ENC, bool FP16>
+__global__ void __launch_bounds__(256)
+quantize_kernel(const uint4* __restrict__ src, uint2* __restrict__ packed, uint8_t* __restrict__ sf,
+                int rows, int nb, int sf_cols) {
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<int64_t>(rows) * nb) return;
+  const int row = static_cast<int>(idx / nb);
+  const int kb = static_cast<int>(idx - static_cast<int64_t>(row) * nb);
+  const uint4 r0 = __ldcs(src + 2 * idx);
+  const uint4 r1 = __ldcs(src + 2 * idx + 1);
+  float v[16];
+  if (FP16) {
+    const __half2* h0 = reinterpret_cast<const __half2*>(&r0);
+    const __half2* h1 = reinterpret_cast<const __half2*>(&r1);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 a = __half22float2(h0[i]);
+      const float2 b = __half22float2(h1[i]);
+      v[2 * i] = a.x; v[2 * i + 1] = a.y;
+      v[8 + 2 * i] = b.x; v[8 + 2 * i + 1] = b.y;
+    }
+  } else {
+    unpack_bf16x8(r0, v);
+    unpack_bf16x8(r1, v + 8);
+  }
+  uint8_t sfb;
+  const uint2 out = quantize_block16<ENC>(v, sfb);
+  packed[idx] = out;
+  sf[sf_offset(row, kb, sf_cols)] = sfb;
+}
+
+// ---------------------------------------------------------------------------
+// Dequantiser (validation helper): one thread per block, fp16 out.
+// ---------------------------------------------------------------------------
+__global__ void dequantize_kernel(const uint2* __restrict__ packed, const uint8_t* __restrict__ sf,
+                                  uint4* __restrict__ out, int rows, int nb, int sf_cols) {
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<int64_t>(rows) * nb) return;
+  const int row = static_cast<int>(idx / nb);
+  const int kb = static_cast<int>(idx - static_cast<int64_t>(row) * nb);
+  const float s = ue4m3_to_float(sf[sf_offset(row, kb, sf_cols)]);
+  const uint2 p = packed[idx];
+  const uint32_t w[2] = {p.x, p.y};
+  __half h[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const uint32_t c = (w[i >> 3] >> (4 * (i & 7))) & 0xfu;
+    const uint32_t m = c & 7u;
+    // e2m1 magnitudes 0,.5,1,1.5,2,3,4,6
+    const float mag = m < 2 ? 0.5f * m : (m & 1 ? 1.5f : 1.0f) * static_cast<float>(1 << ((m >> 1) - 1));
+    h[i] = __float2half_rn((c & 8u) ? -mag * s : mag * s);
+  }
+  out[2 * idx] = *reinterpret_cast<uint4*>(h);
+  out[2 * idx + 1] = *reinterpret_cast<uint4*>(h + 8);
+}
+
+// ---------------------------------------------------------------------------
+// Fused (residual-add +) RMSNorm (-> NVFP4).
+//
+// A CTA is 4 warps.  A row of nb = dim/16 blocks is covered by W in {1,2,4}
+// warps, so a CTA holds 4/W rows.  In pass i lane l of sub-warp w owns block
+// s = i*32*W + w*32 + l: two 16-byte loads per tensor, and consecutive lanes
+// read consecutive 32-byte pieces, so every pass of a warp is one contiguous
+// 1 KiB segment per tensor.  All loads of the row are issued before the first
+// use; the row then lives in registers (ITERS*16 fp32 per lane) through the
+// sum-of-squares reduction, so global memory is read once and written once.
+//
+// The summation order is fixed (per-lane running sum in pass and element
+// order with separately rounded multiply and add, xor butterfly 16..1, then
+// warp totals in warp order) so that a CPU restatement reproduces rstd bit
+// for bit.
+// ---------------------------------------------------------------------------
+struct NormParams {
+  uint4* residual;        // bf16 [rows, dim] or null (in/out)
+  const uint4* x;         // bf16 [rows, dim]
+  const uint4* weight;    // bf16 [dim] or null
+  uint4* normed;          // bf16 [rows, dim] or null
+  uint2* packed;          // u8   [rows, dim/2] or null when QUANT is false
+  uint8_t* sf;            // swizzled scales
+  int rows, nb, sf_cols;
+  float eps, inv_global_scale;
+  float dim_f;
+  unsigned flags;
+};
+
+template <int ITERS, int W, bool HAS_RES, bool QUANT, int ENC>
+__global__ void __launch_bounds__(128)
+norm_quant_kernel(const NormParams p) {
+  __shared__ float warp_sums[4];
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  constexpr int ROWS_PER_CTA = 4 / W;
+  const int row = blockIdx.x * ROWS_PER_CTA + warp / W;
+  const int sub = warp % W;
+  const bool row_ok = row < p.rows;
+  const int64_t row_base = static_cast<int64_t>(row) * p.nb;   // in blocks
+
+  float v[ITERS][16];
+  float part = 0.f;
+
+  // ---- issue every load of the row --------------------------------------
+  uint4 xr[ITERS][2];
+  uint4 rr[HAS_RES ? ITERS : 1][2];
+#pragma unroll
+  for (int i = 0; i < ITERS; ++i) {
+    const int s = i * 32 * W + sub * 32 + lane;
+    if (row_ok && s < p.nb) {
+      xr[i][0] = __ldcs(p.x + 2 * (row_base + s));
+      xr[i][1] = __ldcs(p.x + 2 * (row_base + s) + 1);
+      if (HAS_RES) {
+        rr[i][0] = __ldcs(p.residual + 2 * (row_base + s));
+        rr[i][1] = __ldcs(p.residual + 2 * (row_base + s) + 1);
+      }
+    } else {
+      xr[i][0] = xr[i][1] = make_uint4(0, 0, 0, 0);
+      if (HAS_RES) rr[i][0] = rr[i][1] = make_uint4(0, 0, 0, 0);
+    }
+  }
+
+  // ---- residual add, in-place store, running sum of squares -------------
+#pragma unroll
+  for (int i = 0; i < ITERS; ++i) {
+    const int s = i * 32 * W + sub * 32 + lane;
+    unpack_bf16x8(xr[i][0], v[i]);
+    unpack_bf16x8(xr[i][1], v[i] + 8);
+    if (HAS_RES) {
+      float r[16];
+      unpack_bf16x8(rr[i][0], r);
+      unpack_bf16x8(rr[i][1], r + 8);
+#pragma unroll
+      for (int j = 0; j < 16; ++j) v[i][j] = __fadd_rn(r[j], v[i][j]);
+      uint4 o0, o1;
+      o0.x = pack_bf16x2(v[i][0], v[i][1]);   o0.y = pack_bf16x2(v[i][2], v[i][3]);
+      o0.z = pack_bf16x2(v[i][4], v[i][5]);   o0.w = pack_bf16x2(v[i][6], v[i][7]);
+      o1.x = pack_bf16x2(v[i][8], v[i][9]);   o1.y = pack_bf16x2(v[i][10], v[i][11]);
+      o1.z = pack_bf16x2(v[i][12], v[i][13]); o1.w = pack_bf16x2(v[i][14], v[i][15]);
+      if (row_ok && s < p.nb) {
+        __stcs(p.residual + 2 * (row_base + s), o0);
+        __stcs(p.residual + 2 * (row_base + s) + 1, o1);
+      }
+      // sum of squares always comes from the fp32 sums
+#pragma unroll
+      for (int j = 0; j < 16; ++j) part = __fadd_rn(part, __fmul_rn(v[i][j], v[i][j]));
+      if (p.flags & FRT_PRODUCER_NORM_FROM_BF16_RESIDUAL) {   // norm input = rounded residual
+        unpack_bf16x8(o0, v[i]);
+        unpack_bf16x8(o1, v[i] + 8);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) part = __fadd_rn(part, __fmul_rn(v[i][j], v[i][j]));
+    }
+  }
+
+  // ---- row reduction -------------------------------------------------------
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) part = __fadd_rn(part, __shfl_xor_sync(0xffffffffu, part, o));
+  float ssq = part;
+  if (W > 1) {
+    if (lane == 0) warp_sums[warp] = part;
+    __syncthreads();
+    const int first = (warp / W) * W;
+    ssq = warp_sums[first];
+#pragma unroll
+    for (int w = 1; w < W; ++w) ssq = __fadd_rn(ssq, warp_sums[first + w]);
+  }
+  const float rstd = __frsqrt_rn(__fadd_rn(__fdiv_rn(ssq, p.dim_f), p.eps));
+  if (!row_ok) return;
+
+  // ---- scale, (round,) quantise, store ----------------------------------------
+  const bool one_plus = p.flags & FRT_PRODUCER_ONE_PLUS_W;
+  const bool round_bf16 = p.flags & FRT_PRODUCER_ROUND_BF16;
+  const bool use_gs = p.inv_global_scale != 1.0f;
+#pragma unroll
+  for (int i = 0; i < ITERS; ++i) {
+    const int s = i * 32 * W + sub * 32 + lane;
+    if (s >= p.nb) continue;
+    float g[16];
+    if (p.weight != nullptr) {
+      const uint4 w0 = __ldg(p.weight + 2 * s);
+      const uint4 w1 = __ldg(p.weight + 2 * s + 1);
+      unpack_bf16x8(w0, g);
+      unpack_bf16x8(w1, g + 8);
+      if (one_plus) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) g[j] = __fadd_rn(1.f, g[j]);
+      }
+#pragma unroll
+      for (int j = 0; j < 16; ++j) v[i][j] = __fmul_rn(__fmul_rn(v[i][j], rstd), g[j]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) v[i][j] = __fmul_rn(v[i][j], rstd);
+    }
+    if (use_gs) {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) v[i][j] = __fmul_rn(v[i][j], p.inv_global_scale);
+    }
+    if (p.normed != nullptr || round_bf16) {
+      uint4 o0, o1;
+      o0.x = pack_bf16x2(v[i][0], v[i][1]);   o0.y = pack_bf16x2(v[i][2], v[i][3]);
+      o0.z = pack_bf16x2(v[i][4], v[i][5]);   o0.w = pack_bf16x2(v[i][6], v[i][7]);
+      o1.x = pack_bf16x2(v[i][8], v[i][9]);   o1.y = pack_bf16x2(v[i][10], v[i][11]);
+      o1.z = pack_bf16x2(v[i][12], v[i][13]); o1.w = pack_bf16x2(v[i][14], v[i][15]);
+      if (p.normed != nullptr) {
+        p.normed[2 * (row_base + s)] = o0;
+        p.normed[2 * (row_base + s) + 1] = o1;
+      }
+      if (round_bf16) {
+        unpack_bf16x8(o0, v[i]);
+        unpack_bf16x8(o1, v[i] + 8);
+      }
+    }
+    if (QUANT) {
+      uint8_t sfb;
+      uint2 out;
+      if (p.flags & FRT_PRODUCER_RNE_E2M1) out = quantize_block16<kEncRne>(v[i], sfb);
+      else out = quantize_block16<ENC>(v[i], sfb);
+      p.packed[row_base + s] = out;
+      p.sf[sf_offset(row, s, p.sf_cols)] = sfb;
+    }
+  }
+}
+
+template <int ITERS, int W>
+int launch_norm(const NormParams& p, bool has_res, bool quant, cudaStream_t st) {
+  const int rows_per_cta = 4 / W;
+  const dim3 grid((p.rows + rows_per_cta - 1) / rows_per_cta), block(128);
+  const bool chain = g_opt_quant_encoder == 1;
+#define FRT_LAUNCH(HR, Q, E) norm_quant_kernel<ITERS, W, HR, Q, E><<<grid, block, 0, st>>>(p)
+  if (!quant) {
+    if (has_res) FRT_LAUNCH(true, false, kEncHw); else FRT_LAUNCH(false, false, kEncHw);
+  } else if (chain) {
+    if (has_res) FRT_LAUNCH(true, true, kEncChain); else FRT_LAUNCH(false, true, kEncChain);
+  } else {
+    if (has_res) FRT_LAUNCH(true, true, kEncHw); else FRT_LAUNCH(false, true, kEncHw);
+  }
+#undef FRT_LAUNCH
+  return launch_result();
+}
+
+int dispatch_norm(NormParams& p, bool has_res, bool quant, cudaStream_t st) {
+  const int nb = p.nb;
+  if (nb <= 32) return launch_norm<1, 1>(p, has_res, quant, st);
+  if (nb <= 64) return launch_norm<2, 1>(p, has_res, quant, st);
+  if (nb <= 128) return launch_norm<4, 1>(p, has_res, quant, st);
+  if (nb <= 256) return launch_norm<8, 1>(p, has_res, quant, st);
+  if (nb <= 512) return launch_norm<8, 2>(p, has_res, quant, st);
+  return launch_norm<8, 4>(p, has_res, quant, st);
+}
+
+int check_norm_args(const void* x, int rows, int dim) {
+  if (!x) return FRT_E_NULL;
+  if (rows <= 0 || dim <= 0 || dim % 16 != 0) return FRT_E_SHAPE;
+  if (dim > 16384) return FRT_E_UNSUPPORTED;
+  return FRT_OK;
+}
+
+}  // namespace
+}  // namespace frt
+
+using namespace frt;
+
+extern "C" {
+
+const char* frt_error_string(int rc) {
+  switch (rc) {
+    case FRT_OK: return "ok";
+    case FRT_E_NULL: return "a required pointer is null";
+    case FRT_E_SHAPE: return "invalid shape (non-positive or not divisible as required)";
+    case FRT_E_ALIGN: return "pointer alignment violated";
+    case FRT_E_UNSUPPORTED: return "shape outside the supported range";
+    case FRT_E_LAUNCH: return "CUDA launch failed";
+    case FRT_E_DEVICE: return "device is not compute capability 10.x (B200)";
+    case FRT_E_DRIVER: return "tensor-map encode failed";
+    case FRT_E_TOO_LARGE: return "size beyond the fixed maximum of this entry point";
+    default: return "unknown error";
+  }
+}
+
+int64_t frt_nvfp4_sf_swizzled_bytes(int rows, int dim) {
+  if (rows <= 0 || dim <= 0) return 0;
+  return static_cast<int64_t>((rows + 127) / 128) * ((dim + 63) / 64) * 512;
+}
+
+int64_t frt_nvfp4_sf_offset(int row, int k, int dim) { return sf_offset(row, k >> 4, (dim + 63) >> 6); }
+
+int64_t frt_launch_count(void) { return g_launches.load(); }
+
+int frt_set_option(int key, int value) {
+  int prev = -1;
+  if (key == FRT_OPT_QUANT_ENCODER) { prev = g_opt_quant_encoder; g_opt_quant_encoder = value; }
+  if (key == FRT_OPT_GEMM_CONFIG) { prev = g_opt_gemm_config; g_opt_gemm_config = value; }
+  return prev;
+}
+
+int frt_nvfp4_sf_linear_to_swizzled(const void* src, void* dst, int rows, int dim, void* stream) {
+  if (!src || !dst) return FRT_E_NULL;
+  if (rows <= 0 || dim <= 0 || dim % 16 != 0) return FRT_E_SHAPE;
+  if (!aligned(dst, 4)) return FRT_E_ALIGN;
+  const int nb = dim / 16, sf_cols = (dim + 63) / 64;
+  const bool vec_ok = aligned(src, 4) && (nb & 3) == 0;   // else byte moves
+  const dim3 block(128), grid((sf_cols + 127) / 128, rows);
+  sf_linear_to_swizzled_kernel<<<grid, block, 0, as_stream(stream)>>>(
+      static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst), rows, nb, sf_cols, vec_ok);
+  return launch_result();
+}
+
+int frt_nvfp4_quantize(const void* src, int src_dtype, void* packed, void* sf, int rows, int dim, void* stream) {
+  if (!src || !packed || !sf) return FRT_E_NULL;
+  if (rows <= 0 || dim <= 0 || dim % 16 != 0) return FRT_E_SHAPE;
+  if (src_dtype != FRT_DTYPE_BF16 && src_dtype != FRT_DTYPE_FP16) return FRT_E_UNSUPPORTED;
+  if (!aligned(src, 16) || !aligned(packed, 8)) return FRT_E_ALIGN;
+  const int nb = dim / 16, sf_cols = (dim + 63) / 64;
+  const int64_t total = static_cast<int64_t>(rows) * nb;
+  const dim3 block(256), grid(static_cast<unsigned>((total + 255) / 256));
+  auto s = static_cast<const uint4*>(src);
+  auto pk = static_cast<uint2*>(packed);
+  auto sfp = static_cast<uint8_t*>(sf);
+  cudaStream_t st = as_stream(stream);
+  const bool chain = g_opt_quant_encoder == 1;
+  if (src_dtype == FRT_DTYPE_FP16) {
+    if (chain) quantize_kernel<kEncChain, true><<<grid, block, 0, st>>>(s, pk, sfp, rows, nb, sf_cols);
+    else quantize_kernel<kEncHw, true><<<grid, block, 0, st>>>(s, pk, sfp, rows, nb, sf_cols);
+  } else {
+    if (chain) quantize_kernel<kEncChain, false><<<grid, block, 0, st>>>(s, pk, sfp, rows, nb, sf_cols);
+    else quantize_kernel<kEncHw, false><<<grid, block, 0, st>>>(s, pk, sfp, rows, nb, sf_cols);
+  }
+  return launch_result();
+}
+
+int frt_nvfp4_dequantize_fp16(const void* packed, const void* sf, void* out, int rows, int dim, void* stream) {
+  if (!packed || !sf || !out) return FRT_E_NULL;
+  if (rows <= 0 || dim <= 0 || dim % 16 != 0) return FRT_E_SHAPE;
+  if (!aligned(out, 16) || !aligned(packed, 8)) return FRT_E_ALIGN;
+  const int nb = dim / 16, sf_cols = (dim + 63) / 64;
+  const int64_t total = static_cast<int64_t>(rows) * nb;
+  dequantize_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, as_stream(stream)>>>(
+      static_cast<const uint2*>(packed), static_cast<const uint8_t*>(sf), static_cast<uint4*>(out), rows, nb, sf_cols);
+  return launch_result();
+}
+
+int frt_norm_quant_nvfp4(void* residual, const void* x, const void* weight, float eps, float inv_global_scale,
+                         void* normed, void* packed, void* sf, int rows, int dim, unsigned flags, void* stream) {
+  if (int rc = check_norm_args(x, rows, dim)) return rc;
+  if (!packed || !sf) return FRT_E_NULL;
+  if (!aligned(x, 16) || !aligned(residual, 16) || !aligned(weight, 16) || !aligned(normed, 16) ||
+      !aligned(packed, 8))
+    return FRT_E_ALIGN;
+  NormParams p{};
+  p.residual = static_cast<uint4*>(residual);
+  p.x = static_cast<const uint4*>(x);
+  p.weight = static_cast<const uint4*>(weight);
+  p.normed = static_cast<uint4*>(normed);
+  p.packed = static_cast<uint2*>(packed);
+  p.sf = static_cast<uint8_t*>(sf);
+  p.rows = rows; p.nb = dim / 16; p.sf_cols = (dim + 63) / 64;
+  p.eps = eps; p.inv_global_scale = inv_global_scale; p.dim_f = static_cast<float>(dim);
+  p.flags = flags;
+  return dispatch_norm(p, residual != nullptr, true, as_stream(stream));
+}
+
+int frt_rms_norm_bf16(const void* x, const void* weight, void* out, int rows, int dim, float eps, void* stream) {
+  if (int rc = check_norm_args(x, rows, dim)) return rc;
+  if (!weight || !out) return FRT_E_NULL;
+  if (!aligned(x, 16) || !aligned(weight, 16) || !aligned(out, 16)) return FRT_E_ALIGN;
+  NormParams p{};
+  p.x = static_cast<const uint4*>(x);
+  p.weight = static_cast<const uint4*>(weight);
+  p.normed = static_cast<uint4*>(out);
+  p.rows = rows; p.nb = dim / 16; p.sf_cols = (dim + 63) / 64;
+  p.eps = eps; p.inv_global_scale = 1.0f; p.dim_f = static_cast<float>(dim);
+  return dispatch_norm(p, false, false, as_stream(stream));
+}
+
+int frt_residual_add_rms_norm_bf16(void* residual, const void* x, const void* weight, void* out,
+                                   int rows, int dim, float eps, void* stream) {
+  if (int rc = check_norm_args(x, rows, dim)) return rc;
+  if (!residual || !weight || !out) return FRT_E_NULL;
+  if (!aligned(x, 16) || !aligned(weight, 16) || !aligned(out, 16) || !aligned(residual, 16)) return FRT_E_ALIGN;
+  NormParams p{};
+  p.residual = static_cast<uint4*>(residual);
+  p.x = static_cast<const uint4*>(x);
+  p.weight = static_cast<const uint4*>(weight);
+  p.normed = static_cast<uint4*>(out);
+  p.rows = rows; p.nb = dim / 16; p.sf_cols = (dim + 63) / 64;
+  p.eps = eps; p.inv_global_scale = 1.0f; p.dim_f = static_cast<float>(dim);
+  p.flags = FRT_PRODUCER_NORM_FROM_BF16_RESIDUAL;
+  return dispatch_norm(p, true, false, as_stream(stream));
+}
+
+}  // extern "C"

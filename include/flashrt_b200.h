@@ -1,0 +1,164 @@
+/*
+ * flashrt_b200.h -- C ABI of the B200 (sm_100a) NVFP4 low-bit linear path.
+ *
+ * Every entry point takes plain device pointers, int sizes, float scalars and
+ * a CUDA stream handle (cudaStream_t passed as void*), launches asynchronously
+ * on that stream and returns 0 on success or a negative FRT_E_* code.  Nothing
+ * here allocates, synchronises or keeps host state between calls (except
+ * where a comment says otherwise), so every call can be captured into a CUDA
+ * graph.  The caller owns every buffer.
+ *
+ * Each declaration cites the reference interface it replaces, as
+ * <path inside the reference project>:<line>.
+ */
+#ifndef FLASHRT_B200_H_
+#define FLASHRT_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- return codes ------------------------------------------------------ */
+#define FRT_OK               0
+#define FRT_E_NULL          -1   /* a required pointer is null                  */
+#define FRT_E_SHAPE         -2   /* a size is non-positive or not divisible     */
+#define FRT_E_ALIGN         -3   /* a pointer misses its alignment              */
+#define FRT_E_UNSUPPORTED   -4   /* shape outside what the kernels cover        */
+#define FRT_E_LAUNCH        -5   /* the CUDA runtime refused the launch         */
+#define FRT_E_DEVICE        -6   /* current device is not compute capability 10 */
+#define FRT_E_DRIVER        -7   /* tensor-map encode failed                    */
+#define FRT_E_TOO_LARGE     -8   /* size beyond a documented fixed maximum      */
+
+const char* frt_error_string(int rc);
+
+/* ---- element types ----------------------------------------------------- */
+#define FRT_DTYPE_BF16 0
+#define FRT_DTYPE_FP16 1
+
+/* ---- scale-factor layout ------------------------------------------------
+ * Bytes of the swizzled UE4M3 scale buffer of a [rows, dim] NVFP4 tensor:
+ * ceil(rows/128) * ceil(dim/64) * 512.
+ * replaces nvfp4_sf_swizzled_bytes, flashrt-nvfp4/csrc/nvfp4_sf_reshape_sm120.cuh:26 */
+int64_t frt_nvfp4_sf_swizzled_bytes(int rows, int dim);
+
+/* Byte offset of the scale of (row, element k) inside that buffer.
+ * replaces sfa_offset_128x64, fp4-gemm/csrc/sfa_layout.cuh:12 */
+int64_t frt_nvfp4_sf_offset(int row, int k, int dim);
+
+/* linear [rows, dim/16] u8 -> swizzled; padding bytes of dst are not written.
+ * replaces nvfp4_sf_linear_to_swizzled, flashrt-nvfp4/csrc/nvfp4_sf_reshape_sm120.cuh:33 */
+int frt_nvfp4_sf_linear_to_swizzled(const void* src_linear, void* dst_swizzled,
+                                    int rows, int dim, void* stream);
+
+/* ---- stand-alone quantiser / dequantiser --------------------------------
+ * src [rows, dim] bf16 or fp16 (16-byte aligned, dim % 16 == 0) ->
+ * packed [rows, dim/2] u8 (8-byte aligned) + swizzled UE4M3 scales.
+ * Rule: d = max(amax/6, 1e-12); sf = e4m3_rn(d); q = v * (1/float(sf));
+ * e2m1 code by thresholds {.25,.75,1.25,1.75,2.5,3.5,5} with ties to the
+ * smaller magnitude; sign bit = q < 0.  Padding scale bytes are not written.
+ * replaces quantize_fp4_dynamic_sfa_bf16_vec, fp4-gemm/csrc/quantize/quantize_fp4_sfa_bf16.cuh:20
+ * and quantize_fp4_dynamic_sfa_fp16/_bf16, fp4-gemm/csrc/quantize/quantize_fp4_sfa.cuh:8,24 */
+int frt_nvfp4_quantize(const void* src, int src_dtype, void* packed, void* sf_swizzled,
+                       int rows, int dim, void* stream);
+
+/* packed + swizzled scales -> fp16 [rows, dim] (exact).
+ * replaces dequantize_fp4_sfa_fp16, fp4-gemm/csrc/dequantize_fp4_sfa.cuh:12 */
+int frt_nvfp4_dequantize_fp16(const void* packed, const void* sf_swizzled, void* out_fp16,
+                              int rows, int dim, void* stream);
+
+/* ---- RMSNorm family (bf16) ---------------------------------------------
+ * out = bf16(x * rsqrt(mean(x^2) + eps) * w); dim % 16 == 0, dim <= 16384.
+ * replaces rms_norm_bf16, flashrt-residual-norm-quant/csrc/residual_norm_quant.cuh:9 */
+int frt_rms_norm_bf16(const void* x, const void* weight, void* out,
+                      int rows, int dim, float eps, void* stream);
+
+/* residual <- bf16(residual + x) in place; rstd from the fp32 sums; the
+ * output pass uses the rounded bf16 residual.
+ * replaces residual_add_rms_norm_bf16, flashrt-residual-norm-quant/csrc/residual_norm_quant.cuh:48 */
+int frt_residual_add_rms_norm_bf16(void* residual, const void* x, const void* weight, void* out,
+                                   int rows, int dim, float eps, void* stream);
+
+/* ---- fused (residual-add +) RMSNorm -> NVFP4 producer -------------------
+ * One pass over HBM: reads x (and residual), writes residual in place,
+ * packed e2m1, swizzled UE4M3 scales and, if `normed` is non-null, the bf16
+ * value of the quantiser input.  Flags select the reference op's arithmetic:
+ *   0 with residual : residual_add_rms_norm_quant_nvfp4_swizzled_bf16 --
+ *       v = ((res+x)_fp32 * rstd) * w, not re-rounded, rule-A quantised
+ *       (fp4-fused-ops/csrc/fused_fp4/cosmos3_edge_fp4.cuh:17)
+ *   ONE_PLUS_W | ROUND_BF16 without residual : rms_norm_quantize_fp4_sfa_bf16
+ *       (fp4-fused-ops/csrc/kernels/rms_norm_quantize_fp4_sfa_bf16.cuh:7)
+ *   RNE_E2M1 | ROUND_BF16 | NORM_FROM_BF16_RESIDUAL : residual_add_rms_norm_nvfp4_bf16
+ *       (fp4-fused-ops/csrc/fused_fp4/pi05_bf16_fp4_producers.cuh, rms_norm_nvfp4_bf16)
+ * weight may be null (no scaling).  inv_global_scale multiplies the norm
+ * result before quantisation (two-level scaling; pass 1.0f for the
+ * reference's one-level recipe).  dim % 16 == 0, dim <= 16384. */
+#define FRT_PRODUCER_ONE_PLUS_W               1u
+#define FRT_PRODUCER_ROUND_BF16               2u
+#define FRT_PRODUCER_RNE_E2M1                 4u
+#define FRT_PRODUCER_NORM_FROM_BF16_RESIDUAL  8u
+int frt_norm_quant_nvfp4(void* residual, const void* x, const void* weight, float eps,
+                         float inv_global_scale, void* normed, void* packed, void* sf_swizzled,
+                         int rows, int dim, unsigned flags, void* stream);
+
+/* ---- dense NVFP4 A4W4 GEMM, bf16 out ------------------------------------
+ * D[M,N] = bf16(alpha * sum_k A[m,k]*SFA[m,k/16] * B[n,k]*SFB[n,k/16]
+ *               (+ bias[n]) (+ beta * C[m,n])),  fp32 accumulation in TMEM.
+ * A [M,K/2] u8 row-major, B [N,K/2] u8 row-major, scales swizzled, bias bf16
+ * [N] or null, C bf16 [M,N] or null (may alias D), beta in {0,1}.
+ * K % 64 == 0, N % 8 == 0, A/B 16-byte aligned, D/C 16-byte aligned.
+ * Scale buffers must hold frt_nvfp4_sf_swizzled_bytes() bytes; rows of the
+ * last 128-row group beyond M / N may hold anything.
+ * replaces fp4_w4a16_gemm_sm100_bf16out (+ _widen, _pingpong),
+ *   fp4-gemm/csrc/gemm/fp4/cutlass_nvfp4_w4a16_gemm_sm100.cuh, and
+ *   cutlass_fp4_gemm_bias_bf16 / _bias_res_bf16,
+ *   fp4-gemm/csrc/gemm/fp4/cutlass_fp4_gemm_bias_bf16_sm100.cuh;
+ * small M (<= 64) is served by the same entry point through a
+ * weight-streaming configuration, replacing fp4_w4a4_gemv_warpsplit_bf16 /
+ * fp4_w4a4_gemm_warpsplit_mrows_bf16 (fp4-gemm/csrc/gemm/fp4/fp4_w4a4_mma_warpsplit_sm120.cuh). */
+int frt_nvfp4_gemm_bf16(const void* a_packed, const void* sfa, const void* b_packed, const void* sfb,
+                        const void* bias, const void* c, void* d,
+                        int M, int N, int K, float alpha, float beta, void* stream);
+
+/* ---- grouped (MoE) NVFP4 GEMM, bf16 out ---------------------------------
+ * Rows of `a_packed` [rows, K/2] are expert-sorted; their scales are one
+ * swizzled buffer over all rows (indexed by global row).  Expert e owns the
+ * stacked weights b_stack + e*b_stride (bytes) [N,K/2] and scales
+ * sfb_stack + e*sfb_stride.  out[r,:] = bf16(alpha[e(r)] * A[r,:] . W[e(r)]^T).
+ * Exactly one of the two descriptions of e(r) is given:
+ *   expert_offsets : int32 [num_experts+1] device array, expert e owns rows
+ *                    [off[e], off[e+1]); rows >= off[num_experts] untouched.
+ *   tile_expert    : int32 [rows/tile_rows] device array, tile t (tile_rows in
+ *                    {16,64} rows) uses expert tile_expert[t]; negative = skip
+ *                    (those output rows are left untouched).
+ * K % 64 == 0, N % 8 == 0.  `work` is caller-owned scratch of
+ * frt_nvfp4_grouped_gemm_workspace_bytes() bytes (device, 16-byte aligned).
+ * replaces moe_blocktile_mma_sm120_bf16 / moe_m64_mma_sm120_bf16 / moe_m16_mma_sm120_bf16,
+ *   grouped-moe-gemm/csrc/moe_blocktile_mma_sm120.cuh */
+int64_t frt_nvfp4_grouped_gemm_workspace_bytes(int rows, int num_experts);
+int frt_nvfp4_grouped_gemm_bf16(const void* a_packed, const void* sfa,
+                                const void* b_stack, const void* sfb_stack, const void* alpha,
+                                const void* expert_offsets, const void* tile_expert, int tile_rows,
+                                void* out, int rows, int N, int K, int num_experts,
+                                int64_t b_stride, int64_t sfb_stride,
+                                void* work, void* stream);
+
+/* ---- status / tuning -----------------------------------------------------
+ * Device-side waits are bounded; a wait that runs out records a code in a
+ * per-device status word and the kernel returns.  This call copies the word to
+ * the host (synchronises `stream`) and clears it: 0 = no kernel gave up. */
+int frt_device_status(void* stream, unsigned* status_out);
+
+/* Number of kernels this library has launched from the calling process. */
+int64_t frt_launch_count(void);
+
+/* Tuning / debugging switches; see the FRT_OPT_* keys. Returns previous value. */
+#define FRT_OPT_QUANT_ENCODER   1   /* 0 = hardware-cvt encoder (default), 1 = compare chain */
+#define FRT_OPT_GEMM_CONFIG     2   /* 0 = automatic, otherwise a configuration id          */
+int frt_set_option(int key, int value);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLASHRT_B200_H_ */

@@ -1,0 +1,91 @@
+// extern "C" doors into the reference's own CUDA launchers, so that GPU tests
+// can run the UNMODIFIED reference kernels beside ours (test infrastructure;
+// built by oracle/Makefile into oracle/_ref/, never linked into the product).
+// Only declarations are taken from the reference headers at build time.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+
+#include "quantize_fp4_sfa.cuh"                 // fp4-gemm/csrc/quantize
+#include "quantize_fp4_sfa_bf16.cuh"            // fp4-gemm/csrc/quantize
+#include "dequantize_fp4_sfa.cuh"               // fp4-gemm/csrc
+#include "nvfp4_sf_reshape_sm120.cuh"           // flashrt-nvfp4/csrc
+#include "residual_norm_quant.cuh"              // flashrt-residual-norm-quant/csrc
+#include "kernels/rms_norm_quantize_fp4_sfa_bf16.cuh"   // fp4-fused-ops/csrc
+#ifdef REF_HAVE_CUTLASS
+#define FLASHRT_HAVE_COSMOS3_EDGE 1
+#include "fused_fp4/cosmos3_edge_fp4.cuh"       // fp4-fused-ops/csrc
+#include "cutlass_nvfp4_w4a16_gemm_sm100.cuh"   // fp4-gemm/csrc/gemm/fp4
+#endif
+
+#define S(x) reinterpret_cast<cudaStream_t>(x)
+
+extern "C" {
+
+int ref_has_cutlass() {
+#ifdef REF_HAVE_CUTLASS
+  return 1;
+#else
+  return 0;
+#endif
+}
+
+// K4: the vectorised bf16 "reference quantizer"
+int ref_quantize_bf16_vec(const void* src, void* packed, void* sfa, int rows, int dim, void* st) {
+  return flash_rt::fp4::quantize_fp4_dynamic_sfa_bf16_vec(src, packed, sfa, rows, dim, false, S(st));
+}
+// K3: scalar bf16 / fp16 quantizers
+int ref_quantize_bf16(const void* src, void* packed, void* sfa, int rows, int dim, void* st) {
+  return flash_rt::fp4::quantize_fp4_dynamic_sfa_bf16(src, packed, sfa, rows, dim, false, S(st));
+}
+int ref_quantize_fp16(const void* src, void* packed, void* sfa, int rows, int dim, void* st) {
+  return flash_rt::fp4::quantize_fp4_dynamic_sfa_fp16(src, packed, sfa, rows, dim, false, S(st));
+}
+// K6
+int ref_dequantize_fp16(const void* packed, const void* sfa, void* out, int rows, int dim, void* st) {
+  flash_rt::fused_fp4::dequantize_fp4_sfa_fp16(static_cast<const uint8_t*>(packed), static_cast<const uint8_t*>(sfa),
+                                               static_cast<__half*>(out), rows, dim, false, S(st));
+  return 0;
+}
+// K2
+int ref_sf_linear_to_swizzled(const void* src, void* dst, int rows, int dim, void* st) {
+  return flash_rt::fp4::nvfp4_sf_linear_to_swizzled(src, dst, rows, dim, false, S(st));
+}
+// K7 / K8
+int ref_rms_norm_bf16(const void* x, const void* w, void* out, int rows, int dim, float eps, void* st) {
+  flash_rt::residual_norm_quant::rms_norm_bf16(x, w, out, rows, dim, eps, S(st));
+  return 0;
+}
+int ref_residual_add_rms_norm_bf16(void* res, const void* x, const void* w, void* out, int rows, int dim,
+                                   float eps, void* st) {
+  flash_rt::residual_norm_quant::residual_add_rms_norm_bf16(res, x, w, out, rows, dim, eps, S(st));
+  return 0;
+}
+// K13
+int ref_rms_norm_quantize_bf16(const void* x, const void* w, float eps, void* normed, void* packed, void* sfa,
+                               int rows, int dim, void* st) {
+  return flash_rt::fp4::rms_norm_quantize_fp4_sfa_bf16(x, w, eps, normed, packed, sfa, rows, dim, S(st));
+}
+
+#ifdef REF_HAVE_CUTLASS
+// K10: residual_add_rms_norm_quant_nvfp4_swizzled_bf16
+int ref_res_rms_fp4_bf16(void* res, const void* x, const void* w, void* packed, void* sfa, int rows, int dim,
+                         float eps, void* st) {
+  flash_rt::fused_fp4::cosmos3_edge_res_rms_fp4_sfa_bf16(
+      static_cast<__nv_bfloat16*>(res), static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
+      static_cast<uint8_t*>(packed), static_cast<uint8_t*>(sfa), rows, dim, eps, S(st));
+  return 0;
+}
+// K15 / K16: the reference's CUTLASS sm100 GEMM (cluster 1x1x1), bf16 out
+int ref_gemm_sm100_bf16(const void* a, const void* b, void* d, int M, int N, int K, const void* sfa,
+                        const void* sfb, float alpha, int widen, void* st) {
+  if (widen)
+    flash_rt::gemm::fp4_w4a16_gemm_sm100_bf16out_widen(a, b, d, M, N, K, sfa, sfb, alpha, S(st));
+  else
+    flash_rt::gemm::fp4_w4a16_gemm_sm100_bf16out(a, b, d, M, N, K, sfa, sfb, alpha, S(st));
+  return 0;
+}
+#endif
+
+}  // extern "C"

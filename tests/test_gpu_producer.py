@@ -1,0 +1,220 @@
+"""GPU parity of the HBM-bound kernels, through the C ABI:
+bit-exact against the CPU oracle and, where oracle/_ref is built, against the
+reference's own CUDA kernels running on the same GPU."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from tests.gpu_common import (DEV, O, alloc_fp4, bits, capi, quantize, randn_bf16, ref_lib, sf_bytes,  # noqa: E402
+                              sf_linear)
+
+P = capi.ptr
+
+
+def st():
+    return capi.stream_ptr()
+
+
+@pytest.mark.parametrize("rows,dim", [(1, 1024), (2, 4096), (31, 4096), (33, 4096), (127, 2048), (129, 4096),
+                                      (16, 12288), (64, 16384), (130, 80), (5, 16)])
+def test_sf_layout(rows, dim):
+    g = torch.Generator().manual_seed(rows * 7 + dim)
+    lin = torch.randint(0, 256, (rows, dim // 16), generator=g, dtype=torch.uint8)
+    out = torch.full((sf_bytes(rows, dim),), 0xAB, dtype=torch.uint8, device=DEV)
+    capi.check(capi.lib().frt_nvfp4_sf_linear_to_swizzled(P(lin.to(DEV)), P(out), rows, dim, st()))
+    want = O.sf_linear_to_swizzled(lin.numpy())
+    got = out.cpu().numpy()
+    offs = O.sf_offsets(rows, dim).reshape(-1)
+    np.testing.assert_array_equal(got[offs], want[offs])
+    mask = np.ones(got.size, bool)
+    mask[offs] = False
+    assert np.all(got[mask] == 0xAB)          # padding bytes are left alone
+
+
+@pytest.mark.parametrize("encoder", [0, 1])
+@pytest.mark.parametrize("rows,dim,scale,dtype", [
+    (1, 5120, 1.5, torch.bfloat16), (8, 5120, 1.5, torch.float16), (128, 512, 1.5, torch.bfloat16),
+    (257, 4096, 1.0, torch.bfloat16), (63, 2048, 0.02, torch.bfloat16), (130, 4096, 0.25, torch.float16),
+    (4096, 4096, 1.0, torch.bfloat16)])
+def test_quantizer_bit_exact(rows, dim, scale, dtype, encoder):
+    g = torch.Generator().manual_seed(8100 + rows + dim)
+    x = (torch.randn(rows, dim, generator=g) * scale).to(dtype)
+    x[0, :16] = 0                      # an all-zero block
+    x[0, 16:32] = 2.0 ** -13           # scale rounds to zero
+    x[0, 32] = -0.0
+    prev = capi.lib().frt_set_option(1, encoder)
+    try:
+        packed, sf = alloc_fp4(rows, dim, fill=0)
+        quantize(x.to(DEV), packed, sf)
+    finally:
+        capi.lib().frt_set_option(1, prev)
+    want_p, want_s = O.quantize_nvfp4(x.float().numpy())
+    np.testing.assert_array_equal(sf.cpu().numpy(), O.sf_linear_to_swizzled(want_s))
+    np.testing.assert_array_equal(packed.cpu().numpy(), want_p)
+    ref = ref_lib()
+    if ref is not None:
+        rp, rs = alloc_fp4(rows, dim, fill=0)
+        fn = ref.ref_quantize_bf16_vec if dtype == torch.bfloat16 else ref.ref_quantize_fp16
+        assert fn(P(x.to(DEV)), P(rp), P(rs), rows, dim, st()) == 0
+        torch.cuda.synchronize()
+        assert torch.equal(rp, packed) and torch.equal(rs, sf)
+
+
+def test_dequantize_exact():
+    rows, dim = 130, 1024
+    g = torch.Generator().manual_seed(3)
+    packed = torch.randint(0, 256, (rows, dim // 2), generator=g, dtype=torch.uint8)
+    lin = torch.randint(0, 0x7F, (rows, dim // 16), generator=g, dtype=torch.uint8)
+    sf = torch.from_numpy(O.sf_linear_to_swizzled(lin.numpy()))
+    out = torch.empty(rows, dim, dtype=torch.float16, device=DEV)
+    capi.check(capi.lib().frt_nvfp4_dequantize_fp16(P(packed.to(DEV)), P(sf.to(DEV)), P(out), rows, dim, st()))
+    want = torch.from_numpy(O.dequantize_nvfp4(packed.numpy(), lin.numpy())).to(torch.float16)
+    assert torch.equal(out.cpu().view(torch.int16), want.view(torch.int16))      # exact, signed zeros included
+
+
+CASES = [(1, 1024), (16, 128), (63, 2048), (128, 4096), (257, 4096), (33, 5120), (9, 8192), (5, 12288), (3, 16384)]
+
+
+@pytest.mark.parametrize("rows,dim", CASES)
+def test_rms_norm_bf16(rows, dim):
+    x, w = randn_bf16((rows, dim), 23 + rows), randn_bf16((dim,), 24, 0.1, 1.0)
+    out = torch.empty(rows, dim, dtype=torch.bfloat16, device=DEV)
+    capi.check(capi.lib().frt_rms_norm_bf16(P(x.to(DEV)), P(w.to(DEV)), P(out), rows, dim, 1e-6, st()))
+    np.testing.assert_array_equal(bits(out), O.rms_norm_bf16(bits(x), bits(w), 1e-6))
+    ref = ref_lib()
+    if ref is not None and dim % 2 == 0:
+        ro = torch.empty_like(out)
+        ref.ref_rms_norm_bf16(P(x.to(DEV)), P(w.to(DEV)), P(ro), rows, dim, C.c_float(1e-6), st())
+        torch.cuda.synchronize()
+        assert (ro.float() - out.float()).abs().max() <= 2.0 ** -6   # reference's own tolerance (p99 2^-6)
+        assert (ro != out).float().mean() < 0.01
+
+
+@pytest.mark.parametrize("rows,dim", CASES)
+def test_residual_add_rms_norm_bf16(rows, dim):
+    x, r, w = randn_bf16((rows, dim), 1 + rows), randn_bf16((rows, dim), 2 + rows), randn_bf16((dim,), 3, 0.1, 1.0)
+    res = r.to(DEV).clone()
+    out = torch.empty(rows, dim, dtype=torch.bfloat16, device=DEV)
+    capi.check(capi.lib().frt_residual_add_rms_norm_bf16(P(res), P(x.to(DEV)), P(w.to(DEV)), P(out), rows, dim,
+                                                         1e-6, st()))
+    want_res, want_y = O.residual_add_rms_norm_bf16(bits(r), bits(x), bits(w), 1e-6)
+    np.testing.assert_array_equal(bits(res), want_res)
+    np.testing.assert_array_equal(bits(out), want_y)
+    ref = ref_lib()
+    if ref is not None:
+        rres, ro = r.to(DEV).clone(), torch.empty_like(out)
+        ref.ref_residual_add_rms_norm_bf16(P(rres), P(x.to(DEV)), P(w.to(DEV)), P(ro), rows, dim, C.c_float(1e-6), st())
+        torch.cuda.synchronize()
+        assert torch.equal(rres, res)                                   # in-place residual exactly equal
+        assert (ro.float() - out.float()).abs().max() <= 2.0 ** -6
+
+
+@pytest.mark.parametrize("encoder", [0, 1])
+@pytest.mark.parametrize("rows,dim", CASES + [(4096, 4096)])
+def test_fused_residual_norm_quant(rows, dim, encoder):
+    """residual_add_rms_norm_quant_nvfp4_swizzled_bf16 semantics, bit-exact
+    against the oracle (same summation order) and, end to end, against the
+    reference's fused kernel up to its different fp32 summation order."""
+    x, r, w = randn_bf16((rows, dim), 11 + rows), randn_bf16((rows, dim), 12 + rows), randn_bf16((dim,), 13, 0.1, 1.0)
+    res = r.to(DEV).clone()
+    packed, sf = alloc_fp4(rows, dim)
+    normed = torch.empty(rows, dim, dtype=torch.bfloat16, device=DEV)
+    prev = capi.lib().frt_set_option(1, encoder)
+    try:
+        capi.check(capi.lib().frt_norm_quant_nvfp4(P(res), P(x.to(DEV)), P(w.to(DEV)), 1e-6, 1.0, P(normed),
+                                                   P(packed), P(sf), rows, dim, 0, st()))
+    finally:
+        capi.lib().frt_set_option(1, prev)
+    want = O.fused_norm_quant(bits(x), bits(w), 1e-6, res_bits=bits(r))
+    np.testing.assert_array_equal(bits(res), want["residual"])
+    np.testing.assert_array_equal(bits(normed), want["normed"])
+    np.testing.assert_array_equal(sf.cpu().numpy(), O.sf_linear_to_swizzled(want["sf_linear"]))
+    np.testing.assert_array_equal(packed.cpu().numpy(), want["packed"])
+    ref = ref_lib()
+    if ref is not None and ref.ref_has_cutlass() and dim // 16 <= 1024:
+        rres = r.to(DEV).clone()
+        rp, rs = alloc_fp4(rows, dim)
+        ref.ref_res_rms_fp4_bf16(P(rres), P(x.to(DEV)), P(w.to(DEV)), P(rp), P(rs), rows, dim, C.c_float(1e-6), st())
+        torch.cuda.synchronize()
+        assert torch.equal(rres, res)
+        # rstd may differ in the last bit (other summation order): allow a sliver of code flips
+        code_mismatch = (O.unpack_codes(rp.cpu().numpy()) != O.unpack_codes(packed.cpu().numpy())).mean()
+        sf_mismatch = (rs != sf).float().mean().item()
+        assert code_mismatch < 2e-3 and sf_mismatch < 2e-3, (code_mismatch, sf_mismatch)
+
+
+@pytest.mark.parametrize("rows,dim", [(1, 2048), (63, 2048), (257, 4096)])
+def test_rms_norm_quantize_emits_normed(rows, dim):
+    """rms_norm_quantize_fp4_sfa_bf16 semantics ((1+w), bf16-rounded, `normed`
+    emitted): quantiser(normed) bit-exact, normed within one bf16 step of the
+    reference kernel."""
+    x, w = randn_bf16((rows, dim), 2026 + rows, 0.2), randn_bf16((dim,), 2027, 0.05)
+    packed, sf = alloc_fp4(rows, dim)
+    normed = torch.empty(rows, dim, dtype=torch.bfloat16, device=DEV)
+    flags = 1 | 2
+    capi.check(capi.lib().frt_norm_quant_nvfp4(None, P(x.to(DEV)), P(w.to(DEV)), 1e-6, 1.0, P(normed), P(packed),
+                                               P(sf), rows, dim, flags, st()))
+    want = O.fused_norm_quant(bits(x), bits(w), 1e-6, flags=flags)
+    np.testing.assert_array_equal(bits(normed), want["normed"])
+    np.testing.assert_array_equal(packed.cpu().numpy(), want["packed"])
+    np.testing.assert_array_equal(sf_linear(sf, rows, dim), want["sf_linear"])
+    qp, qs = quantize(normed)                      # the stand-alone quantiser on our own normed
+    assert torch.equal(qp, packed) and torch.equal(qs, sf)
+    expected = (x.float() * torch.rsqrt(x.float().square().mean(dim=1, keepdim=True) + 1e-6)
+                * (1.0 + w.float())).bfloat16()
+    assert (normed.cpu().float() - expected.float()).abs().max() <= 0.015625
+    ref = ref_lib()
+    if ref is not None and dim <= 8192:
+        rn, (rp, rs) = torch.empty_like(normed), alloc_fp4(rows, dim)
+        assert ref.ref_rms_norm_quantize_bf16(P(x.to(DEV)), P(w.to(DEV)), C.c_float(1e-6), P(rn), P(rp), P(rs),
+                                              rows, dim, st()) == 0
+        torch.cuda.synchronize()
+        assert (rn.float() - normed.float()).abs().max() <= 0.015625
+        assert (rn != normed).float().mean() < 0.01
+
+
+def test_rule_b_variant():
+    rows, dim = 33, 2048
+    x, r, w = randn_bf16((rows, dim), 5), randn_bf16((rows, dim), 6), randn_bf16((dim,), 7, 0.1, 1.0)
+    res = r.to(DEV).clone()
+    packed, sf = alloc_fp4(rows, dim)
+    flags = 2 | 4 | 8
+    capi.check(capi.lib().frt_norm_quant_nvfp4(P(res), P(x.to(DEV)), P(w.to(DEV)), 1e-6, 1.0, None, P(packed), P(sf),
+                                               rows, dim, flags, st()))
+    want = O.fused_norm_quant(bits(x), bits(w), 1e-6, res_bits=bits(r), flags=flags)
+    np.testing.assert_array_equal(bits(res), want["residual"])
+    np.testing.assert_array_equal(packed.cpu().numpy(), want["packed"])
+    np.testing.assert_array_equal(sf_linear(sf, rows, dim), want["sf_linear"])
+
+
+def test_two_level_global_scale():
+    rows, dim = 17, 4096
+    x, r, w = randn_bf16((rows, dim), 8), randn_bf16((rows, dim), 9), randn_bf16((dim,), 10, 0.1, 1.0)
+    base = O.fused_norm_quant(bits(x), bits(w), 1e-6, res_bits=bits(r))
+    amax = np.abs(O.bf16_bits_to_f32(base["normed"])).max()
+    g = np.float32(amax) / np.float32(6 * 448)
+    inv_g = float(np.float32(1.0) / g)
+    res = r.to(DEV).clone()
+    packed, sf = alloc_fp4(rows, dim)
+    capi.check(capi.lib().frt_norm_quant_nvfp4(P(res), P(x.to(DEV)), P(w.to(DEV)), 1e-6, inv_g, None, P(packed),
+                                               P(sf), rows, dim, 0, st()))
+    want = O.fused_norm_quant(bits(x), bits(w), 1e-6, res_bits=bits(r), inv_global_scale=inv_g)
+    np.testing.assert_array_equal(packed.cpu().numpy(), want["packed"])
+    np.testing.assert_array_equal(sf_linear(sf, rows, dim), want["sf_linear"])
+
+
+def test_argument_errors():
+    L = capi.lib()
+    x = torch.zeros(4, 64, dtype=torch.bfloat16, device=DEV)
+    p, s = alloc_fp4(4, 64)
+    assert L.frt_nvfp4_quantize(None, 0, P(p), P(s), 4, 64, st()) == -1
+    assert L.frt_nvfp4_quantize(P(x), 0, P(p), P(s), 4, 40, st()) == -2          # dim % 16
+    assert L.frt_nvfp4_quantize(P(x), 0, P(p), P(s), 0, 64, st()) == -2
+    assert L.frt_nvfp4_quantize(C.c_void_p(x.data_ptr() + 2), 0, P(p), P(s), 4, 64, st()) == -3
+    assert L.frt_norm_quant_nvfp4(None, P(x), None, 1e-6, 1.0, None, P(p), P(s), 4, 32768, 0, st()) == -4
+    assert L.frt_nvfp4_sf_linear_to_swizzled(P(s), P(s), 0, 64, st()) == -2
+    assert b"null" in L.frt_error_string(-1)
