@@ -78,7 +78,7 @@ __global__ void dequantize_kernel(const uint2* __restrict__ packed, const uint8_
   const float s = ue4m3_to_float(sf[sf_offset(row, kb, sf_cols)]);
   const uint2 p = packed[idx];
   const uint32_t w[2] = {p.x, p.y};
-  __half h[16];
+  __align__(16) __half h[16];
 #pragma unroll
   for (int i = 0; i < 16; ++i) {
     const uint32_t c = (w[i >> 3] >> (4 * (i & 7))) & 0xfu;
