@@ -1,0 +1,464 @@
+#!/usr/bin/env python3
+"""Benchmark of the NVFP4 low-bit linear hot path on B200.
+
+One "step" is one pass of the path over a Qwen3-8B-shaped decoder layer's
+linears at M = 4096 tokens (synthetic data, random weights of that shape):
+
+    producer(residual, hidden) -> QKV GEMM 4096->6144      O GEMM 4096->4096 (NVFP4 input resident)
+    producer(residual, hidden) -> gate/up GEMM 4096->24576 down GEMM 12288->4096 (NVFP4 input resident)
+
+`value` is GEMM TFLOP/s of the whole step (2*M*N*K summed over the four GEMMs,
+divided by the step time including the two producer launches), inputs resident
+in HBM.  `e2e` is the same metric through the torch operator API with the
+step's bf16 inputs in pinned host memory and the step's result read back to
+the host inside the timed region.  With N > 1 ranks (torchrun) the weights are
+column-sharded, activations replicated, outputs stay sharded; the all-gather
+of the outputs is timed separately.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c5]
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+sys.path.insert(0, str(ROOT / "flashrt-hf-kernels_b200" / "torch-ext"))
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+
+L2_BYTES = 126 << 20
+EPS = 1e-6
+
+WORKLOADS = {
+    # name: (tokens, hidden, [(layer, N, K, fed_by_producer)])
+    "c2": ("qwen3-8b-prefill-m4096", 4096, 4096,
+           [("qkv", 6144, 4096, True), ("o", 4096, 4096, False), ("gate_up", 24576, 4096, True),
+            ("down", 4096, 12288, False)]),
+    "c5": ("llama3-70b-ffn-m8192", 8192, 8192,
+           [("gate_up", 57344, 8192, True), ("down", 8192, 28672, False)]),
+}
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return dict(hbm_gbs=d["hbm_gbs"], fp4_tflops=4.0 * d["bf16_tflops_sustained"],
+                    fp4_tflops_burst=4.0 * d["bf16_tflops"], source="measured (MEASURED_PEAKS.json; FP4 = 4 x bf16)")
+    return dict(hbm_gbs=6650.0, fp4_tflops=4.0 * 1400.0, fp4_tflops_burst=4.0 * 1590.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40,
+                 "hw_power_brake": 0x80}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                for k, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            time.sleep(0.005)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["nvml unavailable"]}
+        return {"sm_mhz": int(statistics.median(self.samples)), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons)}
+
+
+# ----------------------------------------------------------------------------
+# our arm
+# ----------------------------------------------------------------------------
+class Layer:
+    """Device-resident tensors of one rank's shard of the workload."""
+
+    def __init__(self, key, rank, world, dev, seed=1234):
+        import fp4_gemm
+        from flashrt_b200_core import alloc_fp4
+        self.name, self.M, self.H, layers = WORKLOADS[key]
+        g = torch.Generator(device=dev).manual_seed(seed)
+        rn = lambda *s, scale=1.0: (torch.randn(*s, generator=g, device=dev) * scale).to(torch.bfloat16)
+        self.hidden, self.residual0 = rn(self.M, self.H), rn(self.M, self.H)
+        self.residual = self.residual0.clone()
+        self.norm_w = (1.0 + 0.1 * torch.randn(self.H, generator=g, device=dev)).to(torch.bfloat16)
+        self.act_packed, self.act_sf = alloc_fp4(self.M, self.H, dev)
+        self.gemms = []
+        self.flops_total = 0.0
+        for lname, n, k, fed in layers:
+            assert n % (world * 128) == 0, "column shard must keep whole 128-row scale groups"
+            n_loc = n // world
+            # quantise the full-width weight in slabs so every rank derives the same bytes for its shard
+            w = rn(n_loc, k, scale=0.02)
+            wp, wsf = fp4_gemm.quantize_fp4_sfa_bf16(w, is_sfb=True)
+            del w
+            if fed:
+                a_p, a_sf = self.act_packed, self.act_sf
+            else:
+                a_p, a_sf = fp4_gemm.quantize_fp4_sfa_bf16(rn(self.M, k))
+            out = torch.empty(self.M, n_loc, device=dev, dtype=torch.bfloat16)
+            self.gemms.append(dict(name=lname, n=n, n_loc=n_loc, k=k, fed=fed, wp=wp, wsf=wsf, a_p=a_p, a_sf=a_sf,
+                                   out=out))
+            self.flops_total += 2.0 * self.M * n * k
+        self.bytes_streamed = sum(g_["wp"].numel() + g_["wsf"].numel() + g_["out"].numel() * 2 +
+                                  g_["a_p"].numel() for g_ in self.gemms) + 2 * 3 * self.M * self.H * 2
+
+    def step_capi(self, capi, st, ev=None):
+        """one pass through the C ABI (resident inputs); optional (start,end) events per kernel"""
+        L = capi.lib()
+        P = capi.ptr
+        launches = 0
+        for i, g_ in enumerate(self.gemms):
+            if g_["fed"]:
+                if ev is not None:
+                    ev[("producer", i)][0].record()
+                rc = L.frt_norm_quant_nvfp4(P(self.residual), P(self.hidden), P(self.norm_w), EPS, 1.0, None,
+                                            P(self.act_packed), P(self.act_sf), self.M, self.H, 0, st)
+                if ev is not None:
+                    ev[("producer", i)][1].record()
+                assert rc == 0, rc
+                launches += 1
+            if ev is not None:
+                ev[(g_["name"], i)][0].record()
+            rc = L.frt_nvfp4_gemm_bf16(P(g_["a_p"]), P(g_["a_sf"]), P(g_["wp"]), P(g_["wsf"]), None, None,
+                                       P(g_["out"]), self.M, g_["n_loc"], g_["k"], 1.0, 0.0, st)
+            if ev is not None:
+                ev[(g_["name"], i)][1].record()
+            assert rc == 0, rc
+            launches += 1
+        return launches
+
+    def step_ops(self, hidden, residual):
+        """one pass through the torch operator API; returns the last GEMM's output"""
+        import fp4_fused_ops
+        import fp4_gemm
+        out = None
+        for g_ in self.gemms:
+            if g_["fed"]:
+                fp4_fused_ops.residual_add_rms_norm_quant_nvfp4_swizzled_bf16(
+                    residual, hidden, self.norm_w, EPS, packed=self.act_packed, sfa=self.act_sf)
+            out = fp4_gemm.nvfp4_gemm_bf16(g_["a_p"], g_["wp"], g_["a_sf"], g_["wsf"], out=g_["out"])
+        return out
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch.distributed as dist
+    from flashrt_b200_core import capi, load
+    load()
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    peaks = measured_peaks()
+    layer = Layer(args.workload, rank, world, dev)
+    st = capi.stream_ptr()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        layer.step_capi(capi, st)
+    barrier()
+    keys = [("producer", i) for i, g_ in enumerate(layer.gemms) if g_["fed"]] + \
+           [(g_["name"], i) for i, g_ in enumerate(layer.gemms)]
+    events = [{k: (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for k in keys}
+              for _ in range(args.steps)]
+    launches0 = capi.lib().frt_launch_count()
+    with ClockSampler(local_rank) as clocks:
+        barrier()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for s in range(args.steps):
+            layer.step_capi(capi, st, events[s])
+        t1.record()
+        barrier()
+    ms_total = t0.elapsed_time(t1)
+    launches = capi.lib().frt_launch_count() - launches0
+    if world > 1:
+        t = torch.tensor([ms_total], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_step = ms_total / args.steps
+    value = layer.flops_total / (ms_step * 1e-3) / 1e12
+
+    per_kernel = {}
+    for k in keys:
+        per_kernel[k] = statistics.mean(e[k][0].elapsed_time(e[k][1]) for e in events)
+    gemm_ms = sum(v for k, v in per_kernel.items() if k[0] != "producer")
+    prod_ms = [v for k, v in per_kernel.items() if k[0] == "producer"]
+    dom = max((k for k in per_kernel if k[0] != "producer"), key=lambda k: per_kernel[k])
+    dom_g = layer.gemms[dom[1]]
+    dom_flops = 2.0 * layer.M * dom_g["n_loc"] * dom_g["k"]
+    achieved = dom_flops / (per_kernel[dom] * 1e-3) / 1e12
+    prod_bytes = layer.M * layer.H * 6.5625
+    detail = {
+        "gemm_only_tflops": layer.flops_total / world / (gemm_ms * 1e-3) / 1e12 * world,
+        "per_kernel_us": {f"{k[0]}": round(v * 1e3, 2) for k, v in per_kernel.items()},
+        "per_gemm_tflops": {layer.gemms[k[1]]["name"]: round(2.0 * layer.M * layer.gemms[k[1]]["n_loc"] *
+                            layer.gemms[k[1]]["k"] / (v * 1e-3) / 1e12, 1) for k, v in per_kernel.items()
+                            if k[0] != "producer"},
+        "producer_gbs": round(prod_bytes / (statistics.mean(prod_ms) * 1e-3) / 1e9, 1) if prod_ms else None,
+        "producer_frac_of_hbm_measured": round(prod_bytes / (statistics.mean(prod_ms) * 1e-3) / 1e9 /
+                                               peaks["hbm_gbs"], 3) if prod_ms else None,
+    }
+
+    # ---- end to end through the torch operator API with host buffers ----------
+    host_h = torch.empty(layer.M, layer.H, dtype=torch.bfloat16).pin_memory()
+    host_r = torch.empty(layer.M, layer.H, dtype=torch.bfloat16).pin_memory()
+    host_h.copy_(layer.hidden.cpu())
+    host_r.copy_(layer.residual0.cpu())
+    last = layer.gemms[-1]["out"]
+    host_out = [torch.empty(last.shape, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+    dev_in = [(torch.empty_like(layer.hidden), torch.empty_like(layer.hidden)) for _ in range(2)]
+    copy_s, comp_s, out_s = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+    h2d = 2 * layer.M * layer.H * 2
+    d2h = last.numel() * 2
+
+    def e2e_steps(n):
+        in_ready = [torch.cuda.Event(), torch.cuda.Event()]
+        in_free = [torch.cuda.Event(), torch.cuda.Event()]
+        out_ready, out_free = torch.cuda.Event(), torch.cuda.Event()
+        for s in range(n):
+            b = s & 1
+            with torch.cuda.stream(copy_s):
+                if s >= 2:
+                    copy_s.wait_event(in_free[b])
+                dev_in[b][0].copy_(host_h, non_blocking=True)
+                dev_in[b][1].copy_(host_r, non_blocking=True)
+                in_ready[b].record(copy_s)
+            with torch.cuda.stream(comp_s):
+                comp_s.wait_event(in_ready[b])
+                if s >= 1:
+                    comp_s.wait_event(out_free)
+                out = layer.step_ops(dev_in[b][0], dev_in[b][1])
+                in_free[b].record(comp_s)
+                out_ready.record(comp_s)
+            with torch.cuda.stream(out_s):
+                out_s.wait_event(out_ready)
+                host_out[b].copy_(out, non_blocking=True)
+                out_free.record(out_s)
+        for s_ in (copy_s, comp_s, out_s):
+            s_.synchronize()
+
+    e2e_steps(max(3, args.warmup // 4))
+    barrier()
+    e2e_n = max(10, args.steps // 4)
+    w0 = time.perf_counter()
+    e2e_steps(e2e_n)
+    barrier()
+    e2e_ms = (time.perf_counter() - w0) * 1e3 / e2e_n
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_val = layer.flops_total / (e2e_ms * 1e-3) / 1e12
+
+    # ---- all-gather of the sharded outputs, timed separately -------------------
+    allgather = None
+    if world > 1:
+        big = max(layer.gemms, key=lambda g_: g_["out"].numel())
+        gathered = torch.empty((world,) + tuple(big["out"].shape), device=dev, dtype=torch.bfloat16)
+        for _ in range(3):
+            dist.all_gather_into_tensor(gathered, big["out"])
+        barrier()
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a0.record()
+        for _ in range(10):
+            dist.all_gather_into_tensor(gathered, big["out"])
+        a1.record()
+        barrier()
+        ag_ms = a0.elapsed_time(a1) / 10
+        t = torch.tensor([ag_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ag_ms = float(t.item())
+        tot = gathered.numel() * 2
+        allgather = {"layer": big["name"], "ms": round(ag_ms, 4), "bytes_total": tot,
+                     "bus_gbs": round(tot * (world - 1) / world / (ag_ms * 1e-3) / 1e9, 1), "backend": "nccl"}
+        del gathered
+
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cpu_baseline = run_cpu_port(args, steps=1, sample_rows=32)
+
+    if rank == 0:
+        line = {
+            "metric": "nvfp4_linear_path_tflops", "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_step, 5), "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "nvfp4 (e2m1 x ue4m3, fp32 accumulate, bf16 out)",
+            "data": "synthetic",
+            "config": {"workload": layer.name, "tokens": layer.M, "hidden": layer.H,
+                       "layers": {g_["name"]: [g_["n"], g_["k"]] for g_ in layer.gemms},
+                       "parallelism": f"column-sharded x{world}, activations replicated" if world > 1 else "single GPU",
+                       "l2": f"inputs larger than L2: each step streams {layer.bytes_streamed >> 20} MiB "
+                             f"({L2_BYTES >> 20} MiB L2), every tensor touched once per step"},
+            "e2e": {"value": round(e2e_val, 2), "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_ms, 4),
+                    "api": "torch ops fp4_fused_ops.residual_add_rms_norm_quant_nvfp4_swizzled_bf16 + "
+                           "fp4_gemm.nvfp4_gemm_bf16; pinned host in/out, copies overlapped on side streams"},
+            "gpu_launches": int(launches),
+            "clocks": clocks.summary(),
+            "roofline": {"bound": "tensor", "kernel": f"nvfp4_gemm_kernel ({dom_g['name']} "
+                         f"{layer.M}x{dom_g['n_loc']}x{dom_g['k']})", "achieved": round(achieved, 1),
+                         "peak": round(peaks["fp4_tflops"], 1), "unit": "TFLOP/s",
+                         "frac": round(achieved / peaks["fp4_tflops"], 4),
+                         "peak_note": peaks["source"] + ", sustained figure (kernel timed inside a long step)",
+                         "frac_of_burst_peak": round(achieved / peaks["fp4_tflops_burst"], 4),
+                         "frac_of_nominal_9000": round(achieved / 9000.0, 4),
+                         "traffic": None},
+            "detail": detail,
+        }
+        traffic_file = ROOT / "profiles" / "gemm_dram_traffic.json"
+        if traffic_file.exists():
+            try:
+                line["roofline"]["traffic"] = json.loads(traffic_file.read_text()).get(dom_g["name"])
+            except Exception:
+                pass
+        if allgather:
+            line["allgather_separate"] = allgather
+        if cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline
+        print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------
+# CPU arm: the reference path restated for the host (oracle port)
+# ----------------------------------------------------------------------------
+def run_cpu_port(args, steps, sample_rows, warmup=0):
+    """Times the pure-torch/numpy restatement of the reference path on the host
+    cores for `sample_rows` tokens of the workload (weights dequantised once,
+    as bind-time work)."""
+    from oracle import nvfp4_oracle as O
+    name, M, H, layers = WORKLOADS[args.workload]
+    rng = np.random.default_rng(7)
+    threads = torch.get_num_threads()
+    bf = lambda a: O.f32_to_bf16_bits(a.astype(np.float32))
+    hidden, residual = bf(rng.standard_normal((sample_rows, H))), bf(rng.standard_normal((sample_rows, H)))
+    norm_w = bf(1 + 0.1 * rng.standard_normal(H))
+    weights = []
+    flops = 0.0
+    for lname, n, k, fed in layers:
+        # synthetic NVFP4 weight bytes (random codes, scales around N(0,.02) blocks), dequantised once
+        wp = rng.integers(0, 256, (n, k // 2), dtype=np.uint8)
+        wsf = rng.integers(20, 36, (n, k // 16), dtype=np.uint8)
+        wdq = torch.from_numpy(O.dequantize_nvfp4(wp, wsf))
+        act = None if fed else O.quantize_nvfp4(rng.standard_normal((sample_rows, k)).astype(np.float32))
+        weights.append((lname, wdq, fed, act))
+        flops += 2.0 * sample_rows * n * k
+
+    def step(res):
+        out = None
+        for lname, wdq, fed, act in weights:
+            if fed:
+                q = O.fused_norm_quant(hidden, norm_w, EPS, res_bits=res)
+                res = q["residual"]
+                a = torch.from_numpy(O.dequantize_nvfp4(q["packed"], q["sf_linear"]))
+            else:
+                a = torch.from_numpy(O.dequantize_nvfp4(*act))
+            out = (a @ wdq.T).to(torch.bfloat16)
+        return out
+
+    for _ in range(warmup):
+        step(residual)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step(residual)
+    dt = (time.perf_counter() - t0) / steps
+    return {"value": round(flops / dt / 1e12, 5), "unit": "TFLOP/s", "cores": threads, "kind": "port",
+            "ms_per_step_sample": round(dt * 1e3, 2),
+            "sample": f"{sample_rows} of {M} tokens through all {len(layers)} linears of {name} "
+                      f"(norm+quantise in numpy, dequantise + fp32 matmul in CPU torch, {threads} threads; "
+                      f"weights dequantised once outside the timed region)"}
+
+
+def run_reference(args, rank, world):
+    """`--impl reference`: the reference's own CPU path for this metric.  The
+    reference ships no CPU kernels; its CPU-runnable form of the path is the
+    pure-torch oracle its tests use, restated under oracle/ (kind "port")."""
+    if rank != 0:
+        return
+    rows = 64
+    res = run_cpu_port(args, steps=max(1, min(args.steps, 3)), sample_rows=rows, warmup=min(args.warmup, 1))
+    name, M, H, layers = WORKLOADS[args.workload]
+    line = {"impl": "reference", "metric": "nvfp4_linear_path_tflops", "value": res["value"], "unit": "TFLOP/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(res["ms_per_step_sample"] * M / rows, 3), "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "fp32 (dequantised NVFP4)", "data": "synthetic",
+            "config": {"workload": name, "tokens": M, "hidden": H,
+                       "layers": {l[0]: [l[1], l[2]] for l in layers}, "parallelism": "host CPU"},
+            "cpu_baseline": {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")},
+            "e2e": {"value": res["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (B200); there is no CPU fallback for the product path")
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    try:
+        run_ours(args, rank, world, local_rank)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -76,7 +76,7 @@ def build_ext(force=False):
            f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}", *inc, str(src), "-o", str(EXT),
            f"-L{LIB.parent}", "-lflashrt_b200", f"-Wl,-rpath,$ORIGIN/../../lib",
            f"-L{torch_lib}", "-ltorch", "-ltorch_cpu", "-lc10", "-ltorch_cuda", "-lc10_cuda",
-           "-L/usr/local/cuda/lib64", "-lcudart"]
+           ]
     run(cmd)
     return EXT
 

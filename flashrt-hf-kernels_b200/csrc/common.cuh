@@ -17,6 +17,7 @@ namespace frt {
 extern std::atomic<int64_t> g_launches;     // kernels launched by this library
 extern int g_opt_quant_encoder;             // FRT_OPT_QUANT_ENCODER
 extern int g_opt_gemm_config;               // FRT_OPT_GEMM_CONFIG
+extern int g_opt_gemm_debug;                // experiment switches of the GEMM kernel
 
 // Status word written by kernels whose bounded waits ran out (one per device
 // context, lives in device global memory of this library).

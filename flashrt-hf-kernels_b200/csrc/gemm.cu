@@ -56,6 +56,7 @@ struct GemmParams {
   int ldd;                  // row stride of d and c, in elements
   float alpha, beta;
   int group_m;              // raster: tiles walk GROUP_M p-tiles before the next q-tile
+  int dbg;                  // experiment switches (0 in production)
 };
 
 template <int BN, int STAGES>
@@ -168,10 +169,18 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
   } else if (warp == 1) {
     // ===================== MMA issuer =====================
     if (ptx::elect_one()) {
-      int it = 0, tl = 0;
+      // Descriptors differ between stages and k-tiles only in their low word
+      // (address >> 4), so the loop adds small constants to 32-bit values.
+      const uint32_t smem0 = ptx::smem_u32(smem);
+      const uint64_t op_desc = ptx::desc_sw128_kmajor(smem0);
+      const uint64_t sf_desc = ptx::desc_sf_32x16(smem0 + L::A_BYTES + L::B_BYTES);
+      const uint32_t op_hi = static_cast<uint32_t>(op_desc >> 32), op_lo0 = static_cast<uint32_t>(op_desc);
+      const uint32_t sf_hi = static_cast<uint32_t>(sf_desc >> 32), sf_lo0 = static_cast<uint32_t>(sf_desc);
+      const bool copy_always = !(p.dbg & 2);
+      int s = 0, tl = 0;
+      uint32_t ph = 0, sfbuf = 0;
+      bool aborted = false;
       for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x, ++tl) {
-        int pt, qt;
-        tile_coords(t, p, pt, qt);
         const int a = tl % ACC;
         const uint32_t aph = (tl / ACC) & 1;
         if (!ptx::mbar_wait_bounded(&acc_empty[a], aph ^ 1, WAIT_LIMIT)) {
@@ -179,36 +188,53 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
         }
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base + a * BN;
-        const int q_col_off = ((qt * BN) & 127) >> 5;       // tile start inside its first 128-row scale group
-        for (int ks = 0; ks < k_stages; ++ks, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
+        // tile start inside its first 128-row scale group, in 32-row TMEM columns
+        int pt, qt;
+        tile_coords(t, p, pt, qt);
+        const uint32_t qoff = (static_cast<uint32_t>(qt * BN) & 127u) >> 5;
+        for (int ks = 0; ks < k_stages; ++ks) {
           if (!ptx::mbar_wait_bounded(&full[s], ph, WAIT_LIMIT)) {
-            atomicOr(&g_status_word, 8u); *abort_flag = 1; break;
+            atomicOr(&g_status_word, 8u); *abort_flag = 1; aborted = true; break;
           }
           ptx::tc_fence_after();
-          const uint32_t st = ptx::smem_u32(smem + s * L::STAGE_BYTES);
-          const uint32_t sf_tmem = tmem_base + ACC_COLS + (it & 1) * SF_COLS;
-          const uint64_t a_desc = ptx::desc_sw128_kmajor(st);
-          const uint64_t b_desc = ptx::desc_sw128_kmajor(st + L::A_BYTES);
+          const uint32_t a_lo = op_lo0 + s * (L::STAGE_BYTES >> 4);
+          const uint32_t b_lo = a_lo + (L::A_BYTES >> 4);
+          const uint32_t sfp_lo = sf_lo0 + s * (L::STAGE_BYTES >> 4);
+          const uint32_t sfq_lo = sfp_lo + (L::SFP_BYTES >> 4);
+          const uint32_t sf_tmem = tmem_base + ACC_COLS + sfbuf * SF_COLS;
           const int kts = min(KT_PER_STAGE, p.k_tiles - ks * KT_PER_STAGE);
-          for (int kt = 0; kt < kts; ++kt) {
-            const uint32_t sfp_t = sf_tmem + kt * 4;
-            const uint32_t sfq_t = sf_tmem + KT_PER_STAGE * 4 + kt * SFQ_COLS_PER_KT;
-            ptx::tc_cp_32x128b_warpx4(sfp_t, ptx::desc_sf_32x16(st + L::A_BYTES + L::B_BYTES + kt * SF_TILE));
+          const bool do_copy = copy_always || (tl == 0 && ks < 2);
+          if (kts == KT_PER_STAGE) {
 #pragma unroll
-            for (int b = 0; b < L::SFQ_BLOCKS; ++b)
-              ptx::tc_cp_32x128b_warpx4(
-                  sfq_t + 4 * b,
-                  ptx::desc_sf_32x16(st + L::A_BYTES + L::B_BYTES + L::SFP_BYTES +
-                                     (b * KT_PER_STAGE + kt) * SF_TILE));
-            // +2 per k-tile: 32 bytes (64 e2m1) along K inside the 128-byte swizzle span
-            ptx::tc_mma_nvf4(d_tmem, a_desc + 2 * kt, b_desc + 2 * kt, IDESC, sfp_t, sfq_t + q_col_off,
-                             (ks | kt) != 0);
+            for (int kt = 0; kt < KT_PER_STAGE; ++kt) {
+              const uint32_t sfp_t = sf_tmem + kt * 4;
+              const uint32_t sfq_t = sf_tmem + KT_PER_STAGE * 4 + kt * SFQ_COLS_PER_KT;
+              if (do_copy) {
+                ptx::tc_cp_32x128b_warpx4(sfp_t, sfp_lo + kt * (SF_TILE >> 4), sf_hi);
+#pragma unroll
+                for (int b = 0; b < L::SFQ_BLOCKS; ++b)
+                  ptx::tc_cp_32x128b_warpx4(sfq_t + 4 * b, sfq_lo + (b * KT_PER_STAGE + kt) * (SF_TILE >> 4), sf_hi);
+              }
+              // +2 per k-tile: 32 bytes (64 e2m1) along K inside the 128-byte swizzle span
+              ptx::tc_mma_nvf4(d_tmem, a_lo + 2 * kt, b_lo + 2 * kt, op_hi, IDESC, sfp_t, sfq_t + qoff,
+                               (ks | kt) != 0);
+            }
+          } else {
+            for (int kt = 0; kt < kts; ++kt) {
+              const uint32_t sfp_t = sf_tmem + kt * 4;
+              const uint32_t sfq_t = sf_tmem + KT_PER_STAGE * 4 + kt * SFQ_COLS_PER_KT;
+              ptx::tc_cp_32x128b_warpx4(sfp_t, sfp_lo + kt * (SF_TILE >> 4), sf_hi);
+              for (int b = 0; b < L::SFQ_BLOCKS; ++b)
+                ptx::tc_cp_32x128b_warpx4(sfq_t + 4 * b, sfq_lo + (b * KT_PER_STAGE + kt) * (SF_TILE >> 4), sf_hi);
+              ptx::tc_mma_nvf4(d_tmem, a_lo + 2 * kt, b_lo + 2 * kt, op_hi, IDESC, sfp_t, sfq_t + qoff,
+                               (ks | kt) != 0);
+            }
           }
           ptx::tc_commit(&empty[s]);
+          sfbuf ^= 1u;
+          if (++s == STAGES) { s = 0; ph ^= 1u; }
         }
-        if (*abort_flag) break;
+        if (aborted) break;
         ptx::tc_commit(&acc_full[a]);
       }
     }
@@ -268,7 +294,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
               uint4 o;
               o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
               o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
-              *reinterpret_cast<uint4*>(p.d + off + 8 * g) = o;
+              if (!(p.dbg & 1)) *reinterpret_cast<uint4*>(p.d + off + 8 * g) = o;
             }
           }
         } else {
@@ -390,6 +416,7 @@ int run_gemm(const void* p_packed, const void* sfp, int P, const void* q_packed,
   p.ldd = ldd;
   p.alpha = alpha; p.beta = beta;
   p.group_m = 16;
+  p.dbg = g_opt_gemm_debug;
 
   // configuration: 1 = 128x128 (2 acc), 2 = 128x256 (1 acc), 3 = 128x192 (2 acc);
   // swapped: 11 = N16, 12 = N32, 13 = N64, 14 = N128

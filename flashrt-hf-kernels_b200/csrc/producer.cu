@@ -9,6 +9,7 @@ namespace frt {
 std::atomic<int64_t> g_launches{0};
 int g_opt_quant_encoder = 0;
 int g_opt_gemm_config = 0;
+int g_opt_gemm_debug = 0;
 
 namespace {
 
@@ -326,6 +327,7 @@ int frt_set_option(int key, int value) {
   int prev = -1;
   if (key == FRT_OPT_QUANT_ENCODER) { prev = g_opt_quant_encoder; g_opt_quant_encoder = value; }
   if (key == FRT_OPT_GEMM_CONFIG) { prev = g_opt_gemm_config; g_opt_gemm_config = value; }
+  if (key == 3) { prev = g_opt_gemm_debug; g_opt_gemm_debug = value; }
   return prev;
 }
 

@@ -111,18 +111,26 @@ __device__ __forceinline__ void tc_commit(uint64_t* bar) {
 
 // shared -> TMEM copy of 32 rows x 128 bit, replicated into the four 32-lane
 // quarters (scale-factor staging).
-__device__ __forceinline__ void tc_cp_32x128b_warpx4(uint32_t taddr, uint64_t sdesc) {
-  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+__device__ __forceinline__ void tc_cp_32x128b_warpx4(uint32_t taddr, uint32_t desc_lo, uint32_t desc_hi) {
+  asm volatile(
+      "{\n\t.reg .b64 d;\n\t"
+      "mov.b64 d, {%1, %2};\n\t"
+      "tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], d;\n\t}"
+      ::"r"(taddr), "r"(desc_lo), "r"(desc_hi) : "memory");
 }
 
 // D[tmem] (+)= A[smem] * B[smem], e2m1 x e2m1 with UE4M3 scales per 16 elements.
-__device__ __forceinline__ void tc_mma_nvf4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                            uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+__device__ __forceinline__ void tc_mma_nvf4(uint32_t d_tmem, uint32_t a_desc_lo, uint32_t b_desc_lo,
+                                            uint32_t desc_hi, uint32_t idesc, uint32_t sfa_tmem,
+                                            uint32_t sfb_tmem, uint32_t accumulate) {
   asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %6, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %3};\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %7, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], da, db, %4, [%5], [%6], p;\n\t}"
+      ::"r"(d_tmem), "r"(a_desc_lo), "r"(b_desc_lo), "r"(desc_hi), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem),
+        "r"(accumulate)
       : "memory");
 }
 

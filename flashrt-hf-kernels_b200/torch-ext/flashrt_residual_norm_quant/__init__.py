@@ -1,0 +1,51 @@
+"""BF16 RMSNorm ops (B200 build) with the reference package's function names
+(flashrt-residual-norm-quant/torch-ext/flashrt_residual_norm_quant/__init__.py:97-175).
+The FP8 and LayerNorm members of that package are outside the NVFP4 path and
+are not provided here."""
+from __future__ import annotations
+
+import torch
+
+from ._ops import add_op_namespace_prefix, ops
+
+
+def _check(x, other, name):
+    if x.dim() != 2 or other.shape != x.shape:
+        raise RuntimeError(f"{name} and x must have the same 2D shape")
+
+
+@torch.library.register_fake(add_op_namespace_prefix("rms_norm_bf16"))
+def _rms_norm_fake(x, weight, eps, out) -> None:
+    _check(x, out, "out")
+    if weight.shape != (x.shape[1],):
+        raise RuntimeError("weight must have shape (x.shape[1],)")
+    return None
+
+
+@torch.library.register_fake(add_op_namespace_prefix("residual_add_rms_norm_bf16"))
+def _residual_add_rms_norm_fake(residual, x, weight, eps, out) -> None:
+    if residual.shape != x.shape:
+        raise RuntimeError("residual and x must have the same shape")
+    _check(x, out, "out")
+    if weight.shape != (x.shape[1],):
+        raise RuntimeError("weight must have shape (x.shape[1],)")
+    return None
+
+
+def rms_norm_bf16(x, weight, eps: float = 1e-6, out=None):
+    """BF16 RMSNorm with affine weight."""
+    if out is None:
+        out = torch.empty_like(x, dtype=torch.bfloat16)
+    ops.rms_norm_bf16(x, weight, float(eps), out)
+    return out
+
+
+def residual_add_rms_norm_bf16(residual, x, weight, eps: float = 1e-6, out=None):
+    """In-place ``residual += x`` followed by weighted BF16 RMSNorm."""
+    if out is None:
+        out = torch.empty_like(x, dtype=torch.bfloat16)
+    ops.residual_add_rms_norm_bf16(residual, x, weight, float(eps), out)
+    return out
+
+
+__all__ = ["rms_norm_bf16", "residual_add_rms_norm_bf16"]

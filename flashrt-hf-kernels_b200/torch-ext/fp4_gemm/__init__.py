@@ -1,0 +1,193 @@
+"""NVFP4 A4W4 GEMM and quantise helpers (B200 build) with the reference
+package's function names (fp4-gemm/torch-ext/fp4_gemm/__init__.py).  Only the
+members on the NVFP4 linear path are provided; `variant`, `warps` and `stages`
+are accepted for call compatibility and do not select kernels: the tile
+configuration follows from the shape."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from flashrt_b200_core import alloc_fp4 as _alloc_fp4, sfa_size_bytes
+
+from ._ops import add_op_namespace_prefix, ops
+
+
+def capabilities() -> dict:
+    """Facts about this build (mirrors the reference's capabilities() dict)."""
+    return {
+        "arch": "sm_100a",
+        "device": "NVIDIA B200",
+        "gemm": "tcgen05.mma kind::mxf4nvf4 (block 16, UE4M3), TMEM accumulators, TMA-fed, persistent",
+        "outputs": ("bf16",),
+        "epilogues": ("alpha", "bias", "residual", "bias+residual"),
+        "k_alignment": 32,
+        "n_alignment": 8,
+        "small_m_max": 64,
+        "quantizer_rule": "thresholds, ties to the smaller magnitude; scale = e4m3_rn(max(amax/6, 1e-12))",
+        "graph_safe": True,
+        "errors": "exceptions",
+    }
+
+
+def _gemm_fake_check(a, b, out):
+    if a.dim() != 2 or b.dim() != 2 or a.shape[1] != b.shape[1]:
+        raise RuntimeError("a_packed and b_packed must be (M, K/2) and (N, K/2)")
+    if out.shape != (a.shape[0], b.shape[0]):
+        raise RuntimeError("out must have shape (M, N)")
+
+
+@torch.library.register_fake(add_op_namespace_prefix("nvfp4_gemm_bf16"))
+def _gemm_fake(a_packed, b_packed, sfa, sfb, out, alpha=1.0, variant=-1) -> None:
+    _gemm_fake_check(a_packed, b_packed, out)
+    return None
+
+
+@torch.library.register_fake(add_op_namespace_prefix("fp4_w4a16_linear_bf16"))
+def _linear_fake(a_packed, b_packed, sfa, sfb, out, alpha=1.0, variant=-1) -> None:
+    _gemm_fake_check(a_packed, b_packed, out)
+    return None
+
+
+@torch.library.register_fake(add_op_namespace_prefix("nvfp4_gemm_bias_bf16"))
+def _bias_fake(a, b, sfa, sfb, bias, out) -> None:
+    _gemm_fake_check(a, b, out)
+    return None
+
+
+@torch.library.register_fake(add_op_namespace_prefix("nvfp4_gemm_bias_residual_bf16"))
+def _bias_residual_fake(a, b, sfa, sfb, bias, residual, out) -> None:
+    _gemm_fake_check(a, b, out)
+    return None
+
+
+@torch.library.register_fake(add_op_namespace_prefix("nvfp4_gemm_residual_bf16"))
+def _residual_fake(a, b, sfa, sfb, residual, out, alpha=1.0) -> None:
+    _gemm_fake_check(a, b, out)
+    return None
+
+
+@torch.library.register_fake(add_op_namespace_prefix("fp4_w4a4_gemv_warpsplit_bf16"))
+def _gemv_fake(a, b, sfa, sfb, out, alpha=1.0, warps=4, stages=4) -> None:
+    return None
+
+
+@torch.library.register_fake(add_op_namespace_prefix("fp4_w4a4_gemm_warpsplit_mrows_bf16"))
+def _mrows_fake(a, b, sfa, sfb, out, alpha=1.0, warps=2, stages=6) -> None:
+    return None
+
+
+@torch.library.register_fake(add_op_namespace_prefix("quantize_fp4_sfa_fp16"))
+def _quantize_fp16_fake(x, packed, sfa, is_sfb=False) -> None:
+    return None
+
+
+@torch.library.register_fake(add_op_namespace_prefix("quantize_fp4_sfa_bf16"))
+def _quantize_bf16_fake(x, packed, sfa, is_sfb=False) -> None:
+    return None
+
+
+@torch.library.register_fake(add_op_namespace_prefix("dequantize_fp4_sfa_fp16"))
+def _dequantize_fake(packed, sfa, out, is_sfb=False) -> None:
+    return None
+
+
+def quantize_fp4_sfa_fp16(x, packed=None, sfa=None, is_sfb: bool = False):
+    if packed is None or sfa is None:
+        packed, sfa = _alloc_fp4(x.shape[0], x.shape[1], x.device)
+    ops.quantize_fp4_sfa_fp16(x, packed, sfa, bool(is_sfb))
+    return packed, sfa
+
+
+def quantize_fp4_sfa_bf16(x, packed=None, sfa=None, is_sfb: bool = False):
+    if packed is None or sfa is None:
+        packed, sfa = _alloc_fp4(x.shape[0], x.shape[1], x.device)
+    ops.quantize_fp4_sfa_bf16(x, packed, sfa, bool(is_sfb))
+    return packed, sfa
+
+
+def dequantize_fp4_sfa_fp16(packed, sfa, out=None, is_sfb: bool = False):
+    if out is None:
+        out = torch.empty((packed.shape[0], packed.shape[1] * 2), device=packed.device, dtype=torch.float16)
+    ops.dequantize_fp4_sfa_fp16(packed, sfa, out, bool(is_sfb))
+    return out
+
+
+def _out_like(a_packed, b_packed):
+    return torch.empty((a_packed.shape[0], b_packed.shape[0]), device=a_packed.device, dtype=torch.bfloat16)
+
+
+def nvfp4_gemm_bf16(a_packed, b_packed, sfa, sfb, alpha: float = 1.0, out=None, variant: int = -1):
+    """out[M,N] = bf16(alpha * A . B^T) for packed NVFP4 A [M,K/2], B [N,K/2]."""
+    if out is None:
+        out = _out_like(a_packed, b_packed)
+    ops.nvfp4_gemm_bf16(a_packed, b_packed, sfa, sfb, out, float(alpha), int(variant))
+    return out
+
+
+def fp4_w4a16_linear_bf16(a_packed, b_packed, sfa, sfb, alpha: float = 1.0, out=None, variant: int = -1):
+    """Compatibility alias for :func:`nvfp4_gemm_bf16`."""
+    return nvfp4_gemm_bf16(a_packed, b_packed, sfa, sfb, alpha=alpha, out=out, variant=variant)
+
+
+def nvfp4_gemm_bias_bf16(a_packed, b_packed, sfa, sfb, bias, *, out=None):
+    if out is None:
+        out = _out_like(a_packed, b_packed)
+    ops.nvfp4_gemm_bias_bf16(a_packed, b_packed, sfa, sfb, bias, out)
+    return out
+
+
+def nvfp4_gemm_bias_residual_bf16(a_packed, b_packed, sfa, sfb, bias, residual, *, out=None):
+    if out is None:
+        out = torch.empty_like(residual)
+    ops.nvfp4_gemm_bias_residual_bf16(a_packed, b_packed, sfa, sfb, bias, residual, out)
+    return out
+
+
+def nvfp4_gemm_residual_bf16(a_packed, b_packed, sfa, sfb, residual, alpha: float = 1.0, out=None):
+    if out is None:
+        out = torch.empty_like(residual)
+    ops.nvfp4_gemm_residual_bf16(a_packed, b_packed, sfa, sfb, residual, out, float(alpha))
+    return out
+
+
+def fp4_w4a4_gemv_warpsplit_bf16(a_packed, b_packed, sfa, sfb, *, alpha: float = 1.0, warps: int = 4,
+                                 stages: int = 4, out: Optional[torch.Tensor] = None):
+    """M = 1 decode row (weight-streaming configuration of the same GEMM)."""
+    if out is None:
+        out = torch.empty((1, b_packed.shape[0]), device=a_packed.device, dtype=torch.bfloat16)
+    ops.fp4_w4a4_gemv_warpsplit_bf16(a_packed, b_packed, sfa, sfb, out, float(alpha), int(warps), int(stages))
+    return out
+
+
+def fp4_w4a4_gemm_warpsplit_mrows_bf16(a_packed, b_packed, sfa, sfb, *, alpha: float = 1.0, warps: int = 2,
+                                       stages: int = 6, out: Optional[torch.Tensor] = None):
+    """1..16 rows riding one weight stream."""
+    if out is None:
+        out = _out_like(a_packed, b_packed)
+    ops.fp4_w4a4_gemm_warpsplit_mrows_bf16(a_packed, b_packed, sfa, sfb, out, float(alpha), int(warps),
+                                           int(stages))
+    return out
+
+
+def pack_nvfp4_weight_bf16(weight: torch.Tensor, bias: Optional[torch.Tensor] = None):
+    """Bind-time packing of a [N, K] bf16 weight: zero-pads N to a multiple of 8
+    and K to a multiple of 32, quantises, and returns
+    (packed, sfb, padded_bias, (logical_n, logical_k))."""
+    n, k = weight.shape
+    pn, pk = (n + 7) // 8 * 8, (k + 31) // 32 * 32
+    w = weight.to(torch.bfloat16)
+    if (pn, pk) != (n, k):
+        w = torch.nn.functional.pad(w, (0, pk - k, 0, pn - n))
+    packed, sfb = quantize_fp4_sfa_bf16(w.contiguous(), is_sfb=True)
+    padded_bias = None
+    if bias is not None:
+        padded_bias = torch.nn.functional.pad(bias.to(torch.bfloat16), (0, pn - n)).contiguous()
+    return packed, sfb, padded_bias, (n, k)
+
+
+__all__ = ["capabilities", "sfa_size_bytes", "quantize_fp4_sfa_fp16", "quantize_fp4_sfa_bf16",
+           "dequantize_fp4_sfa_fp16", "nvfp4_gemm_bf16", "fp4_w4a16_linear_bf16", "nvfp4_gemm_bias_bf16",
+           "nvfp4_gemm_bias_residual_bf16", "nvfp4_gemm_residual_bf16", "fp4_w4a4_gemv_warpsplit_bf16",
+           "fp4_w4a4_gemm_warpsplit_mrows_bf16", "pack_nvfp4_weight_bf16"]
