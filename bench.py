@@ -279,13 +279,14 @@ def run_ours(args, rank, world, local_rank):
         for s_ in (copy_s, comp_s, out_s):
             s_.synchronize()
 
-    e2e_steps(max(3, args.warmup // 4))
+    e2e_n = 0 if args.no_e2e else max(10, args.steps // 4)
+    if e2e_n:
+        e2e_steps(max(3, args.warmup // 4))
     barrier()
-    e2e_n = max(10, args.steps // 4)
     w0 = time.perf_counter()
     e2e_steps(e2e_n)
     barrier()
-    e2e_ms = (time.perf_counter() - w0) * 1e3 / e2e_n
+    e2e_ms = (time.perf_counter() - w0) * 1e3 / max(e2e_n, 1)
     if world > 1:
         t = torch.tensor([e2e_ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -438,6 +439,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))

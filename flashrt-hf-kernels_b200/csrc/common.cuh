@@ -73,12 +73,13 @@ __device__ __forceinline__ uint32_t e2m1_rule_a_chain(float q) {
 // nearest even; replacing |q| by the float just below it with its lowest
 // mantissa bit set puts the value strictly on the rule-A side of every
 // threshold (thresholds have a clear low bit), so no tie is ever seen and the
-// hardware result equals the compare chain.  `q + 0` turns -0 into +0, whose
-// sign bit the chain would not set.
+// hardware result equals the compare chain.  The caller produces q as
+// fma(v, inv, +0): the rounding of v*inv is unchanged and a -0 product becomes
+// +0, whose sign bit the chain would not set.
 __device__ __forceinline__ float rule_a_nudge(float q) {
-  const uint32_t u = __float_as_uint(__fadd_rn(q, 0.f));
+  const uint32_t u = __float_as_uint(q);
   const uint32_t mag = u & 0x7fffffffu;
-  const uint32_t nudged = ((mag == 0u ? 1u : mag) - 1u) | 1u;
+  const uint32_t nudged = (max(mag, 1u) - 1u) | 1u;
   return __uint_as_float((u & 0x80000000u) | nudged);
 }
 
@@ -105,8 +106,14 @@ __device__ __forceinline__ uint2 quantize_block16(const float (&v)[16], uint8_t&
   uint32_t w[2] = {0u, 0u};
 #pragma unroll
   for (int p = 0; p < 8; ++p) {
-    const float q0 = __fmul_rn(v[2 * p], inv);
-    const float q1 = __fmul_rn(v[2 * p + 1], inv);
+    float q0, q1;
+    if (ENC == kEncHw) {
+      q0 = __fmaf_rn(v[2 * p], inv, 0.f);
+      q1 = __fmaf_rn(v[2 * p + 1], inv, 0.f);
+    } else {
+      q0 = __fmul_rn(v[2 * p], inv);
+      q1 = __fmul_rn(v[2 * p + 1], inv);
+    }
     uint32_t byte;
     if (ENC == kEncHw) byte = e2m1x2_rule_a_hw(q0, q1);
     else if (ENC == kEncRne) byte = e2m1x2_rne_hw(q0, q1);

@@ -323,6 +323,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
   if (warp == 1) ptx::tmem_dealloc(tmem_base, 512);
 }
 
+#include "gemm_pair.cuh"
+
 // ---------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------
@@ -349,6 +351,20 @@ int make_operand_map(CUtensorMap* map, const void* base, int rows, int K, int bo
   const cuuint32_t estr[2] = {1, 1};
   const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? FRT_OK : FRT_E_DRIVER;
+}
+
+// swizzled scale buffer as [row_blocks][sf_cols][512 bytes]; box = `blocks` row groups x 4 k-tiles
+int make_sf_map(CUtensorMap* map, const void* base, int rows, int sf_cols, int blocks) {
+  auto enc = get_encode();
+  if (!enc) return FRT_E_DRIVER;
+  const cuuint64_t dims[3] = {128, static_cast<cuuint64_t>(sf_cols), static_cast<cuuint64_t>((rows + 127) / 128)};
+  const cuuint64_t strides[2] = {512, static_cast<cuuint64_t>(sf_cols) * 512};
+  const cuuint32_t box[3] = {128, KT_PER_STAGE, static_cast<cuuint32_t>(blocks)};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<void*>(base), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? FRT_OK : FRT_E_DRIVER;
 }
@@ -389,6 +405,31 @@ int launch_gemm(const CUtensorMap& mp, const CUtensorMap& mq, GemmParams& p, int
   return launch_result();
 }
 
+template <int BN, int STAGES>
+int launch_gemm_pair(const void* p_packed, const void* q_packed, GemmParams& p, int sms, cudaStream_t st) {
+  using L = PairLayout<BN, STAGES>;
+  auto kern = nvfp4_gemm_pair_kernel<BN, STAGES>;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_set[dev & 63]) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL) != cudaSuccess)
+      return FRT_E_LAUNCH;
+    attr_set[dev & 63] = true;
+  }
+  PairMaps maps;
+  if (int rc = make_operand_map(&maps.p, p_packed, p.P, p.K, 128)) return rc;
+  if (int rc = make_operand_map(&maps.q, q_packed, p.Q, p.K, BN / 2)) return rc;
+  if (int rc = make_sf_map(&maps.sfp, p.sfp, p.P, p.sf_cols, 1)) return rc;
+  if (int rc = make_sf_map(&maps.sfq, p.sfq, p.Q, p.sf_cols, L::SFQ_BLOCKS)) return rc;
+  p.q_tiles = (p.Q + BN - 1) / BN;
+  p.p_tiles = (p.P + 255) / 256;
+  const int tiles = p.p_tiles * p.q_tiles;
+  const int pairs = tiles < sms / 2 ? tiles : sms / 2;
+  kern<<<2 * pairs, 192, L::TOTAL, st>>>(maps, p);
+  return launch_result();
+}
+
 }  // namespace
 
 unsigned* device_status_word() {
@@ -418,12 +459,21 @@ int run_gemm(const void* p_packed, const void* sfp, int P, const void* q_packed,
   p.group_m = 16;
   p.dbg = g_opt_gemm_debug;
 
-  // configuration: 1 = 128x128 (2 acc), 2 = 128x256 (1 acc), 3 = 128x192 (2 acc);
-  // swapped: 11 = N16, 12 = N32, 13 = N64, 14 = N128
+  // configuration: one CTA per tile: 1 = 128x128 (2 acc), 2 = 128x256 (1 acc), 3 = 128x192 (2 acc);
+  // CTA pair per tile: 4 = 256x256, 5 = 256x192, 6 = 256x128;
+  // swapped (small token counts): 11 = N16, 12 = N32, 13 = N64, 14 = N128
   int cfg = config;
   if (cfg == 0) {
     if (swap) cfg = Q <= 16 ? 11 : Q <= 32 ? 12 : Q <= 64 ? 13 : 14;
-    else cfg = 2;
+    else cfg = P > 128 ? 4 : (K >= 8192 ? 2 : 3);
+  }
+  if (cfg >= 4 && cfg <= 6) {
+    if (swap) return FRT_E_UNSUPPORTED;
+    switch (cfg) {
+      case 4: return launch_gemm_pair<256, 5>(p_packed, q_packed, p, di.sms, st);
+      case 5: return launch_gemm_pair<192, 6>(p_packed, q_packed, p, di.sms, st);
+      default: return launch_gemm_pair<128, 7>(p_packed, q_packed, p, di.sms, st);
+    }
   }
   int bn = 0;
   switch (cfg) {

@@ -1,0 +1,268 @@
+// CTA-pair (tcgen05 cta_group::2) form of the NVFP4 GEMM for prefill shapes.
+// Included by gemm.cu inside its unnamed namespace (shares GemmParams, the
+// status word and the tile raster).
+//
+// Two CTAs on one TPC form a cluster and compute a 256 x BN output tile: CTA r
+// owns rows [128 r, 128 r + 128) of the tile (its accumulator lives in its own
+// TMEM) and stages only ITS half of the operands - 128 rows of P and BN/2 rows
+// of Q per K stage - so every byte of P and Q crosses L2 -> shared memory once
+// per pair instead of once per CTA, and the Q tile read by the tensor cores is
+// gathered from both CTAs' shared memory.  Scale factors: each CTA stages the
+// scales of its own P rows and of all BN Q rows.  No load is multicast.
+//
+//   warp 0   TMA producer of this CTA's half (tensor maps for operands AND scale
+//            tiles); completion bytes of both CTAs are credited to the leader's
+//            `full` barrier.
+//   warp 1   leader CTA only: tcgen05.cp (scales smem -> TMEM, both CTAs) and
+//            tcgen05.mma cta_group::2; tcgen05.commit multicast to both CTAs'
+//            `empty` / `acc_full` barriers.
+//   warps 2..5 epilogue of this CTA's 128 rows.
+//
+// TMEM (512 columns per CTA): two 128 x BN fp32 accumulators and one scale
+// buffer.  For BN = 256 the accumulators overlap ([0,256) and [208,464), scales
+// at [464,512)): the epilogue of tile t drains the shared columns first and
+// releases them, so the mainloop of tile t+1 runs under the rest of the drain.
+#pragma once
+
+struct PairMaps {
+  CUtensorMap p, q, sfp, sfq;
+};
+
+template <int BN, int STAGES>
+struct PairLayout {
+  static constexpr int A_BYTES = 128 * 128;              // this CTA's 128 rows of P
+  static constexpr int B_BYTES = (BN / 2) * 128;         // this CTA's half of the Q tile
+  static constexpr int SFQ_BLOCKS = BN <= 128 ? 1 : 2;
+  static constexpr int SFP_BYTES = KT_PER_STAGE * SF_TILE;
+  static constexpr int SFQ_BYTES = SFQ_BLOCKS * KT_PER_STAGE * SF_TILE;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFP_BYTES + SFQ_BYTES;
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 + 256;
+  static constexpr int SF_COLS = KT_PER_STAGE * (4 + SFQ_BLOCKS * 4);
+  // accumulator placement: disjoint when they fit, else overlapping by OVERLAP columns
+  static constexpr int ACC1 = (2 * BN + SF_COLS <= 512) ? BN : 512 - SF_COLS - BN;
+  static constexpr int OVERLAP = BN - ACC1;              // 0 when disjoint
+  static constexpr int SF_BASE = ACC1 + BN;
+  static_assert(SF_BASE + SF_COLS <= 512, "TMEM budget");
+  static_assert(BN % 32 == 0 && OVERLAP >= 0, "tile shape");
+};
+
+template <int BN, int STAGES>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p) {
+  using L = PairLayout<BN, STAGES>;
+  constexpr int SFQ_COLS_PER_KT = L::SFQ_BLOCKS * 4;
+  constexpr uint32_t IDESC = ptx::idesc_nvf4(256, BN);
+  constexpr int CHUNKS = BN / 32;
+  constexpr int RELEASE_CHUNKS = (L::OVERLAP + 31) / 32;   // chunks that cover the shared columns
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * L::STAGE_BYTES);
+  uint64_t* full = bars;                    // [STAGES] used in the leader: both CTAs' TMA bytes
+  uint64_t* empty = bars + STAGES;          // [STAGES] in each CTA: multicast commit from the leader
+  uint64_t* acc_full = bars + 2 * STAGES;   // [2] in each CTA: multicast commit from the leader
+  uint64_t* acc_free = acc_full + 2;        // [1] used in the leader: 8 epilogue warps of the pair
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_free + 1);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = ptx::cluster_ctarank();
+  const bool leader = rank == 0;
+  const int pair_id = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  const int total_tiles = p.p_tiles * p.q_tiles;
+  const int k_stages = (p.k_tiles + KT_PER_STAGE - 1) / KT_PER_STAGE;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < STAGES; ++i) { ptx::mbar_init(&full[i], 1); ptx::mbar_init(&empty[i], 1); }
+    ptx::mbar_init(&acc_full[0], 1);
+    ptx::mbar_init(&acc_full[1], 1);
+    ptx::mbar_init(acc_free, 8);
+    *abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::prefetch_tensormap(&maps.p);
+    ptx::prefetch_tensormap(&maps.q);
+    ptx::prefetch_tensormap(&maps.sfp);
+    ptx::prefetch_tensormap(&maps.sfq);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc_pair(tmem_slot, 512);
+    ptx::tmem_relinquish_pair();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  // both CTAs' barriers must be initialised before either signals the other
+  ptx::cluster_arrive();
+  ptx::cluster_wait();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ===================== TMA producer (both CTAs) =====================
+    if (ptx::elect_one()) {
+      const uint32_t smem0 = ptx::smem_u32(smem);
+      const uint32_t full0 = ptx::smem_u32(full) & 0xFEFFFFFFu;   // the leader CTA's barrier array
+      int s = 0, it = 0;
+      uint32_t ph = 0;
+      for (int t = pair_id; t < total_tiles && !*abort_flag; t += num_pairs) {
+        int pt, qt;
+        tile_coords(t, p, pt, qt);
+        const int p_row = pt * 256 + static_cast<int>(rank) * 128;
+        const int q_row = qt * BN + static_cast<int>(rank) * (BN / 2);
+        const int p_blk = p_row >> 7;
+        const int q_blk = (qt * BN) >> 7;
+        for (int ks = 0; ks < k_stages; ++ks, ++it) {
+          if (!ptx::mbar_wait_bounded(&empty[s], ph ^ 1, WAIT_LIMIT)) {
+            atomicOr(&g_status_word, 1u); *abort_flag = 1; break;
+          }
+          const uint32_t st = smem0 + s * L::STAGE_BYTES;
+          const uint32_t bar = full0 + s * 8;
+          if (leader) ptx::mbar_expect_tx(&full[s], 2 * L::STAGE_BYTES);
+          ptx::tma_load_2d_pair(st, &maps.p, bar, ks * 128, p_row);
+          ptx::tma_load_2d_pair(st + L::A_BYTES, &maps.q, bar, ks * 128, q_row);
+          ptx::tma_load_3d_pair(st + L::A_BYTES + L::B_BYTES, &maps.sfp, bar, 0, ks * KT_PER_STAGE, p_blk);
+          ptx::tma_load_3d_pair(st + L::A_BYTES + L::B_BYTES + L::SFP_BYTES, &maps.sfq, bar, 0, ks * KT_PER_STAGE,
+                                q_blk);
+          if (++s == STAGES) { s = 0; ph ^= 1u; }
+        }
+      }
+      if (!*abort_flag) {   // drain: every armed stage has been consumed before this CTA may exit
+        for (int i = 0; i < STAGES && i < it; ++i) {
+          const int j = it - 1 - i;
+          if (!ptx::mbar_wait_bounded(&empty[j % STAGES], (j / STAGES) & 1, WAIT_LIMIT)) {
+            atomicOr(&g_status_word, 2u); break;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ===================== MMA issuer (leader CTA) =====================
+    if (leader && ptx::elect_one()) {
+      const uint32_t smem0 = ptx::smem_u32(smem);
+      const uint64_t op_desc = ptx::desc_sw128_kmajor(smem0);
+      const uint64_t sf_desc = ptx::desc_sf_32x16(smem0 + L::A_BYTES + L::B_BYTES);
+      const uint32_t op_hi = static_cast<uint32_t>(op_desc >> 32), op_lo0 = static_cast<uint32_t>(op_desc);
+      const uint32_t sf_hi = static_cast<uint32_t>(sf_desc >> 32), sf_lo0 = static_cast<uint32_t>(sf_desc);
+      const uint32_t sf_tmem = tmem_base + L::SF_BASE;
+      int s = 0, tl = 0;
+      uint32_t ph = 0;
+      bool aborted = false;
+      for (int t = pair_id; t < total_tiles && !*abort_flag; t += num_pairs, ++tl) {
+        const int a = tl & 1;
+        // tile tl may start once the epilogues of tile tl-1 have drained the columns the two
+        // accumulators share (which also means tile tl-2, same accumulator, is fully drained)
+        if (tl > 0 && !ptx::mbar_wait_bounded(acc_free, (tl - 1) & 1, WAIT_LIMIT)) {
+          atomicOr(&g_status_word, 4u); *abort_flag = 1; break;
+        }
+        ptx::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (a ? L::ACC1 : 0);
+        int pt, qt;
+        tile_coords(t, p, pt, qt);
+        const uint32_t qoff = (static_cast<uint32_t>(qt * BN) & 127u) >> 5;
+        for (int ks = 0; ks < k_stages; ++ks) {
+          if (!ptx::mbar_wait_bounded(&full[s], ph, WAIT_LIMIT)) {
+            atomicOr(&g_status_word, 8u); *abort_flag = 1; aborted = true; break;
+          }
+          ptx::tc_fence_after();
+          const uint32_t a_lo = op_lo0 + s * (L::STAGE_BYTES >> 4);
+          const uint32_t b_lo = a_lo + (L::A_BYTES >> 4);
+          const uint32_t sfp_lo = sf_lo0 + s * (L::STAGE_BYTES >> 4);
+          const uint32_t sfq_lo = sfp_lo + (L::SFP_BYTES >> 4);
+          const int kts = min(KT_PER_STAGE, p.k_tiles - ks * KT_PER_STAGE);
+#pragma unroll
+          for (int kt = 0; kt < KT_PER_STAGE; ++kt) {
+            if (kt < kts) {
+              const uint32_t sfp_t = sf_tmem + kt * 4;
+              const uint32_t sfq_t = sf_tmem + KT_PER_STAGE * 4 + kt * SFQ_COLS_PER_KT;
+              ptx::tc_cp_32x128b_warpx4_pair(sfp_t, sfp_lo + kt * (SF_TILE >> 4), sf_hi);
+#pragma unroll
+              for (int b = 0; b < L::SFQ_BLOCKS; ++b)
+                ptx::tc_cp_32x128b_warpx4_pair(sfq_t + 4 * b, sfq_lo + (b * KT_PER_STAGE + kt) * (SF_TILE >> 4),
+                                               sf_hi);
+              ptx::tc_mma_nvf4_pair(d_tmem, a_lo + 2 * kt, b_lo + 2 * kt, op_hi, IDESC, sfp_t, sfq_t + qoff,
+                                    (ks | kt) != 0);
+            }
+          }
+          ptx::tc_commit_pair(&empty[s], 3);
+          if (++s == STAGES) { s = 0; ph ^= 1u; }
+        }
+        if (aborted) break;
+        ptx::tc_commit_pair(&acc_full[a], 3);
+      }
+    }
+  } else {
+    // ===================== epilogue (warps 2..5, both CTAs) =====================
+    const int quarter = warp & 3;
+    const uint32_t free_addr = ptx::mapa(ptx::smem_u32(acc_free), 0);   // the leader's barrier
+    int tl = 0;
+    for (int t = pair_id; t < total_tiles && !*abort_flag; t += num_pairs, ++tl) {
+      int pt, qt;
+      tile_coords(t, p, pt, qt);
+      const int a = tl & 1;
+      if (!ptx::mbar_wait_bounded(&acc_full[a], (tl >> 1) & 1, WAIT_LIMIT)) {
+        if (lane == 0) { atomicOr(&g_status_word, 16u); *abort_flag = 1; }
+        break;
+      }
+      ptx::tc_fence_after();
+      const int prow = pt * 256 + static_cast<int>(rank) * 128 + quarter * 32 + lane;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + (a ? L::ACC1 : 0);
+      bool released = false;
+#pragma unroll 1
+      for (int i = 0; i < CHUNKS; ++i) {
+        // accumulator 0 shares its HIGH columns, accumulator 1 its LOW columns: drain those first
+        const int cchunk = a ? i : CHUNKS - 1 - i;
+        if (i == RELEASE_CHUNKS && !released) {
+          ptx::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive_cluster(free_addr);
+          released = true;
+        }
+        const int q_base = qt * BN + cchunk * 32;
+        if (q_base >= p.Q) continue;                        // warp-uniform
+        uint32_t r[32];
+        ptx::tc_ld_32x32b_x32(taddr + cchunk * 32, r);
+        ptx::tc_wait_ld();
+        if (prow < p.P) {
+          const int64_t off = static_cast<int64_t>(prow) * p.ldd + q_base;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const int col = q_base + 8 * g;
+            if (col >= p.Q) break;
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[8 * g + j]) * p.alpha;
+            if (p.bias != nullptr) {
+              float b[8];
+              unpack_bf16x8(__ldg(reinterpret_cast<const uint4*>(p.bias + col)), b);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[j] += b[j];
+            }
+            if (p.c != nullptr) {
+              float cc[8];
+              unpack_bf16x8(*reinterpret_cast<const uint4*>(p.c + off + 8 * g), cc);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[j] += p.beta * cc[j];
+            }
+            uint4 o;
+            o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
+            o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
+            if (!(p.dbg & 1)) *reinterpret_cast<uint4*>(p.d + off + 8 * g) = o;
+          }
+        }
+      }
+      if (!released) {                                      // RELEASE_CHUNKS == CHUNKS or 0 handled here
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive_cluster(free_addr);
+      }
+    }
+  }
+
+  // Neither CTA may free TMEM or exit while the other can still touch it.
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::cluster_arrive();
+  ptx::cluster_wait();
+  if (warp == 1) ptx::tmem_dealloc_pair(tmem_base, 512);
+}

@@ -95,18 +95,21 @@ __global__ void dequantize_kernel(const uint2* __restrict__ packed, const uint8_
 // ---------------------------------------------------------------------------
 // Fused (residual-add +) RMSNorm (-> NVFP4).
 //
-// A CTA is 4 warps.  A row of nb = dim/16 blocks is covered by W in {1,2,4}
-// warps, so a CTA holds 4/W rows.  In pass i lane l of sub-warp w owns block
-// s = i*32*W + w*32 + l: two 16-byte loads per tensor, and consecutive lanes
-// read consecutive 32-byte pieces, so every pass of a warp is one contiguous
-// 1 KiB segment per tensor.  All loads of the row are issued before the first
-// use; the row then lives in registers (ITERS*16 fp32 per lane) through the
-// sum-of-squares reduction, so global memory is read once and written once.
+// One thread owns one 16-element block of a row for the whole kernel: two
+// 16-byte loads per input tensor, the values stay in registers through the
+// row reduction, then scale / quantise / store.  A row of nb = dim/16 blocks
+// is covered by TPR threads (a power of two >= nb, 32..1024); a CTA is
+// max(TPR, 256) threads and holds 256/TPR rows when TPR < 256.  Consecutive
+// threads read consecutive 32-byte pieces, so every warp access is one
+// contiguous 1 KiB segment, and global memory is read once and written once.
+// Small per-thread state (about 50 registers) keeps all 64 warps of an SM
+// resident, which is what hides the HBM latency.
 //
-// The summation order is fixed (per-lane running sum in pass and element
-// order with separately rounded multiply and add, xor butterfly 16..1, then
-// warp totals in warp order) so that a CPU restatement reproduces rstd bit
-// for bit.
+// The summation order is fixed so that a CPU restatement reproduces rstd bit
+// for bit: each thread sums v*v over its 16 elements in order (separately
+// rounded multiply and add), a warp combines its 32 threads with an xor
+// butterfly (offsets 16,8,4,2,1), and the row total adds the warp totals in
+// warp order.
 // ---------------------------------------------------------------------------
 struct NormParams {
   uint4* residual;        // bf16 [rows, dim] or null (in/out)
@@ -121,149 +124,128 @@ struct NormParams {
   unsigned flags;
 };
 
-template <int ITERS, int W, bool HAS_RES, bool QUANT, int ENC>
-__global__ void __launch_bounds__(128)
+__device__ __forceinline__ void pack16_bf16(const float (&v)[16], uint4& o0, uint4& o1) {
+  o0.x = pack_bf16x2(v[0], v[1]);   o0.y = pack_bf16x2(v[2], v[3]);
+  o0.z = pack_bf16x2(v[4], v[5]);   o0.w = pack_bf16x2(v[6], v[7]);
+  o1.x = pack_bf16x2(v[8], v[9]);   o1.y = pack_bf16x2(v[10], v[11]);
+  o1.z = pack_bf16x2(v[12], v[13]); o1.w = pack_bf16x2(v[14], v[15]);
+}
+
+template <int TPR, bool HAS_RES, bool QUANT, int ENC>
+__global__ void __launch_bounds__(TPR > 256 ? TPR : 256)
 norm_quant_kernel(const NormParams p) {
-  __shared__ float warp_sums[4];
+  constexpr int CTA = TPR > 256 ? TPR : 256;
+  constexpr int ROWS_PER_CTA = CTA / TPR;
+  constexpr int WPR = TPR / 32;                       // warps per row
+  __shared__ float warp_sums[CTA / 32];
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
-  constexpr int ROWS_PER_CTA = 4 / W;
-  const int row = blockIdx.x * ROWS_PER_CTA + warp / W;
-  const int sub = warp % W;
-  const bool row_ok = row < p.rows;
-  const int64_t row_base = static_cast<int64_t>(row) * p.nb;   // in blocks
+  const int row = blockIdx.x * ROWS_PER_CTA + threadIdx.x / TPR;
+  const int s = threadIdx.x % TPR;                    // block index inside the row
+  const bool ok = row < p.rows && s < p.nb;
+  const int64_t idx = static_cast<int64_t>(row) * p.nb + s;
 
-  float v[ITERS][16];
-  float part = 0.f;
-
-  // ---- issue every load of the row --------------------------------------
-  uint4 xr[ITERS][2];
-  uint4 rr[HAS_RES ? ITERS : 1][2];
-#pragma unroll
-  for (int i = 0; i < ITERS; ++i) {
-    const int s = i * 32 * W + sub * 32 + lane;
-    if (row_ok && s < p.nb) {
-      xr[i][0] = __ldcs(p.x + 2 * (row_base + s));
-      xr[i][1] = __ldcs(p.x + 2 * (row_base + s) + 1);
-      if (HAS_RES) {
-        rr[i][0] = __ldcs(p.residual + 2 * (row_base + s));
-        rr[i][1] = __ldcs(p.residual + 2 * (row_base + s) + 1);
-      }
-    } else {
-      xr[i][0] = xr[i][1] = make_uint4(0, 0, 0, 0);
-      if (HAS_RES) rr[i][0] = rr[i][1] = make_uint4(0, 0, 0, 0);
+  float v[16];
+  uint4 x0 = make_uint4(0, 0, 0, 0), x1 = x0, r0 = x0, r1 = x0;
+  if (ok) {
+    x0 = __ldcs(p.x + 2 * idx);
+    x1 = __ldcs(p.x + 2 * idx + 1);
+    if (HAS_RES) {
+      r0 = __ldcs(p.residual + 2 * idx);
+      r1 = __ldcs(p.residual + 2 * idx + 1);
     }
   }
-
-  // ---- residual add, in-place store, running sum of squares -------------
+  unpack_bf16x8(x0, v);
+  unpack_bf16x8(x1, v + 8);
+  float part = 0.f;
+  if (HAS_RES) {
+    float r[16];
+    unpack_bf16x8(r0, r);
+    unpack_bf16x8(r1, r + 8);
 #pragma unroll
-  for (int i = 0; i < ITERS; ++i) {
-    const int s = i * 32 * W + sub * 32 + lane;
-    unpack_bf16x8(xr[i][0], v[i]);
-    unpack_bf16x8(xr[i][1], v[i] + 8);
-    if (HAS_RES) {
-      float r[16];
-      unpack_bf16x8(rr[i][0], r);
-      unpack_bf16x8(rr[i][1], r + 8);
-#pragma unroll
-      for (int j = 0; j < 16; ++j) v[i][j] = __fadd_rn(r[j], v[i][j]);
-      uint4 o0, o1;
-      o0.x = pack_bf16x2(v[i][0], v[i][1]);   o0.y = pack_bf16x2(v[i][2], v[i][3]);
-      o0.z = pack_bf16x2(v[i][4], v[i][5]);   o0.w = pack_bf16x2(v[i][6], v[i][7]);
-      o1.x = pack_bf16x2(v[i][8], v[i][9]);   o1.y = pack_bf16x2(v[i][10], v[i][11]);
-      o1.z = pack_bf16x2(v[i][12], v[i][13]); o1.w = pack_bf16x2(v[i][14], v[i][15]);
-      if (row_ok && s < p.nb) {
-        __stcs(p.residual + 2 * (row_base + s), o0);
-        __stcs(p.residual + 2 * (row_base + s) + 1, o1);
-      }
-      // sum of squares always comes from the fp32 sums
-#pragma unroll
-      for (int j = 0; j < 16; ++j) part = __fadd_rn(part, __fmul_rn(v[i][j], v[i][j]));
-      if (p.flags & FRT_PRODUCER_NORM_FROM_BF16_RESIDUAL) {   // norm input = rounded residual
-        unpack_bf16x8(o0, v[i]);
-        unpack_bf16x8(o1, v[i] + 8);
-      }
-    } else {
-#pragma unroll
-      for (int j = 0; j < 16; ++j) part = __fadd_rn(part, __fmul_rn(v[i][j], v[i][j]));
+    for (int j = 0; j < 16; ++j) v[j] = __fadd_rn(r[j], v[j]);
+    uint4 o0, o1;
+    pack16_bf16(v, o0, o1);
+    if (ok) {
+      __stcs(p.residual + 2 * idx, o0);
+      __stcs(p.residual + 2 * idx + 1, o1);
     }
+    // the sum of squares always comes from the fp32 sums
+#pragma unroll
+    for (int j = 0; j < 16; ++j) part = __fadd_rn(part, __fmul_rn(v[j], v[j]));
+    if (p.flags & FRT_PRODUCER_NORM_FROM_BF16_RESIDUAL) {   // norm input = the rounded residual
+      unpack_bf16x8(o0, v);
+      unpack_bf16x8(o1, v + 8);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) part = __fadd_rn(part, __fmul_rn(v[j], v[j]));
   }
 
   // ---- row reduction -------------------------------------------------------
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) part = __fadd_rn(part, __shfl_xor_sync(0xffffffffu, part, o));
   float ssq = part;
-  if (W > 1) {
+  if (WPR > 1) {
     if (lane == 0) warp_sums[warp] = part;
     __syncthreads();
-    const int first = (warp / W) * W;
+    const int first = (warp / WPR) * WPR;
     ssq = warp_sums[first];
 #pragma unroll
-    for (int w = 1; w < W; ++w) ssq = __fadd_rn(ssq, warp_sums[first + w]);
+    for (int w = 1; w < WPR; ++w) ssq = __fadd_rn(ssq, warp_sums[first + w]);
   }
+  if (!ok) return;
   const float rstd = __frsqrt_rn(__fadd_rn(__fdiv_rn(ssq, p.dim_f), p.eps));
-  if (!row_ok) return;
 
-  // ---- scale, (round,) quantise, store ----------------------------------------
-  const bool one_plus = p.flags & FRT_PRODUCER_ONE_PLUS_W;
-  const bool round_bf16 = p.flags & FRT_PRODUCER_ROUND_BF16;
-  const bool use_gs = p.inv_global_scale != 1.0f;
-#pragma unroll
-  for (int i = 0; i < ITERS; ++i) {
-    const int s = i * 32 * W + sub * 32 + lane;
-    if (s >= p.nb) continue;
+  // ---- scale, (round,) quantise, store -------------------------------------
+  if (p.weight != nullptr) {
     float g[16];
-    if (p.weight != nullptr) {
-      const uint4 w0 = __ldg(p.weight + 2 * s);
-      const uint4 w1 = __ldg(p.weight + 2 * s + 1);
-      unpack_bf16x8(w0, g);
-      unpack_bf16x8(w1, g + 8);
-      if (one_plus) {
+    unpack_bf16x8(__ldg(p.weight + 2 * s), g);
+    unpack_bf16x8(__ldg(p.weight + 2 * s + 1), g + 8);
+    if (p.flags & FRT_PRODUCER_ONE_PLUS_W) {
 #pragma unroll
-        for (int j = 0; j < 16; ++j) g[j] = __fadd_rn(1.f, g[j]);
-      }
+      for (int j = 0; j < 16; ++j) g[j] = __fadd_rn(1.f, g[j]);
+    }
 #pragma unroll
-      for (int j = 0; j < 16; ++j) v[i][j] = __fmul_rn(__fmul_rn(v[i][j], rstd), g[j]);
-    } else {
+    for (int j = 0; j < 16; ++j) v[j] = __fmul_rn(__fmul_rn(v[j], rstd), g[j]);
+  } else {
 #pragma unroll
-      for (int j = 0; j < 16; ++j) v[i][j] = __fmul_rn(v[i][j], rstd);
-    }
-    if (use_gs) {
+    for (int j = 0; j < 16; ++j) v[j] = __fmul_rn(v[j], rstd);
+  }
+  if (p.inv_global_scale != 1.0f) {
 #pragma unroll
-      for (int j = 0; j < 16; ++j) v[i][j] = __fmul_rn(v[i][j], p.inv_global_scale);
+    for (int j = 0; j < 16; ++j) v[j] = __fmul_rn(v[j], p.inv_global_scale);
+  }
+  const bool round_bf16 = p.flags & FRT_PRODUCER_ROUND_BF16;
+  if (p.normed != nullptr || round_bf16) {
+    uint4 o0, o1;
+    pack16_bf16(v, o0, o1);
+    if (p.normed != nullptr) {
+      p.normed[2 * idx] = o0;
+      p.normed[2 * idx + 1] = o1;
     }
-    if (p.normed != nullptr || round_bf16) {
-      uint4 o0, o1;
-      o0.x = pack_bf16x2(v[i][0], v[i][1]);   o0.y = pack_bf16x2(v[i][2], v[i][3]);
-      o0.z = pack_bf16x2(v[i][4], v[i][5]);   o0.w = pack_bf16x2(v[i][6], v[i][7]);
-      o1.x = pack_bf16x2(v[i][8], v[i][9]);   o1.y = pack_bf16x2(v[i][10], v[i][11]);
-      o1.z = pack_bf16x2(v[i][12], v[i][13]); o1.w = pack_bf16x2(v[i][14], v[i][15]);
-      if (p.normed != nullptr) {
-        p.normed[2 * (row_base + s)] = o0;
-        p.normed[2 * (row_base + s) + 1] = o1;
-      }
-      if (round_bf16) {
-        unpack_bf16x8(o0, v[i]);
-        unpack_bf16x8(o1, v[i] + 8);
-      }
+    if (round_bf16) {
+      unpack_bf16x8(o0, v);
+      unpack_bf16x8(o1, v + 8);
     }
-    if (QUANT) {
-      uint8_t sfb;
-      uint2 out;
-      if (p.flags & FRT_PRODUCER_RNE_E2M1) out = quantize_block16<kEncRne>(v[i], sfb);
-      else out = quantize_block16<ENC>(v[i], sfb);
-      p.packed[row_base + s] = out;
-      p.sf[sf_offset(row, s, p.sf_cols)] = sfb;
-    }
+  }
+  if (QUANT) {
+    uint8_t sfb;
+    uint2 out;
+    if (p.flags & FRT_PRODUCER_RNE_E2M1) out = quantize_block16<kEncRne>(v, sfb);
+    else out = quantize_block16<ENC>(v, sfb);
+    p.packed[idx] = out;
+    p.sf[sf_offset(row, s, p.sf_cols)] = sfb;
   }
 }
 
-template <int ITERS, int W>
+template <int TPR>
 int launch_norm(const NormParams& p, bool has_res, bool quant, cudaStream_t st) {
-  const int rows_per_cta = 4 / W;
-  const dim3 grid((p.rows + rows_per_cta - 1) / rows_per_cta), block(128);
+  constexpr int CTA = TPR > 256 ? TPR : 256;
+  constexpr int rows_per_cta = CTA / TPR;
+  const dim3 grid((p.rows + rows_per_cta - 1) / rows_per_cta), block(CTA);
   const bool chain = g_opt_quant_encoder == 1;
-#define FRT_LAUNCH(HR, Q, E) norm_quant_kernel<ITERS, W, HR, Q, E><<<grid, block, 0, st>>>(p)
+#define FRT_LAUNCH(HR, Q, E) norm_quant_kernel<TPR, HR, Q, E><<<grid, block, 0, st>>>(p)
   if (!quant) {
     if (has_res) FRT_LAUNCH(true, false, kEncHw); else FRT_LAUNCH(false, false, kEncHw);
   } else if (chain) {
@@ -277,12 +259,12 @@ int launch_norm(const NormParams& p, bool has_res, bool quant, cudaStream_t st) 
 
 int dispatch_norm(NormParams& p, bool has_res, bool quant, cudaStream_t st) {
   const int nb = p.nb;
-  if (nb <= 32) return launch_norm<1, 1>(p, has_res, quant, st);
-  if (nb <= 64) return launch_norm<2, 1>(p, has_res, quant, st);
-  if (nb <= 128) return launch_norm<4, 1>(p, has_res, quant, st);
-  if (nb <= 256) return launch_norm<8, 1>(p, has_res, quant, st);
-  if (nb <= 512) return launch_norm<8, 2>(p, has_res, quant, st);
-  return launch_norm<8, 4>(p, has_res, quant, st);
+  if (nb <= 32) return launch_norm<32>(p, has_res, quant, st);
+  if (nb <= 64) return launch_norm<64>(p, has_res, quant, st);
+  if (nb <= 128) return launch_norm<128>(p, has_res, quant, st);
+  if (nb <= 256) return launch_norm<256>(p, has_res, quant, st);
+  if (nb <= 512) return launch_norm<512>(p, has_res, quant, st);
+  return launch_norm<1024>(p, has_res, quant, st);
 }
 
 int check_norm_args(const void* x, int rows, int dim) {
