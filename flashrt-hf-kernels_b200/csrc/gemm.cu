@@ -57,6 +57,7 @@ struct GemmParams {
   float alpha, beta;
   int group_m;              // raster: tiles walk GROUP_M p-tiles before the next q-tile
   int dbg;                  // experiment switches (0 in production)
+  const float* alpha_stack; // grouped: per-expert alpha
 };
 
 template <int BN, int STAGES>
@@ -407,8 +408,8 @@ int launch_gemm(const CUtensorMap& mp, const CUtensorMap& mq, GemmParams& p, int
 
 template <int BN, int STAGES>
 int launch_gemm_pair(const void* p_packed, const void* q_packed, GemmParams& p, int sms, cudaStream_t st) {
-  using L = PairLayout<BN, STAGES>;
-  auto kern = nvfp4_gemm_pair_kernel<BN, STAGES>;
+  using L = PairLayout<BN, STAGES, false>;
+  auto kern = nvfp4_gemm_pair_kernel<BN, STAGES, false>;
   static bool attr_set[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -426,11 +427,125 @@ int launch_gemm_pair(const void* p_packed, const void* q_packed, GemmParams& p, 
   p.p_tiles = (p.P + 255) / 256;
   const int tiles = p.p_tiles * p.q_tiles;
   const int pairs = tiles < sms / 2 ? tiles : sms / 2;
-  kern<<<2 * pairs, 192, L::TOTAL, st>>>(maps, p);
+  kern<<<2 * pairs, 192, L::TOTAL, st>>>(maps, p, nullptr);
   return launch_result();
 }
 
+// ---------------------------------------------------------------------------
+// grouped (MoE): plan kernel + launch
+// ---------------------------------------------------------------------------
+// Windows start on a multiple of 64 rows: the scales of a window are addressed in
+// TMEM as a column offset (one column per 32 rows) from a 128-row group, and the
+// MMA takes that scale address only at even columns.
+__device__ __forceinline__ void emit_windows(GroupWork* work, int max_items, int lo, int hi, int expert) {
+  for (int start = lo & ~63; start < hi; start += 256) {
+    const int len = min(256, (hi - start + 31) & ~31);
+    const int slot = atomicAdd(&work->count, 1);
+    if (slot < max_items) {
+      GroupItem it{};
+      it.q_row0 = start; it.n_tokens = len;
+      it.lo = max(lo, start); it.hi = min(hi, start + len);
+      it.expert = expert;
+      work->items[slot] = it;
+    }
+  }
+}
+
+// Turns either description of "which expert owns which rows" into windows of
+// at most 256 rows that start on a multiple of 64.
+__global__ void group_plan_kernel(const int* __restrict__ offsets, const int* __restrict__ tile_expert, int tile_rows,
+                                  int rows, int num_experts, int num_tiles, GroupWork* work, int max_items) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (offsets != nullptr) {
+    if (i >= num_experts) return;
+    const int lo = max(0, min(offsets[i], rows)), hi = max(0, min(offsets[i + 1], rows));
+    if (hi > lo) emit_windows(work, max_items, lo, hi, i);
+  } else {
+    if (i >= num_tiles) return;
+    const int e = tile_expert[i];
+    if (e < 0 || e >= num_experts || (i > 0 && tile_expert[i - 1] == e)) return;   // not the first tile of a run
+    int j = i + 1;
+    while (j < num_tiles && tile_expert[j] == e) ++j;
+    emit_windows(work, max_items, i * tile_rows, j * tile_rows, e);
+  }
+}
+
+int make_weight_stack_map(CUtensorMap* map, const void* base, int n, int K, int experts, int64_t stride) {
+  auto enc = get_encode();
+  if (!enc) return FRT_E_DRIVER;
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(K / 2), static_cast<cuuint64_t>(n), static_cast<cuuint64_t>(experts)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(K / 2), static_cast<cuuint64_t>(stride)};
+  const cuuint32_t box[3] = {128, 128, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? FRT_OK : FRT_E_DRIVER;
+}
+
+int make_sf_stack_map(CUtensorMap* map, const void* base, int n, int sf_cols, int experts, int64_t stride) {
+  auto enc = get_encode();
+  if (!enc) return FRT_E_DRIVER;
+  const cuuint64_t dims[4] = {128, static_cast<cuuint64_t>(sf_cols), static_cast<cuuint64_t>((n + 127) / 128),
+                              static_cast<cuuint64_t>(experts)};
+  const cuuint64_t strides[3] = {512, static_cast<cuuint64_t>(sf_cols) * 512, static_cast<cuuint64_t>(stride)};
+  const cuuint32_t box[4] = {128, KT_PER_STAGE, 1, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, const_cast<void*>(base), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? FRT_OK : FRT_E_DRIVER;
+}
+
 }  // namespace
+
+int64_t grouped_max_items(int rows, int experts) { return static_cast<int64_t>(rows) / 64 + 2ll * experts + 8; }
+
+int run_grouped(const void* a, const void* sfa, const void* b_stack, const void* sfb_stack, const void* alpha,
+                const void* offsets, const void* tile_expert, int tile_rows, void* out, int rows, int N, int K,
+                int experts, int64_t b_stride, int64_t sfb_stride, void* workspace, cudaStream_t st) {
+  const DeviceInfo di = device_info();
+  if (!di.ok || di.cc_major != 10) return FRT_E_DEVICE;
+  constexpr int BN = 256, STAGES = 5;
+  using L = PairLayout<BN, STAGES, true>;
+  auto kern = nvfp4_gemm_pair_kernel<BN, STAGES, true>;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_set[dev & 63]) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL) != cudaSuccess)
+      return FRT_E_LAUNCH;
+    attr_set[dev & 63] = true;
+  }
+  GemmParams p{};
+  p.P = N; p.Q = rows; p.K = K;
+  p.k_tiles = (K + 63) / 64;
+  p.sf_cols = p.k_tiles;
+  p.d = static_cast<__nv_bfloat16*>(out);
+  p.ldd = N;
+  p.alpha = 1.f;
+  p.alpha_stack = static_cast<const float*>(alpha);
+  p.p_tiles = (N + 255) / 256;
+  p.q_tiles = 0;
+  p.group_m = 1;
+  PairMaps maps;
+  if (int rc = make_weight_stack_map(&maps.p, b_stack, N, K, experts, b_stride)) return rc;
+  if (int rc = make_operand_map(&maps.q, a, rows, K, BN / 2)) return rc;
+  if (int rc = make_sf_stack_map(&maps.sfp, sfb_stack, N, p.sf_cols, experts, sfb_stride)) return rc;
+  if (int rc = make_sf_map(&maps.sfq, sfa, rows, p.sf_cols, L::SFQ_BLOCKS)) return rc;
+  auto* work = static_cast<GroupWork*>(workspace);
+  const int max_items = static_cast<int>(grouped_max_items(rows, experts));
+  if (cudaMemsetAsync(work, 0, 16, st) != cudaSuccess) return FRT_E_LAUNCH;
+  const int num_tiles = tile_rows > 0 ? rows / tile_rows : 0;
+  const int plan_threads = offsets ? experts : num_tiles;
+  group_plan_kernel<<<(plan_threads + 255) / 256, 256, 0, st>>>(
+      static_cast<const int*>(offsets), static_cast<const int*>(tile_expert), tile_rows, rows, experts, num_tiles, work,
+      max_items);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  kern<<<2 * (di.sms / 2), 192, L::TOTAL, st>>>(maps, p, work);
+  return launch_result();
+}
+
 
 unsigned* device_status_word() {
   unsigned* ptr = nullptr;
@@ -465,7 +580,14 @@ int run_gemm(const void* p_packed, const void* sfp, int P, const void* q_packed,
   int cfg = config;
   if (cfg == 0) {
     if (swap) cfg = Q <= 16 ? 11 : Q <= 32 ? 12 : Q <= 64 ? 13 : 14;
-    else cfg = P > 128 ? 4 : (K >= 8192 ? 2 : 3);
+    else if (P > 128) {
+      // CTA pairs: 256x256 tiles unless 256x192 tiles fill the last wave better
+      const int pairs = di.sms / 2, pt = (P + 255) / 256;
+      const int w256 = (pt * ((Q + 255) / 256) + pairs - 1) / pairs, w192 = (pt * ((Q + 191) / 192) + pairs - 1) / pairs;
+      cfg = (w192 * 192 * 100 < w256 * 256 * 97) ? 5 : 4;
+    } else {
+      cfg = K >= 8192 ? 2 : 3;      // long K amortises the single-accumulator 128x256 tile
+    }
   }
   if (cfg >= 4 && cfg <= 6) {
     if (swap) return FRT_E_UNSUPPORTED;

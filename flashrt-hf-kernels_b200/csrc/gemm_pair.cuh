@@ -28,11 +28,27 @@ struct PairMaps {
   CUtensorMap p, q, sfp, sfq;
 };
 
-template <int BN, int STAGES>
+// One unit of grouped work: a window of expert-sorted token rows that one
+// expert's weights are applied to.  Built on the device by group_plan_kernel.
+struct GroupItem {
+  int q_row0;      // first token row of the window (multiple of 64)
+  int n_tokens;    // window length, multiple of 32, <= 256 (the UMMA N of the tile)
+  int lo, hi;      // token rows [lo, hi) of the window that belong to `expert`
+  int expert;
+  int pad[3];
+};
+struct GroupWork {
+  int count;       // number of items
+  int pad[3];
+  GroupItem items[1];
+};
+
+template <int BN, int STAGES, bool GROUPED = false>
 struct PairLayout {
   static constexpr int A_BYTES = 128 * 128;              // this CTA's 128 rows of P
   static constexpr int B_BYTES = (BN / 2) * 128;         // this CTA's half of the Q tile
-  static constexpr int SFQ_BLOCKS = BN <= 128 ? 1 : 2;
+  // 128-row scale groups a Q tile can touch (a grouped window starts at any multiple of 64)
+  static constexpr int SFQ_BLOCKS = GROUPED ? 3 : (BN <= 128 ? 1 : 2);
   static constexpr int SFP_BYTES = KT_PER_STAGE * SF_TILE;
   static constexpr int SFQ_BYTES = SFQ_BLOCKS * KT_PER_STAGE * SF_TILE;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFP_BYTES + SFQ_BYTES;
@@ -46,10 +62,14 @@ struct PairLayout {
   static_assert(BN % 32 == 0 && OVERLAP >= 0, "tile shape");
 };
 
-template <int BN, int STAGES>
+// GROUPED: P = one expert's weights (3-D / 4-D tensor maps with the expert as the
+// outer coordinate), Q = a window of token rows; the output tile is written
+// transposed (out[token, weight_row]) and masked to the rows of that expert.
+template <int BN, int STAGES, bool GROUPED>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
-nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p) {
-  using L = PairLayout<BN, STAGES>;
+nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p,
+                       const GroupWork* __restrict__ work) {
+  using L = PairLayout<BN, STAGES, GROUPED>;
   constexpr int SFQ_COLS_PER_KT = L::SFQ_BLOCKS * 4;
   constexpr uint32_t IDESC = ptx::idesc_nvf4(256, BN);
   constexpr int CHUNKS = BN / 32;
@@ -71,7 +91,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
   const bool leader = rank == 0;
   const int pair_id = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
-  const int total_tiles = p.p_tiles * p.q_tiles;
+  const int total_tiles = GROUPED ? work->count * p.p_tiles : p.p_tiles * p.q_tiles;
   const int k_stages = (p.k_tiles + KT_PER_STAGE - 1) / KT_PER_STAGE;
 
   if (threadIdx.x == 0) {
@@ -106,12 +126,20 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
       int s = 0, it = 0;
       uint32_t ph = 0;
       for (int t = pair_id; t < total_tiles && !*abort_flag; t += num_pairs) {
-        int pt, qt;
-        tile_coords(t, p, pt, qt);
+        int pt, qt, q_row, q_blk, expert = 0;
+        if (GROUPED) {
+          const GroupItem item = work->items[t / p.p_tiles];
+          pt = t % p.p_tiles;
+          q_row = item.q_row0 + static_cast<int>(rank) * (item.n_tokens >> 1);
+          q_blk = item.q_row0 >> 7;
+          expert = item.expert;
+        } else {
+          tile_coords(t, p, pt, qt);
+          q_row = qt * BN + static_cast<int>(rank) * (BN / 2);
+          q_blk = (qt * BN) >> 7;
+        }
         const int p_row = pt * 256 + static_cast<int>(rank) * 128;
-        const int q_row = qt * BN + static_cast<int>(rank) * (BN / 2);
         const int p_blk = p_row >> 7;
-        const int q_blk = (qt * BN) >> 7;
         for (int ks = 0; ks < k_stages; ++ks, ++it) {
           if (!ptx::mbar_wait_bounded(&empty[s], ph ^ 1, WAIT_LIMIT)) {
             atomicOr(&g_status_word, 1u); *abort_flag = 1; break;
@@ -119,9 +147,14 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
           const uint32_t st = smem0 + s * L::STAGE_BYTES;
           const uint32_t bar = full0 + s * 8;
           if (leader) ptx::mbar_expect_tx(&full[s], 2 * L::STAGE_BYTES);
-          ptx::tma_load_2d_pair(st, &maps.p, bar, ks * 128, p_row);
+          if (GROUPED) {
+            ptx::tma_load_3d_pair(st, &maps.p, bar, ks * 128, p_row, expert);
+            ptx::tma_load_4d_pair(st + L::A_BYTES + L::B_BYTES, &maps.sfp, bar, 0, ks * KT_PER_STAGE, p_blk, expert);
+          } else {
+            ptx::tma_load_2d_pair(st, &maps.p, bar, ks * 128, p_row);
+            ptx::tma_load_3d_pair(st + L::A_BYTES + L::B_BYTES, &maps.sfp, bar, 0, ks * KT_PER_STAGE, p_blk);
+          }
           ptx::tma_load_2d_pair(st + L::A_BYTES, &maps.q, bar, ks * 128, q_row);
-          ptx::tma_load_3d_pair(st + L::A_BYTES + L::B_BYTES, &maps.sfp, bar, 0, ks * KT_PER_STAGE, p_blk);
           ptx::tma_load_3d_pair(st + L::A_BYTES + L::B_BYTES + L::SFP_BYTES, &maps.sfq, bar, 0, ks * KT_PER_STAGE,
                                 q_blk);
           if (++s == STAGES) { s = 0; ph ^= 1u; }
@@ -157,9 +190,16 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
         }
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base + (a ? L::ACC1 : 0);
-        int pt, qt;
-        tile_coords(t, p, pt, qt);
-        const uint32_t qoff = (static_cast<uint32_t>(qt * BN) & 127u) >> 5;
+        uint32_t qoff, idesc = IDESC;
+        if (GROUPED) {
+          const GroupItem item = work->items[t / p.p_tiles];
+          qoff = (static_cast<uint32_t>(item.q_row0) & 127u) >> 5;
+          idesc = ptx::idesc_nvf4(256, item.n_tokens);
+        } else {
+          int pt, qt;
+          tile_coords(t, p, pt, qt);
+          qoff = (static_cast<uint32_t>(qt * BN) & 127u) >> 5;
+        }
         for (int ks = 0; ks < k_stages; ++ks) {
           if (!ptx::mbar_wait_bounded(&full[s], ph, WAIT_LIMIT)) {
             atomicOr(&g_status_word, 8u); *abort_flag = 1; aborted = true; break;
@@ -180,7 +220,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
               for (int b = 0; b < L::SFQ_BLOCKS; ++b)
                 ptx::tc_cp_32x128b_warpx4_pair(sfq_t + 4 * b, sfq_lo + (b * KT_PER_STAGE + kt) * (SF_TILE >> 4),
                                                sf_hi);
-              ptx::tc_mma_nvf4_pair(d_tmem, a_lo + 2 * kt, b_lo + 2 * kt, op_hi, IDESC, sfp_t, sfq_t + qoff,
+              ptx::tc_mma_nvf4_pair(d_tmem, a_lo + 2 * kt, b_lo + 2 * kt, op_hi, idesc, sfp_t, sfq_t + qoff,
                                     (ks | kt) != 0);
             }
           }
@@ -197,8 +237,16 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
     const uint32_t free_addr = ptx::mapa(ptx::smem_u32(acc_free), 0);   // the leader's barrier
     int tl = 0;
     for (int t = pair_id; t < total_tiles && !*abort_flag; t += num_pairs, ++tl) {
-      int pt, qt;
-      tile_coords(t, p, pt, qt);
+      int pt, qt = 0;
+      GroupItem item{};
+      float alpha = p.alpha;
+      if (GROUPED) {
+        item = work->items[t / p.p_tiles];
+        pt = t % p.p_tiles;
+        alpha = p.alpha_stack[item.expert];
+      } else {
+        tile_coords(t, p, pt, qt);
+      }
       const int a = tl & 1;
       if (!ptx::mbar_wait_bounded(&acc_full[a], (tl >> 1) & 1, WAIT_LIMIT)) {
         if (lane == 0) { atomicOr(&g_status_word, 16u); *abort_flag = 1; }
@@ -217,6 +265,23 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
           __syncwarp();
           if (lane == 0) ptx::mbar_arrive_cluster(free_addr);
           released = true;
+        }
+        if (GROUPED) {
+          // thread = one weight row (output column prow); tile columns = token rows
+          const int tok0 = item.q_row0 + cchunk * 32;
+          if (cchunk * 32 >= item.n_tokens || tok0 >= item.hi || tok0 + 32 <= item.lo) continue;   // warp-uniform
+          uint32_t r[32];
+          ptx::tc_ld_32x32b_x32(taddr + cchunk * 32, r);
+          ptx::tc_wait_ld();
+          if (prow < p.P) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int tok = tok0 + j;
+              if (tok >= item.lo && tok < item.hi)
+                p.d[static_cast<int64_t>(tok) * p.ldd + prow] = __float2bfloat16_rn(__uint_as_float(r[j]) * alpha);
+            }
+          }
+          continue;
         }
         const int q_base = qt * BN + cchunk * 32;
         if (q_base >= p.Q) continue;                        // warp-uniform

@@ -195,6 +195,14 @@ __device__ __forceinline__ void tma_load_3d_pair(uint32_t smem_dst, const CUtens
       : "memory");
 }
 
+__device__ __forceinline__ void tma_load_4d_pair(uint32_t smem_dst, const CUtensorMap* map, uint32_t bar_addr,
+                                                 int32_t x, int32_t y, int32_t z, int32_t w) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_addr), "r"(x), "r"(y), "r"(z), "r"(w)
+      : "memory");
+}
+
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
                ::"r"(smem_u32(smem_result)), "r"(ncols) : "memory");

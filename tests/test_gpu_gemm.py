@@ -69,7 +69,7 @@ def test_gemm_vs_oracle(m, n, k):
     assert_close(out, oracle_out(ap, sfa, bp, sfb, m, n, k))
 
 
-@pytest.mark.parametrize("cfg", [1, 2, 3])
+@pytest.mark.parametrize("cfg", [1, 2, 3, 4, 5, 6])
 @pytest.mark.parametrize("m,n,k", [(128, 256, 256), (256, 768, 1024), (300, 1000, 704), (512, 576, 2048)])
 def test_every_tile_configuration(m, n, k, cfg):
     ap, sfa, bp, sfb = make_quantized(m, n, k, 9000 + m + n + k)
