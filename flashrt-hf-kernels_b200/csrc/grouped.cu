@@ -11,6 +11,36 @@ int run_grouped(const void* a, const void* sfa, const void* b_stack, const void*
 
 using namespace frt;
 
+namespace {
+
+// Work-list storage for the entry point that allocates nothing.  It is part of
+// the library image: every GPU that loads the library carries these bytes until
+// the process exits.  Sized for FRT_GROUPED_STATIC_MAX_ROWS rows and
+// FRT_GROUPED_STATIC_MAX_EXPERTS experts (16 + 32 * (rows/64 + 2*experts + 8)).
+constexpr int64_t kStaticScratchBytes =
+    16 + 32 * (FRT_GROUPED_STATIC_MAX_ROWS / 64 + 2ll * FRT_GROUPED_STATIC_MAX_EXPERTS + 8);
+static __device__ __align__(256) unsigned char g_grouped_static_scratch[kStaticScratchBytes];
+
+// In host code the array's name is only a handle for the runtime, not a device
+// address; the address each device gave the array is looked up once per device.
+void* g_static_scratch_ptr[64] = {};
+std::atomic<bool> g_static_scratch_ready[64] = {};
+
+int static_scratch(void** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FRT_E_DEVICE;
+  if (!g_static_scratch_ready[dev].load(std::memory_order_acquire)) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_grouped_static_scratch) != cudaSuccess || ptr == nullptr) return FRT_E_LAUNCH;
+    g_static_scratch_ptr[dev] = ptr;            // same value from every thread that races here
+    g_static_scratch_ready[dev].store(true, std::memory_order_release);
+  }
+  *out = g_static_scratch_ptr[dev];
+  return FRT_OK;
+}
+
+}  // namespace
+
 extern "C" {
 
 int64_t frt_nvfp4_grouped_gemm_workspace_bytes(int rows, int num_experts) {
@@ -35,6 +65,19 @@ int frt_nvfp4_grouped_gemm_bf16(const void* a_packed, const void* sfa, const voi
   return run_grouped(a_packed, sfa, b_stack, sfb_stack, alpha, expert_offsets, tile_expert,
                      tile_expert ? tile_rows : 0, out, rows, N, K, num_experts, b_stride, sfb_stride, work,
                      as_stream(stream));
+}
+
+int frt_nvfp4_grouped_gemm_bf16_noalloc(const void* a_packed, const void* sfa, const void* b_stack,
+                                        const void* sfb_stack, const void* alpha, const void* expert_offsets,
+                                        const void* tile_expert, int tile_rows, void* out, int rows, int N, int K,
+                                        int num_experts, int64_t b_stride, int64_t sfb_stride, void* stream) {
+  if (rows > FRT_GROUPED_STATIC_MAX_ROWS || num_experts > FRT_GROUPED_STATIC_MAX_EXPERTS) return FRT_E_TOO_LARGE;
+  void* scratch = nullptr;
+  if (int rc = static_scratch(&scratch)) return rc;
+  // the plan kernel's item counter is the only part of the scratch that must start at
+  // zero; the shared launch path clears it on `stream` before planning
+  return frt_nvfp4_grouped_gemm_bf16(a_packed, sfa, b_stack, sfb_stack, alpha, expert_offsets, tile_expert,
+                                     tile_rows, out, rows, N, K, num_experts, b_stride, sfb_stride, scratch, stream);
 }
 
 }  // extern "C"

@@ -27,6 +27,7 @@ SIGNATURES = {
     "frt_nvfp4_gemm_bf16": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _F, _F, _P]),
     "frt_nvfp4_grouped_gemm_workspace_bytes": (_L, [_I, _I]),
     "frt_nvfp4_grouped_gemm_bf16": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _L, _L, _P, _P]),
+    "frt_nvfp4_grouped_gemm_bf16_noalloc": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _L, _L, _P]),
     "frt_device_status": (_I, [_P, C.POINTER(_U)]),
     "frt_launch_count": (_L, []),
     "frt_set_option": (_I, [_I, _I]),

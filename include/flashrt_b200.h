@@ -144,6 +144,30 @@ int frt_nvfp4_grouped_gemm_bf16(const void* a_packed, const void* sfa,
                                 int64_t b_stride, int64_t sfb_stride,
                                 void* work, void* stream);
 
+/* Same computation for callers that cannot allocate device memory and have no
+ * buffer to lend: a plug-in called from a host runtime that owns the device
+ * allocator and forbids cudaMalloc on its worker threads, a serving process
+ * that has already handed all free device memory to another pool (so an
+ * allocation would fail), or an embedding with a fixed memory map.
+ * The work list lives in a fixed array inside the library instead of `work`;
+ * inputs and outputs are still the caller's.  No counterpart in the reference.
+ *  - Limits: rows <= FRT_GROUPED_STATIC_MAX_ROWS and
+ *    num_experts <= FRT_GROUPED_STATIC_MAX_EXPERTS, else FRT_E_TOO_LARGE.  The
+ *    array (about 192 KiB) is resident on every GPU that loads the library.
+ *  - The first call on a device looks up the array's device address (no
+ *    allocation); make that first call before starting a stream capture.
+ *  - Every call uses the same array: two calls whose kernels can overlap on the
+ *    GPU (different streams, no dependency) race on it.  Calls on one stream,
+ *    or otherwise ordered, are safe; the array keeps the previous call's work
+ *    list and the part that must start at zero is cleared on `stream` by the call. */
+#define FRT_GROUPED_STATIC_MAX_ROWS     131072
+#define FRT_GROUPED_STATIC_MAX_EXPERTS  2048
+int frt_nvfp4_grouped_gemm_bf16_noalloc(const void* a_packed, const void* sfa,
+                                        const void* b_stack, const void* sfb_stack, const void* alpha,
+                                        const void* expert_offsets, const void* tile_expert, int tile_rows,
+                                        void* out, int rows, int N, int K, int num_experts,
+                                        int64_t b_stride, int64_t sfb_stride, void* stream);
+
 /* ---- status / tuning -----------------------------------------------------
  * Device-side waits are bounded; a wait that runs out records a code in a
  * per-device status word and the kernel returns.  This call copies the word to
