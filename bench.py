@@ -297,7 +297,7 @@ def run_ours(args, rank, world, local_rank):
     allgather = None
     if world > 1:
         big = max(layer.gemms, key=lambda g_: g_["out"].numel())
-        gathered = torch.empty((world,) + tuple(big["out"].shape), device=dev, dtype=torch.bfloat16)
+        gathered = torch.empty((world * big["out"].shape[0], big["out"].shape[1]), device=dev, dtype=torch.bfloat16)
         for _ in range(3):
             dist.all_gather_into_tensor(gathered, big["out"])
         barrier()
