@@ -337,7 +337,7 @@ def run_ours(args, rank, world, local_rank):
                            "fp4_gemm.nvfp4_gemm_bf16; pinned host in/out, copies overlapped on side streams"},
             "gpu_launches": int(launches),
             "clocks": clocks.summary(),
-            "roofline": {"bound": "tensor", "kernel": f"nvfp4_gemm_kernel ({dom_g['name']} "
+            "roofline": {"bound": "tensor", "kernel": f"nvfp4_gemm_pair_kernel ({dom_g['name']} "
                          f"{layer.M}x{dom_g['n_loc']}x{dom_g['k']})", "achieved": round(achieved, 1),
                          "peak": round(peaks["fp4_tflops"], 1), "unit": "TFLOP/s",
                          "frac": round(achieved / peaks["fp4_tflops"], 4),

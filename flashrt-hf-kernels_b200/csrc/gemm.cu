@@ -370,6 +370,20 @@ int make_sf_map(CUtensorMap* map, const void* base, int rows, int sf_cols, int b
   return r == CUDA_SUCCESS ? FRT_OK : FRT_E_DRIVER;
 }
 
+// bf16 output [rows, cols] with row pitch `ld` elements; box = 32 columns x 32 rows, 64-byte swizzle
+int make_output_map(CUtensorMap* map, void* base, int rows, int cols, int ld) {
+  auto enc = get_encode();
+  if (!enc) return FRT_E_DRIVER;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+  const cuuint32_t box[2] = {32, 32};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? FRT_OK : FRT_E_DRIVER;
+}
+
 struct DeviceInfo { int sms = 0; int cc_major = 0; bool ok = false; };
 DeviceInfo device_info() {
   // per-device cache (index by current device)
@@ -423,6 +437,7 @@ int launch_gemm_pair(const void* p_packed, const void* q_packed, GemmParams& p, 
   if (int rc = make_operand_map(&maps.q, q_packed, p.Q, p.K, BN / 2)) return rc;
   if (int rc = make_sf_map(&maps.sfp, p.sfp, p.P, p.sf_cols, 1)) return rc;
   if (int rc = make_sf_map(&maps.sfq, p.sfq, p.Q, p.sf_cols, L::SFQ_BLOCKS)) return rc;
+  if (int rc = make_output_map(&maps.d, p.d, p.P, p.Q, p.ldd)) return rc;
   p.q_tiles = (p.Q + BN - 1) / BN;
   p.p_tiles = (p.P + 255) / 256;
   const int tiles = p.p_tiles * p.q_tiles;
@@ -528,11 +543,13 @@ int run_grouped(const void* a, const void* sfa, const void* b_stack, const void*
   p.p_tiles = (N + 255) / 256;
   p.q_tiles = 0;
   p.group_m = 1;
-  PairMaps maps;
+  p.dbg = g_opt_gemm_debug;
+  PairMaps maps{};
   if (int rc = make_weight_stack_map(&maps.p, b_stack, N, K, experts, b_stride)) return rc;
   if (int rc = make_operand_map(&maps.q, a, rows, K, BN / 2)) return rc;
   if (int rc = make_sf_stack_map(&maps.sfp, sfb_stack, N, p.sf_cols, experts, sfb_stride)) return rc;
   if (int rc = make_sf_map(&maps.sfq, sfa, rows, p.sf_cols, L::SFQ_BLOCKS)) return rc;
+  if (int rc = make_output_map(&maps.d, out, rows, N, N)) return rc;
   auto* work = static_cast<GroupWork*>(workspace);
   const int max_items = static_cast<int>(grouped_max_items(rows, experts));
   if (cudaMemsetAsync(work, 0, 16, st) != cudaSuccess) return FRT_E_LAUNCH;
@@ -593,8 +610,8 @@ int run_gemm(const void* p_packed, const void* sfp, int P, const void* q_packed,
     if (swap) return FRT_E_UNSUPPORTED;
     switch (cfg) {
       case 4: return launch_gemm_pair<256, 5>(p_packed, q_packed, p, di.sms, st);
-      case 5: return launch_gemm_pair<192, 6>(p_packed, q_packed, p, di.sms, st);
-      default: return launch_gemm_pair<128, 7>(p_packed, q_packed, p, di.sms, st);
+      case 5: return launch_gemm_pair<192, 5>(p_packed, q_packed, p, di.sms, st);
+      default: return launch_gemm_pair<128, 6>(p_packed, q_packed, p, di.sms, st);
     }
   }
   int bn = 0;

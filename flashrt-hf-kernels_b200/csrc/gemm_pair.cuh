@@ -26,6 +26,7 @@
 
 struct PairMaps {
   CUtensorMap p, q, sfp, sfq;
+  CUtensorMap d;      // bf16 output [M, N], box 32 columns x 32 rows, 64-byte swizzle (dense form only)
 };
 
 // One unit of grouped work: a window of expert-sorted token rows that one
@@ -52,7 +53,11 @@ struct PairLayout {
   static constexpr int SFP_BYTES = KT_PER_STAGE * SF_TILE;
   static constexpr int SFQ_BYTES = SFQ_BLOCKS * KT_PER_STAGE * SF_TILE;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFP_BYTES + SFQ_BYTES;
-  static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 + 256;
+  // epilogue staging: 4 warps x 4 buffers of 32 rows x 64 bytes, written by TMA store
+  static constexpr int STAGE_BUFS = GROUPED ? 2 : 4;     // per epilogue warp
+  static constexpr int STAGING_BYTES = 4 * STAGE_BUFS * 2048;
+  static constexpr int ITEM_CACHE = GROUPED ? 96 : 0;    // this pair's first work items, copied to smem
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + STAGING_BYTES + ITEM_CACHE * 32 + 1024 + 256;
   static constexpr int SF_COLS = KT_PER_STAGE * (4 + SFQ_BLOCKS * 4);
   // accumulator placement: disjoint when they fit, else overlapping by OVERLAP columns
   static constexpr int ACC1 = (2 * BN + SF_COLS <= 512) ? BN : 512 - SF_COLS - BN;
@@ -77,7 +82,9 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * L::STAGE_BYTES);
+  uint8_t* staging = smem + STAGES * L::STAGE_BYTES;
+  GroupItem* item_cache = reinterpret_cast<GroupItem*>(staging + L::STAGING_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + L::STAGING_BYTES + L::ITEM_CACHE * 32);
   uint64_t* full = bars;                    // [STAGES] used in the leader: both CTAs' TMA bytes
   uint64_t* empty = bars + STAGES;          // [STAGES] in each CTA: multicast commit from the leader
   uint64_t* acc_full = bars + 2 * STAGES;   // [2] in each CTA: multicast commit from the leader
@@ -105,6 +112,14 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
     ptx::prefetch_tensormap(&maps.q);
     ptx::prefetch_tensormap(&maps.sfp);
     ptx::prefetch_tensormap(&maps.sfq);
+    ptx::prefetch_tensormap(&maps.d);
+  }
+  if (GROUPED) {
+    // tile i of this pair is global tile pair_id + i * num_pairs; its item is items[tile / p_tiles]
+    for (int i = threadIdx.x; i < L::ITEM_CACHE; i += blockDim.x) {
+      const int t = pair_id + i * num_pairs;
+      if (t < total_tiles) item_cache[i] = work->items[t / p.p_tiles];
+    }
   }
   if (warp == 1) {
     ptx::tmem_alloc_pair(tmem_slot, 512);
@@ -125,10 +140,11 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
       const uint32_t full0 = ptx::smem_u32(full) & 0xFEFFFFFFu;   // the leader CTA's barrier array
       int s = 0, it = 0;
       uint32_t ph = 0;
-      for (int t = pair_id; t < total_tiles && !*abort_flag; t += num_pairs) {
+      int ti = 0;
+      for (int t = pair_id; t < total_tiles && !*abort_flag; t += num_pairs, ++ti) {
         int pt, qt, q_row, q_blk, expert = 0;
         if (GROUPED) {
-          const GroupItem item = work->items[t / p.p_tiles];
+          const GroupItem item = ti < L::ITEM_CACHE ? item_cache[ti] : work->items[t / p.p_tiles];
           pt = t % p.p_tiles;
           q_row = item.q_row0 + static_cast<int>(rank) * (item.n_tokens >> 1);
           q_blk = item.q_row0 >> 7;
@@ -192,7 +208,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
         const uint32_t d_tmem = tmem_base + (a ? L::ACC1 : 0);
         uint32_t qoff, idesc = IDESC;
         if (GROUPED) {
-          const GroupItem item = work->items[t / p.p_tiles];
+          const GroupItem item = tl < L::ITEM_CACHE ? item_cache[tl] : work->items[t / p.p_tiles];
           qoff = (static_cast<uint32_t>(item.q_row0) & 127u) >> 5;
           idesc = ptx::idesc_nvf4(256, item.n_tokens);
         } else {
@@ -235,13 +251,15 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
     // ===================== epilogue (warps 2..5, both CTAs) =====================
     const int quarter = warp & 3;
     const uint32_t free_addr = ptx::mapa(ptx::smem_u32(acc_free), 0);   // the leader's barrier
+    const uint32_t stage_base = ptx::smem_u32(staging) + quarter * (L::STAGE_BUFS * 2048);
+    uint32_t nstore = 0;                  // TMA stores issued by this warp (buffer ring of 4)
     int tl = 0;
     for (int t = pair_id; t < total_tiles && !*abort_flag; t += num_pairs, ++tl) {
       int pt, qt = 0;
       GroupItem item{};
       float alpha = p.alpha;
       if (GROUPED) {
-        item = work->items[t / p.p_tiles];
+        item = tl < L::ITEM_CACHE ? item_cache[tl] : work->items[t / p.p_tiles];
         pt = t % p.p_tiles;
         alpha = p.alpha_stack[item.expert];
       } else {
@@ -273,11 +291,34 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
           uint32_t r[32];
           ptx::tc_ld_32x32b_x32(taddr + cchunk * 32, r);
           ptx::tc_wait_ld();
-          if (prow < p.P) {
+          const int n0 = pt * 256 + static_cast<int>(rank) * 128 + quarter * 32;   // first output column of this warp
+          if (tok0 >= item.lo && tok0 + 32 <= item.hi) {
+            // all 32 token rows belong to the expert: transpose through shared memory
+            // ([token][weight row], 64-byte TMA swizzle) and let TMA write (and clip) the box
+            const uint32_t buf = stage_base + (nstore & 1u) * 2048u;
+            if (nstore >= 2) {
+              if (lane == 0) ptx::bulk_wait_group_read<1>();
+              __syncwarp();
+            }
+            const uint32_t piece = static_cast<uint32_t>(lane) >> 3, within = (static_cast<uint32_t>(lane) & 7u) * 2u;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const __nv_bfloat16 h = __float2bfloat16_rn(__uint_as_float(r[j]) * alpha);
+              const uint32_t addr = buf + j * 64u + ((piece ^ ((static_cast<uint32_t>(j) >> 1) & 3u)) * 16u) + within;
+              asm volatile("st.shared.b16 [%0], %1;" ::"r"(addr), "h"(*reinterpret_cast<const uint16_t*>(&h)) : "memory");
+            }
+            ptx::fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+              if (!(p.dbg & 1)) ptx::tma_store_2d(&maps.d, buf, n0, tok0);
+              ptx::bulk_commit_group();
+            }
+            ++nstore;
+          } else if (prow < p.P) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               const int tok = tok0 + j;
-              if (tok >= item.lo && tok < item.hi)
+              if (tok >= item.lo && tok < item.hi && !(p.dbg & 1))
                 p.d[static_cast<int64_t>(tok) * p.ldd + prow] = __float2bfloat16_rn(__uint_as_float(r[j]) * alpha);
             }
           }
@@ -288,33 +329,47 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
         uint32_t r[32];
         ptx::tc_ld_32x32b_x32(taddr + cchunk * 32, r);
         ptx::tc_wait_ld();
-        if (prow < p.P) {
-          const int64_t off = static_cast<int64_t>(prow) * p.ldd + q_base;
+        // this lane's 32 outputs of row prow -> 64 bytes of bf16 in a staging buffer laid out
+        // as the 64-byte TMA swizzle expects (16-byte piece index ^ ((row >> 1) & 3))
+        const uint32_t buf = stage_base + (nstore & 3u) * 2048u;
+        if (nstore >= 4) {                                  // (dense) the store that last read this buffer is done
+          if (lane == 0) ptx::bulk_wait_group_read<3>();
+          __syncwarp();
+        }
+        const int64_t off = static_cast<int64_t>(prow) * p.ldd + q_base;
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            const int col = q_base + 8 * g;
-            if (col >= p.Q) break;
-            float v[8];
+        for (int g = 0; g < 4; ++g) {
+          const int col = q_base + 8 * g;
+          float v[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[8 * g + j]) * p.alpha;
+          for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[8 * g + j]) * p.alpha;
+          if (col < p.Q) {
             if (p.bias != nullptr) {
               float b[8];
               unpack_bf16x8(__ldg(reinterpret_cast<const uint4*>(p.bias + col)), b);
 #pragma unroll
               for (int j = 0; j < 8; ++j) v[j] += b[j];
             }
-            if (p.c != nullptr) {
+            if (p.c != nullptr && prow < p.P) {
               float cc[8];
               unpack_bf16x8(*reinterpret_cast<const uint4*>(p.c + off + 8 * g), cc);
 #pragma unroll
               for (int j = 0; j < 8; ++j) v[j] += p.beta * cc[j];
             }
-            uint4 o;
-            o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
-            o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
-            if (!(p.dbg & 1)) *reinterpret_cast<uint4*>(p.d + off + 8 * g) = o;
           }
+          const uint32_t piece = static_cast<uint32_t>(g) ^ ((static_cast<uint32_t>(lane) >> 1) & 3u);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
+                       ::"r"(buf + lane * 64u + piece * 16u), "r"(pack_bf16x2(v[0], v[1])),
+                         "r"(pack_bf16x2(v[2], v[3])), "r"(pack_bf16x2(v[4], v[5])), "r"(pack_bf16x2(v[6], v[7]))
+                       : "memory");
         }
+        ptx::fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) {
+          if (!(p.dbg & 1)) ptx::tma_store_2d(&maps.d, buf, q_base, pt * 256 + static_cast<int>(rank) * 128 + quarter * 32);
+          ptx::bulk_commit_group();
+        }
+        ++nstore;
       }
       if (!released) {                                      // RELEASE_CHUNKS == CHUNKS or 0 handled here
         ptx::tc_fence_before();
@@ -322,6 +377,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
         if (lane == 0) ptx::mbar_arrive_cluster(free_addr);
       }
     }
+    if (lane == 0) ptx::bulk_wait_group_all();   // staging must outlive the stores that read it
   }
 
   // Neither CTA may free TMEM or exit while the other can still touch it.
