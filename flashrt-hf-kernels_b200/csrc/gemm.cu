@@ -35,6 +35,7 @@ namespace frt {
 namespace {
 
 __device__ unsigned g_status_word = 0;
+long long* g_trace = nullptr;   // set by frt_debug_set_trace
 
 constexpr int BM = 128;            // UMMA M, rows of P per tile
 constexpr int BK = 256;            // elements of K per smem stage (128 bytes per row)
@@ -58,6 +59,7 @@ struct GemmParams {
   int group_m;              // raster: tiles walk GROUP_M p-tiles before the next q-tile
   int dbg;                  // experiment switches (0 in production)
   const float* alpha_stack; // grouped: per-expert alpha
+  long long* trace;         // clock64 timeline of pair 0, 8 slots per tile (null in production)
 };
 
 template <int BN, int STAGES>
@@ -262,6 +264,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
         uint32_t r[32];
         if (BN % 32 == 0 || cchunk * 32 + 32 <= BN) {
           ptx::tc_ld_32x32b_x32(taddr + cchunk * 32, r);
+          ptx::tc_wait_ld(r);
         } else {
           uint32_t r16[16];
           ptx::tc_ld_32x32b_x16(taddr + cchunk * 32, r16);
@@ -442,7 +445,7 @@ int launch_gemm_pair(const void* p_packed, const void* q_packed, GemmParams& p, 
   p.p_tiles = (p.P + 255) / 256;
   const int tiles = p.p_tiles * p.q_tiles;
   const int pairs = tiles < sms / 2 ? tiles : sms / 2;
-  kern<<<2 * pairs, 192, L::TOTAL, st>>>(maps, p, nullptr);
+  kern<<<2 * pairs, 320, L::TOTAL, st>>>(maps, p, nullptr);
   return launch_result();
 }
 
@@ -543,7 +546,8 @@ int run_grouped(const void* a, const void* sfa, const void* b_stack, const void*
   p.p_tiles = (N + 255) / 256;
   p.q_tiles = 0;
   p.group_m = 1;
-  p.dbg = g_opt_gemm_debug;
+  p.dbg = g_opt_gemm_debug & 0xff;
+  p.trace = g_trace;
   PairMaps maps{};
   if (int rc = make_weight_stack_map(&maps.p, b_stack, N, K, experts, b_stride)) return rc;
   if (int rc = make_operand_map(&maps.q, a, rows, K, BN / 2)) return rc;
@@ -559,7 +563,7 @@ int run_grouped(const void* a, const void* sfa, const void* b_stack, const void*
       static_cast<const int*>(offsets), static_cast<const int*>(tile_expert), tile_rows, rows, experts, num_tiles, work,
       max_items);
   g_launches.fetch_add(1, std::memory_order_relaxed);
-  kern<<<2 * (di.sms / 2), 192, L::TOTAL, st>>>(maps, p, work);
+  kern<<<2 * (di.sms / 2), 320, L::TOTAL, st>>>(maps, p, work);
   return launch_result();
 }
 
@@ -589,7 +593,8 @@ int run_gemm(const void* p_packed, const void* sfp, int P, const void* q_packed,
   p.ldd = ldd;
   p.alpha = alpha; p.beta = beta;
   p.group_m = 16;
-  p.dbg = g_opt_gemm_debug;
+  p.dbg = g_opt_gemm_debug & 0xff;
+  p.trace = g_trace;
 
   // configuration: one CTA per tile: 1 = 128x128 (2 acc), 2 = 128x256 (1 acc), 3 = 128x192 (2 acc);
   // CTA pair per tile: 4 = 256x256, 5 = 256x192, 6 = 256x128;
@@ -598,10 +603,9 @@ int run_gemm(const void* p_packed, const void* sfp, int P, const void* q_packed,
   if (cfg == 0) {
     if (swap) cfg = Q <= 16 ? 11 : Q <= 32 ? 12 : Q <= 64 ? 13 : 14;
     else if (P > 128) {
-      // CTA pairs: 256x256 tiles unless 256x192 tiles fill the last wave better
-      const int pairs = di.sms / 2, pt = (P + 255) / 256;
-      const int w256 = (pt * ((Q + 255) / 256) + pairs - 1) / pairs, w192 = (pt * ((Q + 191) / 192) + pairs - 1) / pairs;
-      cfg = (w192 * 192 * 100 < w256 * 256 * 97) ? 5 : 4;
+      // CTA pairs: 256x256 tiles (measured faster than 256x192 at every Qwen3-8B shape,
+      // wave quantisation included) unless the output is narrower than one such tile
+      cfg = Q <= 128 ? 6 : Q <= 192 ? 5 : 4;
     } else {
       cfg = K >= 8192 ? 2 : 3;      // long K amortises the single-accumulator 128x256 tile
     }
@@ -642,6 +646,8 @@ int run_gemm(const void* p_packed, const void* sfp, int P, const void* q_packed,
 using namespace frt;
 
 extern "C" {
+
+void frt_debug_set_trace(void* ptr) { g_trace = static_cast<long long*>(ptr); }
 
 int frt_nvfp4_gemm_bf16(const void* a, const void* sfa, const void* b, const void* sfb, const void* bias,
                         const void* c, void* d, int M, int N, int K, float alpha, float beta, void* stream) {

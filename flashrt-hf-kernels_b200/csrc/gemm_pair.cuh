@@ -16,7 +16,8 @@
 //   warp 1   leader CTA only: tcgen05.cp (scales smem -> TMEM, both CTAs) and
 //            tcgen05.mma cta_group::2; tcgen05.commit multicast to both CTAs'
 //            `empty` / `acc_full` barriers.
-//   warps 2..5 epilogue of this CTA's 128 rows.
+//   warps 2..9 epilogue of this CTA's 128 rows (TMEM -> registers -> swizzled staging in shared
+//            memory -> TMA store).
 //
 // TMEM (512 columns per CTA): two 128 x BN fp32 accumulators and one scale
 // buffer.  For BN = 256 the accumulators overlap ([0,256) and [208,464), scales
@@ -54,8 +55,8 @@ struct PairLayout {
   static constexpr int SFQ_BYTES = SFQ_BLOCKS * KT_PER_STAGE * SF_TILE;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFP_BYTES + SFQ_BYTES;
   // epilogue staging: 4 warps x 4 buffers of 32 rows x 64 bytes, written by TMA store
-  static constexpr int STAGE_BUFS = GROUPED ? 2 : 4;     // per epilogue warp
-  static constexpr int STAGING_BYTES = 4 * STAGE_BUFS * 2048;
+  static constexpr int SBUFS = GROUPED ? 1 : 2;            // staging buffers (32 rows x 64 B) per epilogue warp
+  static constexpr int STAGING_BYTES = 8 * SBUFS * 2048;
   static constexpr int ITEM_CACHE = GROUPED ? 96 : 0;    // this pair's first work items, copied to smem
   static constexpr int TOTAL = STAGES * STAGE_BYTES + STAGING_BYTES + ITEM_CACHE * 32 + 1024 + 256;
   static constexpr int SF_COLS = KT_PER_STAGE * (4 + SFQ_BLOCKS * 4);
@@ -71,7 +72,7 @@ struct PairLayout {
 // outer coordinate), Q = a window of token rows; the output tile is written
 // transposed (out[token, weight_row]) and masked to the rows of that expert.
 template <int BN, int STAGES, bool GROUPED>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(320, 1)
 nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p,
                        const GroupWork* __restrict__ work) {
   using L = PairLayout<BN, STAGES, GROUPED>;
@@ -88,7 +89,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
   uint64_t* full = bars;                    // [STAGES] used in the leader: both CTAs' TMA bytes
   uint64_t* empty = bars + STAGES;          // [STAGES] in each CTA: multicast commit from the leader
   uint64_t* acc_full = bars + 2 * STAGES;   // [2] in each CTA: multicast commit from the leader
-  uint64_t* acc_free = acc_full + 2;        // [1] used in the leader: 8 epilogue warps of the pair
+  uint64_t* acc_free = acc_full + 2;        // [1] used in the leader: 16 epilogue warps of the pair
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_free + 1);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -105,7 +106,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
     for (int i = 0; i < STAGES; ++i) { ptx::mbar_init(&full[i], 1); ptx::mbar_init(&empty[i], 1); }
     ptx::mbar_init(&acc_full[0], 1);
     ptx::mbar_init(&acc_full[1], 1);
-    ptx::mbar_init(acc_free, 8);
+    ptx::mbar_init(acc_free, 16);
     *abort_flag = 0;
     ptx::fence_barrier_init();
     ptx::prefetch_tensormap(&maps.p);
@@ -201,10 +202,13 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
         const int a = tl & 1;
         // tile tl may start once the epilogues of tile tl-1 have drained the columns the two
         // accumulators share (which also means tile tl-2, same accumulator, is fully drained)
+        const bool tr = p.trace != nullptr && pair_id == 0 && tl < 32;
+        if (tr) p.trace[tl * 8 + 0] = clock64();
         if (tl > 0 && !ptx::mbar_wait_bounded(acc_free, (tl - 1) & 1, WAIT_LIMIT)) {
           atomicOr(&g_status_word, 4u); *abort_flag = 1; break;
         }
         ptx::tc_fence_after();
+        if (tr) p.trace[tl * 8 + 1] = clock64();
         const uint32_t d_tmem = tmem_base + (a ? L::ACC1 : 0);
         uint32_t qoff, idesc = IDESC;
         if (GROUPED) {
@@ -231,11 +235,13 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
             if (kt < kts) {
               const uint32_t sfp_t = sf_tmem + kt * 4;
               const uint32_t sfq_t = sf_tmem + KT_PER_STAGE * 4 + kt * SFQ_COLS_PER_KT;
-              ptx::tc_cp_32x128b_warpx4_pair(sfp_t, sfp_lo + kt * (SF_TILE >> 4), sf_hi);
+              if (!(p.dbg & 2) || (tl == 0 && ks == 0)) {
+                ptx::tc_cp_32x128b_warpx4_pair(sfp_t, sfp_lo + kt * (SF_TILE >> 4), sf_hi);
 #pragma unroll
-              for (int b = 0; b < L::SFQ_BLOCKS; ++b)
-                ptx::tc_cp_32x128b_warpx4_pair(sfq_t + 4 * b, sfq_lo + (b * KT_PER_STAGE + kt) * (SF_TILE >> 4),
-                                               sf_hi);
+                for (int b = 0; b < L::SFQ_BLOCKS; ++b)
+                  ptx::tc_cp_32x128b_warpx4_pair(sfq_t + 4 * b, sfq_lo + (b * KT_PER_STAGE + kt) * (SF_TILE >> 4),
+                                                 sf_hi);
+              }
               ptx::tc_mma_nvf4_pair(d_tmem, a_lo + 2 * kt, b_lo + 2 * kt, op_hi, idesc, sfp_t, sfq_t + qoff,
                                     (ks | kt) != 0);
             }
@@ -245,14 +251,26 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
         }
         if (aborted) break;
         ptx::tc_commit_pair(&acc_full[a], 3);
+        if (tr) p.trace[tl * 8 + 2] = clock64();
       }
     }
   } else {
-    // ===================== epilogue (warps 2..5, both CTAs) =====================
-    const int quarter = warp & 3;
+    // ===================== epilogue (warps 2..9, both CTAs) =====================
+    // Eight warps: warp e covers TMEM lane quarter e & 3 and one half of the tile's
+    // 32-column chunks.  Chunks are drained in an order that reaches the columns the two
+    // accumulators share first (descending for accumulator 0, ascending for 1); the four
+    // warps that own that first half release the shared columns as soon as they are in
+    // registers, the other four when they start the tile.  TMEM loads run one chunk ahead of
+    // the arithmetic.
+    const int ew = warp - 2;
+    const int quarter = warp & 3;          // a warp reaches only the TMEM lanes of sub-partition warp_id % 4
+    const int half = ew >> 2;
+    constexpr int NCH = CHUNKS / 2;                                      // chunks per warp
+    static_assert(CHUNKS % 2 == 0 && RELEASE_CHUNKS <= NCH, "chunk split");
     const uint32_t free_addr = ptx::mapa(ptx::smem_u32(acc_free), 0);   // the leader's barrier
-    const uint32_t stage_base = ptx::smem_u32(staging) + quarter * (L::STAGE_BUFS * 2048);
-    uint32_t nstore = 0;                  // TMA stores issued by this warp (buffer ring of 4)
+    const uint32_t stage_base = ptx::smem_u32(staging) + ew * (L::SBUFS * 2048);
+    const int row_in_tile = static_cast<int>(rank) * 128 + quarter * 32;
+    uint32_t nstore = 0;                  // TMA stores issued by this warp (2 staging buffers)
     int tl = 0;
     for (int t = pair_id; t < total_tiles && !*abort_flag; t += num_pairs, ++tl) {
       int pt, qt = 0;
@@ -271,40 +289,66 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
         break;
       }
       ptx::tc_fence_after();
-      const int prow = pt * 256 + static_cast<int>(rank) * 128 + quarter * 32 + lane;
+      const bool first_half = half == (a ? 0 : 1);          // owns drain positions [0, NCH)
+      const bool tr = p.trace != nullptr && pair_id == 0 && tl < 32 && leader && quarter == 0 && lane == 0;
+      if (tr) p.trace[tl * 8 + (first_half ? 3 : 6)] = clock64();
+      const int prow = pt * 256 + row_in_tile + lane;       // dense: output row; grouped: output column
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + (a ? L::ACC1 : 0);
-      bool released = false;
-#pragma unroll 1
-      for (int i = 0; i < CHUNKS; ++i) {
-        // accumulator 0 shares its HIGH columns, accumulator 1 its LOW columns: drain those first
-        const int cchunk = a ? i : CHUNKS - 1 - i;
-        if (i == RELEASE_CHUNKS && !released) {
-          ptx::tc_fence_before();
-          __syncwarp();
-          if (lane == 0) ptx::mbar_arrive_cluster(free_addr);
-          released = true;
-        }
+      auto chunk_of = [&](int j) {                          // j-th chunk of this warp -> column chunk
+        const int pos = (first_half ? 0 : NCH) + j;
+        return a ? pos : CHUNKS - 1 - pos;
+      };
+      auto chunk_live = [&](int cchunk) {                   // warp-uniform: anything to write?
         if (GROUPED) {
-          // thread = one weight row (output column prow); tile columns = token rows
           const int tok0 = item.q_row0 + cchunk * 32;
-          if (cchunk * 32 >= item.n_tokens || tok0 >= item.hi || tok0 + 32 <= item.lo) continue;   // warp-uniform
-          uint32_t r[32];
-          ptx::tc_ld_32x32b_x32(taddr + cchunk * 32, r);
-          ptx::tc_wait_ld();
-          const int n0 = pt * 256 + static_cast<int>(rank) * 128 + quarter * 32;   // first output column of this warp
+          return cchunk * 32 < item.n_tokens && tok0 < item.hi && tok0 + 32 > item.lo;
+        }
+        return qt * BN + cchunk * 32 < p.Q;
+      };
+      auto release = [&]() {
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          if (leader) ptx::mbar_arrive(acc_free); else ptx::mbar_arrive_cluster(free_addr);
+        }
+      };
+      uint32_t r[2][32];
+      // every warp vouches that it is done with tile tl-1; the warps that own the shared columns
+      // of this tile only after those columns are in their registers
+      if (!first_half || RELEASE_CHUNKS == 0) release();
+      // both register buffers are filled before any arithmetic: the first two chunks of the
+      // first-half warps are exactly the columns the accumulators share
+      static_assert(RELEASE_CHUNKS <= 2 && NCH >= 2, "release after the two prologue loads");
+      if (chunk_live(chunk_of(0))) ptx::tc_ld_32x32b_x32(taddr + chunk_of(0) * 32, r[0]);
+      if (chunk_live(chunk_of(1))) ptx::tc_ld_32x32b_x32(taddr + chunk_of(1) * 32, r[1]);
+      ptx::tc_wait_ld(r[0]);
+      ptx::tc_wait_ld(r[1]);
+      if (first_half && RELEASE_CHUNKS > 0) release();
+      if (tr && first_half) p.trace[tl * 8 + 4] = clock64();
+#pragma unroll
+      for (int j = 0; j < NCH; ++j) {
+        const int cchunk = chunk_of(j);
+        const bool live = chunk_live(cchunk);
+        if (j >= 2) ptx::tc_wait_ld(r[j & 1]);
+        // after the arithmetic of this chunk its buffer is reloaded with chunk j+2 (see loop end)
+        if (live) {
+        const uint32_t (&v32)[32] = r[j & 1];
+        const uint32_t buf = stage_base + (nstore % L::SBUFS) * 2048u;
+        if (GROUPED) {
+          const int tok0 = item.q_row0 + cchunk * 32;
+          const int n0 = pt * 256 + row_in_tile;            // first output column of this warp
           if (tok0 >= item.lo && tok0 + 32 <= item.hi) {
             // all 32 token rows belong to the expert: transpose through shared memory
             // ([token][weight row], 64-byte TMA swizzle) and let TMA write (and clip) the box
-            const uint32_t buf = stage_base + (nstore & 1u) * 2048u;
-            if (nstore >= 2) {
-              if (lane == 0) ptx::bulk_wait_group_read<1>();
+            if (nstore >= L::SBUFS) {
+              if (lane == 0) ptx::bulk_wait_group_read<L::SBUFS - 1>();
               __syncwarp();
             }
             const uint32_t piece = static_cast<uint32_t>(lane) >> 3, within = (static_cast<uint32_t>(lane) & 7u) * 2u;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const __nv_bfloat16 h = __float2bfloat16_rn(__uint_as_float(r[j]) * alpha);
-              const uint32_t addr = buf + j * 64u + ((piece ^ ((static_cast<uint32_t>(j) >> 1) & 3u)) * 16u) + within;
+            for (int jj = 0; jj < 32; ++jj) {
+              const __nv_bfloat16 h = __float2bfloat16_rn(__uint_as_float(v32[jj]) * alpha);
+              const uint32_t addr = buf + jj * 64u + ((piece ^ ((static_cast<uint32_t>(jj) >> 1) & 3u)) * 16u) + within;
               asm volatile("st.shared.b16 [%0], %1;" ::"r"(addr), "h"(*reinterpret_cast<const uint16_t*>(&h)) : "memory");
             }
             ptx::fence_proxy_async();
@@ -316,66 +360,59 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
             ++nstore;
           } else if (prow < p.P) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const int tok = tok0 + j;
+            for (int jj = 0; jj < 32; ++jj) {
+              const int tok = tok0 + jj;
               if (tok >= item.lo && tok < item.hi && !(p.dbg & 1))
-                p.d[static_cast<int64_t>(tok) * p.ldd + prow] = __float2bfloat16_rn(__uint_as_float(r[j]) * alpha);
+                p.d[static_cast<int64_t>(tok) * p.ldd + prow] = __float2bfloat16_rn(__uint_as_float(v32[jj]) * alpha);
             }
           }
-          continue;
-        }
-        const int q_base = qt * BN + cchunk * 32;
-        if (q_base >= p.Q) continue;                        // warp-uniform
-        uint32_t r[32];
-        ptx::tc_ld_32x32b_x32(taddr + cchunk * 32, r);
-        ptx::tc_wait_ld();
-        // this lane's 32 outputs of row prow -> 64 bytes of bf16 in a staging buffer laid out
-        // as the 64-byte TMA swizzle expects (16-byte piece index ^ ((row >> 1) & 3))
-        const uint32_t buf = stage_base + (nstore & 3u) * 2048u;
-        if (nstore >= 4) {                                  // (dense) the store that last read this buffer is done
-          if (lane == 0) ptx::bulk_wait_group_read<3>();
+        } else {
+          // this lane's 32 outputs of row prow -> 64 bytes of bf16 in a staging buffer laid out
+          // as the 64-byte TMA swizzle expects (16-byte piece index ^ ((row >> 1) & 3))
+          const int q_base = qt * BN + cchunk * 32;
+          if (nstore >= L::SBUFS) {                         // the store that last read this buffer is done
+            if (lane == 0) ptx::bulk_wait_group_read<L::SBUFS - 1>();
+            __syncwarp();
+          }
+          const int64_t off = static_cast<int64_t>(prow) * p.ldd + q_base;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const int col = q_base + 8 * g;
+            float v[8];
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj) v[jj] = __uint_as_float(v32[8 * g + jj]) * alpha;
+            if (col < p.Q) {
+              if (p.bias != nullptr) {
+                float bb[8];
+                unpack_bf16x8(__ldg(reinterpret_cast<const uint4*>(p.bias + col)), bb);
+#pragma unroll
+                for (int jj = 0; jj < 8; ++jj) v[jj] += bb[jj];
+              }
+              if (p.c != nullptr && prow < p.P) {
+                float cc[8];
+                unpack_bf16x8(*reinterpret_cast<const uint4*>(p.c + off + 8 * g), cc);
+#pragma unroll
+                for (int jj = 0; jj < 8; ++jj) v[jj] += p.beta * cc[jj];
+              }
+            }
+            const uint32_t piece = static_cast<uint32_t>(g) ^ ((static_cast<uint32_t>(lane) >> 1) & 3u);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
+                         ::"r"(buf + lane * 64u + piece * 16u), "r"(pack_bf16x2(v[0], v[1])),
+                           "r"(pack_bf16x2(v[2], v[3])), "r"(pack_bf16x2(v[4], v[5])), "r"(pack_bf16x2(v[6], v[7]))
+                         : "memory");
+          }
+          ptx::fence_proxy_async();
           __syncwarp();
-        }
-        const int64_t off = static_cast<int64_t>(prow) * p.ldd + q_base;
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          const int col = q_base + 8 * g;
-          float v[8];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[8 * g + j]) * p.alpha;
-          if (col < p.Q) {
-            if (p.bias != nullptr) {
-              float b[8];
-              unpack_bf16x8(__ldg(reinterpret_cast<const uint4*>(p.bias + col)), b);
-#pragma unroll
-              for (int j = 0; j < 8; ++j) v[j] += b[j];
-            }
-            if (p.c != nullptr && prow < p.P) {
-              float cc[8];
-              unpack_bf16x8(*reinterpret_cast<const uint4*>(p.c + off + 8 * g), cc);
-#pragma unroll
-              for (int j = 0; j < 8; ++j) v[j] += p.beta * cc[j];
-            }
+          if (lane == 0) {
+            if (!(p.dbg & 1)) ptx::tma_store_2d(&maps.d, buf, q_base, pt * 256 + row_in_tile);
+            ptx::bulk_commit_group();
           }
-          const uint32_t piece = static_cast<uint32_t>(g) ^ ((static_cast<uint32_t>(lane) >> 1) & 3u);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
-                       ::"r"(buf + lane * 64u + piece * 16u), "r"(pack_bf16x2(v[0], v[1])),
-                         "r"(pack_bf16x2(v[2], v[3])), "r"(pack_bf16x2(v[4], v[5])), "r"(pack_bf16x2(v[6], v[7]))
-                       : "memory");
+          ++nstore;
         }
-        ptx::fence_proxy_async();
-        __syncwarp();
-        if (lane == 0) {
-          if (!(p.dbg & 1)) ptx::tma_store_2d(&maps.d, buf, q_base, pt * 256 + static_cast<int>(rank) * 128 + quarter * 32);
-          ptx::bulk_commit_group();
-        }
-        ++nstore;
+        }   // live
+        if (j + 2 < NCH && chunk_live(chunk_of(j + 2))) ptx::tc_ld_32x32b_x32(taddr + chunk_of(j + 2) * 32, r[j & 1]);
       }
-      if (!released) {                                      // RELEASE_CHUNKS == CHUNKS or 0 handled here
-        ptx::tc_fence_before();
-        __syncwarp();
-        if (lane == 0) ptx::mbar_arrive_cluster(free_addr);
-      }
+      if (tr) p.trace[tl * 8 + (first_half ? 5 : 7)] = clock64();
     }
     if (lane == 0) ptx::bulk_wait_group_all();   // staging must outlive the stores that read it
   }
