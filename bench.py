@@ -46,6 +46,9 @@ WORKLOADS = {
     "c5": ("llama3-70b-ffn-m8192", 8192, 8192,
            [("gate_up", 57344, 8192, True), ("down", 8192, 28672, False)]),
 }
+# Qwen3-30B-A3B-shaped grouped MoE (--workload c4): 128 experts, top-8, 4096 tokens
+MOE = dict(name="qwen3-30b-a3b-moe-4096tok", experts=128, top_k=8, tokens=4096,
+           layers=[("gate_up", 1536, 2048), ("down", 2048, 768)])
 
 
 def measured_peaks():
@@ -112,10 +115,12 @@ class ClockSampler:
 class Layer:
     """Device-resident tensors of one rank's shard of the workload."""
 
-    def __init__(self, key, rank, world, dev, seed=1234):
+    def __init__(self, key, rank, world, dev, seed=1234, tokens=0):
         import fp4_gemm
         from flashrt_b200_core import alloc_fp4
         self.name, self.M, self.H, layers = WORKLOADS[key]
+        if tokens:
+            self.name, self.M = f"{self.name.rsplit('-m', 1)[0]}-m{tokens}", tokens
         g = torch.Generator(device=dev).manual_seed(seed)
         rn = lambda *s, scale=1.0: (torch.randn(*s, generator=g, device=dev) * scale).to(torch.bfloat16)
         self.hidden, self.residual0 = rn(self.M, self.H), rn(self.M, self.H)
@@ -187,7 +192,7 @@ def run_ours(args, rank, world, local_rank):
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
     peaks = measured_peaks()
-    layer = Layer(args.workload, rank, world, dev)
+    layer = Layer(args.workload, rank, world, dev, tokens=args.tokens)
     st = capi.stream_ptr()
 
     def barrier():
@@ -198,6 +203,36 @@ def run_ours(args, rank, world, local_rank):
     for _ in range(args.warmup):
         layer.step_capi(capi, st)
     barrier()
+    if args.graph:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                n_launch = layer.step_capi(capi, capi.stream_ptr())
+        barrier()
+        for _ in range(3):
+            graph.replay()
+        with ClockSampler(local_rank) as clocks:
+            barrier()
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            for _ in range(args.steps):
+                graph.replay()
+            t1.record()
+            barrier()
+        ms = t0.elapsed_time(t1) / args.steps
+        wbytes = sum(0.5625 * g_["n_loc"] * g_["k"] for g_ in layer.gemms)
+        if rank == 0:
+            print(json.dumps({
+                "metric": "nvfp4_linear_path_tflops", "value": round(layer.flops_total / world / (ms * 1e-3) / 1e12, 3),
+                "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": round(ms, 5), "higher_is_better": True, "data": "synthetic", "timing": "cuda graph replay",
+                "config": {"workload": layer.name, "tokens": layer.M},
+                "weight_stream_gbs_whole_step": round(wbytes / (ms * 1e-3) / 1e9, 1),
+                "weight_stream_frac_of_hbm_measured": round(wbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 3),
+                "gpu_launches": n_launch * args.steps, "clocks": clocks.summary()}), flush=True)
+        return
     keys = [("producer", i) for i, g_ in enumerate(layer.gemms) if g_["fed"]] + \
            [(g_["name"], i) for i, g_ in enumerate(layer.gemms)]
     events = [{k: (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for k in keys}
@@ -236,6 +271,7 @@ def run_ours(args, rank, world, local_rank):
         "per_gemm_tflops": {layer.gemms[k[1]]["name"]: round(2.0 * layer.M * layer.gemms[k[1]]["n_loc"] *
                             layer.gemms[k[1]]["k"] / (v * 1e-3) / 1e12, 1) for k, v in per_kernel.items()
                             if k[0] != "producer"},
+        "weight_stream_gbs": round(sum(0.5625 * g_["n_loc"] * g_["k"] for g_ in layer.gemms) / (gemm_ms * 1e-3) / 1e9 * world, 1),
         "producer_gbs": round(prod_bytes / (statistics.mean(prod_ms) * 1e-3) / 1e9, 1) if prod_ms else None,
         "producer_frac_of_hbm_measured": round(prod_bytes / (statistics.mean(prod_ms) * 1e-3) / 1e9 /
                                                peaks["hbm_gbs"], 3) if prod_ms else None,
@@ -360,6 +396,60 @@ def run_ours(args, rank, world, local_rank):
         print(json.dumps(line), flush=True)
 
 
+def run_moe(args, rank, world, local_rank):
+    """Grouped NVFP4 GEMMs of one MoE layer (replicas only: every rank runs the whole workload)."""
+    from flashrt_b200_core import capi, load
+    from oracle.nvfp4_oracle import route_topk       # routing of the synthetic workload (host, set-up only)
+    load()
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    L, P, st = capi.lib(), capi.ptr, capi.stream_ptr()
+    rng = np.random.default_rng(3)
+    _, offs = route_topk(rng.standard_normal((MOE["tokens"], MOE["experts"])).astype(np.float32), MOE["top_k"])
+    rows, experts = int(offs[-1]), MOE["experts"]
+    offs_d = torch.from_numpy(offs).to(dev)
+    alpha = torch.ones(experts, device=dev)
+    work = torch.empty(int(L.frt_nvfp4_grouped_gemm_workspace_bytes(rows, experts)), dtype=torch.uint8, device=dev)
+    sfb = lambda r, k: int(L.frt_nvfp4_sf_swizzled_bytes(r, k))
+    layers, flops = [], 0.0
+    for name, n, k in MOE["layers"]:
+        ap = torch.randint(0, 256, (rows, k // 2), dtype=torch.uint8, device=dev)
+        wp = torch.randint(0, 256, (experts, n, k // 2), dtype=torch.uint8, device=dev)
+        asf = torch.randint(32, 80, (sfb(rows, k),), dtype=torch.uint8, device=dev)
+        wsf = torch.randint(32, 80, (experts, sfb(n, k)), dtype=torch.uint8, device=dev)
+        out = torch.empty(rows, n, dtype=torch.bfloat16, device=dev)
+        layers.append((name, n, k, ap, wp, asf, wsf, out))
+        flops += 2.0 * rows * n * k
+
+    def step():
+        for name, n, k, ap, wp, asf, wsf, out in layers:
+            rc = L.frt_nvfp4_grouped_gemm_bf16(P(ap), P(asf), P(wp), P(wsf), P(alpha), P(offs_d), None, 0, P(out), rows,
+                                               n, k, experts, n * (k // 2), int(wsf.shape[1]), P(work), st)
+            assert rc == 0, rc
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    l0 = L.frt_launch_count()
+    with ClockSampler(local_rank) as clocks:
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(args.steps):
+            step()
+        t1.record()
+        torch.cuda.synchronize()
+    ms = t0.elapsed_time(t1) / args.steps
+    if rank == 0:
+        print(json.dumps({
+            "metric": "nvfp4_grouped_moe_tflops", "value": round(flops / (ms * 1e-3) / 1e12, 2), "unit": "TFLOP/s",
+            "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 5),
+            "higher_is_better": True, "scaling": "replicas only", "vs_baseline": None, "dtype": "nvfp4", "data": "synthetic",
+            "config": {"workload": MOE["name"], "routed_rows": rows, "experts": experts,
+                       "layers": {l[0]: [l[1], l[2]] for l in layers},
+                       "l2": "weights 340 MB + activations per step exceed the 126 MiB L2"},
+            "gpu_launches": int(L.frt_launch_count() - l0), "clocks": clocks.summary()}), flush=True)
+
+
 # ----------------------------------------------------------------------------
 # CPU arm: the reference path restated for the host (oracle port)
 # ----------------------------------------------------------------------------
@@ -437,7 +527,10 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["c4"])
+    ap.add_argument("--tokens", type=int, default=0, help="override the token count M (decode sweep: 1, 4, 16, 64)")
+    ap.add_argument("--graph", action="store_true",
+                    help="time CUDA-graph replays of the step (launch-bound decode shapes); prints a short line")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     args = ap.parse_args()
@@ -455,7 +548,10 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     try:
-        run_ours(args, rank, world, local_rank)
+        if args.workload == "c4":
+            run_moe(args, rank, world, local_rank)
+        else:
+            run_ours(args, rank, world, local_rank)
     finally:
         if world > 1:
             import torch.distributed as dist

@@ -59,6 +59,7 @@ struct GemmParams {
   int group_m;              // raster: tiles walk GROUP_M p-tiles before the next q-tile
   int dbg;                  // experiment switches (0 in production)
   const float* alpha_stack; // grouped: per-expert alpha
+  int splits;               // split-K cluster size (small-M form), 1 otherwise
   long long* trace;         // clock64 timeline of pair 0, 8 slots per tile (null in production)
 };
 
@@ -83,7 +84,12 @@ __device__ __forceinline__ void tile_coords(int t, const GemmParams& p, int& pt,
   qt = r / gsize;
 }
 
-template <int BN, int STAGES, int ACC, bool SWAP>
+// SPLITK (small token counts, SWAP form only): `p.splits` CTAs form a cluster on one tile of 128
+// weight rows; CTA r contracts its share of K, leaves its fp32 partial tile in its own shared
+// memory, and after a cluster barrier every CTA sums a slice of the columns over all ranks
+// through distributed shared memory, in rank order (deterministic), and writes it out.  This is
+// what lets a layer with few 128-row tiles pull weights through every SM.
+template <int BN, int STAGES, int ACC, bool SWAP, bool SPLITK = false>
 __global__ void __launch_bounds__(192, 1)
 nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
                   const GemmParams p) {
@@ -107,7 +113,14 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int total_tiles = p.p_tiles * p.q_tiles;
-  const int k_stages = (p.k_tiles + KT_PER_STAGE - 1) / KT_PER_STAGE;
+  const int k_stages_all = (p.k_tiles + KT_PER_STAGE - 1) / KT_PER_STAGE;
+  static_assert(!SPLITK || SWAP, "split-K exists for the swapped form only");
+  const int krank = SPLITK ? static_cast<int>(ptx::cluster_ctarank()) : 0;
+  const int k_per = SPLITK ? k_stages_all / p.splits : k_stages_all;      // host makes it divide
+  const int ks_begin = krank * k_per;
+  const int k_stages = ks_begin + k_per;                                   // loop bound (exclusive)
+  const int tile_first = SPLITK ? static_cast<int>(blockIdx.x) / p.splits : static_cast<int>(blockIdx.x);
+  const int tile_step = SPLITK ? static_cast<int>(gridDim.x) / p.splits : static_cast<int>(gridDim.x);
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < STAGES; ++i) { ptx::mbar_init(&full[i], 1); ptx::mbar_init(&empty[i], 1); }
@@ -130,12 +143,12 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
     // ===================== TMA producer =====================
     if (ptx::elect_one()) {
       int it = 0;
-      for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
+      for (int t = tile_first; t < total_tiles && !*abort_flag; t += tile_step) {
         int pt, qt;
         tile_coords(t, p, pt, qt);
         const int q0 = qt * BN;
         const int qblk0 = q0 >> 7;
-        for (int ks = 0; ks < k_stages; ++ks, ++it) {
+        for (int ks = ks_begin; ks < k_stages; ++ks, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!ptx::mbar_wait_bounded(&empty[s], ph ^ 1, WAIT_LIMIT)) {
@@ -183,7 +196,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
       int s = 0, tl = 0;
       uint32_t ph = 0, sfbuf = 0;
       bool aborted = false;
-      for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x, ++tl) {
+      for (int t = tile_first; t < total_tiles && !*abort_flag; t += tile_step, ++tl) {
         const int a = tl % ACC;
         const uint32_t aph = (tl / ACC) & 1;
         if (!ptx::mbar_wait_bounded(&acc_empty[a], aph ^ 1, WAIT_LIMIT)) {
@@ -195,7 +208,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
         int pt, qt;
         tile_coords(t, p, pt, qt);
         const uint32_t qoff = (static_cast<uint32_t>(qt * BN) & 127u) >> 5;
-        for (int ks = 0; ks < k_stages; ++ks) {
+        for (int ks = ks_begin; ks < k_stages; ++ks) {
           if (!ptx::mbar_wait_bounded(&full[s], ph, WAIT_LIMIT)) {
             atomicOr(&g_status_word, 8u); *abort_flag = 1; aborted = true; break;
           }
@@ -220,7 +233,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
               }
               // +2 per k-tile: 32 bytes (64 e2m1) along K inside the 128-byte swizzle span
               ptx::tc_mma_nvf4(d_tmem, a_lo + 2 * kt, b_lo + 2 * kt, op_hi, IDESC, sfp_t, sfq_t + qoff,
-                               (ks | kt) != 0);
+                               ks != ks_begin || kt != 0);
             }
           } else {
             for (int kt = 0; kt < kts; ++kt) {
@@ -230,7 +243,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
               for (int b = 0; b < L::SFQ_BLOCKS; ++b)
                 ptx::tc_cp_32x128b_warpx4(sfq_t + 4 * b, sfq_lo + (b * KT_PER_STAGE + kt) * (SF_TILE >> 4), sf_hi);
               ptx::tc_mma_nvf4(d_tmem, a_lo + 2 * kt, b_lo + 2 * kt, op_hi, IDESC, sfp_t, sfq_t + qoff,
-                               (ks | kt) != 0);
+                               ks != ks_begin || kt != 0);
             }
           }
           ptx::tc_commit(&empty[s]);
@@ -245,7 +258,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
     // ===================== epilogue (warps 2..5) =====================
     const int quarter = warp & 3;      // TMEM lanes [32*quarter, +32)
     int tl = 0;
-    for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x, ++tl) {
+    for (int t = tile_first; t < total_tiles && !*abort_flag; t += tile_step, ++tl) {
       int pt, qt;
       tile_coords(t, p, pt, qt);
       const int a = tl % ACC;
@@ -302,6 +315,14 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
             }
           }
         } else {
+          if (SPLITK) {
+            // fp32 partial of this CTA's K share: part[token][weight row in tile], in the (idle) stage ring
+            float* part = reinterpret_cast<float*>(smem);
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (cchunk * 32 + j < BN) part[(cchunk * 32 + j) * BM + quarter * 32 + lane] = __uint_as_float(r[j]);
+            continue;
+          }
           // thread = output column prow (a weight row), columns of the tile = tokens
           const float bias = (p.bias != nullptr && prow < p.P) ? __bfloat162float(p.bias[prow]) : 0.f;
 #pragma unroll
@@ -324,6 +345,42 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
 
   ptx::tc_fence_before();
   __syncthreads();
+  if (SPLITK) {
+    ptx::cluster_arrive();
+    ptx::cluster_wait();                                  // every rank's partial tile is in its shared memory
+    if (warp >= 2 && tile_first < total_tiles && !*abort_flag) {
+      int pt, qt;
+      tile_coords(tile_first, p, pt, qt);
+      const int row = (warp & 3) * 32 + lane;
+      const int prow = pt * BM + row;
+      const uint32_t part0 = ptx::smem_u32(smem);
+      const float bias = (p.bias != nullptr && prow < p.P) ? __bfloat162float(p.bias[prow]) : 0.f;
+      // this rank's slice of the token columns; all remote loads of a column are issued
+      // before the first is used, and summed in rank order
+      uint32_t remote[8];
+#pragma unroll
+      for (int r = 0; r < 8; ++r) remote[r] = ptx::mapa(part0 + static_cast<uint32_t>(row) * 4u, r < p.splits ? r : 0);
+      for (int j = krank; j < BN; j += p.splits) {
+        const int tok = qt * BN + j;
+        if (tok >= p.Q) break;
+        float part[8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+          part[r] = r < p.splits ? ptx::ld_cluster_f32(remote[r] + static_cast<uint32_t>(j * BM) * 4u) : 0.f;
+        float acc = part[0];
+#pragma unroll
+        for (int r = 1; r < 8; ++r) acc += part[r];
+        if (prow < p.P) {
+          const int64_t off = static_cast<int64_t>(tok) * p.ldd + prow;
+          float v = acc * p.alpha + bias;
+          if (p.c != nullptr) v += p.beta * __bfloat162float(p.c[off]);
+          p.d[off] = __float2bfloat16_rn(v);
+        }
+      }
+    }
+    ptx::cluster_arrive();
+    ptx::cluster_wait();                                  // nobody leaves while its partial may still be read
+  }
   if (warp == 1) ptx::tmem_dealloc(tmem_base, 512);
 }
 
@@ -447,6 +504,37 @@ int launch_gemm_pair(const void* p_packed, const void* q_packed, GemmParams& p, 
   const int pairs = tiles < sms / 2 ? tiles : sms / 2;
   kern<<<2 * pairs, 320, L::TOTAL, st>>>(maps, p, nullptr);
   return launch_result();
+}
+
+template <int BN, int STAGES>
+int launch_gemm_splitk(const CUtensorMap& mp, const CUtensorMap& mq, GemmParams& p, cudaStream_t st) {
+  using L = SmemLayout<BN, STAGES>;
+  auto kern = nvfp4_gemm_kernel<BN, STAGES, 1, true, true>;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_set[dev & 63]) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL) != cudaSuccess)
+      return FRT_E_LAUNCH;
+    attr_set[dev & 63] = true;
+  }
+  p.q_tiles = 1;
+  p.p_tiles = (p.P + BM - 1) / BM;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(static_cast<unsigned>(p.p_tiles * p.splits));
+  cfg.blockDim = dim3(192);
+  cfg.dynamicSmemBytes = L::TOTAL;
+  cfg.stream = st;
+  cudaLaunchAttribute attr{};
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = static_cast<unsigned>(p.splits);
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, mp, mq, p);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return e == cudaSuccess ? FRT_OK : FRT_E_LAUNCH;
 }
 
 // ---------------------------------------------------------------------------
@@ -629,6 +717,23 @@ int run_gemm(const void* p_packed, const void* sfp, int P, const void* q_packed,
   CUtensorMap mp, mq;
   if (int rc = make_operand_map(&mp, p_packed, P, K, BM)) return rc;
   if (int rc = make_operand_map(&mq, q_packed, Q, K, bn)) return rc;
+  p.splits = 1;
+  if (swap && Q <= bn && cfg >= 11 && cfg <= 13 && !(g_opt_gemm_debug & 16)) {
+    // few 128-row weight tiles: split K over a cluster so that every SM streams weights
+    const int tiles = (P + BM - 1) / BM, k_stages = (p.k_tiles + KT_PER_STAGE - 1) / KT_PER_STAGE;
+    int want = di.sms / tiles;
+    if (want > 8) want = 8;
+    for (int s = want; s >= 2; --s)
+      if (k_stages % s == 0 && k_stages / s >= 2) { p.splits = s; break; }
+    if (bn == 64 && p.splits < 4) p.splits = 1;   // 64 token columns: the cross-CTA sum only pays off from 4-way
+    if (p.splits > 1) {
+      switch (cfg) {
+        case 11: return launch_gemm_splitk<16, 8>(mp, mq, p, st);
+        case 12: return launch_gemm_splitk<32, 8>(mp, mq, p, st);
+        default: return launch_gemm_splitk<64, 8>(mp, mq, p, st);
+      }
+    }
+  }
   switch (cfg) {
     case 1: return launch_gemm<128, 6, 2, false>(mp, mq, p, di.sms, st);
     case 2: return launch_gemm<256, 4, 1, false>(mp, mq, p, di.sms, st);
