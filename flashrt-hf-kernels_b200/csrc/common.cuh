@@ -76,15 +76,32 @@ __device__ __forceinline__ uint32_t e2m1_rule_a_chain(float q) {
 // hardware result equals the compare chain.  The caller produces q as
 // fma(v, inv, +0): the rounding of v*inv is unchanged and a -0 product becomes
 // +0, whose sign bit the chain would not set.
+//
+// Two forms of the same map m -> (m - 1) | 1 on the magnitude bits m:
+//  * integer form: correct for every input, infinities included;
+//  * float form: q * (1 - 2^-24) rounded toward zero IS the float just below q
+//    in magnitude (the exact product lies in (m-1, m-1/2] units of the last
+//    place, and for m = 2^23 it is the largest float of the binade below), a
+//    zero stays a zero, and the sign is untouched; `| 1` finishes the map.
+//    One multiply on the FMA pipe and one logic op instead of five integer
+//    ops.  It must not see an infinity (inf | 1 is a NaN); q is infinite only
+//    in blocks whose scale byte is 0, which take the integer form.
 __device__ __forceinline__ float rule_a_nudge(float q) {
   const uint32_t u = __float_as_uint(q);
   const uint32_t mag = u & 0x7fffffffu;
   const uint32_t nudged = (max(mag, 1u) - 1u) | 1u;
   return __uint_as_float((u & 0x80000000u) | nudged);
 }
+__device__ __forceinline__ float rule_a_nudge_finite(float q) {
+  return __uint_as_float(__float_as_uint(__fmul_rz(q, 0x1.fffffep-1f)) | 1u);
+}
 
 __device__ __forceinline__ uint32_t e2m1x2_rule_a_hw(float q_lo, float q_hi) {
   return __nv_cvt_float2_to_fp4x2(make_float2(rule_a_nudge(q_lo), rule_a_nudge(q_hi)),
+                                  __NV_E2M1, cudaRoundNearest);
+}
+__device__ __forceinline__ uint32_t e2m1x2_rule_a_hw_finite(float q_lo, float q_hi) {
+  return __nv_cvt_float2_to_fp4x2(make_float2(rule_a_nudge_finite(q_lo), rule_a_nudge_finite(q_hi)),
                                   __NV_E2M1, cudaRoundNearest);
 }
 
@@ -95,14 +112,24 @@ __device__ __forceinline__ uint32_t e2m1x2_rne_hw(float q_lo, float q_hi) {
 
 enum : int { kEncHw = 0, kEncChain = 1, kEncRne = 2 };
 
-// Quantise 16 fp32 values: returns 8 packed bytes in a uint2 and the scale byte.
-template <int ENC>
-__device__ __forceinline__ uint2 quantize_block16(const float (&v)[16], uint8_t& sf_byte) {
-  float amax = 0.f;
-#pragma unroll
-  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
-  sf_byte = block_scale_byte(amax);
-  const float inv = __fdiv_rn(1.f, ue4m3_to_float(sf_byte));
+// max |v_i| over 16 values with the three-input max of sm_100 (max is exact, so the
+// grouping does not matter; a NaN operand is ignored like fmaxf does).
+__device__ __forceinline__ float max3_abs(float a, float b, float c) {
+  float r;
+  asm("max.abs.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+__device__ __forceinline__ float amax16(const float (&v)[16]) {
+  const float a = max3_abs(v[0], v[1], v[2]), b = max3_abs(v[3], v[4], v[5]);
+  const float c = max3_abs(v[6], v[7], v[8]), d = max3_abs(v[9], v[10], v[11]);
+  const float e = max3_abs(v[12], v[13], v[14]);
+  return max3_abs(max3_abs(a, b, c), max3_abs(d, e, v[15]), 0.f);
+}
+
+// Encode 16 fp32 values with the reciprocal `inv` of the block scale: 8 packed bytes.
+// FINITE selects the float form of the nudge (the caller guarantees a non-zero scale).
+template <int ENC, bool FINITE>
+__device__ __forceinline__ uint2 encode_block16(const float (&v)[16], float inv) {
   uint32_t w[2] = {0u, 0u};
 #pragma unroll
   for (int p = 0; p < 8; ++p) {
@@ -115,12 +142,24 @@ __device__ __forceinline__ uint2 quantize_block16(const float (&v)[16], uint8_t&
       q1 = __fmul_rn(v[2 * p + 1], inv);
     }
     uint32_t byte;
-    if (ENC == kEncHw) byte = e2m1x2_rule_a_hw(q0, q1);
+    if (ENC == kEncHw) byte = FINITE ? e2m1x2_rule_a_hw_finite(q0, q1) : e2m1x2_rule_a_hw(q0, q1);
     else if (ENC == kEncRne) byte = e2m1x2_rne_hw(q0, q1);
     else byte = e2m1_rule_a_chain(q0) | (e2m1_rule_a_chain(q1) << 4);
     w[p >> 2] |= (byte & 0xffu) << (8 * (p & 3));
   }
   return make_uint2(w[0], w[1]);
+}
+
+// Quantise 16 fp32 values: returns 8 packed bytes in a uint2 and the scale byte.
+// `inv_lut`, when given, is a 128-entry table of 1/float(scale byte) (the results of the
+// same IEEE division), replacing the conversion and the division.
+template <int ENC>
+__device__ __forceinline__ uint2 quantize_block16(const float (&v)[16], uint8_t& sf_byte,
+                                                  const float* inv_lut = nullptr) {
+  sf_byte = block_scale_byte(amax16(v));
+  const float inv = inv_lut ? __ldg(inv_lut + (sf_byte & 0x7f)) : __fdiv_rn(1.f, ue4m3_to_float(sf_byte));
+  if (ENC == kEncHw && sf_byte != 0) return encode_block16<ENC, true>(v, inv);
+  return encode_block16<ENC, false>(v, inv);
 }
 
 __device__ __forceinline__ void unpack_bf16x8(const uint4& raw, float* out) {

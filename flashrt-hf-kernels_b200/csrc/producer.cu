@@ -3,6 +3,7 @@
 // producer.  Hand-written for sm_100a; every kernel touches each byte of its
 // operands exactly once, with 128-bit loads.
 #include "common.cuh"
+#include "ptx.cuh"
 
 namespace frt {
 
@@ -12,6 +13,32 @@ int g_opt_gemm_config = 0;
 int g_opt_gemm_debug = 0;
 
 namespace {
+
+// 1 / float(b) for every UE4M3 scale byte b (bit patterns of the fp32 results of the IEEE
+// round-to-nearest division; b = 0 gives +inf).  One cached 4-byte load replaces the
+// byte -> half -> float conversion and the division in the quantiser.
+__device__ __align__(16) const uint32_t kInvScaleBits[128] = {
+    0x7f800000u, 0x44000000u, 0x43800000u, 0x432aaaabu, 0x43000000u, 0x42cccccdu, 0x42aaaaabu, 0x42924925u,
+    0x42800000u, 0x42638e39u, 0x424ccccdu, 0x423a2e8cu, 0x422aaaabu, 0x421d89d9u, 0x42124925u, 0x42088889u,
+    0x42000000u, 0x41e38e39u, 0x41cccccdu, 0x41ba2e8cu, 0x41aaaaabu, 0x419d89d9u, 0x41924925u, 0x41888889u,
+    0x41800000u, 0x41638e39u, 0x414ccccdu, 0x413a2e8cu, 0x412aaaabu, 0x411d89d9u, 0x41124925u, 0x41088889u,
+    0x41000000u, 0x40e38e39u, 0x40cccccdu, 0x40ba2e8cu, 0x40aaaaabu, 0x409d89d9u, 0x40924925u, 0x40888889u,
+    0x40800000u, 0x40638e39u, 0x404ccccdu, 0x403a2e8cu, 0x402aaaabu, 0x401d89d9u, 0x40124925u, 0x40088889u,
+    0x40000000u, 0x3fe38e39u, 0x3fcccccdu, 0x3fba2e8cu, 0x3faaaaabu, 0x3f9d89d9u, 0x3f924925u, 0x3f888889u,
+    0x3f800000u, 0x3f638e39u, 0x3f4ccccdu, 0x3f3a2e8cu, 0x3f2aaaabu, 0x3f1d89d9u, 0x3f124925u, 0x3f088889u,
+    0x3f000000u, 0x3ee38e39u, 0x3ecccccdu, 0x3eba2e8cu, 0x3eaaaaabu, 0x3e9d89d9u, 0x3e924925u, 0x3e888889u,
+    0x3e800000u, 0x3e638e39u, 0x3e4ccccdu, 0x3e3a2e8cu, 0x3e2aaaabu, 0x3e1d89d9u, 0x3e124925u, 0x3e088889u,
+    0x3e000000u, 0x3de38e39u, 0x3dcccccdu, 0x3dba2e8cu, 0x3daaaaabu, 0x3d9d89d9u, 0x3d924925u, 0x3d888889u,
+    0x3d800000u, 0x3d638e39u, 0x3d4ccccdu, 0x3d3a2e8cu, 0x3d2aaaabu, 0x3d1d89d9u, 0x3d124925u, 0x3d088889u,
+    0x3d000000u, 0x3ce38e39u, 0x3ccccccdu, 0x3cba2e8cu, 0x3caaaaabu, 0x3c9d89d9u, 0x3c924925u, 0x3c888889u,
+    0x3c800000u, 0x3c638e39u, 0x3c4ccccdu, 0x3c3a2e8cu, 0x3c2aaaabu, 0x3c1d89d9u, 0x3c124925u, 0x3c088889u,
+    0x3c000000u, 0x3be38e39u, 0x3bcccccdu, 0x3bba2e8cu, 0x3baaaaabu, 0x3b9d89d9u, 0x3b924925u, 0x3b888889u,
+    0x3b800000u, 0x3b638e39u, 0x3b4ccccdu, 0x3b3a2e8cu, 0x3b2aaaabu, 0x3b1d89d9u, 0x3b124925u, 0x3b088889u
+};
+
+__device__ __forceinline__ const float* inv_scale_table() {
+  return reinterpret_cast<const float*>(kInvScaleBits);
+}
 
 // ---------------------------------------------------------------------------
 // linear [rows, nb] -> swizzled.  One thread moves the 4 scale bytes of one
@@ -62,7 +89,7 @@ quantize_kernel(const uint4* __restrict__ src, uint2* __restrict__ packed, uint8
     unpack_bf16x8(r1, v + 8);
   }
   uint8_t sfb;
-  const uint2 out = quantize_block16<ENC>(v, sfb);
+  const uint2 out = quantize_block16<ENC>(v, sfb, inv_scale_table());
   packed[idx] = out;
   sf[sf_offset(row, kb, sf_cols)] = sfb;
 }
@@ -232,29 +259,251 @@ norm_quant_kernel(const NormParams p) {
   if (QUANT) {
     uint8_t sfb;
     uint2 out;
-    if (p.flags & FRT_PRODUCER_RNE_E2M1) out = quantize_block16<kEncRne>(v, sfb);
-    else out = quantize_block16<ENC>(v, sfb);
+    if (p.flags & FRT_PRODUCER_RNE_E2M1) out = quantize_block16<kEncRne>(v, sfb, inv_scale_table());
+    else out = quantize_block16<ENC>(v, sfb, inv_scale_table());
     p.packed[idx] = out;
     p.sf[sf_offset(row, s, p.sf_cols)] = sfb;
   }
 }
 
+// ---------------------------------------------------------------------------
+// Streaming form of the same kernel: persistent CTAs, inputs staged through
+// shared memory by bulk copies (TMA engine), three row groups deep.
+//
+// A "group" is the rows one CTA pass covers (CTA / TPR rows, contiguous in
+// memory).  Thread 0 keeps bulk copies of the next groups in flight, so HBM
+// latency is covered by whole groups of bytes per CTA rather than by the few
+// loads a warp can issue before it starts computing; the threads read their 32
+// bytes per tensor from shared memory.  The row-sum barrier doubles as the
+// "stage is free" signal: once every thread is past it, the stage's data is in
+// registers and thread 0 refills it.  Per-thread state that does not change
+// from row to row (the weight in fp32) is set up once per CTA.  Arithmetic, operation order and results are those of
+// norm_quant_kernel.
+// ---------------------------------------------------------------------------
+constexpr int kStreamStages = 3;
+constexpr long long kStreamWaitLimit = 1ll << 31;   // SM clocks, about a second
+
+__device__ __forceinline__ void st_global_v8(void* dst, const uint4& a, const uint4& b) {
+  asm volatile("st.global.cs.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+               ::"l"(dst), "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w)
+               : "memory");
+}
+
+template <int TPR, bool HAS_RES, bool QUANT, int ENC>
+__global__ void __launch_bounds__(TPR > 256 ? TPR : 256, TPR > 256 ? 1024 / TPR : 4)
+norm_quant_stream_kernel(const NormParams p, unsigned* status) {
+  constexpr int CTA = TPR > 256 ? TPR : 256;
+  constexpr int RPC = CTA / TPR;                      // rows per group
+  constexpr int WPR = TPR / 32;                       // warps per row
+  constexpr int TENSORS = HAS_RES ? 2 : 1;
+  constexpr int STAGE_STRIDE = CTA * 32;              // bytes per tensor per stage
+  extern __shared__ __align__(128) unsigned char stage_mem[];
+  __shared__ uint64_t full[kStreamStages];
+  __shared__ float warp_sums[2][CTA / 32];
+
+  const int tid = threadIdx.x;
+  const int lane = tid & 31, warp = tid >> 5;
+  const int local_row = tid / TPR;
+  const int s = tid % TPR;                            // block index inside the row
+  const int n_groups = (p.rows + RPC - 1) / RPC;
+  const uint32_t row_bytes = static_cast<uint32_t>(p.nb) * 32u;
+
+  auto issue = [&](int group, int stage) {            // thread 0 only
+    const int row0 = group * RPC;
+    const int nrows = min(RPC, p.rows - row0);
+    const uint32_t bytes = static_cast<uint32_t>(nrows) * row_bytes;
+    unsigned char* dst = stage_mem + static_cast<size_t>(stage) * TENSORS * STAGE_STRIDE;
+    const size_t src_off = static_cast<size_t>(row0) * row_bytes;
+    ptx::mbar_expect_tx(&full[stage], bytes * TENSORS);
+    ptx::bulk_load(dst, reinterpret_cast<const unsigned char*>(p.x) + src_off, bytes, &full[stage]);
+    if (HAS_RES)
+      ptx::bulk_load(dst + STAGE_STRIDE, reinterpret_cast<const unsigned char*>(p.residual) + src_off, bytes,
+                     &full[stage]);
+  };
+
+  if (tid == 0) {
+#pragma unroll
+    for (int i = 0; i < kStreamStages; ++i) ptx::mbar_init(&full[i], 1);
+    ptx::fence_barrier_init();
+#pragma unroll
+    for (int i = 0; i < kStreamStages; ++i) {
+      const int g = blockIdx.x + i * gridDim.x;
+      if (g < n_groups) issue(g, i);
+    }
+  }
+
+  // per-thread weight (fp32), fixed for the kernel
+  float g[16];
+  const bool has_w = p.weight != nullptr;
+  if (has_w && s < p.nb) {
+    unpack_bf16x8(__ldg(p.weight + 2 * s), g);
+    unpack_bf16x8(__ldg(p.weight + 2 * s + 1), g + 8);
+    if (p.flags & FRT_PRODUCER_ONE_PLUS_W) {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) g[j] = __fadd_rn(1.f, g[j]);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) g[j] = 1.f;
+  }
+  __syncthreads();                                    // barriers initialised
+
+  int it = 0;
+  for (int group = blockIdx.x; group < n_groups; group += gridDim.x, ++it) {
+    const int stage = it % kStreamStages;
+    const uint32_t parity = (it / kStreamStages) & 1;
+    if (!ptx::mbar_wait_bounded(&full[stage], parity, kStreamWaitLimit)) atomicOr(status, 0x100u);
+    const int row = group * RPC + local_row;
+    const bool ok = row < p.rows && s < p.nb;
+    const int64_t idx = static_cast<int64_t>(row) * p.nb + s;
+
+    float v[16];
+    uint4 x0 = make_uint4(0, 0, 0, 0), x1 = x0, r0 = x0, r1 = x0;
+    if (ok) {
+      const uint4* sx = reinterpret_cast<const uint4*>(
+          stage_mem + static_cast<size_t>(stage) * TENSORS * STAGE_STRIDE + static_cast<size_t>(local_row) * row_bytes) + 2 * s;
+      x0 = sx[0];
+      x1 = sx[1];
+      if (HAS_RES) {
+        const uint4* sr = reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned char*>(sx) + STAGE_STRIDE);
+        r0 = sr[0];
+        r1 = sr[1];
+      }
+    }
+    unpack_bf16x8(x0, v);
+    unpack_bf16x8(x1, v + 8);
+    float part = 0.f;
+    if (HAS_RES) {
+      float r[16];
+      unpack_bf16x8(r0, r);
+      unpack_bf16x8(r1, r + 8);
+#pragma unroll
+      for (int j = 0; j < 16; ++j) v[j] = __fadd_rn(r[j], v[j]);
+      uint4 o0, o1;
+      pack16_bf16(v, o0, o1);
+      if (ok) st_global_v8(p.residual + 2 * idx, o0, o1);
+#pragma unroll
+      for (int j = 0; j < 16; ++j) part = __fadd_rn(part, __fmul_rn(v[j], v[j]));
+      if (p.flags & FRT_PRODUCER_NORM_FROM_BF16_RESIDUAL) {
+        unpack_bf16x8(o0, v);
+        unpack_bf16x8(o1, v + 8);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) part = __fadd_rn(part, __fmul_rn(v[j], v[j]));
+    }
+
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) part = __fadd_rn(part, __shfl_xor_sync(0xffffffffu, part, o));
+    float ssq = part;
+    if (WPR > 1 && lane == 0) warp_sums[it & 1][warp] = part;
+    __syncthreads();                                  // warp sums visible; stage data is in registers
+    if (tid == 0) {
+      const int next = group + kStreamStages * gridDim.x;
+      if (next < n_groups) issue(next, stage);
+    }
+    if (WPR > 1) {
+      const int first = (warp / WPR) * WPR;
+      ssq = warp_sums[it & 1][first];
+#pragma unroll
+      for (int w = 1; w < WPR; ++w) ssq = __fadd_rn(ssq, warp_sums[it & 1][first + w]);
+    }
+    if (ok) {
+      const float rstd = __frsqrt_rn(__fadd_rn(__fdiv_rn(ssq, p.dim_f), p.eps));
+      if (has_w) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = __fmul_rn(__fmul_rn(v[j], rstd), g[j]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = __fmul_rn(v[j], rstd);
+      }
+      if (p.inv_global_scale != 1.0f) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = __fmul_rn(v[j], p.inv_global_scale);
+      }
+      const bool round_bf16 = p.flags & FRT_PRODUCER_ROUND_BF16;
+      if (p.normed != nullptr || round_bf16) {
+        uint4 o0, o1;
+        pack16_bf16(v, o0, o1);
+        if (p.normed != nullptr) {
+          p.normed[2 * idx] = o0;
+          p.normed[2 * idx + 1] = o1;
+        }
+        if (round_bf16) {
+          unpack_bf16x8(o0, v);
+          unpack_bf16x8(o1, v + 8);
+        }
+      }
+      if (QUANT) {
+        uint8_t sfb;
+        uint2 out;
+        if (p.flags & FRT_PRODUCER_RNE_E2M1) out = quantize_block16<kEncRne>(v, sfb, inv_scale_table());
+        else out = quantize_block16<ENC>(v, sfb, inv_scale_table());
+        p.packed[idx] = out;
+        p.sf[sf_offset(row, s, p.sf_cols)] = sfb;
+      }
+    }
+  }
+}
+
+template <int TPR, bool HAS_RES, bool QUANT, int ENC>
+int launch_norm_stream(const NormParams& p, cudaStream_t st) {
+  constexpr int CTA = TPR > 256 ? TPR : 256;
+  constexpr int RPC = CTA / TPR;
+  constexpr int smem = kStreamStages * (HAS_RES ? 2 : 1) * CTA * 32;
+  auto kernel = norm_quant_stream_kernel<TPR, HAS_RES, QUANT, ENC>;
+  static int ctas_per_sm[16] = {0};                   // per device, filled on first use
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return FRT_E_DEVICE;
+  if (ctas_per_sm[dev] == 0) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+      return FRT_E_LAUNCH;
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, CTA, smem) != cudaSuccess || n < 1)
+      return FRT_E_LAUNCH;
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return FRT_E_DEVICE;
+    ctas_per_sm[dev] = n * sms;
+  }
+  const int n_groups = (p.rows + RPC - 1) / RPC;
+  const int grid = n_groups < ctas_per_sm[dev] ? n_groups : ctas_per_sm[dev];
+  kernel<<<grid, CTA, smem, st>>>(p, device_status_word());
+  return launch_result();
+}
+
 template <int TPR>
 int launch_norm(const NormParams& p, bool has_res, bool quant, cudaStream_t st) {
-  constexpr int CTA = TPR > 256 ? TPR : 256;
-  constexpr int rows_per_cta = CTA / TPR;
-  const dim3 grid((p.rows + rows_per_cta - 1) / rows_per_cta), block(CTA);
   const bool chain = g_opt_quant_encoder == 1;
+  // Measured on B200: one CTA per row group wins while a row fits 256 threads (64 resident
+  // warps per SM hide the latency by themselves); for wider rows the CTA-wide barrier of a
+  // 512/1024-thread CTA stalls the SM and the staged persistent form is 15-35 % faster.
+  // Debug bits 32 / 64 force one form or the other.
+  const bool stream = (g_opt_gemm_debug & 64) || (!(g_opt_gemm_debug & 32) && TPR > (quant ? 256 : 512));
+  if (!stream) {
+    constexpr int CTA = TPR > 256 ? TPR : 256;
+    constexpr int rows_per_cta = CTA / TPR;
+    const dim3 grid((p.rows + rows_per_cta - 1) / rows_per_cta), block(CTA);
 #define FRT_LAUNCH(HR, Q, E) norm_quant_kernel<TPR, HR, Q, E><<<grid, block, 0, st>>>(p)
-  if (!quant) {
-    if (has_res) FRT_LAUNCH(true, false, kEncHw); else FRT_LAUNCH(false, false, kEncHw);
-  } else if (chain) {
-    if (has_res) FRT_LAUNCH(true, true, kEncChain); else FRT_LAUNCH(false, true, kEncChain);
-  } else {
-    if (has_res) FRT_LAUNCH(true, true, kEncHw); else FRT_LAUNCH(false, true, kEncHw);
-  }
+    if (!quant) {
+      if (has_res) FRT_LAUNCH(true, false, kEncHw); else FRT_LAUNCH(false, false, kEncHw);
+    } else if (chain) {
+      if (has_res) FRT_LAUNCH(true, true, kEncChain); else FRT_LAUNCH(false, true, kEncChain);
+    } else {
+      if (has_res) FRT_LAUNCH(true, true, kEncHw); else FRT_LAUNCH(false, true, kEncHw);
+    }
 #undef FRT_LAUNCH
-  return launch_result();
+    return launch_result();
+  }
+  if (!quant) {
+    return has_res ? launch_norm_stream<TPR, true, false, kEncHw>(p, st)
+                   : launch_norm_stream<TPR, false, false, kEncHw>(p, st);
+  }
+  if (chain) {
+    return has_res ? launch_norm_stream<TPR, true, true, kEncChain>(p, st)
+                   : launch_norm_stream<TPR, false, true, kEncChain>(p, st);
+  }
+  return has_res ? launch_norm_stream<TPR, true, true, kEncHw>(p, st)
+                 : launch_norm_stream<TPR, false, true, kEncHw>(p, st);
 }
 
 int dispatch_norm(NormParams& p, bool has_res, bool quant, cudaStream_t st) {

@@ -64,6 +64,17 @@ def test_quantizer_bit_exact(rows, dim, scale, dtype, encoder):
     x[0, :16] = 0                      # an all-zero block
     x[0, 16:32] = 2.0 ** -13           # scale rounds to zero
     x[0, 32] = -0.0
+    if dim >= 64:
+        x[0, 48:64] = -(2.0 ** -13)    # zero scale, negative values: q = -inf
+    if rows > 1 and dim >= 48:
+        ties = torch.tensor([6, .25, .75, 1.25, 1.75, 2.5, 3.5, 5, -.25, -.75, -1.25, -1.75, -2.5, -3.5, -5, -6])
+        x[1, :16] = ties.to(dtype)                                    # scale 1.0: q hits every threshold
+        up = ties.to(dtype).view(torch.int16) + 1                      # one ulp further from zero
+        x[1, 16:32] = up.view(dtype)
+        x[1, 16], x[1, 31] = 6.0, -6.0
+        down = ties.to(dtype).view(torch.int16) - 1                    # one ulp nearer to zero
+        x[1, 32:48] = down.view(dtype)
+        x[1, 32] = 6.0
     prev = capi.lib().frt_set_option(1, encoder)
     try:
         packed, sf = alloc_fp4(rows, dim, fill=0)
@@ -82,6 +93,33 @@ def test_quantizer_bit_exact(rows, dim, scale, dtype, encoder):
         assert torch.equal(rp, packed) and torch.equal(rs, sf)
 
 
+@pytest.mark.parametrize("encoder", [0, 1])
+def test_quantizer_every_scale_byte(encoder):
+    """one block per UE4M3 scale value 0x01..0x7E (amax = 6 * value), other elements random
+    fractions of it: checks the reciprocal-scale table entry by entry"""
+    lut = np.asarray(O.UE4M3_LUT, dtype=np.float32)
+    g = torch.Generator().manual_seed(77)
+    rows, dim = 126, 64
+    x = torch.zeros(rows, dim)
+    for b in range(1, 127):
+        amax = 6.0 * float(lut[b])
+        for blk in range(4):
+            v = (torch.rand(16, generator=g) * 2 - 1) * amax
+            v[blk] = amax if blk % 2 == 0 else -amax
+            x[b - 1, 16 * blk:16 * blk + 16] = v
+    x = x.bfloat16()
+    prev = capi.lib().frt_set_option(1, encoder)
+    try:
+        packed, sf = alloc_fp4(rows, dim, fill=0)
+        quantize(D(x), packed, sf)
+    finally:
+        capi.lib().frt_set_option(1, prev)
+    want_p, want_s = O.quantize_nvfp4(x.float().numpy())
+    assert set(np.unique(want_s)) >= set(range(1, 127))
+    np.testing.assert_array_equal(sf.cpu().numpy(), O.sf_linear_to_swizzled(want_s))
+    np.testing.assert_array_equal(packed.cpu().numpy(), want_p)
+
+
 def test_dequantize_exact():
     rows, dim = 130, 1024
     g = torch.Generator().manual_seed(3)
@@ -96,9 +134,21 @@ def test_dequantize_exact():
 
 CASES = [(1, 1024), (16, 128), (63, 2048), (128, 4096), (257, 4096), (33, 5120), (9, 8192), (5, 12288), (3, 16384)]
 
+# The norm kernels exist in two forms (one CTA per row group; persistent CTAs fed by bulk
+# copies); the library picks one by row width.  Debug bits 32 / 64 force each form, so
+# every case is checked on both.
+FORMS = [32, 64]
+
+
+@pytest.fixture(params=FORMS, ids=["per_group", "streamed"])
+def form(request):
+    prev = capi.lib().frt_set_option(3, request.param)
+    yield request.param
+    capi.lib().frt_set_option(3, prev)
+
 
 @pytest.mark.parametrize("rows,dim", CASES)
-def test_rms_norm_bf16(rows, dim):
+def test_rms_norm_bf16(rows, dim, form):
     x, w = randn_bf16((rows, dim), 23 + rows), randn_bf16((dim,), 24, 0.1, 1.0)
     out = torch.empty(rows, dim, dtype=torch.bfloat16, device=DEV)
     capi.check(capi.lib().frt_rms_norm_bf16(P(D(x)), P(D(w)), P(out), rows, dim, 1e-6, st()))
@@ -113,7 +163,7 @@ def test_rms_norm_bf16(rows, dim):
 
 
 @pytest.mark.parametrize("rows,dim", CASES)
-def test_residual_add_rms_norm_bf16(rows, dim):
+def test_residual_add_rms_norm_bf16(rows, dim, form):
     x, r, w = randn_bf16((rows, dim), 1 + rows), randn_bf16((rows, dim), 2 + rows), randn_bf16((dim,), 3, 0.1, 1.0)
     res = r.to(DEV).clone()
     out = torch.empty(rows, dim, dtype=torch.bfloat16, device=DEV)
@@ -132,8 +182,8 @@ def test_residual_add_rms_norm_bf16(rows, dim):
 
 
 @pytest.mark.parametrize("encoder", [0, 1])
-@pytest.mark.parametrize("rows,dim", CASES + [(4096, 4096)])
-def test_fused_residual_norm_quant(rows, dim, encoder):
+@pytest.mark.parametrize("rows,dim", CASES + [(4096, 4096), (1500, 3072), (700, 8192)])
+def test_fused_residual_norm_quant(rows, dim, encoder, form):
     """residual_add_rms_norm_quant_nvfp4_swizzled_bf16 semantics, bit-exact
     against the oracle (same summation order) and, end to end, against the
     reference's fused kernel up to its different fp32 summation order."""
