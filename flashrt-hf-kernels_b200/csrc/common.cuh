@@ -112,6 +112,32 @@ __device__ __forceinline__ uint32_t e2m1x2_rne_hw(float q_lo, float q_hi) {
 
 enum : int { kEncHw = 0, kEncChain = 1, kEncRne = 2 };
 
+// 1 / float(b) for every UE4M3 scale byte b (bit patterns of the fp32 results of the IEEE
+// round-to-nearest division; b = 0 gives +inf).  One cached 4-byte load replaces the
+// byte -> half -> float conversion and the division in the quantiser.
+static __device__ __align__(16) const uint32_t kInvScaleBits[128] = {
+    0x7f800000u, 0x44000000u, 0x43800000u, 0x432aaaabu, 0x43000000u, 0x42cccccdu, 0x42aaaaabu, 0x42924925u,
+    0x42800000u, 0x42638e39u, 0x424ccccdu, 0x423a2e8cu, 0x422aaaabu, 0x421d89d9u, 0x42124925u, 0x42088889u,
+    0x42000000u, 0x41e38e39u, 0x41cccccdu, 0x41ba2e8cu, 0x41aaaaabu, 0x419d89d9u, 0x41924925u, 0x41888889u,
+    0x41800000u, 0x41638e39u, 0x414ccccdu, 0x413a2e8cu, 0x412aaaabu, 0x411d89d9u, 0x41124925u, 0x41088889u,
+    0x41000000u, 0x40e38e39u, 0x40cccccdu, 0x40ba2e8cu, 0x40aaaaabu, 0x409d89d9u, 0x40924925u, 0x40888889u,
+    0x40800000u, 0x40638e39u, 0x404ccccdu, 0x403a2e8cu, 0x402aaaabu, 0x401d89d9u, 0x40124925u, 0x40088889u,
+    0x40000000u, 0x3fe38e39u, 0x3fcccccdu, 0x3fba2e8cu, 0x3faaaaabu, 0x3f9d89d9u, 0x3f924925u, 0x3f888889u,
+    0x3f800000u, 0x3f638e39u, 0x3f4ccccdu, 0x3f3a2e8cu, 0x3f2aaaabu, 0x3f1d89d9u, 0x3f124925u, 0x3f088889u,
+    0x3f000000u, 0x3ee38e39u, 0x3ecccccdu, 0x3eba2e8cu, 0x3eaaaaabu, 0x3e9d89d9u, 0x3e924925u, 0x3e888889u,
+    0x3e800000u, 0x3e638e39u, 0x3e4ccccdu, 0x3e3a2e8cu, 0x3e2aaaabu, 0x3e1d89d9u, 0x3e124925u, 0x3e088889u,
+    0x3e000000u, 0x3de38e39u, 0x3dcccccdu, 0x3dba2e8cu, 0x3daaaaabu, 0x3d9d89d9u, 0x3d924925u, 0x3d888889u,
+    0x3d800000u, 0x3d638e39u, 0x3d4ccccdu, 0x3d3a2e8cu, 0x3d2aaaabu, 0x3d1d89d9u, 0x3d124925u, 0x3d088889u,
+    0x3d000000u, 0x3ce38e39u, 0x3ccccccdu, 0x3cba2e8cu, 0x3caaaaabu, 0x3c9d89d9u, 0x3c924925u, 0x3c888889u,
+    0x3c800000u, 0x3c638e39u, 0x3c4ccccdu, 0x3c3a2e8cu, 0x3c2aaaabu, 0x3c1d89d9u, 0x3c124925u, 0x3c088889u,
+    0x3c000000u, 0x3be38e39u, 0x3bcccccdu, 0x3bba2e8cu, 0x3baaaaabu, 0x3b9d89d9u, 0x3b924925u, 0x3b888889u,
+    0x3b800000u, 0x3b638e39u, 0x3b4ccccdu, 0x3b3a2e8cu, 0x3b2aaaabu, 0x3b1d89d9u, 0x3b124925u, 0x3b088889u
+};
+
+__device__ __forceinline__ const float* inv_scale_table() {
+  return reinterpret_cast<const float*>(kInvScaleBits);
+}
+
 // max |v_i| over 16 values with the three-input max of sm_100 (max is exact, so the
 // grouping does not matter; a NaN operand is ignored like fmaxf does).
 __device__ __forceinline__ float max3_abs(float a, float b, float c) {
@@ -169,6 +195,14 @@ __device__ __forceinline__ void unpack_bf16x8(const uint4& raw, float* out) {
     out[2 * i] = __uint_as_float(w[i] << 16);
     out[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
   }
+}
+
+// SwiGLU stage of the NVFP4 producer: bf16((g / (1 + exp(-g))) * u) as fp32, every step a
+// separately rounded fp32 operation (accurate expf, IEEE division), which is what the
+// reference's kernel evaluates.
+__device__ __forceinline__ float swiglu_bf16(float g, float u) {
+  const float s = __fdiv_rn(g, __fadd_rn(1.f, expf(-g)));
+  return __bfloat162float(__float2bfloat16_rn(__fmul_rn(s, u)));
 }
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {

@@ -61,6 +61,10 @@ struct GemmParams {
   const float* alpha_stack; // grouped: per-expert alpha
   int splits;               // split-K cluster size (small-M form), 1 otherwise
   long long* trace;         // clock64 timeline of pair 0, 8 slots per tile (null in production)
+  // SwiGLU -> NVFP4 epilogue: Q holds [gate ; up] (2 * hidden rows); outputs are hidden wide
+  int hidden;
+  uint8_t* out_packed;      // [P, hidden / 2]
+  uint8_t* out_sf;          // swizzled scales of a [P, hidden] tensor
 };
 
 template <int BN, int STAGES>
@@ -506,6 +510,31 @@ int launch_gemm_pair(const void* p_packed, const void* q_packed, GemmParams& p, 
   return launch_result();
 }
 
+// GEMM + SwiGLU + NVFP4 quantiser in one kernel (256 x (128 gate + 128 up) tiles).
+int launch_gemm_swiglu(const void* p_packed, const void* q_packed, GemmParams& p, int sms, cudaStream_t st) {
+  using L = PairLayout<256, 5, false>;
+  auto kern = nvfp4_gemm_pair_kernel<256, 5, false, true>;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_set[dev & 63]) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL) != cudaSuccess)
+      return FRT_E_LAUNCH;
+    attr_set[dev & 63] = true;
+  }
+  PairMaps maps{};
+  if (int rc = make_operand_map(&maps.p, p_packed, p.P, p.K, 128)) return rc;
+  if (int rc = make_operand_map(&maps.q, q_packed, p.Q, p.K, 128)) return rc;
+  if (int rc = make_sf_map(&maps.sfp, p.sfp, p.P, p.sf_cols, 1)) return rc;
+  if (int rc = make_sf_map(&maps.sfq, p.sfq, p.Q, p.sf_cols, 1)) return rc;
+  p.q_tiles = p.hidden / 128;
+  p.p_tiles = (p.P + 255) / 256;
+  const int tiles = p.p_tiles * p.q_tiles;
+  const int pairs = tiles < sms / 2 ? tiles : sms / 2;
+  kern<<<2 * pairs, 576, L::TOTAL, st>>>(maps, p, nullptr);
+  return launch_result();
+}
+
 template <int BN, int STAGES>
 int launch_gemm_splitk(const CUtensorMap& mp, const CUtensorMap& mq, GemmParams& p, cudaStream_t st) {
   using L = SmemLayout<BN, STAGES>;
@@ -767,6 +796,33 @@ int frt_nvfp4_gemm_bf16(const void* a, const void* sfa, const void* b, const voi
   const bool swap = cfg ? cfg >= 11 : (M <= 64);
   if (swap) return run_gemm(b, sfb, N, a, sfa, M, K, bias, cc, d, N, alpha, beta, true, cfg, as_stream(stream));
   return run_gemm(a, sfa, M, b, sfb, N, K, bias, cc, d, N, alpha, beta, false, cfg, as_stream(stream));
+}
+
+int frt_nvfp4_gemm_swiglu_nvfp4(const void* a, const void* sfa, const void* b, const void* sfb, void* out_packed,
+                                void* out_sf, int M, int N2, int K, float alpha, void* stream) {
+  if (!a || !sfa || !b || !sfb || !out_packed || !out_sf) return FRT_E_NULL;
+  if (M <= 0 || N2 <= 0 || K <= 0 || K % 32 != 0 || N2 % 2 != 0) return FRT_E_SHAPE;
+  if ((N2 / 2) % 128 != 0) return FRT_E_UNSUPPORTED;   // a tile is 128 gate + the 128 matching up columns
+  if (!aligned(a, 16) || !aligned(b, 16) || !aligned(out_packed, 16) || !aligned(out_sf, 4) ||
+      !aligned(sfa, 16) || !aligned(sfb, 16))
+    return FRT_E_ALIGN;
+  const DeviceInfo di = device_info();
+  if (!di.ok || di.cc_major != 10) return FRT_E_DEVICE;
+  GemmParams p{};
+  p.P = M; p.Q = N2; p.K = K;
+  p.k_tiles = (K + 63) / 64;
+  p.sf_cols = p.k_tiles;
+  p.sfp = static_cast<const uint8_t*>(sfa);
+  p.sfq = static_cast<const uint8_t*>(sfb);
+  p.sfq_row_blocks = (N2 + 127) / 128;
+  p.alpha = alpha;
+  p.group_m = 16;
+  p.dbg = g_opt_gemm_debug & 0xff;
+  p.trace = g_trace;
+  p.hidden = N2 / 2;
+  p.out_packed = static_cast<uint8_t*>(out_packed);
+  p.out_sf = static_cast<uint8_t*>(out_sf);
+  return launch_gemm_swiglu(a, b, p, di.sms, as_stream(stream));
 }
 
 int frt_device_status(void* stream, unsigned* status_out) {

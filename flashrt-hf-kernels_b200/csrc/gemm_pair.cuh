@@ -71,11 +71,23 @@ struct PairLayout {
 // GROUPED: P = one expert's weights (3-D / 4-D tensor maps with the expert as the
 // outer coordinate), Q = a window of token rows; the output tile is written
 // transposed (out[token, weight_row]) and masked to the rows of that expert.
-template <int BN, int STAGES, bool GROUPED>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(320, 1)
+//
+// SWIGLU (BN = 256, dense): Q = [gate ; up] weights stacked along N (2H rows).  A tile is 128
+// gate columns and the 128 matching up columns: CTA 0 stages gate rows [128 qt, +128), CTA 1
+// up rows [H + 128 qt, +128), so accumulator columns [0,128) are gate and [128,256) up for the
+// same 128 outputs.  The epilogue rounds both to bf16 (what a bf16 GEMM would have written),
+// evaluates bf16(silu(g) * u) and rule-A quantises it: each lane owns one output row and
+// whole 16-element blocks, and writes 16 packed bytes + 2 scale bytes per 32 outputs.  The
+// 2H-wide bf16 intermediate never exists in memory.
+// The SwiGLU form runs 16 epilogue warps (one lane quarter x one group of 32 outputs each):
+// its epilogue is an exponential and a division per output, and only that many warps issue
+// it in less time than the tile's mainloop takes.
+template <int BN, int STAGES, bool GROUPED, bool SWIGLU = false>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(SWIGLU ? 576 : 320, 1)
 nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p,
                        const GroupWork* __restrict__ work) {
   using L = PairLayout<BN, STAGES, GROUPED>;
+  static_assert(!SWIGLU || (BN == 256 && !GROUPED), "the SwiGLU epilogue is a 256-wide dense tile");
   constexpr int SFQ_COLS_PER_KT = L::SFQ_BLOCKS * 4;
   constexpr uint32_t IDESC = ptx::idesc_nvf4(256, BN);
   constexpr int CHUNKS = BN / 32;
@@ -106,14 +118,14 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
     for (int i = 0; i < STAGES; ++i) { ptx::mbar_init(&full[i], 1); ptx::mbar_init(&empty[i], 1); }
     ptx::mbar_init(&acc_full[0], 1);
     ptx::mbar_init(&acc_full[1], 1);
-    ptx::mbar_init(acc_free, 16);
+    ptx::mbar_init(acc_free, SWIGLU ? 32 : 16);   // epilogue warps of the pair
     *abort_flag = 0;
     ptx::fence_barrier_init();
     ptx::prefetch_tensormap(&maps.p);
     ptx::prefetch_tensormap(&maps.q);
     ptx::prefetch_tensormap(&maps.sfp);
     ptx::prefetch_tensormap(&maps.sfq);
-    ptx::prefetch_tensormap(&maps.d);
+    if (!SWIGLU) ptx::prefetch_tensormap(&maps.d);
   }
   if (GROUPED) {
     // tile i of this pair is global tile pair_id + i * num_pairs; its item is items[tile / p_tiles]
@@ -152,8 +164,13 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
           expert = item.expert;
         } else {
           tile_coords(t, p, pt, qt);
-          q_row = qt * BN + static_cast<int>(rank) * (BN / 2);
-          q_blk = (qt * BN) >> 7;
+          if (SWIGLU) {
+            q_row = qt * 128 + static_cast<int>(rank) * p.hidden;
+            q_blk = qt;
+          } else {
+            q_row = qt * BN + static_cast<int>(rank) * (BN / 2);
+            q_blk = (qt * BN) >> 7;
+          }
         }
         const int p_row = pt * 256 + static_cast<int>(rank) * 128;
         const int p_blk = p_row >> 7;
@@ -174,6 +191,9 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
           ptx::tma_load_2d_pair(st + L::A_BYTES, &maps.q, bar, ks * 128, q_row);
           ptx::tma_load_3d_pair(st + L::A_BYTES + L::B_BYTES + L::SFP_BYTES, &maps.sfq, bar, 0, ks * KT_PER_STAGE,
                                 q_blk);
+          if (SWIGLU)   // the map's box is one 128-row group: gate scales above, up scales here
+            ptx::tma_load_3d_pair(st + L::A_BYTES + L::B_BYTES + L::SFP_BYTES + KT_PER_STAGE * SF_TILE, &maps.sfq, bar,
+                                  0, ks * KT_PER_STAGE, (p.hidden >> 7) + q_blk);
           if (++s == STAGES) { s = 0; ph ^= 1u; }
         }
       }
@@ -218,7 +238,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
         } else {
           int pt, qt;
           tile_coords(t, p, pt, qt);
-          qoff = (static_cast<uint32_t>(qt * BN) & 127u) >> 5;
+          qoff = SWIGLU ? 0u : (static_cast<uint32_t>(qt * BN) & 127u) >> 5;
         }
         for (int ks = 0; ks < k_stages; ++ks) {
           if (!ptx::mbar_wait_bounded(&full[s], ph, WAIT_LIMIT)) {
@@ -312,6 +332,48 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
           if (leader) ptx::mbar_arrive(acc_free); else ptx::mbar_arrive_cluster(free_addr);
         }
       };
+      if constexpr (SWIGLU) {
+        // This warp's group of 32 outputs: gate chunk c, up chunk 4 + c.  The accumulators share
+        // the up chunks 2, 3 of accumulator 0 and the gate chunks 0, 1 of accumulator 1: the
+        // warps that read those release after their loads, the others when they start the tile.
+        const int c = ew >> 2;
+        const bool owner = a ? c < 2 : c >= 2;
+        uint32_t rg[32], ru[32];
+        if (!owner) release();
+        ptx::tc_ld_32x32b_x32(taddr + c * 32, rg);
+        ptx::tc_ld_32x32b_x32(taddr + (4 + c) * 32, ru);
+        ptx::tc_wait_ld(rg);
+        ptx::tc_wait_ld(ru);
+        if (owner) release();
+        if (tr && first_half) p.trace[tl * 8 + 4] = clock64();
+        const float* inv_table = inv_scale_table();
+        uint32_t pk[4];
+        uint32_t sfw = 0;
+#pragma unroll
+        for (int b = 0; b < 2; ++b) {
+          float v[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(rg[16 * b + j]) * alpha));
+            const float u = __bfloat162float(__float2bfloat16_rn(__uint_as_float(ru[16 * b + j]) * alpha));
+            v[j] = swiglu_bf16(g, u);
+          }
+          uint8_t sfb;
+          const uint2 o = quantize_block16<kEncHw>(v, sfb, inv_table);
+          pk[2 * b] = o.x;
+          pk[2 * b + 1] = o.y;
+          sfw |= static_cast<uint32_t>(sfb) << (8 * b);
+        }
+        if (prow < p.P && !(p.dbg & 1)) {
+          const int col = qt * 128 + 32 * c;                 // first of the 32 output columns
+          uint8_t* dst = p.out_packed + static_cast<int64_t>(prow) * (p.hidden >> 1) + (col >> 1);
+          *reinterpret_cast<uint4*>(dst) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          *reinterpret_cast<uint16_t*>(p.out_sf + sf_offset(prow, col >> 4, p.hidden >> 6)) =
+              static_cast<uint16_t>(sfw);
+        }
+        if (tr) p.trace[tl * 8 + (first_half ? 5 : 7)] = clock64();
+        continue;
+      }
       uint32_t r[2][32];
       // every warp vouches that it is done with tile tl-1; the warps that own the shared columns
       // of this tile only after those columns are in their registers

@@ -14,32 +14,6 @@ int g_opt_gemm_debug = 0;
 
 namespace {
 
-// 1 / float(b) for every UE4M3 scale byte b (bit patterns of the fp32 results of the IEEE
-// round-to-nearest division; b = 0 gives +inf).  One cached 4-byte load replaces the
-// byte -> half -> float conversion and the division in the quantiser.
-__device__ __align__(16) const uint32_t kInvScaleBits[128] = {
-    0x7f800000u, 0x44000000u, 0x43800000u, 0x432aaaabu, 0x43000000u, 0x42cccccdu, 0x42aaaaabu, 0x42924925u,
-    0x42800000u, 0x42638e39u, 0x424ccccdu, 0x423a2e8cu, 0x422aaaabu, 0x421d89d9u, 0x42124925u, 0x42088889u,
-    0x42000000u, 0x41e38e39u, 0x41cccccdu, 0x41ba2e8cu, 0x41aaaaabu, 0x419d89d9u, 0x41924925u, 0x41888889u,
-    0x41800000u, 0x41638e39u, 0x414ccccdu, 0x413a2e8cu, 0x412aaaabu, 0x411d89d9u, 0x41124925u, 0x41088889u,
-    0x41000000u, 0x40e38e39u, 0x40cccccdu, 0x40ba2e8cu, 0x40aaaaabu, 0x409d89d9u, 0x40924925u, 0x40888889u,
-    0x40800000u, 0x40638e39u, 0x404ccccdu, 0x403a2e8cu, 0x402aaaabu, 0x401d89d9u, 0x40124925u, 0x40088889u,
-    0x40000000u, 0x3fe38e39u, 0x3fcccccdu, 0x3fba2e8cu, 0x3faaaaabu, 0x3f9d89d9u, 0x3f924925u, 0x3f888889u,
-    0x3f800000u, 0x3f638e39u, 0x3f4ccccdu, 0x3f3a2e8cu, 0x3f2aaaabu, 0x3f1d89d9u, 0x3f124925u, 0x3f088889u,
-    0x3f000000u, 0x3ee38e39u, 0x3ecccccdu, 0x3eba2e8cu, 0x3eaaaaabu, 0x3e9d89d9u, 0x3e924925u, 0x3e888889u,
-    0x3e800000u, 0x3e638e39u, 0x3e4ccccdu, 0x3e3a2e8cu, 0x3e2aaaabu, 0x3e1d89d9u, 0x3e124925u, 0x3e088889u,
-    0x3e000000u, 0x3de38e39u, 0x3dcccccdu, 0x3dba2e8cu, 0x3daaaaabu, 0x3d9d89d9u, 0x3d924925u, 0x3d888889u,
-    0x3d800000u, 0x3d638e39u, 0x3d4ccccdu, 0x3d3a2e8cu, 0x3d2aaaabu, 0x3d1d89d9u, 0x3d124925u, 0x3d088889u,
-    0x3d000000u, 0x3ce38e39u, 0x3ccccccdu, 0x3cba2e8cu, 0x3caaaaabu, 0x3c9d89d9u, 0x3c924925u, 0x3c888889u,
-    0x3c800000u, 0x3c638e39u, 0x3c4ccccdu, 0x3c3a2e8cu, 0x3c2aaaabu, 0x3c1d89d9u, 0x3c124925u, 0x3c088889u,
-    0x3c000000u, 0x3be38e39u, 0x3bcccccdu, 0x3bba2e8cu, 0x3baaaaabu, 0x3b9d89d9u, 0x3b924925u, 0x3b888889u,
-    0x3b800000u, 0x3b638e39u, 0x3b4ccccdu, 0x3b3a2e8cu, 0x3b2aaaabu, 0x3b1d89d9u, 0x3b124925u, 0x3b088889u
-};
-
-__device__ __forceinline__ const float* inv_scale_table() {
-  return reinterpret_cast<const float*>(kInvScaleBits);
-}
-
 // ---------------------------------------------------------------------------
 // linear [rows, nb] -> swizzled.  One thread moves the 4 scale bytes of one
 // (row, 64-element group): a 4-byte read (or byte reads at a ragged edge) and
@@ -88,6 +62,35 @@ quantize_kernel(const uint4* __restrict__ src, uint2* __restrict__ packed, uint8
     unpack_bf16x8(r0, v);
     unpack_bf16x8(r1, v + 8);
   }
+  uint8_t sfb;
+  const uint2 out = quantize_block16<ENC>(v, sfb, inv_scale_table());
+  packed[idx] = out;
+  sf[sf_offset(row, kb, sf_cols)] = sfb;
+}
+
+// ---------------------------------------------------------------------------
+// SwiGLU -> NVFP4: merged = [gate | up] bf16 (rows, 2H); one thread per 16 outputs
+// (two 16-byte loads from each half, one 8-byte store).  Instruction-bound (an
+// exponential and a division per element): the GEMM epilogue form of the same
+// arithmetic (gemm_pair.cuh) is the fast path, this kernel the stand-alone op.
+// ---------------------------------------------------------------------------
+template <int ENC>
+__global__ void __launch_bounds__(256)
+silu_mul_quant_kernel(const uint4* __restrict__ merged, uint2* __restrict__ packed, uint8_t* __restrict__ sf,
+                      int rows, int nb, int sf_cols) {
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<int64_t>(rows) * nb) return;
+  const int row = static_cast<int>(idx / nb);
+  const int kb = static_cast<int>(idx - static_cast<int64_t>(row) * nb);
+  const uint4* g_src = merged + static_cast<int64_t>(row) * (4 * nb) + 2 * kb;
+  const uint4* u_src = g_src + 2 * nb;
+  float g[16], u[16], v[16];
+  unpack_bf16x8(__ldcs(g_src), g);
+  unpack_bf16x8(__ldcs(g_src + 1), g + 8);
+  unpack_bf16x8(__ldcs(u_src), u);
+  unpack_bf16x8(__ldcs(u_src + 1), u + 8);
+#pragma unroll
+  for (int j = 0; j < 16; ++j) v[j] = swiglu_bf16(g[j], u[j]);
   uint8_t sfb;
   const uint2 out = quantize_block16<ENC>(v, sfb, inv_scale_table());
   packed[idx] = out;
@@ -594,6 +597,23 @@ int frt_nvfp4_quantize(const void* src, int src_dtype, void* packed, void* sf, i
     if (chain) quantize_kernel<kEncChain, false><<<grid, block, 0, st>>>(s, pk, sfp, rows, nb, sf_cols);
     else quantize_kernel<kEncHw, false><<<grid, block, 0, st>>>(s, pk, sfp, rows, nb, sf_cols);
   }
+  return launch_result();
+}
+
+int frt_silu_mul_quant_nvfp4(const void* merged, void* packed, void* sf, int rows, int hidden, void* stream) {
+  if (!merged || !packed || !sf) return FRT_E_NULL;
+  if (rows <= 0 || hidden <= 0 || hidden % 16 != 0) return FRT_E_SHAPE;
+  if (!aligned(merged, 16) || !aligned(packed, 8)) return FRT_E_ALIGN;
+  const int nb = hidden / 16, sf_cols = (hidden + 63) / 64;
+  const int64_t total = static_cast<int64_t>(rows) * nb;
+  const dim3 block(256), grid(static_cast<unsigned>((total + 255) / 256));
+  auto m = static_cast<const uint4*>(merged);
+  auto pk = static_cast<uint2*>(packed);
+  auto sfp = static_cast<uint8_t*>(sf);
+  if (g_opt_quant_encoder == 1)
+    silu_mul_quant_kernel<kEncChain><<<grid, block, 0, as_stream(stream)>>>(m, pk, sfp, rows, nb, sf_cols);
+  else
+    silu_mul_quant_kernel<kEncHw><<<grid, block, 0, as_stream(stream)>>>(m, pk, sfp, rows, nb, sf_cols);
   return launch_result();
 }
 

@@ -62,6 +62,26 @@ def _dequantize_fake(packed, sfa, out) -> None:
     return None
 
 
+@torch.library.register_fake(add_op_namespace_prefix("silu_mul_quantize_fp4_sfa_bf16"))
+def _silu_mul_quantize_fake(merged, packed, sfa) -> None:
+    if merged.dim() != 2 or merged.shape[1] % 32 != 0:
+        raise RuntimeError("merged must have shape (rows, 2 * hidden), hidden divisible by 16")
+    rows, twice_hidden = merged.shape
+    if packed.shape != (rows, twice_hidden // 4) or sfa.dim() != 1:
+        raise RuntimeError("packed/SFA output shape contract failed")
+    return None
+
+
+def silu_mul_quantize_fp4_sfa_bf16(merged, *, packed=None, sfa=None):
+    """SiLU(gate) * up of ``merged = [gate | up]`` in fp32, rounded to bf16 and quantised to
+    NVFP4 (fp4-fused-ops/torch-ext/fp4_fused_ops/__init__.py:276-288)."""
+    rows, twice_hidden = merged.shape
+    if packed is None or sfa is None:
+        packed, sfa = _alloc_fp4(rows, twice_hidden // 2, merged.device)
+    ops.silu_mul_quantize_fp4_sfa_bf16(merged, packed, sfa)
+    return packed, sfa
+
+
 def rms_norm_quantize_fp4_sfa_bf16(x, weight, eps: float = 1e-6, *, normed=None, packed=None, sfa=None):
     """RMSNorm with residual-form weight ``1 + weight``; emits the bf16 `normed`
     tensor and its NVFP4 quantisation."""
@@ -114,4 +134,4 @@ def dequantize_fp4_sfa_fp16(packed, sfa, out=None):
 
 __all__ = ["sfa_size_bytes", "rms_norm_quantize_fp4_sfa_bf16", "residual_add_rms_norm_nvfp4_bf16",
            "residual_add_rms_norm_quant_nvfp4_swizzled_bf16", "residual_add_rms_norm_quant_nvfp4",
-           "dequantize_fp4_sfa_fp16"]
+           "dequantize_fp4_sfa_fp16", "silu_mul_quantize_fp4_sfa_bf16"]

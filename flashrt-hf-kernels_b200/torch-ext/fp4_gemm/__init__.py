@@ -126,6 +126,33 @@ def nvfp4_gemm_bf16(a_packed, b_packed, sfa, sfb, alpha: float = 1.0, out=None, 
     return out
 
 
+@torch.library.register_fake(add_op_namespace_prefix("nvfp4_gemm_swiglu_nvfp4_bf16"))
+def _gemm_swiglu_fake(a_packed, b_packed, sfa, sfb, out_packed, out_sfa, alpha=1.0) -> None:
+    if a_packed.dim() != 2 or b_packed.dim() != 2 or a_packed.shape[1] != b_packed.shape[1]:
+        raise RuntimeError("a_packed and b_packed must be matrices with the same packed K")
+    if b_packed.shape[0] % 256 != 0:
+        raise RuntimeError("stacked gate/up N must be divisible by 256")
+    if out_packed.shape != (a_packed.shape[0], b_packed.shape[0] // 4) or out_sfa.dim() != 1:
+        raise RuntimeError("out_packed must have shape (M, N / 4) and out_sfa must be flat")
+    return None
+
+
+def nvfp4_gemm_swiglu_nvfp4_bf16(a_packed, b_packed, sfa, sfb, alpha: float = 1.0, *, out_packed=None,
+                                 out_sfa=None):
+    """gate/up projection with the SwiGLU -> NVFP4 producer as the GEMM epilogue.
+
+    ``b_packed`` is the stacked ``[gate ; up]`` weight (2 * hidden rows).  Returns the NVFP4
+    tensor ``(out_packed [M, hidden / 2], out_sfa)`` that
+    ``silu_mul_quantize_fp4_sfa_bf16(nvfp4_gemm_bf16(a, b))`` would produce, bit for bit,
+    without writing the (M, 2 * hidden) bf16 intermediate.  Additive: the reference's
+    FP4-output epilogues (nvfp4_gemm_nvfp4, nvfp4_gemm_geglu_nvfp4_fp16,
+    fp4-gemm/torch-ext/fp4_gemm/__init__.py:591-620) are SM110-only and need a weight repack."""
+    if out_packed is None or out_sfa is None:
+        out_packed, out_sfa = _alloc_fp4(a_packed.shape[0], b_packed.shape[0] // 2, a_packed.device)
+    ops.nvfp4_gemm_swiglu_nvfp4_bf16(a_packed, b_packed, sfa, sfb, out_packed, out_sfa, float(alpha))
+    return out_packed, out_sfa
+
+
 def fp4_w4a16_linear_bf16(a_packed, b_packed, sfa, sfb, alpha: float = 1.0, out=None, variant: int = -1):
     """Compatibility alias for :func:`nvfp4_gemm_bf16`."""
     return nvfp4_gemm_bf16(a_packed, b_packed, sfa, sfb, alpha=alpha, out=out, variant=variant)
@@ -188,6 +215,7 @@ def pack_nvfp4_weight_bf16(weight: torch.Tensor, bias: Optional[torch.Tensor] = 
 
 
 __all__ = ["capabilities", "sfa_size_bytes", "quantize_fp4_sfa_fp16", "quantize_fp4_sfa_bf16",
-           "dequantize_fp4_sfa_fp16", "nvfp4_gemm_bf16", "fp4_w4a16_linear_bf16", "nvfp4_gemm_bias_bf16",
+           "dequantize_fp4_sfa_fp16", "nvfp4_gemm_bf16", "nvfp4_gemm_swiglu_nvfp4_bf16", "fp4_w4a16_linear_bf16",
+           "nvfp4_gemm_bias_bf16",
            "nvfp4_gemm_bias_residual_bf16", "nvfp4_gemm_residual_bf16", "fp4_w4a4_gemv_warpsplit_bf16",
            "fp4_w4a4_gemm_warpsplit_mrows_bf16", "pack_nvfp4_weight_bf16"]

@@ -166,6 +166,35 @@ void nvfp4_gemm_residual_bf16(const Tensor& a, const Tensor& b, const Tensor& sf
                               const Tensor& residual, Tensor& out, double alpha) {
   gemm_call(a, b, sfa, sfb, nullptr, &residual, out, alpha, "nvfp4_gemm_residual_bf16");
 }
+// gate/up GEMM with the SwiGLU -> NVFP4 producer as its epilogue (additive op): b_packed is the
+// stacked [gate ; up] weight (2 * hidden rows); the outputs describe a (M, hidden) NVFP4 tensor.
+void nvfp4_gemm_swiglu_nvfp4_bf16(const Tensor& a, const Tensor& b, const Tensor& sfa, const Tensor& sfb,
+                                  Tensor& out_packed, Tensor& out_sfa, double alpha) {
+  check_dtype(a, torch::kUInt8, "a_packed", "torch.uint8");
+  check_dtype(b, torch::kUInt8, "b_packed", "torch.uint8");
+  check_dtype(sfa, torch::kUInt8, "sfa", "torch.uint8");
+  check_dtype(sfb, torch::kUInt8, "sfb", "torch.uint8");
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2, "a_packed and b_packed must be matrices");
+  TORCH_CHECK(a.size(1) == b.size(1), "a_packed and b_packed must have the same packed K");
+  const int64_t m = a.size(0), n2 = b.size(0), k = a.size(1) * 2;
+  TORCH_CHECK(m > 0 && n2 > 0 && k > 0, "empty GEMM operand");
+  TORCH_CHECK(k % 32 == 0, "K must be divisible by 32 on this device (16-byte packed row pitch)");
+  TORCH_CHECK(n2 % 256 == 0, "stacked gate/up N must be divisible by 256 (hidden divisible by 128)");
+  const int64_t hidden = n2 / 2;
+  check_packed_scales(out_packed, out_sfa, m, hidden, "out_packed", "out_sfa");
+  const int mi = as_int(m, "M"), ni = as_int(n2, "N"), ki = as_int(k, "K");
+  TORCH_CHECK(sfa.numel() >= frt_nvfp4_sf_swizzled_bytes(mi, ki), "sfa is smaller than the swizzled buffer for (M, K)");
+  TORCH_CHECK(sfb.numel() >= frt_nvfp4_sf_swizzled_bytes(ni, ki), "sfb is smaller than the swizzled buffer for (N, K)");
+  check_same_device(a, b, "a_packed", "b_packed");
+  check_same_device(a, sfa, "a_packed", "sfa");
+  check_same_device(a, sfb, "a_packed", "sfb");
+  check_same_device(a, out_packed, "a_packed", "out_packed");
+  check_same_device(a, out_sfa, "a_packed", "out_sfa");
+  c10::cuda::CUDAGuard guard(a.device());
+  check_rc(frt_nvfp4_gemm_swiglu_nvfp4(a.data_ptr(), sfa.data_ptr(), b.data_ptr(), sfb.data_ptr(),
+                                       out_packed.data_ptr(), out_sfa.data_ptr(), mi, ni, ki,
+                                       static_cast<float>(alpha), stream_of(a)), "nvfp4_gemm_swiglu_nvfp4_bf16");
+}
 // Small-M entry points of the reference (SM120 warp-split kernels): same
 // contraction; `warps` / `stages` tuned those kernels and are accepted and ignored.
 void fp4_w4a4_gemv_warpsplit_bf16(const Tensor& a, const Tensor& b, const Tensor& sfa, const Tensor& sfb, Tensor& out,
@@ -242,6 +271,19 @@ void residual_add_rms_norm_nvfp4_bf16(Tensor& residual, const Tensor& x, const c
   producer_call(&residual, x, w, eps, 1.0, nullptr, packed, sfa,
                 FRT_PRODUCER_RNE_E2M1 | FRT_PRODUCER_ROUND_BF16 | FRT_PRODUCER_NORM_FROM_BF16_RESIDUAL,
                 "residual_add_rms_norm_nvfp4_bf16");
+}
+void silu_mul_quantize_fp4_sfa_bf16(const Tensor& merged, Tensor& packed, Tensor& sfa) {
+  check_dtype(merged, torch::kBFloat16, "merged", "torch.bfloat16");
+  TORCH_CHECK(merged.dim() == 2, "merged must have shape (rows, 2 * hidden)");
+  TORCH_CHECK(merged.size(0) > 0, "rows must be positive");
+  TORCH_CHECK(merged.size(1) % 32 == 0, "merged.shape[1] must be divisible by 32");
+  const int64_t rows = merged.size(0), hidden = merged.size(1) / 2;
+  check_packed_scales(packed, sfa, rows, hidden, "packed", "sfa");
+  check_same_device(merged, packed, "merged", "packed");
+  check_same_device(merged, sfa, "merged", "sfa");
+  c10::cuda::CUDAGuard guard(merged.device());
+  check_rc(frt_silu_mul_quant_nvfp4(merged.data_ptr(), packed.data_ptr(), sfa.data_ptr(), as_int(rows, "rows"),
+                                    as_int(hidden, "hidden"), stream_of(merged)), "silu_mul_quantize_fp4_sfa_bf16");
 }
 // Additive op: the reference recipe plus an optional second-level (per-tensor)
 // scale and an optional bf16 copy of the quantiser input.
@@ -354,6 +396,8 @@ TORCH_LIBRARY_EXPAND(fp4_gemm_b200, ops) {
   ops.def("quantize_fp4_sfa_fp16(Tensor x, Tensor! packed, Tensor! sfa, bool is_sfb=False) -> ()");
   ops.def("quantize_fp4_sfa_bf16(Tensor x, Tensor! packed, Tensor! sfa, bool is_sfb=False) -> ()");
   ops.def("dequantize_fp4_sfa_fp16(Tensor packed, Tensor sfa, Tensor! out, bool is_sfb=False) -> ()");
+  ops.def("nvfp4_gemm_swiglu_nvfp4_bf16(Tensor a_packed, Tensor b_packed, Tensor sfa, Tensor sfb, Tensor! out_packed, Tensor! out_sfa, float alpha=1.0) -> ()");
+  ops.impl("nvfp4_gemm_swiglu_nvfp4_bf16", torch::kCUDA, &nvfp4_gemm_swiglu_nvfp4_bf16);
   ops.impl("nvfp4_gemm_bf16", torch::kCUDA, &nvfp4_gemm_bf16);
   ops.impl("fp4_w4a16_linear_bf16", torch::kCUDA, &nvfp4_gemm_bf16);
   ops.impl("nvfp4_gemm_bias_bf16", torch::kCUDA, &nvfp4_gemm_bias_bf16);
@@ -373,6 +417,8 @@ TORCH_LIBRARY_EXPAND(fp4_fused_ops_b200, ops) {
   ops.def("residual_add_rms_norm_quant_nvfp4_swizzled_bf16(Tensor! residual, Tensor x, Tensor weight, float eps, Tensor! packed, Tensor! sfa) -> ()");
   ops.def("residual_add_rms_norm_quant_nvfp4_ex(Tensor! residual, Tensor x, Tensor weight, float eps, float inv_global_scale, Tensor!? normed, Tensor! packed, Tensor! sfa) -> ()");
   ops.def("dequantize_fp4_sfa_fp16(Tensor packed, Tensor sfa, Tensor! out) -> ()");
+  ops.def("silu_mul_quantize_fp4_sfa_bf16(Tensor merged, Tensor! packed, Tensor! sfa) -> ()");
+  ops.impl("silu_mul_quantize_fp4_sfa_bf16", torch::kCUDA, &silu_mul_quantize_fp4_sfa_bf16);
   ops.impl("sfa_size_bytes_for", torch::kCUDA, &sfa_size_bytes_for);
   ops.impl("rms_norm_quantize_fp4_sfa_bf16", torch::kCUDA, &rms_norm_quantize_fp4_sfa_bf16);
   ops.impl("residual_add_rms_norm_nvfp4_bf16", torch::kCUDA, &residual_add_rms_norm_nvfp4_bf16);

@@ -121,6 +121,28 @@ int frt_nvfp4_gemm_bf16(const void* a_packed, const void* sfa, const void* b_pac
                         const void* bias, const void* c, void* d,
                         int M, int N, int K, float alpha, float beta, void* stream);
 
+/* ---- SwiGLU -> NVFP4 (the step between the two FFN GEMMs) -----------------
+ * merged [rows, 2*hidden] bf16 = [gate | up] (16-byte aligned, hidden % 16 == 0) ->
+ * packed [rows, hidden/2] + swizzled scales of v = bf16((g / (1 + exp(-g))) * u)
+ * (fp32 arithmetic, accurate expf, IEEE division), rule-A quantised as frt_nvfp4_quantize.
+ * replaces silu_mul_quantize_fp4_sfa_bf16,
+ *   fp4-fused-ops/csrc/kernels/silu_mul_quantize_fp4_sfa_bf16.cuh:18 */
+int frt_silu_mul_quant_nvfp4(const void* merged, void* packed, void* sf_swizzled,
+                             int rows, int hidden, void* stream);
+
+/* The same producer as the epilogue of the gate/up GEMM: B is the [gate ; up] weight
+ * [N2 = 2*hidden, K/2] (gate rows first), and the result is exactly
+ *   frt_silu_mul_quant_nvfp4(frt_nvfp4_gemm_bf16(A, B, alpha))
+ * without the [M, 2*hidden] bf16 intermediate ever reaching memory.
+ * hidden % 128 == 0, K % 32 == 0, out_packed 16-byte aligned.
+ * No single reference entry point does this for SwiGLU/bf16; the nearest are the FP4-out
+ * epilogues nvfp4_gemm_nvfp4 and nvfp4_gemm_geglu_nvfp4_fp16
+ * (fp4-gemm/torch-ext/torch_binding.cpp:579-657), which need an interleaved weight repack and
+ * a scratch buffer; this one takes the plain stacked weight and no scratch. */
+int frt_nvfp4_gemm_swiglu_nvfp4(const void* a_packed, const void* sfa, const void* b_packed, const void* sfb,
+                                void* out_packed, void* out_sf_swizzled,
+                                int M, int N2, int K, float alpha, void* stream);
+
 /* ---- grouped (MoE) NVFP4 GEMM, bf16 out ---------------------------------
  * Rows of `a_packed` [rows, K/2] are expert-sorted; their scales are one
  * swizzled buffer over all rows (indexed by global row).  Expert e owns the

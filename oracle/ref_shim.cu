@@ -13,6 +13,7 @@
 #include "nvfp4_sf_reshape_sm120.cuh"           // flashrt-nvfp4/csrc
 #include "residual_norm_quant.cuh"              // flashrt-residual-norm-quant/csrc
 #include "kernels/rms_norm_quantize_fp4_sfa_bf16.cuh"   // fp4-fused-ops/csrc
+#include "kernels/silu_mul_quantize_fp4_sfa_bf16.cuh"   // fp4-fused-ops/csrc
 #ifdef REF_HAVE_CUTLASS
 #define FLASHRT_HAVE_COSMOS3_EDGE 1
 #include "fused_fp4/cosmos3_edge_fp4.cuh"       // fp4-fused-ops/csrc
@@ -66,6 +67,11 @@ int ref_residual_add_rms_norm_bf16(void* res, const void* x, const void* w, void
 int ref_rms_norm_quantize_bf16(const void* x, const void* w, float eps, void* normed, void* packed, void* sfa,
                                int rows, int dim, void* st) {
   return flash_rt::fp4::rms_norm_quantize_fp4_sfa_bf16(x, w, eps, normed, packed, sfa, rows, dim, S(st));
+}
+
+// SwiGLU -> NVFP4 producer ([gate | up] bf16 (rows, 2H) -> packed + swizzled scales)
+int ref_silu_mul_quantize_bf16(const void* merged, void* packed, void* sfa, int rows, int hidden, void* st) {
+  return flash_rt::fp4::silu_mul_quantize_fp4_sfa_bf16(merged, packed, sfa, rows, hidden, S(st));
 }
 
 #ifdef REF_HAVE_CUTLASS

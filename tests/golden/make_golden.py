@@ -143,6 +143,18 @@ def main():
     norm = dict(x=bf16_bits(x), res=bf16_bits(res), w=bf16_bits(w), eps=np.float32(eps),
                 y=bf16_bits(y), res_out=bf16_bits(res_out), y_res=bf16_bits(y_res))
     np.savez_compressed(HERE / "rms_norm.npz", **norm)
+    # ---- 6. SwiGLU -> NVFP4 producer: the staged value of the reference's production-chain
+    # check (test_fp4_fused_ops.py:483-495: silu(gate.float()) * up.float() -> bf16), on CPU
+    # tensors drawn as the test draws them (randn * 0.2 -> bf16); the quantiser that follows
+    # it in that check is pinned by section 2.
+    swiglu = {}
+    for rows, hidden, seed in [(1, 1024, 2026081701), (7, 1024, 2026081707), (257, 1024, 2026081957)]:
+        g = torch.Generator().manual_seed(seed)
+        merged = (torch.randn(rows, 2 * hidden, generator=g) * 0.2).to(torch.bfloat16)
+        staged = (torch.nn.functional.silu(merged[:, :hidden].float()) * merged[:, hidden:].float()).bfloat16()
+        swiglu[f"merged_{rows}"] = bf16_bits(merged)
+        swiglu[f"staged_{rows}"] = bf16_bits(staged)
+    np.savez_compressed(HERE / "swiglu.npz", **swiglu)
     print("wrote", sorted(p.name for p in HERE.glob("*.npz")))
 
 

@@ -150,3 +150,22 @@ def test_fused_default_is_quantizer_of_its_own_norm():
     # rstd agrees with a float64 evaluation to fp32 rounding noise
     want = 1 / np.sqrt((a.astype(np.float64) ** 2).mean(axis=1) + 1e-6)
     assert np.max(np.abs(out["rstd"] / want - 1)) < 1e-6
+
+
+@pytest.mark.parametrize("rows", [1, 7, 257])
+def test_swiglu_stage_matches_reference_chain(golden_dir, rows):
+    # the staged value of the reference's production-chain check
+    # (fp4-fused-ops/tests/test_fp4_fused_ops.py:483-495)
+    g = load(golden_dir, "swiglu.npz")
+    merged, staged = g[f"merged_{rows}"], g[f"staged_{rows}"]
+    out = O.silu_mul_quantize(merged)
+    np.testing.assert_array_equal(out["staged"], staged)
+    # and the quantiser stage is the rule-A quantiser of those values
+    packed, sf = O.quantize_nvfp4(O.bf16_bits_to_f32(staged))
+    np.testing.assert_array_equal(out["packed"], packed)
+    np.testing.assert_array_equal(out["sf_linear"], sf)
+    # an explicit fp32 evaluation of g / (1 + exp(-g)) * u agrees up to the exponential's last place
+    gate = O.bf16_bits_to_f32(merged[:, : merged.shape[1] // 2])
+    up = O.bf16_bits_to_f32(merged[:, merged.shape[1] // 2:])
+    direct = O.f32_to_bf16_bits((gate / (np.float32(1) + np.exp(-gate, dtype=np.float32))) * up)
+    assert (direct != staged).mean() < 2e-3
