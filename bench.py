@@ -352,6 +352,42 @@ def run_ours(args, rank, world, local_rank):
                      "bus_gbs": round(tot * (world - 1) / world / (ag_ms * 1e-3) / 1e9, 1), "backend": "nccl"}
         del gathered
 
+    # ---- the FFN as a connected chain: gate/up GEMM -> SwiGLU -> NVFP4 -> down GEMM ------
+    # (not part of `value`: in the timed step above the down GEMM reads a resident NVFP4 input)
+    names = [g_["name"] for g_ in layer.gemms]
+    if world == 1 and "gate_up" in names and "down" in names:
+        gu, dn = layer.gemms[names.index("gate_up")], layer.gemms[names.index("down")]
+        Lc, Pc = capi.lib(), capi.ptr
+        hid = gu["n_loc"] // 2
+        if dn["k"] == hid and hid % 128 == 0:
+            def plain():
+                Lc.frt_nvfp4_gemm_bf16(Pc(gu["a_p"]), Pc(gu["a_sf"]), Pc(gu["wp"]), Pc(gu["wsf"]), None, None,
+                                       Pc(gu["out"]), layer.M, gu["n_loc"], gu["k"], 1.0, 0.0, st)
+                Lc.frt_silu_mul_quant_nvfp4(Pc(gu["out"]), Pc(dn["a_p"]), Pc(dn["a_sf"]), layer.M, hid, st)
+                Lc.frt_nvfp4_gemm_bf16(Pc(dn["a_p"]), Pc(dn["a_sf"]), Pc(dn["wp"]), Pc(dn["wsf"]), None, None,
+                                       Pc(dn["out"]), layer.M, dn["n_loc"], dn["k"], 1.0, 0.0, st)
+
+            def fused():
+                Lc.frt_nvfp4_gemm_swiglu_nvfp4(Pc(gu["a_p"]), Pc(gu["a_sf"]), Pc(gu["wp"]), Pc(gu["wsf"]),
+                                               Pc(dn["a_p"]), Pc(dn["a_sf"]), layer.M, gu["n_loc"], gu["k"], 1.0, st)
+                Lc.frt_nvfp4_gemm_bf16(Pc(dn["a_p"]), Pc(dn["a_sf"]), Pc(dn["wp"]), Pc(dn["wsf"]), None, None,
+                                       Pc(dn["out"]), layer.M, dn["n_loc"], dn["k"], 1.0, 0.0, st)
+
+            chain = {}
+            n_it = max(5, min(50, args.steps))
+            for label, fn in (("three_kernels_us", plain), ("swiglu_in_gemm_epilogue_us", fused)):
+                for _ in range(3):
+                    fn()
+                torch.cuda.synchronize()
+                c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                c0.record()
+                for _ in range(n_it):
+                    fn()
+                c1.record()
+                torch.cuda.synchronize()
+                chain[label] = round(c0.elapsed_time(c1) / n_it * 1e3, 1)
+            detail["ffn_chain"] = chain
+
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cpu_baseline = run_cpu_port(args, steps=1, sample_rows=32)
