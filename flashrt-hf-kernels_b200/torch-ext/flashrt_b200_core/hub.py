@@ -25,6 +25,7 @@ _REPOS = {
     "flashrt/flashrt-nvfp4": "flashrt_nvfp4",
     "flashrt/flashrt-residual-norm-quant": "flashrt_residual_norm_quant",
     "flashrt/grouped-moe-gemm": "grouped_moe_gemm",
+    "flashrt/transformer-fused-ops": "transformer_fused_ops",
 }
 
 

@@ -74,4 +74,48 @@ def grouped_nvfp4_gemm_bf16_offsets(input, weight, input_scale, weight_scale, al
     return out
 
 
-__all__ = ["grouped_nvfp4_gemm_bf16", "grouped_nvfp4_gemm_bf16_offsets", "grouped_workspace"]
+@torch.library.register_fake(add_op_namespace_prefix("moe_route_plan"))
+def _route_plan_fake(topk_idx, n_experts, expert_offsets, row_of_pair, token_of_row) -> None:
+    if topk_idx.dim() != 2 or expert_offsets.numel() != n_experts + 1:
+        raise RuntimeError("topk_idx must be (tokens, topk) and expert_offsets must have n_experts + 1 elements")
+    return None
+
+
+@torch.library.register_fake(add_op_namespace_prefix("moe_gather_nvfp4"))
+def _gather_fake(packed, sfa, token_of_row, out_packed, out_sfa) -> None:
+    if packed.dim() != 2 or out_packed.dim() != 2 or packed.shape[1] != out_packed.shape[1]:
+        raise RuntimeError("packed and out_packed must be matrices with the same packed K")
+    return None
+
+
+def moe_route_plan(topk_idx, n_experts: int, *, expert_offsets=None, row_of_pair=None, token_of_row=None):
+    """Stable sort of the (token, slot) routing pairs by expert, on the device.
+
+    Returns ``(expert_offsets [n_experts + 1], row_of_pair [tokens, topk], token_of_row [tokens * topk])``:
+    the offsets drive :func:`grouped_nvfp4_gemm_bf16_offsets`, ``token_of_row`` the gather into
+    expert order, ``row_of_pair`` the weighted un-permute.  (The reference leaves this stage to
+    the caller: grouped-moe-gemm/README.md:13-16.)"""
+    dev = topk_idx.device
+    n = topk_idx.numel()
+    if expert_offsets is None:
+        expert_offsets = torch.empty((n_experts + 1,), device=dev, dtype=torch.int32)
+    if row_of_pair is None:
+        row_of_pair = torch.empty(tuple(topk_idx.shape), device=dev, dtype=torch.int32)
+    if token_of_row is None:
+        token_of_row = torch.empty((n,), device=dev, dtype=torch.int32)
+    ops.moe_route_plan(topk_idx, int(n_experts), expert_offsets, row_of_pair, token_of_row)
+    return expert_offsets, row_of_pair, token_of_row
+
+
+def moe_gather_nvfp4(packed, sfa, token_of_row, *, out_packed=None, out_sfa=None):
+    """NVFP4 rows (packed + swizzled scales) gathered into expert-sorted order."""
+    from flashrt_b200_core import alloc_fp4
+    rows = token_of_row.numel()
+    if out_packed is None or out_sfa is None:
+        out_packed, out_sfa = alloc_fp4(rows, packed.shape[1] * 2, packed.device)
+    ops.moe_gather_nvfp4(packed, sfa, token_of_row, out_packed, out_sfa)
+    return out_packed, out_sfa
+
+
+__all__ = ["grouped_nvfp4_gemm_bf16", "grouped_nvfp4_gemm_bf16_offsets", "grouped_workspace", "moe_route_plan",
+           "moe_gather_nvfp4"]

@@ -10,6 +10,7 @@
 //   flashrt_nvfp4          flashrt-nvfp4/torch-ext/torch_binding.cpp:73-82
 //   flashrt_residual_norm_quant  flashrt-residual-norm-quant/torch-ext/torch_binding.cpp:228-250
 //   grouped_moe_gemm       grouped-moe-gemm/torch-ext/torch_binding.cpp:84-93
+//   transformer_fused_ops  transformer-fused-ops/torch-ext/torch_binding.cpp:735-737 (router, weighted sum only)
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/all.h>
@@ -371,7 +372,97 @@ int64_t grouped_nvfp4_gemm_workspace_size(int64_t rows, int64_t experts) {
   return frt_nvfp4_grouped_gemm_workspace_bytes(as_int(rows, "rows"), as_int(experts, "experts"));
 }
 
+// ------------------------------------------------------------------ MoE routing glue
+// logits (n_experts,) as in the reference, or (tokens, n_experts); outputs (k,) / (tokens, k)
+void router_topk_bf16(const Tensor& logits, Tensor& out_idx, Tensor& out_val, int64_t k) {
+  check_dtype(logits, torch::kBFloat16, "logits", "torch.bfloat16");
+  check_dtype(out_idx, torch::kInt32, "out_idx", "torch.int32");
+  check_dtype(out_val, torch::kFloat32, "out_val", "torch.float32");
+  TORCH_CHECK(logits.dim() == 1 || logits.dim() == 2, "logits must have shape (n_experts,) or (tokens, n_experts)");
+  const int64_t tokens = logits.dim() == 1 ? 1 : logits.size(0), n = logits.size(-1);
+  if (logits.dim() == 1) {
+    TORCH_CHECK(out_idx.sizes() == torch::IntArrayRef({k}) && out_val.sizes() == torch::IntArrayRef({k}),
+                "topk outputs must have shape (k,)");
+  } else {
+    TORCH_CHECK(out_idx.sizes() == torch::IntArrayRef({tokens, k}) && out_val.sizes() == torch::IntArrayRef({tokens, k}),
+                "topk outputs must have shape (tokens, k)");
+  }
+  check_same_device(logits, out_idx, "logits", "out_idx");
+  check_same_device(logits, out_val, "logits", "out_val");
+  c10::cuda::CUDAGuard guard(logits.device());
+  check_rc(frt_router_topk_bf16(logits.data_ptr(), out_idx.data_ptr(), out_val.data_ptr(), as_int(tokens, "tokens"),
+                                as_int(n, "n_experts"), as_int(k, "k"), stream_of(logits)), "router_topk_bf16");
+}
+void moe_weighted_sum_bf16_to_fp32(const Tensor& expert_output, const Tensor& row_indices, const Tensor& router_weight,
+                                   Tensor& out) {
+  check_dtype(expert_output, torch::kBFloat16, "expert_output", "torch.bfloat16");
+  check_dtype(row_indices, torch::kInt32, "row_indices", "torch.int32");
+  check_dtype(router_weight, torch::kFloat32, "router_weight", "torch.float32");
+  check_dtype(out, torch::kFloat32, "out", "torch.float32");
+  TORCH_CHECK(expert_output.dim() == 2, "expert_output must have shape (routed_rows, stride)");
+  TORCH_CHECK(row_indices.dim() == 2 && router_weight.sizes() == row_indices.sizes(),
+              "row_indices and router_weight must have shape (tokens, topk)");
+  TORCH_CHECK(out.dim() == 2 && out.size(0) == row_indices.size(0), "out must have shape (tokens, hidden)");
+  TORCH_CHECK(expert_output.size(1) >= out.size(1), "expert_output stride must cover out hidden size");
+  check_same_device(expert_output, row_indices, "expert_output", "row_indices");
+  check_same_device(expert_output, router_weight, "expert_output", "router_weight");
+  check_same_device(expert_output, out, "expert_output", "out");
+  c10::cuda::CUDAGuard guard(expert_output.device());
+  check_rc(frt_moe_weighted_sum_bf16(expert_output.data_ptr(), row_indices.data_ptr(), router_weight.data_ptr(),
+                                     out.data_ptr(), as_int(row_indices.size(0), "tokens"),
+                                     as_int(row_indices.size(1), "topk"), as_int(out.size(1), "hidden"),
+                                     as_int(expert_output.size(1), "expert_output stride"), stream_of(expert_output)),
+           "moe_weighted_sum_bf16_to_fp32");
+}
+// additive: the routing sort and the gather into expert order that the reference leaves to the caller
+void moe_route_plan(const Tensor& topk_idx, int64_t n_experts, Tensor& expert_offsets, Tensor& row_of_pair,
+                    Tensor& token_of_row) {
+  check_dtype(topk_idx, torch::kInt32, "topk_idx", "torch.int32");
+  check_dtype(expert_offsets, torch::kInt32, "expert_offsets", "torch.int32");
+  check_dtype(row_of_pair, torch::kInt32, "row_of_pair", "torch.int32");
+  check_dtype(token_of_row, torch::kInt32, "token_of_row", "torch.int32");
+  TORCH_CHECK(topk_idx.dim() == 2, "topk_idx must have shape (tokens, topk)");
+  TORCH_CHECK(n_experts > 0 && expert_offsets.numel() == n_experts + 1, "expert_offsets must have n_experts + 1 elements");
+  TORCH_CHECK(row_of_pair.numel() == topk_idx.numel() && token_of_row.numel() == topk_idx.numel(),
+              "row_of_pair and token_of_row must have tokens * topk elements");
+  check_same_device(topk_idx, expert_offsets, "topk_idx", "expert_offsets");
+  check_same_device(topk_idx, row_of_pair, "topk_idx", "row_of_pair");
+  check_same_device(topk_idx, token_of_row, "topk_idx", "token_of_row");
+  c10::cuda::CUDAGuard guard(topk_idx.device());
+  check_rc(frt_moe_route_plan(topk_idx.data_ptr(), as_int(topk_idx.size(0), "tokens"), as_int(topk_idx.size(1), "topk"),
+                              as_int(n_experts, "n_experts"), expert_offsets.data_ptr(), row_of_pair.data_ptr(),
+                              token_of_row.data_ptr(), stream_of(topk_idx)), "moe_route_plan");
+}
+void moe_gather_nvfp4(const Tensor& packed, const Tensor& sfa, const Tensor& token_of_row, Tensor& out_packed,
+                      Tensor& out_sfa) {
+  check_dtype(token_of_row, torch::kInt32, "token_of_row", "torch.int32");
+  TORCH_CHECK(packed.dim() == 2 && out_packed.dim() == 2 && packed.size(1) == out_packed.size(1),
+              "packed and out_packed must be matrices with the same packed K");
+  const int64_t tokens = packed.size(0), rows = out_packed.size(0), K = packed.size(1) * 2;
+  TORCH_CHECK(K % 64 == 0, "K must be divisible by 64");
+  TORCH_CHECK(token_of_row.numel() >= rows, "token_of_row must have one entry per output row");
+  check_packed_scales(packed, sfa, tokens, K, "packed", "sfa");
+  check_packed_scales(out_packed, out_sfa, rows, K, "out_packed", "out_sfa");
+  check_same_device(packed, sfa, "packed", "sfa");
+  check_same_device(packed, token_of_row, "packed", "token_of_row");
+  check_same_device(packed, out_packed, "packed", "out_packed");
+  check_same_device(packed, out_sfa, "packed", "out_sfa");
+  c10::cuda::CUDAGuard guard(packed.device());
+  check_rc(frt_moe_gather_nvfp4(packed.data_ptr(), sfa.data_ptr(), token_of_row.data_ptr(), out_packed.data_ptr(),
+                                out_sfa.data_ptr(), as_int(rows, "rows"), as_int(tokens, "tokens"), as_int(K, "K"),
+                                stream_of(packed)), "moe_gather_nvfp4");
+}
+
 }  // namespace
+
+TORCH_LIBRARY_EXPAND(transformer_fused_ops_b200, ops) {
+  ops.def("nexn2_router_topk_bf16(Tensor logits, Tensor! out_idx, Tensor! out_val, int k) -> ()");
+  ops.def("router_topk_bf16(Tensor logits, Tensor! out_idx, Tensor! out_val, int k) -> ()");
+  ops.def("moe_weighted_sum_bf16_to_fp32(Tensor expert_output, Tensor row_indices, Tensor router_weight, Tensor! out) -> ()");
+  ops.impl("nexn2_router_topk_bf16", torch::kCUDA, &router_topk_bf16);
+  ops.impl("router_topk_bf16", torch::kCUDA, &router_topk_bf16);
+  ops.impl("moe_weighted_sum_bf16_to_fp32", torch::kCUDA, &moe_weighted_sum_bf16_to_fp32);
+}
 
 TORCH_LIBRARY_EXPAND(flashrt_nvfp4_b200, ops) {
   ops.def("nvfp4_sf_linear_to_swizzled(Tensor scales, Tensor! out, int D, bool is_sfb=False) -> ()");
@@ -435,6 +526,10 @@ TORCH_LIBRARY_EXPAND(grouped_moe_gemm_b200, ops) {
   ops.impl("grouped_nvfp4_gemm_bf16_out", torch::kCUDA, &grouped_nvfp4_gemm_bf16_legacy);
   ops.impl("grouped_nvfp4_gemm_bf16_offsets_out", torch::kCUDA, &grouped_nvfp4_gemm_bf16_offsets_out);
   ops.impl("grouped_nvfp4_gemm_workspace_size", &grouped_nvfp4_gemm_workspace_size);
+  ops.def("moe_route_plan(Tensor topk_idx, int n_experts, Tensor! expert_offsets, Tensor! row_of_pair, Tensor! token_of_row) -> ()");
+  ops.def("moe_gather_nvfp4(Tensor packed, Tensor sfa, Tensor token_of_row, Tensor! out_packed, Tensor! out_sfa) -> ()");
+  ops.impl("moe_route_plan", torch::kCUDA, &moe_route_plan);
+  ops.impl("moe_gather_nvfp4", torch::kCUDA, &moe_gather_nvfp4);
 }
 
 REGISTER_EXTENSION(TORCH_EXTENSION_NAME)

@@ -190,6 +190,39 @@ int frt_nvfp4_grouped_gemm_bf16_noalloc(const void* a_packed, const void* sfa,
                                         void* out, int rows, int N, int K, int num_experts,
                                         int64_t b_stride, int64_t sfb_stride, void* stream);
 
+/* ---- MoE routing glue (the stages around the grouped GEMM) -----------------
+ * Exact top-k of bf16 router logits [tokens, n_experts] -> out_idx i32 [tokens, k] and
+ * out_val f32 [tokens, k] (the logits, descending; equal logits in the order the reference's
+ * block reduction yields: bit-reversed low 8 index bits, then index; the caller softmaxes
+ * the k values).  n_experts <= 1024, k <= 32.
+ * replaces nexn2_router_topk_bf16 (one token),
+ *   transformer-fused-ops/csrc/kernels/nexn2_router_topk.cuh:18 */
+int frt_router_topk_bf16(const void* logits, void* out_idx, void* out_val,
+                         int tokens, int n_experts, int k, void* stream);
+
+/* Routing plan = stable sort of the (token, slot) pairs by expert, on the device:
+ *   expert_offsets i32 [n_experts + 1]  rows of expert e are [offsets[e], offsets[e+1])
+ *   row_of_pair    i32 [tokens * k]     expert-sorted row of pair (t, j); -1 if its index is
+ *                                       outside [0, n_experts)
+ *   token_of_row   i32 [tokens * k]     source token of each expert-sorted row
+ * The reference leaves this stage to the caller ("stable routing sort, expert-tile packing
+ * ... remain explicit structure-level stages", grouped-moe-gemm/README.md:13-16). */
+int frt_moe_route_plan(const void* topk_idx, int tokens, int k, int n_experts,
+                       void* expert_offsets, void* row_of_pair, void* token_of_row, void* stream);
+
+/* Gather NVFP4 rows (packed [tokens, K/2] + swizzled scales) into expert-sorted order:
+ * out row r = in row token_of_row[r].  K % 64 == 0.  Same README passage. */
+int frt_moe_gather_nvfp4(const void* packed_in, const void* sf_in, const void* token_of_row,
+                         void* packed_out, void* sf_out, int rows, int tokens, int K, void* stream);
+
+/* Weighted un-permute: out f32 [tokens, hidden] = sum_j weights[t, j] * expert_out[row[t, j], :hidden]
+ * (bf16 rows of pitch `stride` elements), one fused multiply-add per slot in slot order,
+ * negative rows skipped.
+ * replaces moe_weighted_sum_sm120_bf16,
+ *   transformer-fused-ops/csrc/kernels/moe_weighted_sum_sm120.cuh:20 */
+int frt_moe_weighted_sum_bf16(const void* expert_out, const void* row_of_pair, const void* weights,
+                              void* out, int tokens, int k, int hidden, int stride, void* stream);
+
 /* ---- status / tuning -----------------------------------------------------
  * Device-side waits are bounded; a wait that runs out records a code in a
  * per-device status word and the kernel returns.  This call copies the word to

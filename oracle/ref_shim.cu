@@ -14,6 +14,8 @@
 #include "residual_norm_quant.cuh"              // flashrt-residual-norm-quant/csrc
 #include "kernels/rms_norm_quantize_fp4_sfa_bf16.cuh"   // fp4-fused-ops/csrc
 #include "kernels/silu_mul_quantize_fp4_sfa_bf16.cuh"   // fp4-fused-ops/csrc
+#include "kernels/nexn2_router_topk.cuh"               // transformer-fused-ops/csrc
+#include "kernels/moe_weighted_sum_sm120.cuh"          // transformer-fused-ops/csrc
 #ifdef REF_HAVE_CUTLASS
 #define FLASHRT_HAVE_COSMOS3_EDGE 1
 #include "fused_fp4/cosmos3_edge_fp4.cuh"       // fp4-fused-ops/csrc
@@ -72,6 +74,15 @@ int ref_rms_norm_quantize_bf16(const void* x, const void* w, float eps, void* no
 // SwiGLU -> NVFP4 producer ([gate | up] bf16 (rows, 2H) -> packed + swizzled scales)
 int ref_silu_mul_quantize_bf16(const void* merged, void* packed, void* sfa, int rows, int hidden, void* st) {
   return flash_rt::fp4::silu_mul_quantize_fp4_sfa_bf16(merged, packed, sfa, rows, hidden, S(st));
+}
+
+// MoE routing glue of transformer-fused-ops: one-row top-k router, weighted un-permute
+int ref_router_topk_bf16(const void* logits, void* idx, void* val, int n_experts, int k, void* st) {
+  return flash_rt::kernels::nexn2_router_topk_bf16(logits, idx, val, n_experts, k, S(st));
+}
+int ref_moe_weighted_sum_bf16(const void* y, const void* rows, const void* w, void* out, int tokens, int topk,
+                              int hidden, int stride, void* st) {
+  return flash_rt::kernels::moe_weighted_sum_sm120_bf16(y, rows, w, out, tokens, topk, hidden, stride, S(st));
 }
 
 #ifdef REF_HAVE_CUTLASS

@@ -169,3 +169,40 @@ def test_swiglu_stage_matches_reference_chain(golden_dir, rows):
     up = O.bf16_bits_to_f32(merged[:, merged.shape[1] // 2:])
     direct = O.f32_to_bf16_bits((gate / (np.float32(1) + np.exp(-gate, dtype=np.float32))) * up)
     assert (direct != staged).mean() < 2e-3
+
+
+def test_router_topk_and_plan_oracle():
+    # the reference's own check of its router: linspace logits against torch.topk
+    # (transformer-fused-ops/tests/test_transformer_fused_ops.py:736-740)
+    router = torch.linspace(-1.0, 1.0, 256).to(torch.bfloat16)
+    idx, val = O.router_topk(O.torch_bf16_to_bits(router)[None, :], 8)
+    ref_val, ref_idx = torch.topk(router.float(), 8)
+    # bf16 linspace holds ties; both orders must agree on the values, and on indices where unique
+    np.testing.assert_array_equal(val[0], ref_val.numpy())
+    assert set(idx[0].tolist()) <= set(range(256)) and (np.diff(val[0]) <= 0).all()
+    # ties: bit-reversed index order (2 = 0b10 reverses below 1 = 0b01), as the reference's fold gives
+    idx2, val2 = O.router_topk(O.torch_bf16_to_bits(torch.tensor([[1.0, 3.0, 3.0, 2.0]]).bfloat16()), 3)
+    assert idx2.tolist() == [[2, 1, 3]] and val2.tolist() == [[3.0, 3.0, 2.0]]
+    # the plan is the stable sort by expert, consistent with the sort the grouped tests use
+    rng = np.random.default_rng(5)
+    logits = rng.standard_normal((64, 16)).astype(np.float32)
+    top = np.argsort(-logits, axis=1, kind="stable")[:, :4].astype(np.int32)
+    offsets, row_of_pair, token_of_row = O.route_plan(top, 16)
+    sorted_token, offsets2 = O.route_topk(logits, 4)
+    np.testing.assert_array_equal(offsets, offsets2)
+    np.testing.assert_array_equal(token_of_row, sorted_token)
+    for t in range(64):
+        for j in range(4):
+            r = row_of_pair[t, j]
+            assert token_of_row[r] == t and offsets[top[t, j]] <= r < offsets[top[t, j] + 1]
+
+
+def test_weighted_sum_oracle_matches_reference_definition():
+    # transformer-fused-ops/tests/test_transformer_fused_ops.py:748-760 (tolerance 1e-5 there)
+    g = torch.Generator().manual_seed(3)
+    y = torch.randn(37, 384, generator=g).bfloat16()
+    rows = torch.randint(0, 37, (3, 4), generator=g, dtype=torch.int32)
+    w = torch.softmax(torch.randn(3, 4, generator=g), dim=-1)
+    got = O.weighted_sum(O.torch_bf16_to_bits(y), rows.numpy(), w.numpy(), 320)
+    ref = (y[rows.long(), :320].float() * w[..., None]).sum(dim=1)
+    np.testing.assert_allclose(got, ref.numpy(), rtol=1e-5, atol=1e-5)
