@@ -475,6 +475,56 @@ def run_moe(args, rank, world, local_rank):
         t1.record()
         torch.cuda.synchronize()
     ms = t0.elapsed_time(t1) / args.steps
+    launches = int(L.frt_launch_count() - l0)
+
+    # ---- the whole routed layer through the C ABI: router -> plan -> quantise -> gather ->
+    # grouped gate/up -> SwiGLU -> NVFP4 -> grouped down -> weighted un-permute
+    T, E, topk = MOE["tokens"], experts, MOE["top_k"]
+    (_, n1, k1, _, wp1, _, wsf1, out1), (_, n2, k2, _, wp2, _, wsf2, out2) = layers
+    g = torch.Generator(device=dev).manual_seed(11)
+    hidden = torch.randn(T, k1, generator=g, device=dev).to(torch.bfloat16)
+    logits = torch.randn(T, E, generator=g, device=dev).to(torch.bfloat16)
+    idx = torch.empty(T, topk, dtype=torch.int32, device=dev)
+    val = torch.empty(T, topk, dtype=torch.float32, device=dev)
+    off = torch.empty(E + 1, dtype=torch.int32, device=dev)
+    rop = torch.empty(T, topk, dtype=torch.int32, device=dev)
+    tor = torch.empty(T * topk, dtype=torch.int32, device=dev)
+    xp = torch.empty(T, k1 // 2, dtype=torch.uint8, device=dev)
+    xs = torch.zeros(sfb(T, k1), dtype=torch.uint8, device=dev)
+    gp = torch.empty(T * topk, k1 // 2, dtype=torch.uint8, device=dev)
+    gs = torch.zeros(sfb(T * topk, k1), dtype=torch.uint8, device=dev)
+    hp = torch.empty(T * topk, k2 // 2, dtype=torch.uint8, device=dev)
+    hs = torch.zeros(sfb(T * topk, k2), dtype=torch.uint8, device=dev)
+    final = torch.empty(T, n2, dtype=torch.float32, device=dev)
+    R = T * topk
+
+    def routed_layer():
+        rcs = [L.frt_router_topk_bf16(P(logits), P(idx), P(val), T, E, topk, st)]
+        weights = torch.softmax(val, dim=-1)          # k values per token (torch; the reference does the same)
+        rcs += [L.frt_moe_route_plan(P(idx), T, topk, E, P(off), P(rop), P(tor), st),
+                L.frt_nvfp4_quantize(P(hidden), 0, P(xp), P(xs), T, k1, st),
+                L.frt_moe_gather_nvfp4(P(xp), P(xs), P(tor), P(gp), P(gs), R, T, k1, st),
+                L.frt_nvfp4_grouped_gemm_bf16(P(gp), P(gs), P(wp1), P(wsf1), P(alpha), P(off), None, 0, P(out1), R, n1,
+                                              k1, E, n1 * (k1 // 2), int(wsf1.shape[1]), P(work), st),
+                L.frt_silu_mul_quant_nvfp4(P(out1), P(hp), P(hs), R, n1 // 2, st),
+                L.frt_nvfp4_grouped_gemm_bf16(P(hp), P(hs), P(wp2), P(wsf2), P(alpha), P(off), None, 0, P(out2), R, n2,
+                                              k2, E, n2 * (k2 // 2), int(wsf2.shape[1]), P(work), st),
+                L.frt_moe_weighted_sum_bf16(P(out2), P(rop), P(weights), P(final), T, topk, n2, n2, st)]
+        assert not any(rcs), rcs
+
+    routed_us = None
+    if n1 // 2 == k2 and rows == R:
+        for _ in range(3):
+            routed_layer()
+        torch.cuda.synchronize()
+        r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n_it = max(5, min(50, args.steps))
+        r0.record()
+        for _ in range(n_it):
+            routed_layer()
+        r1.record()
+        torch.cuda.synchronize()
+        routed_us = round(r0.elapsed_time(r1) / n_it * 1e3, 1)
     if rank == 0:
         print(json.dumps({
             "metric": "nvfp4_grouped_moe_tflops", "value": round(flops / (ms * 1e-3) / 1e12, 2), "unit": "TFLOP/s",
@@ -483,7 +533,10 @@ def run_moe(args, rank, world, local_rank):
             "config": {"workload": MOE["name"], "routed_rows": rows, "experts": experts,
                        "layers": {l[0]: [l[1], l[2]] for l in layers},
                        "l2": "weights 340 MB + activations per step exceed the 126 MiB L2"},
-            "gpu_launches": int(L.frt_launch_count() - l0), "clocks": clocks.summary()}), flush=True)
+            "detail": {"routed_layer_us": routed_us,
+                       "routed_layer": "router top-k, routing plan, quantise, gather, grouped gate/up, SwiGLU->NVFP4, "
+                                       "grouped down, weighted un-permute (12 launches of this library + one softmax)"},
+            "gpu_launches": launches, "clocks": clocks.summary()}), flush=True)
 
 
 # ----------------------------------------------------------------------------

@@ -70,6 +70,7 @@ plan_count_kernel(const int* __restrict__ idx, int n_pairs, int* __restrict__ of
   __shared__ int warp_counts[kPlanThreads / 32];
   const int e = blockIdx.x;
   int c = 0;
+#pragma unroll 4
   for (int i = threadIdx.x; i < n_pairs; i += kPlanThreads) c += idx[i] == e;
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
@@ -102,33 +103,58 @@ __global__ void __launch_bounds__(1024) plan_scan_kernel(int* __restrict__ offse
   for (int i = lo; i < hi; ++i) { run += offsets[i]; offsets[i] = run; }
 }
 
-__global__ void __launch_bounds__(kPlanThreads)
+// 1024 threads, four consecutive pairs per thread and pass: a pass numbers 4096 pairs with one
+// warp scan, one scan over the 32 warp totals and two barriers.
+constexpr int kPlaceThreads = 1024;
+
+__global__ void __launch_bounds__(kPlaceThreads)
 plan_place_kernel(const int* __restrict__ idx, int n_pairs, int k, int n_experts, const int* __restrict__ offsets,
                   int* __restrict__ row_of_pair, int* __restrict__ token_of_row) {
-  __shared__ int warp_counts[kPlanThreads / 32];
+  __shared__ int warp_totals[kPlaceThreads / 32];
   const int e = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool vec = (n_pairs & 3) == 0 && (reinterpret_cast<uintptr_t>(idx) & 15) == 0;
   int running = offsets[e];
-  for (int base = 0; base < n_pairs; base += kPlanThreads) {
-    const int i = base + threadIdx.x;
-    const int v = i < n_pairs ? idx[i] : -2;
-    const bool hit = v == e;
-    const unsigned ballot = __ballot_sync(0xffffffffu, hit);
-    if (lane == 0) warp_counts[warp] = __popc(ballot);
-    __syncthreads();
-    int before = 0, total = 0;
+  for (int base = 0; base < n_pairs; base += 4 * kPlaceThreads) {
+    const int i0 = base + 4 * threadIdx.x;
+    int v[4] = {-2, -2, -2, -2};
+    if (vec && i0 < n_pairs) {
+      const int4 q = *reinterpret_cast<const int4*>(idx + i0);
+      v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+    } else {
 #pragma unroll
-    for (int w = 0; w < kPlanThreads / 32; ++w) {
-      const int c = warp_counts[w];
-      before += w < warp ? c : 0;
-      total += c;
+      for (int j = 0; j < 4; ++j) if (i0 + j < n_pairs) v[j] = idx[i0 + j];
     }
-    if (hit) {
-      const int row = running + before + __popc(ballot & ((1u << lane) - 1u));
-      row_of_pair[i] = row;
-      token_of_row[row] = i / k;
-    } else if (e == 0 && i < n_pairs && (v < 0 || v >= n_experts)) {
-      row_of_pair[i] = -1;                       // not routed anywhere
+    int mine = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) mine += v[j] == e;
+    int incl = mine;                                   // inclusive scan over the warp
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int up = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += up;
+    }
+    if (lane == 31) warp_totals[warp] = incl;
+    __syncthreads();
+    const int wt = warp_totals[lane];                  // every warp scans the 32 warp totals
+    int wincl = wt;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int up = __shfl_up_sync(0xffffffffu, wincl, o);
+      if (lane >= o) wincl += up;
+    }
+    const int before_warp = __shfl_sync(0xffffffffu, wincl - wt, warp);
+    const int total = __shfl_sync(0xffffffffu, wincl, 31);
+    int row = running + before_warp + incl - mine;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (v[j] == e) {
+        row_of_pair[i0 + j] = row;
+        token_of_row[row] = (i0 + j) / k;
+        ++row;
+      } else if (e == 0 && i0 + j < n_pairs && (v[j] < 0 || v[j] >= n_experts)) {
+        row_of_pair[i0 + j] = -1;                      // not routed anywhere
+      }
     }
     running += total;
     __syncthreads();
@@ -235,7 +261,7 @@ int frt_moe_route_plan(const void* topk_idx, int tokens, int k, int n_experts, v
   if (int rc = launch_result()) return rc;
   plan_scan_kernel<<<1, 1024, 0, st>>>(off, n_experts);
   if (int rc = launch_result()) return rc;
-  plan_place_kernel<<<n_experts, kPlanThreads, 0, st>>>(idx, n_pairs, k, n_experts, off,
+  plan_place_kernel<<<n_experts, kPlaceThreads, 0, st>>>(idx, n_pairs, k, n_experts, off,
                                                          static_cast<int*>(row_of_pair),
                                                          static_cast<int*>(token_of_row));
   return launch_result();
