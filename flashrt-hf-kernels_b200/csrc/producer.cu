@@ -69,6 +69,68 @@ quantize_kernel(const uint4* __restrict__ src, uint2* __restrict__ packed, uint8
 }
 
 // ---------------------------------------------------------------------------
+// Bind-time weight packer with a per-block scale search: of nine candidate scales
+// e4m3(max(amax * (1/6) * m, 1e-12)), m in {.375 ... 1.5}, keep the first with the lowest
+// squared reconstruction error (fp32, fused multiply-adds as the reference's compiled
+// kernel evaluates them), then encode with it.  Not a hot-path kernel.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float e2m1_code_value(uint32_t c) {
+  const uint32_t m = c & 7u;
+  const float mag = m < 2 ? 0.5f * m : (m & 1 ? 1.5f : 1.0f) * static_cast<float>(1 << ((m >> 1) - 1));
+  return (c & 8u) ? -mag : mag;
+}
+
+template <bool FP16>
+__global__ void __launch_bounds__(256)
+quantize_mse_kernel(const uint4* __restrict__ src, uint2* __restrict__ packed, uint8_t* __restrict__ sf,
+                    int rows, int nb, int sf_cols) {
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<int64_t>(rows) * nb) return;
+  const int row = static_cast<int>(idx / nb);
+  const int kb = static_cast<int>(idx - static_cast<int64_t>(row) * nb);
+  const uint4 r0 = __ldcs(src + 2 * idx);
+  const uint4 r1 = __ldcs(src + 2 * idx + 1);
+  float v[16];
+  if (FP16) {
+    const __half2* h0 = reinterpret_cast<const __half2*>(&r0);
+    const __half2* h1 = reinterpret_cast<const __half2*>(&r1);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 a = __half22float2(h0[i]);
+      const float2 b = __half22float2(h1[i]);
+      v[2 * i] = a.x; v[2 * i + 1] = a.y;
+      v[8 + 2 * i] = b.x; v[8 + 2 * i + 1] = b.y;
+    }
+  } else {
+    unpack_bf16x8(r0, v);
+    unpack_bf16x8(r1, v + 8);
+  }
+  const float amax = amax16(v);
+  const float base = __fmul_rn(amax, 1.f / 6.f);
+  const float mult[9] = {.375f, .5f, .625f, .75f, .875f, 1.f, 1.125f, 1.25f, 1.5f};
+  float best_err = INFINITY;
+  uint8_t best = static_cast<uint8_t>(__nv_cvt_float_to_fp8(1e-12f, __NV_SATFINITE, __NV_E4M3));
+#pragma unroll 1
+  for (int c = 0; c < 9; ++c) {
+    const float want = fmaxf(fmaxf(__fmul_rn(base, mult[c]), 1e-12f), 0.f);
+    const uint8_t sq = static_cast<uint8_t>(__nv_cvt_float_to_fp8(want, __NV_SATFINITE, __NV_E4M3));
+    const float scale = ue4m3_to_float(sq);
+    const float inv = __fdiv_rn(1.f, scale);
+    float err = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const uint32_t q = e2m1_rule_a_chain(__fmul_rn(v[i], inv));
+      const float delta = __fmaf_rn(e2m1_code_value(q), scale, -v[i]);
+      err = __fmaf_rn(delta, delta, err);
+    }
+    if (err < best_err) { best_err = err; best = sq; }
+  }
+  const float inv = __fdiv_rn(1.f, ue4m3_to_float(best));
+  packed[idx] = encode_block16<kEncChain, false>(v, inv);
+  sf[sf_offset(row, kb, sf_cols)] = best;
+}
+
+// ---------------------------------------------------------------------------
 // SwiGLU -> NVFP4: merged = [gate | up] bf16 (rows, 2H); one thread per 16 outputs
 // (two 16-byte loads from each half, one 8-byte store).  Instruction-bound (an
 // exponential and a division per element): the GEMM epilogue form of the same
@@ -597,6 +659,24 @@ int frt_nvfp4_quantize(const void* src, int src_dtype, void* packed, void* sf, i
     if (chain) quantize_kernel<kEncChain, false><<<grid, block, 0, st>>>(s, pk, sfp, rows, nb, sf_cols);
     else quantize_kernel<kEncHw, false><<<grid, block, 0, st>>>(s, pk, sfp, rows, nb, sf_cols);
   }
+  return launch_result();
+}
+
+int frt_nvfp4_quantize_mse(const void* src, int src_dtype, void* packed, void* sf, int rows, int dim, void* stream) {
+  if (!src || !packed || !sf) return FRT_E_NULL;
+  if (rows <= 0 || dim <= 0 || dim % 16 != 0) return FRT_E_SHAPE;
+  if (src_dtype != FRT_DTYPE_BF16 && src_dtype != FRT_DTYPE_FP16) return FRT_E_UNSUPPORTED;
+  if (!aligned(src, 16) || !aligned(packed, 8)) return FRT_E_ALIGN;
+  const int nb = dim / 16, sf_cols = (dim + 63) / 64;
+  const int64_t total = static_cast<int64_t>(rows) * nb;
+  const dim3 block(256), grid(static_cast<unsigned>((total + 255) / 256));
+  auto s = static_cast<const uint4*>(src);
+  auto pk = static_cast<uint2*>(packed);
+  auto sfp = static_cast<uint8_t*>(sf);
+  if (src_dtype == FRT_DTYPE_FP16)
+    quantize_mse_kernel<true><<<grid, block, 0, as_stream(stream)>>>(s, pk, sfp, rows, nb, sf_cols);
+  else
+    quantize_mse_kernel<false><<<grid, block, 0, as_stream(stream)>>>(s, pk, sfp, rows, nb, sf_cols);
   return launch_result();
 }
 

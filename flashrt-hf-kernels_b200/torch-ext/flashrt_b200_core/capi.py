@@ -20,6 +20,7 @@ SIGNATURES = {
     "frt_nvfp4_sf_offset": (_L, [_I, _I, _I]),
     "frt_nvfp4_sf_linear_to_swizzled": (_I, [_P, _P, _I, _I, _P]),
     "frt_nvfp4_quantize": (_I, [_P, _I, _P, _P, _I, _I, _P]),
+    "frt_nvfp4_quantize_mse": (_I, [_P, _I, _P, _P, _I, _I, _P]),
     "frt_nvfp4_dequantize_fp16": (_I, [_P, _P, _P, _I, _I, _P]),
     "frt_rms_norm_bf16": (_I, [_P, _P, _P, _I, _I, _F, _P]),
     "frt_residual_add_rms_norm_bf16": (_I, [_P, _P, _P, _P, _I, _I, _F, _P]),

@@ -1,3 +1,3 @@
-from .layers import RMSNorm, FlashRTQuantLinear, FusedNormLinear
+from .layers import RMSNorm, FlashRTQuantLinear, FusedNormLinear, FusedSwiGLUFFN
 
-__all__ = ["RMSNorm", "FlashRTQuantLinear", "FusedNormLinear"]
+__all__ = ["RMSNorm", "FlashRTQuantLinear", "FusedNormLinear", "FusedSwiGLUFFN"]

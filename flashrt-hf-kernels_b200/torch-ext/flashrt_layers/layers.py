@@ -43,9 +43,11 @@ class FlashRTQuantLinear(nn.Module):
         self.register_buffer("bias", None, persistent=False)
 
     @classmethod
-    def from_linear(cls, linear: nn.Linear) -> "FlashRTQuantLinear":
+    def from_linear(cls, linear: nn.Linear, *, mse: bool = False) -> "FlashRTQuantLinear":
         mod = cls(linear.in_features, linear.out_features, linear.bias is not None)
-        packed, sfb, bias, _ = fp4_gemm.pack_nvfp4_weight_bf16(linear.weight.data, linear.bias)
+        weight = linear.weight.data.to(torch.bfloat16).contiguous()
+        bias = None if linear.bias is None else linear.bias.data.to(torch.bfloat16).contiguous()
+        packed, sfb, bias, _ = fp4_gemm.pack_nvfp4_weight_bf16(weight, bias, mse=mse)
         mod.w_packed, mod.w_sfb, mod.bias = packed, sfb, bias
         return mod
 
@@ -64,6 +66,35 @@ class FlashRTQuantLinear(nn.Module):
             x2 = torch.nn.functional.pad(x2, (0, pad))
         a_packed, sfa = fp4_gemm.quantize_fp4_sfa_bf16(x2)
         return self.forward_packed(a_packed, sfa).view(*shape[:-1], self.out_features)
+
+
+class FusedSwiGLUFFN(nn.Module):
+    """down(silu(gate(x)) * up(x)) on NVFP4 activations: the gate/up projection runs as ONE
+    GEMM over the stacked [gate ; up] weight whose epilogue applies SwiGLU and quantises to
+    NVFP4, and the down projection consumes that directly.  Intermediate size must be a
+    multiple of 128 and the projections bias-free (the Llama / Qwen FFN)."""
+
+    def __init__(self, gate: nn.Linear, up: nn.Linear, down: nn.Linear, *, mse: bool = False):
+        super().__init__()
+        assert gate.bias is None and up.bias is None, "gate/up projections must be bias-free"
+        assert gate.out_features == up.out_features == down.in_features and gate.out_features % 128 == 0
+        assert gate.in_features % 32 == 0
+        stacked = torch.cat([gate.weight.data, up.weight.data], dim=0).to(torch.bfloat16).contiguous()
+        quantize = fp4_gemm.quantize_fp4_sfa_mse_bf16 if mse else fp4_gemm.quantize_fp4_sfa_bf16
+        packed, sfb = quantize(stacked, is_sfb=True)
+        self.register_buffer("w_gate_up", packed, persistent=False)
+        self.register_buffer("w_gate_up_sfb", sfb, persistent=False)
+        self.down = FlashRTQuantLinear.from_linear(down, mse=mse)
+
+    def forward_packed(self, a_packed: torch.Tensor, sfa: torch.Tensor) -> torch.Tensor:
+        h_packed, h_sfa = fp4_gemm.nvfp4_gemm_swiglu_nvfp4_bf16(a_packed, self.w_gate_up, sfa, self.w_gate_up_sfb)
+        return self.down.forward_packed(h_packed, h_sfa)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1]).to(torch.bfloat16).contiguous()
+        a_packed, sfa = fp4_gemm.quantize_fp4_sfa_bf16(x2)
+        return self.forward_packed(a_packed, sfa).view(*shape[:-1], self.down.out_features)
 
 
 class FusedNormLinear(nn.Module):

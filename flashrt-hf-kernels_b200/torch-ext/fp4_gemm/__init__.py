@@ -198,24 +198,84 @@ def fp4_w4a4_gemm_warpsplit_mrows_bf16(a_packed, b_packed, sfa, sfb, *, alpha: f
     return out
 
 
-def pack_nvfp4_weight_bf16(weight: torch.Tensor, bias: Optional[torch.Tensor] = None):
-    """Bind-time packing of a [N, K] bf16 weight: zero-pads N to a multiple of 8
-    and K to a multiple of 32, quantises, and returns
-    (packed, sfb, padded_bias, (logical_n, logical_k))."""
-    n, k = weight.shape
-    pn, pk = (n + 7) // 8 * 8, (k + 31) // 32 * 32
-    w = weight.to(torch.bfloat16)
-    if (pn, pk) != (n, k):
-        w = torch.nn.functional.pad(w, (0, pk - k, 0, pn - n))
-    packed, sfb = quantize_fp4_sfa_bf16(w.contiguous(), is_sfb=True)
+@torch.library.register_fake(add_op_namespace_prefix("quantize_fp4_sfa_mse_fp16"))
+def _quant_mse_fake(x, packed, sfa, is_sfb: bool = False) -> None:
+    return None
+
+
+@torch.library.register_fake(add_op_namespace_prefix("quantize_fp4_sfa_mse_bf16"))
+def _quant_mse_bf16_fake(x, packed, sfa, is_sfb: bool = False) -> None:
+    return None
+
+
+def quantize_fp4_sfa_mse_fp16(x, packed=None, sfa=None, is_sfb: bool = False):
+    """Pack FP16 weights using per-block reconstruction-MSE scale search."""
+    if packed is None or sfa is None:
+        packed, sfa = _alloc_fp4(x.shape[0], x.shape[1], x.device)
+    ops.quantize_fp4_sfa_mse_fp16(x, packed, sfa, bool(is_sfb))
+    return packed, sfa
+
+
+def quantize_fp4_sfa_mse_bf16(x, packed=None, sfa=None, is_sfb: bool = False):
+    """Pack BF16 weights using per-block reconstruction-MSE scale search."""
+    if packed is None or sfa is None:
+        packed, sfa = _alloc_fp4(x.shape[0], x.shape[1], x.device)
+    ops.quantize_fp4_sfa_mse_bf16(x, packed, sfa, bool(is_sfb))
+    return packed, sfa
+
+
+def aligned_fp4_dim(dim: int, alignment: int = 32) -> int:
+    """Physical FP4 GEMM dimension of a logical dimension (fp4-gemm/torch-ext/fp4_gemm/__init__.py:342-346)."""
+    if dim <= 0 or alignment <= 0 or alignment % 16 != 0:
+        raise ValueError("dim must be positive and alignment divisible by 16")
+    return ((dim + alignment - 1) // alignment) * alignment
+
+
+def quantize_fp4_sfa_padded_bf16(x, *, alignment: int = 32, is_sfb: bool = False):
+    """Bind-time BF16 pack with zero padding of the last dimension; returns
+    (packed, sfa, logical_dim).  Allocates: not a hot-path op."""
+    if x.ndim != 2 or x.dtype != torch.bfloat16:
+        raise ValueError("x must be a 2-D BF16 tensor")
+    logical_dim = int(x.shape[1])
+    physical_dim = aligned_fp4_dim(logical_dim, alignment)
+    if physical_dim == logical_dim:
+        padded = x.contiguous()
+    else:
+        padded = torch.zeros((x.shape[0], physical_dim), device=x.device, dtype=x.dtype)
+        padded[:, :logical_dim].copy_(x)
+    packed, sfa = quantize_fp4_sfa_bf16(padded, is_sfb=is_sfb)
+    return packed, sfa, logical_dim
+
+
+def pack_nvfp4_weight_bf16(weight: torch.Tensor, bias: Optional[torch.Tensor] = None, *, alignment: int = 32,
+                           mse: bool = False):
+    """Bind-time packing of a logical ``(N, K)`` BF16 weight: zero-pads both dimensions to
+    `alignment` (4304 -> 4320 and the like), quantises (optionally with the MSE scale search)
+    and returns ``(packed, sfb, padded_bias, (logical_n, logical_k))``
+    (fp4-gemm/torch-ext/fp4_gemm/__init__.py:376-411)."""
+    if weight.ndim != 2 or weight.dtype != torch.bfloat16:
+        raise ValueError("weight must be a 2-D BF16 tensor")
+    logical_n, logical_k = map(int, weight.shape)
+    physical_n = aligned_fp4_dim(logical_n, alignment)
+    physical_k = aligned_fp4_dim(logical_k, alignment)
+    padded_weight = torch.zeros((physical_n, physical_k), device=weight.device, dtype=weight.dtype)
+    padded_weight[:logical_n, :logical_k].copy_(weight)
+    quantize = quantize_fp4_sfa_mse_bf16 if mse else quantize_fp4_sfa_bf16
+    packed, sfb = quantize(padded_weight, is_sfb=True)
     padded_bias = None
     if bias is not None:
-        padded_bias = torch.nn.functional.pad(bias.to(torch.bfloat16), (0, pn - n)).contiguous()
-    return packed, sfb, padded_bias, (n, k)
+        if bias.ndim != 1 or bias.numel() != logical_n:
+            raise ValueError("bias must have shape (N,)")
+        if bias.dtype != torch.bfloat16 or bias.device != weight.device:
+            raise ValueError("bias must match the weight dtype and device")
+        padded_bias = torch.zeros((physical_n,), device=bias.device, dtype=bias.dtype)
+        padded_bias[:logical_n].copy_(bias)
+    return packed, sfb, padded_bias, (logical_n, logical_k)
 
 
 __all__ = ["capabilities", "sfa_size_bytes", "quantize_fp4_sfa_fp16", "quantize_fp4_sfa_bf16",
            "dequantize_fp4_sfa_fp16", "nvfp4_gemm_bf16", "nvfp4_gemm_swiglu_nvfp4_bf16", "fp4_w4a16_linear_bf16",
            "nvfp4_gemm_bias_bf16",
            "nvfp4_gemm_bias_residual_bf16", "nvfp4_gemm_residual_bf16", "fp4_w4a4_gemv_warpsplit_bf16",
-           "fp4_w4a4_gemm_warpsplit_mrows_bf16", "pack_nvfp4_weight_bf16"]
+           "fp4_w4a4_gemm_warpsplit_mrows_bf16", "pack_nvfp4_weight_bf16", "quantize_fp4_sfa_mse_fp16",
+           "quantize_fp4_sfa_mse_bf16", "aligned_fp4_dim", "quantize_fp4_sfa_padded_bf16"]

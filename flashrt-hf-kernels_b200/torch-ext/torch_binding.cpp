@@ -86,6 +86,24 @@ void quantize_common(const Tensor& x, Tensor& packed, Tensor& sfa, c10::ScalarTy
   check_rc(frt_nvfp4_quantize(x.data_ptr(), frt_dt, packed.data_ptr(), sfa.data_ptr(), as_int(x.size(0), "rows"),
                               as_int(x.size(1), "dim"), stream_of(x)), op);
 }
+void quantize_mse_common(const Tensor& x, Tensor& packed, Tensor& sfa, c10::ScalarType dt, int frt_dt,
+                         const char* dt_name, const char* op) {
+  check_dtype(x, dt, "x", dt_name);
+  TORCH_CHECK(x.dim() == 2, "x must have shape (rows, dim)");
+  TORCH_CHECK(x.size(1) % 16 == 0, "dim must be divisible by 16");
+  check_packed_scales(packed, sfa, x.size(0), x.size(1), "packed", "sfa");
+  check_same_device(x, packed, "x", "packed");
+  check_same_device(x, sfa, "x", "sfa");
+  c10::cuda::CUDAGuard guard(x.device());
+  check_rc(frt_nvfp4_quantize_mse(x.data_ptr(), frt_dt, packed.data_ptr(), sfa.data_ptr(), as_int(x.size(0), "rows"),
+                                  as_int(x.size(1), "dim"), stream_of(x)), op);
+}
+void quantize_fp4_sfa_mse_bf16(const Tensor& x, Tensor& packed, Tensor& sfa, bool) {
+  quantize_mse_common(x, packed, sfa, torch::kBFloat16, FRT_DTYPE_BF16, "torch.bfloat16", "quantize_fp4_sfa_mse_bf16");
+}
+void quantize_fp4_sfa_mse_fp16(const Tensor& x, Tensor& packed, Tensor& sfa, bool) {
+  quantize_mse_common(x, packed, sfa, torch::kFloat16, FRT_DTYPE_FP16, "torch.float16", "quantize_fp4_sfa_mse_fp16");
+}
 void quantize_fp4_sfa_bf16(const Tensor& x, Tensor& packed, Tensor& sfa, bool) {
   quantize_common(x, packed, sfa, torch::kBFloat16, FRT_DTYPE_BF16, "torch.bfloat16", "quantize_fp4_sfa_bf16");
 }
@@ -487,6 +505,10 @@ TORCH_LIBRARY_EXPAND(fp4_gemm_b200, ops) {
   ops.def("quantize_fp4_sfa_fp16(Tensor x, Tensor! packed, Tensor! sfa, bool is_sfb=False) -> ()");
   ops.def("quantize_fp4_sfa_bf16(Tensor x, Tensor! packed, Tensor! sfa, bool is_sfb=False) -> ()");
   ops.def("dequantize_fp4_sfa_fp16(Tensor packed, Tensor sfa, Tensor! out, bool is_sfb=False) -> ()");
+  ops.def("quantize_fp4_sfa_mse_fp16(Tensor x, Tensor! packed, Tensor! sfa, bool is_sfb=False) -> ()");
+  ops.def("quantize_fp4_sfa_mse_bf16(Tensor x, Tensor! packed, Tensor! sfa, bool is_sfb=False) -> ()");
+  ops.impl("quantize_fp4_sfa_mse_fp16", torch::kCUDA, &quantize_fp4_sfa_mse_fp16);
+  ops.impl("quantize_fp4_sfa_mse_bf16", torch::kCUDA, &quantize_fp4_sfa_mse_bf16);
   ops.def("nvfp4_gemm_swiglu_nvfp4_bf16(Tensor a_packed, Tensor b_packed, Tensor sfa, Tensor sfb, Tensor! out_packed, Tensor! out_sfa, float alpha=1.0) -> ()");
   ops.impl("nvfp4_gemm_swiglu_nvfp4_bf16", torch::kCUDA, &nvfp4_gemm_swiglu_nvfp4_bf16);
   ops.impl("nvfp4_gemm_bf16", torch::kCUDA, &nvfp4_gemm_bf16);

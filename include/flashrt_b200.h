@@ -63,6 +63,13 @@ int frt_nvfp4_sf_linear_to_swizzled(const void* src_linear, void* dst_swizzled,
 int frt_nvfp4_quantize(const void* src, int src_dtype, void* packed, void* sf_swizzled,
                        int rows, int dim, void* stream);
 
+/* Bind-time weight packer: same layout as frt_nvfp4_quantize, but each block's scale is the
+ * first of nine candidates e4m3(max(amax * (1/6) * m, 1e-12)), m = .375 .5 .625 .75 .875 1
+ * 1.125 1.25 1.5, with the lowest squared reconstruction error.
+ * replaces quantize_fp4_dynamic_sfa_mse_fp16/_bf16, fp4-gemm/csrc/quantize/quantize_fp4_sfa.cuh:32,36 */
+int frt_nvfp4_quantize_mse(const void* src, int src_dtype, void* packed, void* sf_swizzled,
+                           int rows, int dim, void* stream);
+
 /* packed + swizzled scales -> fp16 [rows, dim] (exact).
  * replaces dequantize_fp4_sfa_fp16, fp4-gemm/csrc/dequantize_fp4_sfa.cuh:12 */
 int frt_nvfp4_dequantize_fp16(const void* packed, const void* sf_swizzled, void* out_fp16,

@@ -46,6 +46,12 @@ int ref_quantize_fp16(const void* src, void* packed, void* sfa, int rows, int di
   return flash_rt::fp4::quantize_fp4_dynamic_sfa_fp16(src, packed, sfa, rows, dim, false, S(st));
 }
 // K6
+int ref_quantize_mse_bf16(const void* src, void* packed, void* sfa, int rows, int dim, void* st) {
+  return flash_rt::fp4::quantize_fp4_dynamic_sfa_mse_bf16(src, packed, sfa, rows, dim, true, S(st));
+}
+int ref_quantize_mse_fp16(const void* src, void* packed, void* sfa, int rows, int dim, void* st) {
+  return flash_rt::fp4::quantize_fp4_dynamic_sfa_mse_fp16(src, packed, sfa, rows, dim, true, S(st));
+}
 int ref_dequantize_fp16(const void* packed, const void* sfa, void* out, int rows, int dim, void* st) {
   flash_rt::fused_fp4::dequantize_fp4_sfa_fp16(static_cast<const uint8_t*>(packed), static_cast<const uint8_t*>(sfa),
                                                static_cast<__half*>(out), rows, dim, false, S(st));

@@ -1,0 +1,80 @@
+"""Bind-time weight tools: MSE scale-search packer (bytes equal to the reference's CUDA kernel and
+to the CPU oracle), padded packing, and the layer modules built on them."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from tests.gpu_common import DEV, O, alloc_fp4, capi, randn_bf16, ref_lib, sf_linear  # noqa: E402
+
+P = capi.ptr
+
+
+def st():
+    return capi.stream_ptr()
+
+
+@pytest.mark.parametrize("rows,dim,scale,dtype", [(64, 256, 0.02, torch.bfloat16), (130, 4096, 1.0, torch.bfloat16),
+                                                   (7, 512, 0.5, torch.float16), (257, 1024, 3.0, torch.float16)])
+def test_mse_packer_bit_exact(rows, dim, scale, dtype):
+    g = torch.Generator().manual_seed(rows + dim)
+    x = (torch.randn(rows, dim, generator=g) * scale).to(dtype)
+    x[0, :16] = 0
+    x[0, 16:32] = 2.0 ** -13
+    dx = x.to(DEV)
+    packed, sf = alloc_fp4(rows, dim)
+    capi.check(capi.lib().frt_nvfp4_quantize_mse(P(dx), 0 if dtype == torch.bfloat16 else 1, P(packed), P(sf), rows,
+                                                 dim, st()))
+    ref = ref_lib()
+    if ref is not None:
+        rp, rs = alloc_fp4(rows, dim)
+        fn = ref.ref_quantize_mse_bf16 if dtype == torch.bfloat16 else ref.ref_quantize_mse_fp16
+        assert fn(P(dx), P(rp), P(rs), rows, dim, st()) == 0
+        torch.cuda.synchronize()
+        assert torch.equal(rp, packed) and torch.equal(rs, sf)
+    want_p, want_s = O.quantize_nvfp4_mse(x.float().numpy())
+    np.testing.assert_array_equal(sf_linear(sf, rows, dim), want_s)
+    np.testing.assert_array_equal(packed.cpu().numpy(), want_p)
+    # the reference's acceptance check (fp4-gemm/tests/test_fp4_gemm.py:1624-1643): never worse than round-to-nearest
+    rtn_p, rtn_s = O.quantize_nvfp4(x.float().numpy())
+    err = lambda p, s: float(((O.dequantize_nvfp4(p, s) - x.float().numpy()) ** 2).mean())
+    assert err(want_p, want_s) <= err(rtn_p, rtn_s) + 1e-8
+
+
+def test_padded_pack_and_layers():
+    import fp4_gemm
+    from flashrt_layers import FlashRTQuantLinear, FusedSwiGLUFFN
+    assert fp4_gemm.aligned_fp4_dim(4304) == 4320          # fp4-gemm/tests/test_fp4_gemm.py:1703-1711
+    w = randn_bf16((72, 4304), 5, 0.05).to(DEV)
+    b = randn_bf16((72,), 6).to(DEV)
+    packed, sfb, bias, (n, k) = fp4_gemm.pack_nvfp4_weight_bf16(w, b, mse=True)
+    assert packed.shape == (96, 2160) and bias.shape == (96,) and (n, k) == (72, 4304)
+    assert torch.equal(bias[:72], b) and not bias[72:].any()
+    p2, s2, logical = fp4_gemm.quantize_fp4_sfa_padded_bf16(w)
+    assert p2.shape == (72, 2160) and logical == 4304
+
+    torch.manual_seed(0)
+    lin = torch.nn.Linear(4304, 72, bias=True, device=DEV, dtype=torch.bfloat16)
+    q = FlashRTQuantLinear.from_linear(lin)
+    x = randn_bf16((33, 4304), 8).to(DEV)
+    got, ref = q(x), lin(x)
+    rel = ((got.float() - ref.float()).norm() / ref.float().norm()).item()
+    assert got.shape == ref.shape and rel < 0.2        # A4W4 against the unquantised layer (about 0.14 expected)
+
+    gate = torch.nn.Linear(256, 384, bias=False, device=DEV, dtype=torch.bfloat16)
+    up = torch.nn.Linear(256, 384, bias=False, device=DEV, dtype=torch.bfloat16)
+    down = torch.nn.Linear(384, 256, bias=False, device=DEV, dtype=torch.bfloat16)
+    ffn = FusedSwiGLUFFN(gate, up, down)
+    x = randn_bf16((200, 256), 9).to(DEV)
+    got = ffn(x)
+    # the same chain with separate kernels gives the same bytes
+    a_p, a_s = fp4_gemm.quantize_fp4_sfa_bf16(x)
+    import fp4_fused_ops
+    merged = fp4_gemm.nvfp4_gemm_bf16(a_p, ffn.w_gate_up, a_s, ffn.w_gate_up_sfb)
+    h_p, h_s = fp4_fused_ops.silu_mul_quantize_fp4_sfa_bf16(merged)
+    want = ffn.down.forward_packed(h_p, h_s)
+    assert torch.equal(got, want)
+    ref = down(torch.nn.functional.silu(gate(x).float()).to(torch.bfloat16) * up(x))
+    cos = torch.nn.functional.cosine_similarity(got.float().flatten(), ref.float().flatten(), dim=0).item()
+    assert cos > 0.95
