@@ -273,9 +273,38 @@ def pack_nvfp4_weight_bf16(weight: torch.Tensor, bias: Optional[torch.Tensor] = 
     return packed, sfb, padded_bias, (logical_n, logical_k)
 
 
+def adopt_modelopt_nvfp4_weight(weight_packed: torch.Tensor, weight_scale: torch.Tensor,
+                                weight_scale_2: torch.Tensor):
+    """Bind-time adoption of a standard ModelOpt NVFP4 (two-level) weight for the A4W4 GEMM.
+
+    Inputs: ``weight[N, K/2]`` uint8 (two e2m1 codes per byte, low nibble first, the layout
+    this path uses), ``weight_scale[N, K/16]`` float8_e4m3fn (or its uint8 bytes) in row-major
+    order, and the scalar per-tensor ``weight_scale_2``.  Returns ``(b_packed, sfb, alpha)``:
+    the packed weight unchanged, the block scales re-laid into the swizzled buffer the tensor
+    cores read, and the global scale as a float to multiply into the GEMM's ``alpha``
+    (together with the activation's global scale, when it has one).  The dequantisation this
+    reproduces is the one the reference's oracle uses for such weights
+    (fp4-gemm/tests/test_fp4_gemm.py:1150-1164)."""
+    import flashrt_nvfp4
+    if weight_packed.dtype != torch.uint8 or weight_packed.ndim != 2:
+        raise ValueError("weight_packed must be uint8 with shape (N, K / 2)")
+    n, k = weight_packed.shape[0], weight_packed.shape[1] * 2
+    if k % 32 != 0:
+        raise ValueError("K must be divisible by 32")
+    if tuple(weight_scale.shape) != (n, k // 16):
+        raise ValueError("weight_scale must have shape (N, K / 16)")
+    if weight_scale_2.numel() != 1:
+        raise ValueError("weight_scale_2 must contain one global scale")
+    scale_bytes = weight_scale.contiguous().view(torch.uint8)
+    if bool((scale_bytes & 0x80).any()):
+        raise ValueError("block scales must be non-negative (UE4M3)")
+    sfb = flashrt_nvfp4.nvfp4_sf_linear_to_swizzled(scale_bytes, is_sfb=True)
+    return weight_packed.contiguous(), sfb, float(weight_scale_2.float().item())
+
+
 __all__ = ["capabilities", "sfa_size_bytes", "quantize_fp4_sfa_fp16", "quantize_fp4_sfa_bf16",
            "dequantize_fp4_sfa_fp16", "nvfp4_gemm_bf16", "nvfp4_gemm_swiglu_nvfp4_bf16", "fp4_w4a16_linear_bf16",
            "nvfp4_gemm_bias_bf16",
            "nvfp4_gemm_bias_residual_bf16", "nvfp4_gemm_residual_bf16", "fp4_w4a4_gemv_warpsplit_bf16",
            "fp4_w4a4_gemm_warpsplit_mrows_bf16", "pack_nvfp4_weight_bf16", "quantize_fp4_sfa_mse_fp16",
-           "quantize_fp4_sfa_mse_bf16", "aligned_fp4_dim", "quantize_fp4_sfa_padded_bf16"]
+           "quantize_fp4_sfa_mse_bf16", "aligned_fp4_dim", "quantize_fp4_sfa_padded_bf16", "adopt_modelopt_nvfp4_weight"]

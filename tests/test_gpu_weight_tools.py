@@ -78,3 +78,27 @@ def test_padded_pack_and_layers():
     ref = down(torch.nn.functional.silu(gate(x).float()).to(torch.bfloat16) * up(x))
     cos = torch.nn.functional.cosine_similarity(got.float().flatten(), ref.float().flatten(), dim=0).item()
     assert cos > 0.95
+
+
+def test_adopt_modelopt_two_level_weight():
+    """A ModelOpt-style two-level NVFP4 weight (block scales relative to a per-tensor scale)
+    runs through the A4W4 GEMM with the global scale folded into alpha and matches the
+    dequantise-then-matmul oracle of such weights (fp4-gemm/tests/test_fp4_gemm.py:1150-1164)."""
+    import fp4_gemm
+    n, k, m = 256, 512, 96
+    w = randn_bf16((n, k), 21, 0.02).float()
+    global_scale = w.abs().max() / (6.0 * 448.0)                       # weight_scale_2
+    packed_np, sf_np = O.quantize_nvfp4((w / global_scale).numpy())   # level 1 on the rescaled tensor
+    weight = torch.from_numpy(packed_np).to(DEV)
+    weight_scale = torch.from_numpy(sf_np).view(torch.float8_e4m3fn).to(DEV)
+    b_packed, sfb, alpha = fp4_gemm.adopt_modelopt_nvfp4_weight(weight, weight_scale, global_scale.to(DEV))
+    x = randn_bf16((m, k), 22).to(DEV)
+    a_packed, sfa = fp4_gemm.quantize_fp4_sfa_bf16(x)
+    out = fp4_gemm.nvfp4_gemm_bf16(a_packed, b_packed, sfa, sfb, alpha=alpha)
+    w_deq = torch.from_numpy(O.dequantize_nvfp4(packed_np, sf_np)) * global_scale
+    a_deq = torch.from_numpy(O.dequantize_nvfp4(a_packed.cpu().numpy(), sf_linear(sfa, m, k)))
+    want = (a_deq @ w_deq.T).to(torch.bfloat16)
+    rel, cos = O.gemm_error_metrics(out.cpu(), want)
+    assert rel <= 1e-2 and cos >= 0.999, (rel, cos)
+    with pytest.raises(ValueError, match="one global scale"):
+        fp4_gemm.adopt_modelopt_nvfp4_weight(weight, weight_scale, torch.ones(2))
