@@ -125,6 +125,22 @@ def residual_add_rms_norm_quant_nvfp4(residual, x, weight, eps: float = 1e-6, *,
     return packed, sfa
 
 
+@torch.library.register_fake(add_op_namespace_prefix("rms_norm_quant_nvfp4_ex"))
+def _rms_norm_quant_ex_fake(x, weight, eps, normed, packed, sfa, one_plus_weight=False, round_bf16=True) -> None:
+    _check_producer(x, packed, sfa)
+    return None
+
+
+def rms_norm_quant_nvfp4(x, weight, eps: float = 1e-6, *, one_plus_weight: bool = False, round_bf16: bool = True,
+                         normed=None, packed=None, sfa=None):
+    """Additive variant without a residual: RMSNorm with a plain (or ``1 + weight``) weight,
+    NVFP4 of the result and, when `normed` is given, its bf16 copy in the same pass."""
+    if packed is None or sfa is None:
+        packed, sfa = _alloc_fp4(x.shape[0], x.shape[1], x.device)
+    ops.rms_norm_quant_nvfp4_ex(x, weight, float(eps), normed, packed, sfa, bool(one_plus_weight), bool(round_bf16))
+    return packed, sfa
+
+
 def dequantize_fp4_sfa_fp16(packed, sfa, out=None):
     if out is None:
         out = torch.empty((packed.shape[0], packed.shape[1] * 2), device=packed.device, dtype=torch.float16)
@@ -134,4 +150,4 @@ def dequantize_fp4_sfa_fp16(packed, sfa, out=None):
 
 __all__ = ["sfa_size_bytes", "rms_norm_quantize_fp4_sfa_bf16", "residual_add_rms_norm_nvfp4_bf16",
            "residual_add_rms_norm_quant_nvfp4_swizzled_bf16", "residual_add_rms_norm_quant_nvfp4",
-           "dequantize_fp4_sfa_fp16", "silu_mul_quantize_fp4_sfa_bf16"]
+           "dequantize_fp4_sfa_fp16", "silu_mul_quantize_fp4_sfa_bf16", "rms_norm_quant_nvfp4"]

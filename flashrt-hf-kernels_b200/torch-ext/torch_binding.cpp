@@ -313,6 +313,15 @@ void residual_add_rms_norm_quant_nvfp4_ex(Tensor& residual, const Tensor& x, con
   producer_call(&residual, x, &weight, eps, inv_global_scale, normed.has_value() ? &n : nullptr, packed, sfa, 0u,
                 "residual_add_rms_norm_quant_nvfp4_ex");
 }
+// Additive op: RMSNorm (plain or 1 + weight) -> NVFP4 without a residual, optional bf16 copy of
+// the normalised tensor (what transformers' decoder layers pass on to the projections).
+void rms_norm_quant_nvfp4_ex(const Tensor& x, const Tensor& weight, double eps, const c10::optional<Tensor>& normed,
+                             Tensor& packed, Tensor& sfa, bool one_plus_weight, bool round_bf16) {
+  Tensor n = normed.has_value() ? normed.value() : Tensor();
+  producer_call(nullptr, x, &weight, eps, 1.0, normed.has_value() ? &n : nullptr, packed, sfa,
+                (one_plus_weight ? FRT_PRODUCER_ONE_PLUS_W : 0u) | (round_bf16 ? FRT_PRODUCER_ROUND_BF16 : 0u),
+                "rms_norm_quant_nvfp4_ex");
+}
 int64_t sfa_size_bytes_for(const Tensor& /*anchor*/, int64_t rows, int64_t dim, bool /*is_sfb*/) {
   TORCH_CHECK(rows > 0 && dim > 0 && dim % 16 == 0, "rows must be positive and dim positive/divisible by 16");
   return frt_nvfp4_sf_swizzled_bytes(as_int(rows, "rows"), as_int(dim, "dim"));
@@ -531,6 +540,8 @@ TORCH_LIBRARY_EXPAND(fp4_fused_ops_b200, ops) {
   ops.def("residual_add_rms_norm_quant_nvfp4_ex(Tensor! residual, Tensor x, Tensor weight, float eps, float inv_global_scale, Tensor!? normed, Tensor! packed, Tensor! sfa) -> ()");
   ops.def("dequantize_fp4_sfa_fp16(Tensor packed, Tensor sfa, Tensor! out) -> ()");
   ops.def("silu_mul_quantize_fp4_sfa_bf16(Tensor merged, Tensor! packed, Tensor! sfa) -> ()");
+  ops.def("rms_norm_quant_nvfp4_ex(Tensor x, Tensor weight, float eps, Tensor!? normed, Tensor! packed, Tensor! sfa, bool one_plus_weight=False, bool round_bf16=True) -> ()");
+  ops.impl("rms_norm_quant_nvfp4_ex", torch::kCUDA, &rms_norm_quant_nvfp4_ex);
   ops.impl("silu_mul_quantize_fp4_sfa_bf16", torch::kCUDA, &silu_mul_quantize_fp4_sfa_bf16);
   ops.impl("sfa_size_bytes_for", torch::kCUDA, &sfa_size_bytes_for);
   ops.impl("rms_norm_quantize_fp4_sfa_bf16", torch::kCUDA, &rms_norm_quantize_fp4_sfa_bf16);

@@ -102,3 +102,34 @@ def test_adopt_modelopt_two_level_weight():
     assert rel <= 1e-2 and cos >= 0.999, (rel, cos)
     with pytest.raises(ValueError, match="one global scale"):
         fp4_gemm.adopt_modelopt_nvfp4_weight(weight, weight_scale, torch.ones(2))
+
+
+def test_transformers_decoder_conversion():
+    """A small random Qwen3 through `convert_decoder_model`: the fused conversion (norm+quant in one kernel, shared
+    activations, SwiGLU epilogue) agrees with the per-linear conversion, and both stay close to the bf16 model."""
+    transformers = pytest.importorskip("transformers")
+    from flashrt_layers.transformers_backend import NormQuant, SharedInputFFN, convert_decoder_model
+    cfg = transformers.Qwen3Config(hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4,
+                                   num_key_value_heads=2, head_dim=64, vocab_size=512, max_position_embeddings=256)
+    torch.manual_seed(0)
+    base = transformers.Qwen3ForCausalLM(cfg).to(DEV, torch.bfloat16).eval()
+    ids = torch.randint(0, 512, (2, 48), device=DEV)
+    import copy
+    with torch.no_grad():
+        ref = base(ids).logits.float()
+        plain = copy.deepcopy(base)
+        assert convert_decoder_model(plain, fuse=False) == 14
+        fused = copy.deepcopy(base)
+        assert convert_decoder_model(fused, fuse=True) == 14
+        assert isinstance(fused.model.layers[0].mlp, SharedInputFFN)
+        assert isinstance(fused.model.layers[0].input_layernorm, NormQuant)
+        out_plain = plain(ids).logits.float()
+        out_fused = fused(ids).logits.float()
+    cos = lambda a, b: torch.nn.functional.cosine_similarity(a.flatten(), b.flatten(), dim=0).item()
+    # A4W4 on every projection of a random-weight model: about 0.95 against bf16 (each linear alone is ~0.99)
+    assert cos(out_plain, ref) > 0.9 and cos(out_fused, ref) > 0.9, (cos(out_plain, ref), cos(out_fused, ref))
+    # the fused norm multiplies by the weight in fp32 (transformers rounds to bf16 first): a few codes flip
+    assert cos(out_fused, out_plain) > 0.99, cos(out_fused, out_plain)
+    # the shared quantisation was used: one producer call per norm, no per-linear quantise of that tensor
+    layer = fused.model.layers[0]
+    assert layer.self_attn.q_proj.source is layer.input_layernorm.produced
