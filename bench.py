@@ -11,11 +11,16 @@ linears at M = 4096 tokens (synthetic data, random weights of that shape):
 divided by the step time including the two producer launches), inputs resident
 in HBM.  `e2e` is the same metric through the torch operator API with the
 step's bf16 inputs in pinned host memory and the step's result read back to
-the host inside the timed region.  With N > 1 ranks (torchrun) the weights are
-column-sharded, activations replicated, outputs stay sharded; the all-gather
-of the outputs is timed separately.
+the host inside the timed region.  With N > 1 ranks (torchrun) every rank runs
+the step on its own M tokens with replicated weights (token-sharded, no
+collective: weak scaling, `value` = N ranks' flops / max time); the same line
+carries `column_sharded`: the fixed M-token problem with the weights
+column-sharded over the ranks, activations replicated, outputs left sharded
+(strong scaling), and the NCCL all-gather of those outputs timed separately.
+`--sharding columns` makes that form the headline instead.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c5]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c5|c4]
+                    [--sharding tokens|columns] [--tokens M --graph]
 """
 from __future__ import annotations
 
@@ -115,15 +120,19 @@ class ClockSampler:
 class Layer:
     """Device-resident tensors of one rank's shard of the workload."""
 
-    def __init__(self, key, rank, world, dev, seed=1234, tokens=0):
+    def __init__(self, key, rank, world, dev, seed=1234, tokens=0, act_seed=None):
+        """`world` column shards of the weights (1 = whole weights); `act_seed` draws this rank's own
+        activations (token-sharded runs), the weights always come from `seed`."""
         import fp4_gemm
         from flashrt_b200_core import alloc_fp4
         self.name, self.M, self.H, layers = WORKLOADS[key]
         if tokens:
             self.name, self.M = f"{self.name.rsplit('-m', 1)[0]}-m{tokens}", tokens
         g = torch.Generator(device=dev).manual_seed(seed)
+        ga = torch.Generator(device=dev).manual_seed(seed + 1 if act_seed is None else act_seed)
         rn = lambda *s, scale=1.0: (torch.randn(*s, generator=g, device=dev) * scale).to(torch.bfloat16)
-        self.hidden, self.residual0 = rn(self.M, self.H), rn(self.M, self.H)
+        rna = lambda *s: torch.randn(*s, generator=ga, device=dev).to(torch.bfloat16)
+        self.hidden, self.residual0 = rna(self.M, self.H), rna(self.M, self.H)
         self.residual = self.residual0.clone()
         self.norm_w = (1.0 + 0.1 * torch.randn(self.H, generator=g, device=dev)).to(torch.bfloat16)
         self.act_packed, self.act_sf = alloc_fp4(self.M, self.H, dev)
@@ -139,7 +148,7 @@ class Layer:
             if fed:
                 a_p, a_sf = self.act_packed, self.act_sf
             else:
-                a_p, a_sf = fp4_gemm.quantize_fp4_sfa_bf16(rn(self.M, k))
+                a_p, a_sf = fp4_gemm.quantize_fp4_sfa_bf16(rna(self.M, k))
             out = torch.empty(self.M, n_loc, device=dev, dtype=torch.bfloat16)
             self.gemms.append(dict(name=lname, n=n, n_loc=n_loc, k=k, fed=fed, wp=wp, wsf=wsf, a_p=a_p, a_sf=a_sf,
                                    out=out))
@@ -154,20 +163,22 @@ class Layer:
         launches = 0
         for i, g_ in enumerate(self.gemms):
             if g_["fed"]:
-                if ev is not None:
-                    ev[("producer", i)][0].record()
+                pe = ev.get(("producer", i)) if ev is not None else None
+                if pe:
+                    pe[0].record()
                 rc = L.frt_norm_quant_nvfp4(P(self.residual), P(self.hidden), P(self.norm_w), EPS, 1.0, None,
                                             P(self.act_packed), P(self.act_sf), self.M, self.H, 0, st)
-                if ev is not None:
-                    ev[("producer", i)][1].record()
+                if pe:
+                    pe[1].record()
                 assert rc == 0, rc
                 launches += 1
-            if ev is not None:
-                ev[(g_["name"], i)][0].record()
+            ge = ev.get((g_["name"], i)) if ev is not None else None
+            if ge:
+                ge[0].record()
             rc = L.frt_nvfp4_gemm_bf16(P(g_["a_p"]), P(g_["a_sf"]), P(g_["wp"]), P(g_["wsf"]), None, None,
                                        P(g_["out"]), self.M, g_["n_loc"], g_["k"], 1.0, 0.0, st)
-            if ev is not None:
-                ev[(g_["name"], i)][1].record()
+            if ge:
+                ge[1].record()
             assert rc == 0, rc
             launches += 1
         return launches
@@ -192,7 +203,14 @@ def run_ours(args, rank, world, local_rank):
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
     peaks = measured_peaks()
-    layer = Layer(args.workload, rank, world, dev, tokens=args.tokens)
+    # N > 1: by default every rank runs the whole step on its OWN tokens (weights replicated, no
+    # collective: weak scaling); --sharding columns runs the fixed problem with column-sharded weights
+    # and replicated activations (strong scaling), which the token-sharded run also reports beside it.
+    tokens_mode = world > 1 and args.sharding != "columns"
+    col_world = 1 if tokens_mode else world
+    layer = Layer(args.workload, rank, col_world, dev, tokens=args.tokens,
+                  act_seed=7000 + rank if tokens_mode else None)
+    job_flops = layer.flops_total * (world if tokens_mode else 1)
     st = capi.stream_ptr()
 
     def barrier():
@@ -225,7 +243,7 @@ def run_ours(args, rank, world, local_rank):
         wbytes = sum(0.5625 * g_["n_loc"] * g_["k"] for g_ in layer.gemms)
         if rank == 0:
             print(json.dumps({
-                "metric": "nvfp4_linear_path_tflops", "value": round(layer.flops_total / world / (ms * 1e-3) / 1e12, 3),
+                "metric": "nvfp4_linear_path_tflops", "value": round(job_flops / (ms * 1e-3) / 1e12, 3),
                 "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": round(ms, 5), "higher_is_better": True, "data": "synthetic", "timing": "cuda graph replay",
                 "config": {"workload": layer.name, "tokens": layer.M},
@@ -235,7 +253,12 @@ def run_ours(args, rank, world, local_rank):
         return
     keys = [("producer", i) for i, g_ in enumerate(layer.gemms) if g_["fed"]] + \
            [(g_["name"], i) for i, g_ in enumerate(layer.gemms)]
-    events = [{k: (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for k in keys}
+    # Inside the timed region only the dominant kernel (the GEMM with the most flops) is bracketed by
+    # events: a pair of event records costs a few microseconds of stream time, and twelve of them per
+    # step would take ~8 % off `value`.  The per-kernel table comes from a second pass below.
+    dom_i = max(range(len(layer.gemms)), key=lambda i: layer.gemms[i]["n_loc"] * layer.gemms[i]["k"])
+    dom = (layer.gemms[dom_i]["name"], dom_i)
+    events = [{dom: (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))}
               for _ in range(args.steps)]
     launches0 = capi.lib().frt_launch_count()
     with ClockSampler(local_rank) as clocks:
@@ -253,20 +276,27 @@ def run_ours(args, rank, world, local_rank):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_total = float(t.item())
     ms_step = ms_total / args.steps
-    value = layer.flops_total / (ms_step * 1e-3) / 1e12
+    value = job_flops / (ms_step * 1e-3) / 1e12
 
+    dom_ms = statistics.mean(e[dom][0].elapsed_time(e[dom][1]) for e in events)
+    # second pass (not part of `value`): every kernel bracketed by events
+    n_detail = max(5, min(50, args.steps))
+    ev2 = [{k: (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for k in keys}
+           for _ in range(n_detail)]
+    for s_ in range(n_detail):
+        layer.step_capi(capi, st, ev2[s_])
+    torch.cuda.synchronize()
     per_kernel = {}
     for k in keys:
-        per_kernel[k] = statistics.mean(e[k][0].elapsed_time(e[k][1]) for e in events)
+        per_kernel[k] = statistics.mean(e[k][0].elapsed_time(e[k][1]) for e in ev2)
     gemm_ms = sum(v for k, v in per_kernel.items() if k[0] != "producer")
     prod_ms = [v for k, v in per_kernel.items() if k[0] == "producer"]
-    dom = max((k for k in per_kernel if k[0] != "producer"), key=lambda k: per_kernel[k])
     dom_g = layer.gemms[dom[1]]
     dom_flops = 2.0 * layer.M * dom_g["n_loc"] * dom_g["k"]
-    achieved = dom_flops / (per_kernel[dom] * 1e-3) / 1e12
+    achieved = dom_flops / (dom_ms * 1e-3) / 1e12
     prod_bytes = layer.M * layer.H * 6.5625
     detail = {
-        "gemm_only_tflops": layer.flops_total / world / (gemm_ms * 1e-3) / 1e12 * world,
+        "gemm_only_tflops": job_flops / (gemm_ms * 1e-3) / 1e12,
         "per_kernel_us": {f"{k[0]}": round(v * 1e3, 2) for k, v in per_kernel.items()},
         "per_gemm_tflops": {layer.gemms[k[1]]["name"]: round(2.0 * layer.M * layer.gemms[k[1]]["n_loc"] *
                             layer.gemms[k[1]]["k"] / (v * 1e-3) / 1e12, 1) for k, v in per_kernel.items()
@@ -286,8 +316,8 @@ def run_ours(args, rank, world, local_rank):
     host_out = [torch.empty(last.shape, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
     dev_in = [(torch.empty_like(layer.hidden), torch.empty_like(layer.hidden)) for _ in range(2)]
     copy_s, comp_s, out_s = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
-    h2d = 2 * layer.M * layer.H * 2
-    d2h = last.numel() * 2
+    h2d = 2 * layer.M * layer.H * 2 * world          # whole job: every rank copies its step inputs
+    d2h = last.numel() * 2 * world
 
     def e2e_steps(n):
         in_ready = [torch.cuda.Event(), torch.cuda.Event()]
@@ -327,12 +357,11 @@ def run_ours(args, rank, world, local_rank):
         t = torch.tensor([e2e_ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item())
-    e2e_val = layer.flops_total / (e2e_ms * 1e-3) / 1e12
+    e2e_val = job_flops / (e2e_ms * 1e-3) / 1e12
 
     # ---- all-gather of the sharded outputs, timed separately -------------------
-    allgather = None
-    if world > 1:
-        big = max(layer.gemms, key=lambda g_: g_["out"].numel())
+    def time_allgather(lay):
+        big = max(lay.gemms, key=lambda g_: g_["out"].numel())
         gathered = torch.empty((world * big["out"].shape[0], big["out"].shape[1]), device=dev, dtype=torch.bfloat16)
         for _ in range(3):
             dist.all_gather_into_tensor(gathered, big["out"])
@@ -348,9 +377,35 @@ def run_ours(args, rank, world, local_rank):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ag_ms = float(t.item())
         tot = gathered.numel() * 2
-        allgather = {"layer": big["name"], "ms": round(ag_ms, 4), "bytes_total": tot,
-                     "bus_gbs": round(tot * (world - 1) / world / (ag_ms * 1e-3) / 1e9, 1), "backend": "nccl"}
         del gathered
+        return {"layer": big["name"], "ms": round(ag_ms, 4), "bytes_total": tot,
+                "bus_gbs": round(tot * (world - 1) / world / (ag_ms * 1e-3) / 1e9, 1), "backend": "nccl"}
+
+    # ---- all-gather of the column-sharded outputs, timed separately; in a token-sharded run the
+    # column-sharded form of the same (fixed-size) problem is measured here as well
+    allgather = column_sharded = None
+    if world > 1 and not tokens_mode:
+        allgather = time_allgather(layer)
+    elif world > 1:
+        col = Layer(args.workload, rank, world, dev, tokens=args.tokens)
+        for _ in range(args.warmup):
+            col.step_capi(capi, st)
+        barrier()
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        c0.record()
+        for _ in range(args.steps):
+            col.step_capi(capi, st)
+        c1.record()
+        barrier()
+        t = torch.tensor([c0.elapsed_time(c1) / args.steps], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        col_ms = float(t.item())
+        column_sharded = {"value": round(col.flops_total / (col_ms * 1e-3) / 1e12, 2), "unit": "TFLOP/s",
+                          "ms_per_step": round(col_ms, 5), "scaling": "strong",
+                          "what": f"the same workload at a fixed {col.M} tokens, weights column-sharded x{world}, "
+                                  "activations replicated, outputs left sharded",
+                          "allgather_separate": time_allgather(col)}
+        del col
 
     # ---- the FFN as a connected chain: gate/up GEMM -> SwiGLU -> NVFP4 -> down GEMM ------
     # (not part of `value`: in the timed step above the down GEMM reads a resident NVFP4 input)
@@ -396,11 +451,15 @@ def run_ours(args, rank, world, local_rank):
         line = {
             "metric": "nvfp4_linear_path_tflops", "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_step, 5), "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "nvfp4 (e2m1 x ue4m3, fp32 accumulate, bf16 out)",
+            "scaling": "weak" if tokens_mode else "strong", "vs_baseline": None,
+            "dtype": "nvfp4 (e2m1 x ue4m3, fp32 accumulate, bf16 out)",
             "data": "synthetic",
             "config": {"workload": layer.name, "tokens": layer.M, "hidden": layer.H,
                        "layers": {g_["name"]: [g_["n"], g_["k"]] for g_ in layer.gemms},
-                       "parallelism": f"column-sharded x{world}, activations replicated" if world > 1 else "single GPU",
+                       "global_tokens": layer.M * (world if tokens_mode else 1),
+                       "parallelism": (f"token-sharded x{world}: every rank runs the step on its own {layer.M} tokens, "
+                                       "weights replicated, no collective" if tokens_mode else
+                                       f"column-sharded x{world}, activations replicated" if world > 1 else "single GPU"),
                        "l2": f"inputs larger than L2: each step streams {layer.bytes_streamed >> 20} MiB "
                              f"({L2_BYTES >> 20} MiB L2), every tensor touched once per step"},
             "e2e": {"value": round(e2e_val, 2), "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
@@ -427,6 +486,8 @@ def run_ours(args, rank, world, local_rank):
                 pass
         if allgather:
             line["allgather_separate"] = allgather
+        if column_sharded:
+            line["column_sharded"] = column_sharded
         if cpu_baseline:
             line["cpu_baseline"] = cpu_baseline
         print(json.dumps(line), flush=True)
@@ -620,6 +681,9 @@ def main():
     ap.add_argument("--tokens", type=int, default=0, help="override the token count M (decode sweep: 1, 4, 16, 64)")
     ap.add_argument("--graph", action="store_true",
                     help="time CUDA-graph replays of the step (launch-bound decode shapes); prints a short line")
+    ap.add_argument("--sharding", default="tokens", choices=["tokens", "columns"],
+                    help="N > 1: tokens = data-parallel over token rows (weak scaling, default); columns = "
+                         "column-sharded weights on the fixed problem (strong scaling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     args = ap.parse_args()

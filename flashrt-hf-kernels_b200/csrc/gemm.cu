@@ -720,9 +720,20 @@ int run_gemm(const void* p_packed, const void* sfp, int P, const void* q_packed,
   if (cfg == 0) {
     if (swap) cfg = Q <= 16 ? 11 : Q <= 32 ? 12 : Q <= 64 ? 13 : 14;
     else if (P > 128) {
-      // CTA pairs: 256x256 tiles (measured faster than 256x192 at every Qwen3-8B shape,
-      // wave quantisation included) unless the output is narrower than one such tile
-      cfg = Q <= 128 ? 6 : Q <= 192 ? 5 : 4;
+      // CTA pairs.  Estimated time = waves x cost of one tile, with the measured relative
+      // tile costs 256-wide 1.0, 192-wide 0.878, 128-wide 0.665 (narrower tiles move more bytes
+      // per flop through the ~64 B/clk an SM takes in from L2).  256x256 wins at every full
+      // Qwen3-8B / Llama-70B shape; narrower tiles win when a column shard leaves fewer 256-wide
+      // tiles than CTA pairs.
+      const int pairs = di.sms / 2, p_tiles = (P + 255) / 256;
+      const int widths[3] = {256, 192, 128}, cfgs[3] = {4, 5, 6};
+      const float cost[3] = {1.0f, 0.878f, 0.665f};
+      float best = 0.f;
+      for (int i = 0; i < 3; ++i) {
+        const int tiles = p_tiles * ((Q + widths[i] - 1) / widths[i]);
+        const float t = static_cast<float>((tiles + pairs - 1) / pairs) * cost[i];
+        if (i == 0 || t < best * 0.97f) { best = t; cfg = cfgs[i]; }   // prefer the wider tile on near-ties
+      }
     } else {
       cfg = K >= 8192 ? 2 : 3;      // long K amortises the single-accumulator 128x256 tile
     }
