@@ -200,6 +200,8 @@ def run_ours(args, rank, world, local_rank):
     import torch.distributed as dist
     from flashrt_b200_core import capi, load
     load()
+    if args.no_pdl:
+        capi.lib().frt_set_option(4, 0)
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
     peaks = measured_peaks()
@@ -684,6 +686,8 @@ def main():
     ap.add_argument("--sharding", default="tokens", choices=["tokens", "columns"],
                     help="N > 1: tokens = data-parallel over token rows (weak scaling, default); columns = "
                          "column-sharded weights on the fixed problem (strong scaling)")
+    ap.add_argument("--no-pdl", action="store_true",
+                    help="plain kernel launches instead of programmatic dependent launches (A/B)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     args = ap.parse_args()

@@ -18,6 +18,7 @@ extern std::atomic<int64_t> g_launches;     // kernels launched by this library
 extern int g_opt_quant_encoder;             // FRT_OPT_QUANT_ENCODER
 extern int g_opt_gemm_config;               // FRT_OPT_GEMM_CONFIG
 extern int g_opt_gemm_debug;                // experiment switches of the GEMM kernel
+extern int g_opt_pdl;                       // FRT_OPT_PDL: programmatic dependent launch (default on)
 
 // Status word written by kernels whose bounded waits ran out (one per device
 // context, lives in device global memory of this library).
@@ -30,6 +31,29 @@ inline int launch_result() {
   return cudaGetLastError() == cudaSuccess ? FRT_OK : FRT_E_LAUNCH;
 }
 
+// Launch with the "programmatic stream serialization" attribute: the grid may start while the
+// previous kernel of the stream is still running (its CTAs become resident as resources free up and
+// run their prologue), and every kernel launched this way executes griddepcontrol.wait before it
+// touches global memory, which blocks until the previous grid has completed and its writes are
+// visible.  Hides launch latency and kernel prologues behind the predecessor's tail; capturable in
+// CUDA graphs (programmatic edges).
+template <typename... KArgs, typename... Args>
+inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  if (g_opt_pdl) {
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 inline bool aligned(const void* p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 
 // Byte offset of the UE4M3 scale of (row, 16-element block kb) in the swizzled
@@ -40,6 +64,10 @@ __host__ __device__ __forceinline__ int64_t sf_offset(int row, int kb, int sf_co
 }
 
 #ifdef __CUDACC__
+// Device side of launch_pdl (no-ops for a kernel launched without the attribute).
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ---- NVFP4 block quantiser -------------------------------------------------
 
 // UE4M3 byte -> fp32 (exact).

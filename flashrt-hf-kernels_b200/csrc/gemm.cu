@@ -93,8 +93,15 @@ __device__ __forceinline__ void tile_coords(int t, const GemmParams& p, int& pt,
 // memory, and after a cluster barrier every CTA sums a slice of the columns over all ranks
 // through distributed shared memory, in rank order (deterministic), and writes it out.  This is
 // what lets a layer with few 128-row tiles pull weights through every SM.
+//
+// Small token counts (SWAP, BN <= 32): two CTAs fit an SM (4 stages of ~22 KB, 256 TMEM columns
+// each), and the kernel is launched as a programmatic dependent: its CTAs become resident beside
+// the previous kernel's, and the TMA thread loads the WEIGHT halves of its first stages (weights
+// are not written by any kernel of the stream) before it waits for the previous grid; only the
+// activation halves wait.  The weight stream of kernel n+1 thus overlaps kernel n, which is what a
+// chain of latency-bound decode GEMMs needs.
 template <int BN, int STAGES, int ACC, bool SWAP, bool SPLITK = false>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(192, (SWAP && BN <= 32) ? 2 : 1)
 nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
                   const GemmParams p) {
   using L = SmemLayout<BN, STAGES>;
@@ -102,6 +109,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
   constexpr int SF_COLS = KT_PER_STAGE * (4 + SFQ_COLS_PER_KT);    // per SF buffer
   constexpr int ACC_COLS = ACC * BN;
   static_assert(ACC_COLS + 2 * SF_COLS <= 512, "TMEM budget");
+  constexpr uint32_t TMEM_COLS = (ACC_COLS + 2 * SF_COLS <= 256) ? 256 : 512;
   constexpr uint32_t IDESC = ptx::idesc_nvf4(BM, BN);
 
   extern __shared__ uint8_t smem_raw[];
@@ -114,6 +122,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + ACC);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
+  pdl_launch_dependents();
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int total_tiles = p.p_tiles * p.q_tiles;
@@ -135,18 +144,40 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
     ptx::prefetch_tensormap(&map_q);
   }
   if (warp == 1) {
-    ptx::tmem_alloc(tmem_slot, 512);
+    ptx::tmem_alloc(tmem_slot, TMEM_COLS);
     ptx::tmem_relinquish();
   }
   ptx::tc_fence_before();
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Everything above overlapped the previous kernel of the stream.  From here on global memory:
+  // all warps wait for the previous grid, except the TMA thread, which first issues the loads
+  // that cannot depend on it (see below).
+  if (warp != 0) pdl_wait();
 
   if (warp == 0) {
     // ===================== TMA producer =====================
     if (ptx::elect_one()) {
       int it = 0;
+      int n_pre = 0;          // leading stages whose weight half was loaded before the wait
+      if (SWAP && tile_first < total_tiles) {
+        int pt, qt;
+        tile_coords(tile_first, p, pt, qt);
+        const int qblk0 = (qt * BN) >> 7;
+        int nblk = 0;
+        for (int b = 0; b < L::SFQ_BLOCKS; ++b) nblk += (qblk0 + b < p.sfq_row_blocks) ? 1 : 0;
+        for (int ks = ks_begin; ks < k_stages && n_pre < STAGES; ++ks, ++n_pre) {
+          uint8_t* st = smem + n_pre * L::STAGE_BYTES;
+          const int kts = min(KT_PER_STAGE, p.k_tiles - ks * KT_PER_STAGE);
+          ptx::mbar_expect_tx(&full[n_pre], L::A_BYTES + L::B_BYTES + kts * SF_TILE * (1 + nblk));
+          ptx::tma_load_2d(st, &map_p, &full[n_pre], ks * 128, pt * BM);
+          ptx::bulk_load(st + L::A_BYTES + L::B_BYTES,
+                         p.sfp + (static_cast<int64_t>(pt) * p.sf_cols + ks * KT_PER_STAGE) * SF_TILE,
+                         kts * SF_TILE, &full[n_pre]);
+        }
+      }
+      pdl_wait();
       for (int t = tile_first; t < total_tiles && !*abort_flag; t += tile_step) {
         int pt, qt;
         tile_coords(t, p, pt, qt);
@@ -155,20 +186,22 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
         for (int ks = ks_begin; ks < k_stages; ++ks, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
-          if (!ptx::mbar_wait_bounded(&empty[s], ph ^ 1, WAIT_LIMIT)) {
-            atomicOr(&g_status_word, 1u); *abort_flag = 1; break;
-          }
           uint8_t* st = smem + s * L::STAGE_BYTES;
           const int kts = min(KT_PER_STAGE, p.k_tiles - ks * KT_PER_STAGE);
           int nblk = 0;
           for (int b = 0; b < L::SFQ_BLOCKS; ++b) nblk += (qblk0 + b < p.sfq_row_blocks) ? 1 : 0;
-          const uint32_t bytes = L::A_BYTES + L::B_BYTES + kts * SF_TILE * (1 + nblk);
-          ptx::mbar_expect_tx(&full[s], bytes);
-          ptx::tma_load_2d(st, &map_p, &full[s], ks * 128, pt * BM);
+          if (it >= n_pre) {   // (the first n_pre stages were armed, and their P half loaded, above)
+            if (!ptx::mbar_wait_bounded(&empty[s], ph ^ 1, WAIT_LIMIT)) {
+              atomicOr(&g_status_word, 1u); *abort_flag = 1; break;
+            }
+            const uint32_t bytes = L::A_BYTES + L::B_BYTES + kts * SF_TILE * (1 + nblk);
+            ptx::mbar_expect_tx(&full[s], bytes);
+            ptx::tma_load_2d(st, &map_p, &full[s], ks * 128, pt * BM);
+            ptx::bulk_load(st + L::A_BYTES + L::B_BYTES,
+                           p.sfp + (static_cast<int64_t>(pt) * p.sf_cols + ks * KT_PER_STAGE) * SF_TILE,
+                           kts * SF_TILE, &full[s]);
+          }
           ptx::tma_load_2d(st + L::A_BYTES, &map_q, &full[s], ks * 128, q0);
-          ptx::bulk_load(st + L::A_BYTES + L::B_BYTES,
-                         p.sfp + (static_cast<int64_t>(pt) * p.sf_cols + ks * KT_PER_STAGE) * SF_TILE,
-                         kts * SF_TILE, &full[s]);
           for (int b = 0; b < nblk; ++b)
             ptx::bulk_load(st + L::A_BYTES + L::B_BYTES + L::SFP_BYTES + b * KT_PER_STAGE * SF_TILE,
                            p.sfq + (static_cast<int64_t>(qblk0 + b) * p.sf_cols + ks * KT_PER_STAGE) * SF_TILE,
@@ -385,7 +418,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
     ptx::cluster_arrive();
     ptx::cluster_wait();                                  // nobody leaves while its partial may still be read
   }
-  if (warp == 1) ptx::tmem_dealloc(tmem_base, 512);
+  if (warp == 1) ptx::tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
 #include "gemm_pair.cuh"
@@ -479,8 +512,9 @@ int launch_gemm(const CUtensorMap& mp, const CUtensorMap& mq, GemmParams& p, int
   p.q_tiles = (p.Q + BN - 1) / BN;
   p.p_tiles = (p.P + BM - 1) / BM;
   const int tiles = p.p_tiles * p.q_tiles;
-  const int grid = tiles < sms ? tiles : sms;
-  kern<<<grid, 192, L::TOTAL, st>>>(mp, mq, p);
+  const int slots = (SWAP && BN <= 32) ? 2 * sms : sms;      // two small CTAs fit an SM
+  const int grid = tiles < slots ? tiles : slots;
+  launch_pdl(kern, dim3(grid), dim3(192), L::TOTAL, st, mp, mq, p);
   return launch_result();
 }
 
@@ -506,7 +540,7 @@ int launch_gemm_pair(const void* p_packed, const void* q_packed, GemmParams& p, 
   p.p_tiles = (p.P + 255) / 256;
   const int tiles = p.p_tiles * p.q_tiles;
   const int pairs = tiles < sms / 2 ? tiles : sms / 2;
-  kern<<<2 * pairs, 320, L::TOTAL, st>>>(maps, p, nullptr);
+  launch_pdl(kern, dim3(2 * pairs), dim3(320), L::TOTAL, st, maps, p, static_cast<const GroupWork*>(nullptr));
   return launch_result();
 }
 
@@ -531,7 +565,7 @@ int launch_gemm_swiglu(const void* p_packed, const void* q_packed, GemmParams& p
   p.p_tiles = (p.P + 255) / 256;
   const int tiles = p.p_tiles * p.q_tiles;
   const int pairs = tiles < sms / 2 ? tiles : sms / 2;
-  kern<<<2 * pairs, 576, L::TOTAL, st>>>(maps, p, nullptr);
+  launch_pdl(kern, dim3(2 * pairs), dim3(576), L::TOTAL, st, maps, p, static_cast<const GroupWork*>(nullptr));
   return launch_result();
 }
 
@@ -554,13 +588,15 @@ int launch_gemm_splitk(const CUtensorMap& mp, const CUtensorMap& mq, GemmParams&
   cfg.blockDim = dim3(192);
   cfg.dynamicSmemBytes = L::TOTAL;
   cfg.stream = st;
-  cudaLaunchAttribute attr{};
-  attr.id = cudaLaunchAttributeClusterDimension;
-  attr.val.clusterDim.x = static_cast<unsigned>(p.splits);
-  attr.val.clusterDim.y = 1;
-  attr.val.clusterDim.z = 1;
-  cfg.attrs = &attr;
-  cfg.numAttrs = 1;
+  cudaLaunchAttribute attr[2] = {};
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = static_cast<unsigned>(p.splits);
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_opt_pdl ? 2 : 1;
   const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, mp, mq, p);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return e == cudaSuccess ? FRT_OK : FRT_E_LAUNCH;
@@ -590,6 +626,8 @@ __device__ __forceinline__ void emit_windows(GroupWork* work, int max_items, int
 // at most 256 rows that start on a multiple of 64.
 __global__ void group_plan_kernel(const int* __restrict__ offsets, const int* __restrict__ tile_expert, int tile_rows,
                                   int rows, int num_experts, int num_tiles, GroupWork* work, int max_items) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (offsets != nullptr) {
     if (i >= num_experts) return;
@@ -676,11 +714,10 @@ int run_grouped(const void* a, const void* sfa, const void* b_stack, const void*
   if (cudaMemsetAsync(work, 0, 16, st) != cudaSuccess) return FRT_E_LAUNCH;
   const int num_tiles = tile_rows > 0 ? rows / tile_rows : 0;
   const int plan_threads = offsets ? experts : num_tiles;
-  group_plan_kernel<<<(plan_threads + 255) / 256, 256, 0, st>>>(
-      static_cast<const int*>(offsets), static_cast<const int*>(tile_expert), tile_rows, rows, experts, num_tiles, work,
-      max_items);
+  launch_pdl(group_plan_kernel, dim3((plan_threads + 255) / 256), dim3(256), 0, st, static_cast<const int*>(offsets),
+             static_cast<const int*>(tile_expert), tile_rows, rows, experts, num_tiles, work, max_items);
   g_launches.fetch_add(1, std::memory_order_relaxed);
-  kern<<<2 * (di.sms / 2), 320, L::TOTAL, st>>>(maps, p, work);
+  launch_pdl(kern, dim3(2 * (di.sms / 2)), dim3(320), L::TOTAL, st, maps, p, static_cast<const GroupWork*>(work));
   return launch_result();
 }
 
@@ -761,15 +798,15 @@ int run_gemm(const void* p_packed, const void* sfp, int P, const void* q_packed,
   if (swap && Q <= bn && cfg >= 11 && cfg <= 13 && !(g_opt_gemm_debug & 16)) {
     // few 128-row weight tiles: split K over a cluster so that every SM streams weights
     const int tiles = (P + BM - 1) / BM, k_stages = (p.k_tiles + KT_PER_STAGE - 1) / KT_PER_STAGE;
-    int want = di.sms / tiles;
+    int want = (bn <= 32 ? 2 * di.sms : di.sms) / tiles;     // two CTAs of the 16/32-token forms fit an SM
     if (want > 8) want = 8;
     for (int s = want; s >= 2; --s)
       if (k_stages % s == 0 && k_stages / s >= 2) { p.splits = s; break; }
     if (bn == 64 && p.splits < 4) p.splits = 1;   // 64 token columns: the cross-CTA sum only pays off from 4-way
     if (p.splits > 1) {
       switch (cfg) {
-        case 11: return launch_gemm_splitk<16, 8>(mp, mq, p, st);
-        case 12: return launch_gemm_splitk<32, 8>(mp, mq, p, st);
+        case 11: return launch_gemm_splitk<16, 5>(mp, mq, p, st);
+        case 12: return launch_gemm_splitk<32, 4>(mp, mq, p, st);
         default: return launch_gemm_splitk<64, 8>(mp, mq, p, st);
       }
     }
@@ -778,8 +815,8 @@ int run_gemm(const void* p_packed, const void* sfp, int P, const void* q_packed,
     case 1: return launch_gemm<128, 6, 2, false>(mp, mq, p, di.sms, st);
     case 2: return launch_gemm<256, 4, 1, false>(mp, mq, p, di.sms, st);
     case 3: return launch_gemm<192, 4, 2, false>(mp, mq, p, di.sms, st);
-    case 11: return launch_gemm<16, 8, 2, true>(mp, mq, p, di.sms, st);
-    case 12: return launch_gemm<32, 8, 2, true>(mp, mq, p, di.sms, st);
+    case 11: return launch_gemm<16, 5, 2, true>(mp, mq, p, di.sms, st);
+    case 12: return launch_gemm<32, 4, 2, true>(mp, mq, p, di.sms, st);
     case 13: return launch_gemm<64, 8, 2, true>(mp, mq, p, di.sms, st);
     case 14: return launch_gemm<128, 6, 2, true>(mp, mq, p, di.sms, st);
   }

@@ -111,7 +111,8 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
   const bool leader = rank == 0;
   const int pair_id = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
-  const int total_tiles = GROUPED ? work->count * p.p_tiles : p.p_tiles * p.q_tiles;
+  pdl_launch_dependents();
+  int total_tiles = GROUPED ? 0 : p.p_tiles * p.q_tiles;     // grouped: read from the plan after the wait below
   const int k_stages = (p.k_tiles + KT_PER_STAGE - 1) / KT_PER_STAGE;
 
   if (threadIdx.x == 0) {
@@ -127,16 +128,18 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
     ptx::prefetch_tensormap(&maps.sfq);
     if (!SWIGLU) ptx::prefetch_tensormap(&maps.d);
   }
+  if (warp == 1) {
+    ptx::tmem_alloc_pair(tmem_slot, 512);
+    ptx::tmem_relinquish_pair();
+  }
+  pdl_wait();                 // everything above overlapped the previous kernel; global memory from here on
   if (GROUPED) {
+    total_tiles = work->count * p.p_tiles;
     // tile i of this pair is global tile pair_id + i * num_pairs; its item is items[tile / p_tiles]
     for (int i = threadIdx.x; i < L::ITEM_CACHE; i += blockDim.x) {
       const int t = pair_id + i * num_pairs;
       if (t < total_tiles) item_cache[i] = work->items[t / p.p_tiles];
     }
-  }
-  if (warp == 1) {
-    ptx::tmem_alloc_pair(tmem_slot, 512);
-    ptx::tmem_relinquish_pair();
   }
   ptx::tc_fence_before();
   __syncthreads();

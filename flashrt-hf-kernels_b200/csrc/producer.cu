@@ -11,6 +11,7 @@ std::atomic<int64_t> g_launches{0};
 int g_opt_quant_encoder = 0;
 int g_opt_gemm_config = 0;
 int g_opt_gemm_debug = 0;
+int g_opt_pdl = 1;
 
 namespace {
 
@@ -41,6 +42,8 @@ template <int ENC, bool FP16>
 __global__ void __launch_bounds__(256)
 quantize_kernel(const uint4* __restrict__ src, uint2* __restrict__ packed, uint8_t* __restrict__ sf,
                 int rows, int nb, int sf_cols) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= static_cast<int64_t>(rows) * nb) return;
   const int row = static_cast<int>(idx / nb);
@@ -140,6 +143,8 @@ template <int ENC>
 __global__ void __launch_bounds__(256)
 silu_mul_quant_kernel(const uint4* __restrict__ merged, uint2* __restrict__ packed, uint8_t* __restrict__ sf,
                       int rows, int nb, int sf_cols) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= static_cast<int64_t>(rows) * nb) return;
   const int row = static_cast<int>(idx / nb);
@@ -226,6 +231,8 @@ __device__ __forceinline__ void pack16_bf16(const float (&v)[16], uint4& o0, uin
 template <int TPR, bool HAS_RES, bool QUANT, int ENC>
 __global__ void __launch_bounds__(TPR > 256 ? TPR : 256)
 norm_quant_kernel(const NormParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int CTA = TPR > 256 ? TPR : 256;
   constexpr int ROWS_PER_CTA = CTA / TPR;
   constexpr int WPR = TPR / 32;                       // warps per row
@@ -372,6 +379,8 @@ norm_quant_stream_kernel(const NormParams p, unsigned* status) {
   const int s = tid % TPR;                            // block index inside the row
   const int n_groups = (p.rows + RPC - 1) / RPC;
   const uint32_t row_bytes = static_cast<uint32_t>(p.nb) * 32u;
+  pdl_launch_dependents();
+  pdl_wait();
 
   auto issue = [&](int group, int stage) {            // thread 0 only
     const int row0 = group * RPC;
@@ -532,7 +541,7 @@ int launch_norm_stream(const NormParams& p, cudaStream_t st) {
   }
   const int n_groups = (p.rows + RPC - 1) / RPC;
   const int grid = n_groups < ctas_per_sm[dev] ? n_groups : ctas_per_sm[dev];
-  kernel<<<grid, CTA, smem, st>>>(p, device_status_word());
+  launch_pdl(kernel, dim3(grid), dim3(CTA), smem, st, p, device_status_word());
   return launch_result();
 }
 
@@ -548,7 +557,7 @@ int launch_norm(const NormParams& p, bool has_res, bool quant, cudaStream_t st) 
     constexpr int CTA = TPR > 256 ? TPR : 256;
     constexpr int rows_per_cta = CTA / TPR;
     const dim3 grid((p.rows + rows_per_cta - 1) / rows_per_cta), block(CTA);
-#define FRT_LAUNCH(HR, Q, E) norm_quant_kernel<TPR, HR, Q, E><<<grid, block, 0, st>>>(p)
+#define FRT_LAUNCH(HR, Q, E) launch_pdl(norm_quant_kernel<TPR, HR, Q, E>, grid, block, 0, st, p)
     if (!quant) {
       if (has_res) FRT_LAUNCH(true, false, kEncHw); else FRT_LAUNCH(false, false, kEncHw);
     } else if (chain) {
@@ -624,6 +633,7 @@ int frt_set_option(int key, int value) {
   if (key == FRT_OPT_QUANT_ENCODER) { prev = g_opt_quant_encoder; g_opt_quant_encoder = value; }
   if (key == FRT_OPT_GEMM_CONFIG) { prev = g_opt_gemm_config; g_opt_gemm_config = value; }
   if (key == 3) { prev = g_opt_gemm_debug; g_opt_gemm_debug = value; }
+  if (key == FRT_OPT_PDL) { prev = g_opt_pdl; g_opt_pdl = value; }
   return prev;
 }
 
@@ -653,11 +663,11 @@ int frt_nvfp4_quantize(const void* src, int src_dtype, void* packed, void* sf, i
   cudaStream_t st = as_stream(stream);
   const bool chain = g_opt_quant_encoder == 1;
   if (src_dtype == FRT_DTYPE_FP16) {
-    if (chain) quantize_kernel<kEncChain, true><<<grid, block, 0, st>>>(s, pk, sfp, rows, nb, sf_cols);
-    else quantize_kernel<kEncHw, true><<<grid, block, 0, st>>>(s, pk, sfp, rows, nb, sf_cols);
+    if (chain) launch_pdl(quantize_kernel<kEncChain, true>, grid, block, 0, st, s, pk, sfp, rows, nb, sf_cols);
+    else launch_pdl(quantize_kernel<kEncHw, true>, grid, block, 0, st, s, pk, sfp, rows, nb, sf_cols);
   } else {
-    if (chain) quantize_kernel<kEncChain, false><<<grid, block, 0, st>>>(s, pk, sfp, rows, nb, sf_cols);
-    else quantize_kernel<kEncHw, false><<<grid, block, 0, st>>>(s, pk, sfp, rows, nb, sf_cols);
+    if (chain) launch_pdl(quantize_kernel<kEncChain, false>, grid, block, 0, st, s, pk, sfp, rows, nb, sf_cols);
+    else launch_pdl(quantize_kernel<kEncHw, false>, grid, block, 0, st, s, pk, sfp, rows, nb, sf_cols);
   }
   return launch_result();
 }
@@ -691,9 +701,9 @@ int frt_silu_mul_quant_nvfp4(const void* merged, void* packed, void* sf, int row
   auto pk = static_cast<uint2*>(packed);
   auto sfp = static_cast<uint8_t*>(sf);
   if (g_opt_quant_encoder == 1)
-    silu_mul_quant_kernel<kEncChain><<<grid, block, 0, as_stream(stream)>>>(m, pk, sfp, rows, nb, sf_cols);
+    launch_pdl(silu_mul_quant_kernel<kEncChain>, grid, block, 0, as_stream(stream), m, pk, sfp, rows, nb, sf_cols);
   else
-    silu_mul_quant_kernel<kEncHw><<<grid, block, 0, as_stream(stream)>>>(m, pk, sfp, rows, nb, sf_cols);
+    launch_pdl(silu_mul_quant_kernel<kEncHw>, grid, block, 0, as_stream(stream), m, pk, sfp, rows, nb, sf_cols);
   return launch_result();
 }
 

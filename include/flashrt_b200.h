@@ -242,6 +242,9 @@ int64_t frt_launch_count(void);
 /* Tuning / debugging switches; see the FRT_OPT_* keys. Returns previous value. */
 #define FRT_OPT_QUANT_ENCODER   1   /* 0 = hardware-cvt encoder (default), 1 = compare chain */
 #define FRT_OPT_GEMM_CONFIG     2   /* 0 = automatic, otherwise a configuration id          */
+#define FRT_OPT_PDL             4   /* 1 = launch kernels with programmatic stream serialization
+                                       (default): a kernel's prologue overlaps the tail of the
+                                       previous kernel of the stream; 0 = plain launches      */
 int frt_set_option(int key, int value);
 
 #ifdef __cplusplus
