@@ -609,9 +609,15 @@ int launch_gemm_splitk(const CUtensorMap& mp, const CUtensorMap& mq, GemmParams&
 // TMEM as a column offset (one column per 32 rows) from a 128-row group, and the
 // MMA takes that scale address only at even columns.
 __device__ __forceinline__ void emit_windows(GroupWork* work, int max_items, int lo, int hi, int expert) {
-  for (int start = lo & ~63; start < hi; start += 256) {
+  // All windows of one expert take consecutive slots: their tiles then run at about the same
+  // time on neighbouring CTA pairs and the expert's weights leave HBM once (with one slot per
+  // atomic the windows of an expert ended up hundreds of tiles apart and the weights, long
+  // evicted from L2, were streamed again for each).
+  const int first = lo & ~63;
+  const int n_win = (hi - first + 255) / 256;
+  int slot = atomicAdd(&work->count, n_win);
+  for (int start = first; start < hi; start += 256, ++slot) {
     const int len = min(256, (hi - start + 31) & ~31);
-    const int slot = atomicAdd(&work->count, 1);
     if (slot < max_items) {
       GroupItem it{};
       it.q_row0 = start; it.n_tokens = len;
@@ -674,12 +680,13 @@ int make_sf_stack_map(CUtensorMap* map, const void* base, int n, int sf_cols, in
 
 int64_t grouped_max_items(int rows, int experts) { return static_cast<int64_t>(rows) / 64 + 2ll * experts + 8; }
 
-int run_grouped(const void* a, const void* sfa, const void* b_stack, const void* sfb_stack, const void* alpha,
+template <int STAGES>
+int run_grouped_impl(const void* a, const void* sfa, const void* b_stack, const void* sfb_stack, const void* alpha,
                 const void* offsets, const void* tile_expert, int tile_rows, void* out, int rows, int N, int K,
                 int experts, int64_t b_stride, int64_t sfb_stride, void* workspace, cudaStream_t st) {
   const DeviceInfo di = device_info();
   if (!di.ok || di.cc_major != 10) return FRT_E_DEVICE;
-  constexpr int BN = 256, STAGES = 5;
+  constexpr int BN = 256;
   using L = PairLayout<BN, STAGES, true>;
   auto kern = nvfp4_gemm_pair_kernel<BN, STAGES, true>;
   static bool attr_set[64] = {};
@@ -705,9 +712,9 @@ int run_grouped(const void* a, const void* sfa, const void* b_stack, const void*
   p.trace = g_trace;
   PairMaps maps{};
   if (int rc = make_weight_stack_map(&maps.p, b_stack, N, K, experts, b_stride)) return rc;
-  if (int rc = make_operand_map(&maps.q, a, rows, K, BN / 2)) return rc;
+  if (int rc = make_operand_map(&maps.q, a, rows, K, 32)) return rc;          // token windows load in 32-row boxes
   if (int rc = make_sf_stack_map(&maps.sfp, sfb_stack, N, p.sf_cols, experts, sfb_stride)) return rc;
-  if (int rc = make_sf_map(&maps.sfq, sfa, rows, p.sf_cols, L::SFQ_BLOCKS)) return rc;
+  if (int rc = make_sf_map(&maps.sfq, sfa, rows, p.sf_cols, 1)) return rc;      // one 128-row scale group per load
   if (int rc = make_output_map(&maps.d, out, rows, N, N)) return rc;
   auto* work = static_cast<GroupWork*>(workspace);
   const int max_items = static_cast<int>(grouped_max_items(rows, experts));
@@ -721,6 +728,19 @@ int run_grouped(const void* a, const void* sfa, const void* b_stack, const void*
   return launch_result();
 }
 
+
+// Long K: the tile is bound by streaming the expert's weights, so the fifth pipeline stage (more
+// bytes in flight per SM) matters; short K: the tile is bound by its epilogue, so the shared memory
+// goes to a second store-staging buffer per warp instead.
+int run_grouped(const void* a, const void* sfa, const void* b_stack, const void* sfb_stack, const void* alpha,
+                const void* offsets, const void* tile_expert, int tile_rows, void* out, int rows, int N, int K,
+                int experts, int64_t b_stride, int64_t sfb_stride, void* workspace, cudaStream_t st) {
+  if (K >= 1536)
+    return run_grouped_impl<5>(a, sfa, b_stack, sfb_stack, alpha, offsets, tile_expert, tile_rows, out, rows, N, K,
+                               experts, b_stride, sfb_stride, workspace, st);
+  return run_grouped_impl<4>(a, sfa, b_stack, sfb_stack, alpha, offsets, tile_expert, tile_rows, out, rows, N, K,
+                             experts, b_stride, sfb_stride, workspace, st);
+}
 
 unsigned* device_status_word() {
   unsigned* ptr = nullptr;

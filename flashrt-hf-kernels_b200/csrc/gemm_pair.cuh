@@ -47,6 +47,7 @@ struct GroupWork {
 
 template <int BN, int STAGES, bool GROUPED = false>
 struct PairLayout {
+
   static constexpr int A_BYTES = 128 * 128;              // this CTA's 128 rows of P
   static constexpr int B_BYTES = (BN / 2) * 128;         // this CTA's half of the Q tile
   // 128-row scale groups a Q tile can touch (a grouped window starts at any multiple of 64)
@@ -55,7 +56,9 @@ struct PairLayout {
   static constexpr int SFQ_BYTES = SFQ_BLOCKS * KT_PER_STAGE * SF_TILE;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFP_BYTES + SFQ_BYTES;
   // epilogue staging: 4 warps x 4 buffers of 32 rows x 64 bytes, written by TMA store
-  static constexpr int SBUFS = GROUPED ? 1 : 2;            // staging buffers (32 rows x 64 B) per epilogue warp
+  // store staging: buffers of 32 rows x 64 B per epilogue warp (8 warps stage stores; the 5-stage
+  // grouped form has room for one buffer each, the others for two)
+  static constexpr int SBUFS = (GROUPED && STAGES >= 5) ? 1 : 2;
   static constexpr int STAGING_BYTES = 8 * SBUFS * 2048;
   static constexpr int ITEM_CACHE = GROUPED ? 96 : 0;    // this pair's first work items, copied to smem
   static constexpr int TOTAL = STAGES * STAGE_BYTES + STAGING_BYTES + ITEM_CACHE * 32 + 1024 + 256;
@@ -159,12 +162,15 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
       int ti = 0;
       for (int t = pair_id; t < total_tiles && !*abort_flag; t += num_pairs, ++ti) {
         int pt, qt, q_row, q_blk, expert = 0;
+        int nq = 0, nsf = 0;       // grouped: 32-row Q boxes per CTA, 128-row scale groups the window touches
         if (GROUPED) {
           const GroupItem item = ti < L::ITEM_CACHE ? item_cache[ti] : work->items[t / p.p_tiles];
           pt = t % p.p_tiles;
           q_row = item.q_row0 + static_cast<int>(rank) * (item.n_tokens >> 1);
           q_blk = item.q_row0 >> 7;
           expert = item.expert;
+          nq = ((item.n_tokens >> 1) + 31) >> 5;
+          nsf = ((item.q_row0 + item.n_tokens - 1) >> 7) - q_blk + 1;
         } else {
           tile_coords(t, p, pt, qt);
           if (SWIGLU) {
@@ -183,11 +189,22 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
           }
           const uint32_t st = smem0 + s * L::STAGE_BYTES;
           const uint32_t bar = full0 + s * 8;
-          if (leader) ptx::mbar_expect_tx(&full[s], 2 * L::STAGE_BYTES);
           if (GROUPED) {
+            // the token window is loaded at its size: 32-row boxes of Q and only the scale groups it touches
+            if (leader)
+              ptx::mbar_expect_tx(&full[s], 2 * (L::A_BYTES + L::SFP_BYTES + nq * 4096 + nsf * KT_PER_STAGE * SF_TILE));
             ptx::tma_load_3d_pair(st, &maps.p, bar, ks * 128, p_row, expert);
             ptx::tma_load_4d_pair(st + L::A_BYTES + L::B_BYTES, &maps.sfp, bar, 0, ks * KT_PER_STAGE, p_blk, expert);
-          } else {
+            for (int i = 0; i < nq; ++i)
+              ptx::tma_load_2d_pair(st + L::A_BYTES + i * 4096, &maps.q, bar, ks * 128, q_row + 32 * i);
+            for (int b = 0; b < nsf; ++b)
+              ptx::tma_load_3d_pair(st + L::A_BYTES + L::B_BYTES + L::SFP_BYTES + b * KT_PER_STAGE * SF_TILE, &maps.sfq,
+                                    bar, 0, ks * KT_PER_STAGE, q_blk + b);
+            if (++s == STAGES) { s = 0; ph ^= 1u; }
+            continue;
+          }
+          if (leader) ptx::mbar_expect_tx(&full[s], 2 * L::STAGE_BYTES);
+          {
             ptx::tma_load_2d_pair(st, &maps.p, bar, ks * 128, p_row);
             ptx::tma_load_3d_pair(st + L::A_BYTES + L::B_BYTES, &maps.sfp, bar, 0, ks * KT_PER_STAGE, p_blk);
           }
@@ -287,11 +304,15 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
     // the arithmetic.
     const int ew = warp - 2;
     const int quarter = warp & 3;          // a warp reaches only the TMEM lanes of sub-partition warp_id % 4
-    const int half = ew >> 2;
-    constexpr int NCH = CHUNKS / 2;                                      // chunks per warp
-    static_assert(CHUNKS % 2 == 0 && RELEASE_CHUNKS <= NCH, "chunk split");
+    const int half = ew >> 2;                                            // which share of the chunks (0 .. PARTS-1)
+    // 8 epilogue warps split the chunks in two shares (16 in the SwiGLU form, which has its own loop below;
+    // 16 warps were tried for the grouped form too: 6 % faster at K = 768, 4 % slower at K = 2048)
+    constexpr int PARTS = SWIGLU ? 4 : 2;
+    constexpr int NCH = CHUNKS / PARTS;                                  // chunks per warp
+    constexpr int WARP_BUFS = L::SBUFS;                                  // staging buffers per warp
+    static_assert(CHUNKS % PARTS == 0 && RELEASE_CHUNKS <= NCH, "chunk split");
     const uint32_t free_addr = ptx::mapa(ptx::smem_u32(acc_free), 0);   // the leader's barrier
-    const uint32_t stage_base = ptx::smem_u32(staging) + ew * (L::SBUFS * 2048);
+    const uint32_t stage_base = ptx::smem_u32(staging) + ew * (WARP_BUFS * 2048);
     const int row_in_tile = static_cast<int>(rank) * 128 + quarter * 32;
     uint32_t nstore = 0;                  // TMA stores issued by this warp (2 staging buffers)
     int tl = 0;
@@ -312,13 +333,14 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
         break;
       }
       ptx::tc_fence_after();
-      const bool first_half = half == (a ? 0 : 1);          // owns drain positions [0, NCH)
+      const int drain_rank = a ? half : PARTS - 1 - half;   // this warp owns drain positions [rank * NCH, +NCH)
+      const bool first_half = drain_rank == 0;              // ... the first of which are the shared columns
       const bool tr = p.trace != nullptr && pair_id == 0 && tl < 32 && leader && quarter == 0 && lane == 0;
       if (tr) p.trace[tl * 8 + (first_half ? 3 : 6)] = clock64();
       const int prow = pt * 256 + row_in_tile + lane;       // dense: output row; grouped: output column
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + (a ? L::ACC1 : 0);
       auto chunk_of = [&](int j) {                          // j-th chunk of this warp -> column chunk
-        const int pos = (first_half ? 0 : NCH) + j;
+        const int pos = drain_rank * NCH + j;
         return a ? pos : CHUNKS - 1 - pos;
       };
       auto chunk_live = [&](int cchunk) {                   // warp-uniform: anything to write?
@@ -398,15 +420,15 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
         // after the arithmetic of this chunk its buffer is reloaded with chunk j+2 (see loop end)
         if (live) {
         const uint32_t (&v32)[32] = r[j & 1];
-        const uint32_t buf = stage_base + (nstore % L::SBUFS) * 2048u;
+        const uint32_t buf = stage_base + (nstore % WARP_BUFS) * 2048u;
         if (GROUPED) {
           const int tok0 = item.q_row0 + cchunk * 32;
           const int n0 = pt * 256 + row_in_tile;            // first output column of this warp
           if (tok0 >= item.lo && tok0 + 32 <= item.hi) {
             // all 32 token rows belong to the expert: transpose through shared memory
             // ([token][weight row], 64-byte TMA swizzle) and let TMA write (and clip) the box
-            if (nstore >= L::SBUFS) {
-              if (lane == 0) ptx::bulk_wait_group_read<L::SBUFS - 1>();
+            if (nstore >= WARP_BUFS) {
+              if (lane == 0) ptx::bulk_wait_group_read<WARP_BUFS - 1>();
               __syncwarp();
             }
             const uint32_t piece = static_cast<uint32_t>(lane) >> 3, within = (static_cast<uint32_t>(lane) & 7u) * 2u;
@@ -435,8 +457,8 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
           // this lane's 32 outputs of row prow -> 64 bytes of bf16 in a staging buffer laid out
           // as the 64-byte TMA swizzle expects (16-byte piece index ^ ((row >> 1) & 3))
           const int q_base = qt * BN + cchunk * 32;
-          if (nstore >= L::SBUFS) {                         // the store that last read this buffer is done
-            if (lane == 0) ptx::bulk_wait_group_read<L::SBUFS - 1>();
+          if (nstore >= WARP_BUFS) {                         // the store that last read this buffer is done
+            if (lane == 0) ptx::bulk_wait_group_read<WARP_BUFS - 1>();
             __syncwarp();
           }
           const int64_t off = static_cast<int64_t>(prow) * p.ldd + q_base;
