@@ -612,7 +612,9 @@ def run_cpu_port(args, steps, sample_rows, warmup=0):
     from oracle import nvfp4_oracle as O
     name, M, H, layers = WORKLOADS[args.workload]
     rng = np.random.default_rng(7)
-    threads = torch.get_num_threads()
+    # every host thread this process may use (a launcher may have pinned OMP_NUM_THREADS to 1)
+    threads = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    torch.set_num_threads(threads)
     bf = lambda a: O.f32_to_bf16_bits(a.astype(np.float32))
     hidden, residual = bf(rng.standard_normal((sample_rows, H))), bf(rng.standard_normal((sample_rows, H)))
     norm_w = bf(1 + 0.1 * rng.standard_normal(H))
@@ -659,10 +661,11 @@ def run_reference(args, rank, world):
     if rank != 0:
         return
     rows = 64
-    res = run_cpu_port(args, steps=max(1, min(args.steps, 3)), sample_rows=rows, warmup=min(args.warmup, 1))
+    steps_run = max(1, min(args.steps, 3))       # bounded: each step is a 64-token sample of the workload
+    res = run_cpu_port(args, steps=steps_run, sample_rows=rows, warmup=min(args.warmup, 1))
     name, M, H, layers = WORKLOADS[args.workload]
     line = {"impl": "reference", "metric": "nvfp4_linear_path_tflops", "value": res["value"], "unit": "TFLOP/s",
-            "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "n_gpus": world, "steps": steps_run, "warmup": min(args.warmup, 1),
             "ms_per_step": round(res["ms_per_step_sample"] * M / rows, 3), "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "fp32 (dequantised NVFP4)", "data": "synthetic",
             "config": {"workload": name, "tokens": M, "hidden": H,

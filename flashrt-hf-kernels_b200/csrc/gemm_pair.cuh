@@ -27,6 +27,7 @@
 
 struct PairMaps {
   CUtensorMap p, q, sfp, sfq;
+  CUtensorMap q32;    // Q with a 32-row box (dense form: the narrow tiles of the last wave)
   CUtensorMap d;      // bf16 output [M, N], box 32 columns x 32 rows, 64-byte swizzle (dense form only)
 };
 
@@ -44,6 +45,22 @@ struct GroupWork {
   int pad[3];
   GroupItem items[1];
 };
+
+// Dense form, last wave: when the tile count is not a multiple of the CTA-pair count, the tiles of
+// the last (partial) wave are cut into 2 or 4 column slices so that every pair gets one; a work
+// unit below `tail_first` is a whole tile, above it a slice of width 256 / tail_split.
+__device__ __forceinline__ void decode_unit(int u, const GemmParams& p, int& pt, int& qt, int& col0, int& width) {
+  int t = u;
+  col0 = 0;
+  width = 256;
+  if (u >= p.tail_first) {
+    const int v = u - p.tail_first;
+    t = p.tail_first + v / p.tail_split;
+    width = 256 / p.tail_split;
+    col0 = (v % p.tail_split) * width;
+  }
+  tile_coords(t, p, pt, qt);
+}
 
 template <int BN, int STAGES, bool GROUPED = false>
 struct PairLayout {
@@ -115,7 +132,9 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
   const int pair_id = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
   pdl_launch_dependents();
-  int total_tiles = GROUPED ? 0 : p.p_tiles * p.q_tiles;     // grouped: read from the plan after the wait below
+  // work units: grouped: read from the plan after the wait below; dense: tiles, the last wave sliced
+  int total_tiles = GROUPED ? 0 : (SWIGLU || BN != 256) ? p.p_tiles * p.q_tiles : p.units;
+  constexpr bool SLICED = !GROUPED && !SWIGLU && BN == 256;
   const int k_stages = (p.k_tiles + KT_PER_STAGE - 1) / KT_PER_STAGE;
 
   if (threadIdx.x == 0) {
@@ -171,6 +190,12 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
           expert = item.expert;
           nq = ((item.n_tokens >> 1) + 31) >> 5;
           nsf = ((item.q_row0 + item.n_tokens - 1) >> 7) - q_blk + 1;
+        } else if (SLICED) {
+          int col0, width;
+          decode_unit(t, p, pt, qt, col0, width);
+          q_row = qt * BN + col0 + static_cast<int>(rank) * (width >> 1);
+          q_blk = (qt * BN + col0) >> 7;
+          nq = width == 256 ? 0 : width >> 6;       // 32-row boxes per CTA of a slice; 0 = one 128-row box
         } else {
           tile_coords(t, p, pt, qt);
           if (SWIGLU) {
@@ -203,12 +228,17 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
             if (++s == STAGES) { s = 0; ph ^= 1u; }
             continue;
           }
-          if (leader) ptx::mbar_expect_tx(&full[s], 2 * L::STAGE_BYTES);
+          if (leader) ptx::mbar_expect_tx(&full[s], 2 * (L::STAGE_BYTES - (nq ? L::B_BYTES - nq * 4096 : 0)));
           {
             ptx::tma_load_2d_pair(st, &maps.p, bar, ks * 128, p_row);
             ptx::tma_load_3d_pair(st + L::A_BYTES + L::B_BYTES, &maps.sfp, bar, 0, ks * KT_PER_STAGE, p_blk);
           }
-          ptx::tma_load_2d_pair(st + L::A_BYTES, &maps.q, bar, ks * 128, q_row);
+          if (SLICED && nq) {
+            for (int i = 0; i < nq; ++i)
+              ptx::tma_load_2d_pair(st + L::A_BYTES + i * 4096, &maps.q32, bar, ks * 128, q_row + 32 * i);
+          } else {
+            ptx::tma_load_2d_pair(st + L::A_BYTES, &maps.q, bar, ks * 128, q_row);
+          }
           ptx::tma_load_3d_pair(st + L::A_BYTES + L::B_BYTES + L::SFP_BYTES, &maps.sfq, bar, 0, ks * KT_PER_STAGE,
                                 q_blk);
           if (SWIGLU)   // the map's box is one 128-row group: gate scales above, up scales here
@@ -255,6 +285,11 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
           const GroupItem item = tl < L::ITEM_CACHE ? item_cache[tl] : work->items[t / p.p_tiles];
           qoff = (static_cast<uint32_t>(item.q_row0) & 127u) >> 5;
           idesc = ptx::idesc_nvf4(256, item.n_tokens);
+        } else if (SLICED) {
+          int pt, qt, col0, width;
+          decode_unit(t, p, pt, qt, col0, width);
+          qoff = (static_cast<uint32_t>(qt * BN + col0) & 127u) >> 5;
+          if (width != 256) idesc = ptx::idesc_nvf4(256, width);
         } else {
           int pt, qt;
           tile_coords(t, p, pt, qt);
@@ -317,13 +352,15 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
     uint32_t nstore = 0;                  // TMA stores issued by this warp (2 staging buffers)
     int tl = 0;
     for (int t = pair_id; t < total_tiles && !*abort_flag; t += num_pairs, ++tl) {
-      int pt, qt = 0;
+      int pt, qt = 0, col0 = 0, width = BN;
       GroupItem item{};
       float alpha = p.alpha;
       if (GROUPED) {
         item = tl < L::ITEM_CACHE ? item_cache[tl] : work->items[t / p.p_tiles];
         pt = t % p.p_tiles;
         alpha = p.alpha_stack[item.expert];
+      } else if (SLICED) {
+        decode_unit(t, p, pt, qt, col0, width);
       } else {
         tile_coords(t, p, pt, qt);
       }
@@ -348,7 +385,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
           const int tok0 = item.q_row0 + cchunk * 32;
           return cchunk * 32 < item.n_tokens && tok0 < item.hi && tok0 + 32 > item.lo;
         }
-        return qt * BN + cchunk * 32 < p.Q;
+        return cchunk * 32 < width && qt * BN + col0 + cchunk * 32 < p.Q;
       };
       auto release = [&]() {
         ptx::tc_fence_before();
@@ -456,7 +493,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
         } else {
           // this lane's 32 outputs of row prow -> 64 bytes of bf16 in a staging buffer laid out
           // as the 64-byte TMA swizzle expects (16-byte piece index ^ ((row >> 1) & 3))
-          const int q_base = qt * BN + cchunk * 32;
+          const int q_base = qt * BN + col0 + cchunk * 32;
           if (nstore >= WARP_BUFS) {                         // the store that last read this buffer is done
             if (lane == 0) ptx::bulk_wait_group_read<WARP_BUFS - 1>();
             __syncwarp();
