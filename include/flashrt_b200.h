@@ -211,7 +211,8 @@ int frt_router_topk_bf16(const void* logits, void* out_idx, void* out_val,
  *   expert_offsets i32 [n_experts + 1]  rows of expert e are [offsets[e], offsets[e+1])
  *   row_of_pair    i32 [tokens * k]     expert-sorted row of pair (t, j); -1 if its index is
  *                                       outside [0, n_experts)
- *   token_of_row   i32 [tokens * k]     source token of each expert-sorted row
+ *   token_of_row   i32 [tokens * k]     source token of each expert-sorted row (entries at and
+ *                                       beyond expert_offsets[n_experts] are not written)
  * The reference leaves this stage to the caller ("stable routing sort, expert-tile packing
  * ... remain explicit structure-level stages", grouped-moe-gemm/README.md:13-16). */
 int frt_moe_route_plan(const void* topk_idx, int tokens, int k, int n_experts,

@@ -1,6 +1,8 @@
 """The C-ABI library loads on a machine without a GPU and exports every symbol
 that include/flashrt_b200.h declares (no compute calls here)."""
 import re
+
+import pytest
 import sys
 from pathlib import Path
 
@@ -38,3 +40,16 @@ def test_host_only_entry_points():
         assert lib.frt_nvfp4_sf_offset(r, kb * 16, 704) == offs[r, kb]
     assert lib.frt_error_string(0) == b"ok"
     assert lib.frt_launch_count() >= 0
+
+
+def test_header_is_plain_c(tmp_path):
+    """the boundary is a C ABI: the header must compile as C99 with no C++ or torch types"""
+    import shutil
+    import subprocess
+    cc = shutil.which("gcc") or shutil.which("cc")
+    if cc is None:
+        pytest.skip("no C compiler")
+    src = tmp_path / "use_header.c"
+    src.write_text('#include "flashrt_b200.h"\nint main(void) { return frt_error_string(0) == 0; }\n')
+    root = Path(__file__).resolve().parent.parent
+    subprocess.run([cc, "-std=c99", "-Wall", "-Werror", f"-I{root / 'include'}", "-fsyntax-only", str(src)], check=True)
