@@ -215,11 +215,30 @@ struct NormParams {
   uint4* normed;          // bf16 [rows, dim] or null
   uint2* packed;          // u8   [rows, dim/2] or null when QUANT is false
   uint8_t* sf;            // swizzled scales
+  uint4* out_fp8;         // e4m3 [rows, dim] or null: static-scale FP8 output of the normalised values
+  const float* fp8_scale; // device scalar: out_fp8 = e4m3(clamp(v / scale, +-448))
   int rows, nb, sf_cols;
   float eps, inv_global_scale;
   float dim_f;
   unsigned flags;
 };
+
+// 16 fp32 values -> 16 e4m3 bytes with a static scale: e4m3_rn(clamp(v * inv_scale, +-448))
+// (flashrt-residual-norm-quant/csrc/residual_norm_quant.cu:54-57).
+__device__ __forceinline__ uint4 fp8_static16(const float (&v)[16], float inv_scale) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint32_t word = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float q = fminf(fmaxf(__fmul_rn(v[4 * i + j], inv_scale), -448.f), 448.f);
+      word |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(q, __NV_SATFINITE, __NV_E4M3)) << (8 * j);
+    }
+    w[i] = word;
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
 
 __device__ __forceinline__ void pack16_bf16(const float (&v)[16], uint4& o0, uint4& o1) {
   o0.x = pack_bf16x2(v[0], v[1]);   o0.y = pack_bf16x2(v[2], v[3]);
@@ -328,6 +347,7 @@ norm_quant_kernel(const NormParams p) {
       unpack_bf16x8(o1, v + 8);
     }
   }
+  if (!QUANT && p.out_fp8 != nullptr) p.out_fp8[idx] = fp8_static16(v, __fdiv_rn(1.f, __ldg(p.fp8_scale)));
   if (QUANT) {
     uint8_t sfb;
     uint2 out;
@@ -336,6 +356,89 @@ norm_quant_kernel(const NormParams p) {
     p.packed[idx] = out;
     p.sf[sf_offset(row, s, p.sf_cols)] = sfb;
   }
+}
+
+// ---------------------------------------------------------------------------
+// LayerNorm (bf16, affine weight and bias): the same one-thread-per-block cover as the RMSNorm
+// kernel with two row reductions (mean, then the squared deviations), fp32 throughout:
+//   y = bf16(((x - mean) * inv_std) * w + b).
+// Summation order of each reduction: thread over its 16 elements in order, warp butterfly,
+// warps in order.
+// ---------------------------------------------------------------------------
+template <int TPR>
+__global__ void __launch_bounds__(TPR > 256 ? TPR : 256)
+layer_norm_kernel(const uint4* __restrict__ x, const uint4* __restrict__ weight, const uint4* __restrict__ bias,
+                  uint4* __restrict__ out, int rows, int nb, float dim_f, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int CTA = TPR > 256 ? TPR : 256;
+  constexpr int ROWS_PER_CTA = CTA / TPR;
+  constexpr int WPR = TPR / 32;
+  __shared__ float warp_sums[2][CTA / 32];
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int row = blockIdx.x * ROWS_PER_CTA + threadIdx.x / TPR;
+  const int s = threadIdx.x % TPR;
+  const bool ok = row < rows && s < nb;
+  const int64_t idx = static_cast<int64_t>(row) * nb + s;
+  float v[16];
+  uint4 x0 = make_uint4(0, 0, 0, 0), x1 = x0;
+  if (ok) {
+    x0 = __ldcs(x + 2 * idx);
+    x1 = __ldcs(x + 2 * idx + 1);
+  }
+  unpack_bf16x8(x0, v);
+  unpack_bf16x8(x1, v + 8);
+  auto row_total = [&](float part, int buf) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) part = __fadd_rn(part, __shfl_xor_sync(0xffffffffu, part, o));
+    float total = part;
+    if (WPR > 1) {
+      if (lane == 0) warp_sums[buf][warp] = part;
+      __syncthreads();
+      const int first = (warp / WPR) * WPR;
+      total = warp_sums[buf][first];
+#pragma unroll
+      for (int w = 1; w < WPR; ++w) total = __fadd_rn(total, warp_sums[buf][first + w]);
+    }
+    return total;
+  };
+  float part = 0.f;
+#pragma unroll
+  for (int j = 0; j < 16; ++j) part = __fadd_rn(part, v[j]);
+  const float mean = __fdiv_rn(row_total(part, 0), dim_f);
+  part = 0.f;
+  if (ok) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const float d = __fsub_rn(v[j], mean);
+      part = __fadd_rn(part, __fmul_rn(d, d));
+    }
+  }
+  const float inv_std = __frsqrt_rn(__fadd_rn(__fdiv_rn(row_total(part, 1), dim_f), eps));
+  if (!ok) return;
+  float g[16], b[16];
+  unpack_bf16x8(__ldg(weight + 2 * s), g);
+  unpack_bf16x8(__ldg(weight + 2 * s + 1), g + 8);
+  unpack_bf16x8(__ldg(bias + 2 * s), b);
+  unpack_bf16x8(__ldg(bias + 2 * s + 1), b + 8);
+#pragma unroll
+  for (int j = 0; j < 16; ++j)
+    v[j] = __fadd_rn(__fmul_rn(__fmul_rn(__fsub_rn(v[j], mean), inv_std), g[j]), b[j]);
+  uint4 o0, o1;
+  pack16_bf16(v, o0, o1);
+  out[2 * idx] = o0;
+  out[2 * idx + 1] = o1;
+}
+
+template <int TPR>
+int launch_layer_norm(const uint4* x, const uint4* w, const uint4* b, uint4* out, int rows, int nb, float dim_f,
+                      float eps, cudaStream_t st) {
+  constexpr int CTA = TPR > 256 ? TPR : 256;
+  constexpr int rows_per_cta = CTA / TPR;
+  launch_pdl(layer_norm_kernel<TPR>, dim3((rows + rows_per_cta - 1) / rows_per_cta), dim3(CTA), 0, st, x, w, b, out,
+             rows, nb, dim_f, eps);
+  return launch_result();
 }
 
 // ---------------------------------------------------------------------------
@@ -552,7 +655,8 @@ int launch_norm(const NormParams& p, bool has_res, bool quant, cudaStream_t st) 
   // warps per SM hide the latency by themselves); for wider rows the CTA-wide barrier of a
   // 512/1024-thread CTA stalls the SM and the staged persistent form is 15-35 % faster.
   // Debug bits 32 / 64 force one form or the other.
-  const bool stream = (g_opt_gemm_debug & 64) || (!(g_opt_gemm_debug & 32) && TPR > (quant ? 256 : 512));
+  const bool stream = p.out_fp8 == nullptr &&
+                      ((g_opt_gemm_debug & 64) || (!(g_opt_gemm_debug & 32) && TPR > (quant ? 256 : 512)));
   if (!stream) {
     constexpr int CTA = TPR > 256 ? TPR : 256;
     constexpr int rows_per_cta = CTA / TPR;
@@ -749,6 +853,44 @@ int frt_rms_norm_bf16(const void* x, const void* weight, void* out, int rows, in
   p.rows = rows; p.nb = dim / 16; p.sf_cols = (dim + 63) / 64;
   p.eps = eps; p.inv_global_scale = 1.0f; p.dim_f = static_cast<float>(dim);
   return dispatch_norm(p, false, false, as_stream(stream));
+}
+
+int frt_layer_norm_bf16(const void* x, const void* weight, const void* bias, void* out, int rows, int dim, float eps,
+                        void* stream) {
+  if (int rc = check_norm_args(x, rows, dim)) return rc;
+  if (!weight || !bias || !out) return FRT_E_NULL;
+  if (!aligned(x, 16) || !aligned(weight, 16) || !aligned(bias, 16) || !aligned(out, 16)) return FRT_E_ALIGN;
+  const int nb = dim / 16;
+  auto xs = static_cast<const uint4*>(x);
+  auto w = static_cast<const uint4*>(weight);
+  auto b = static_cast<const uint4*>(bias);
+  auto o = static_cast<uint4*>(out);
+  const float dim_f = static_cast<float>(dim);
+  cudaStream_t st = as_stream(stream);
+  if (nb <= 32) return launch_layer_norm<32>(xs, w, b, o, rows, nb, dim_f, eps, st);
+  if (nb <= 64) return launch_layer_norm<64>(xs, w, b, o, rows, nb, dim_f, eps, st);
+  if (nb <= 128) return launch_layer_norm<128>(xs, w, b, o, rows, nb, dim_f, eps, st);
+  if (nb <= 256) return launch_layer_norm<256>(xs, w, b, o, rows, nb, dim_f, eps, st);
+  if (nb <= 512) return launch_layer_norm<512>(xs, w, b, o, rows, nb, dim_f, eps, st);
+  return launch_layer_norm<1024>(xs, w, b, o, rows, nb, dim_f, eps, st);
+}
+
+int frt_rms_norm_quant_fp8(void* residual, const void* x, const void* weight, const void* scale, void* out_fp8,
+                           int rows, int dim, float eps, void* stream) {
+  if (int rc = check_norm_args(x, rows, dim)) return rc;
+  if (!weight || !scale || !out_fp8) return FRT_E_NULL;
+  if (!aligned(x, 16) || !aligned(weight, 16) || !aligned(out_fp8, 16) || !aligned(residual, 16) || !aligned(scale, 4))
+    return FRT_E_ALIGN;
+  NormParams p{};
+  p.residual = static_cast<uint4*>(residual);
+  p.x = static_cast<const uint4*>(x);
+  p.weight = static_cast<const uint4*>(weight);
+  p.out_fp8 = static_cast<uint4*>(out_fp8);
+  p.fp8_scale = static_cast<const float*>(scale);
+  p.rows = rows; p.nb = dim / 16; p.sf_cols = (dim + 63) / 64;
+  p.eps = eps; p.inv_global_scale = 1.0f; p.dim_f = static_cast<float>(dim);
+  p.flags = residual ? FRT_PRODUCER_NORM_FROM_BF16_RESIDUAL : 0u;
+  return dispatch_norm(p, residual != nullptr, false, as_stream(stream));
 }
 
 int frt_residual_add_rms_norm_bf16(void* residual, const void* x, const void* weight, void* out,

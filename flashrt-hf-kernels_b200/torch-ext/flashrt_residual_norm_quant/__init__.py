@@ -1,7 +1,6 @@
-"""BF16 RMSNorm ops (B200 build) with the reference package's function names
-(flashrt-residual-norm-quant/torch-ext/flashrt_residual_norm_quant/__init__.py:97-175).
-The FP8 and LayerNorm members of that package are outside the NVFP4 path and
-are not provided here."""
+"""The norm package (B200 build): BF16 RMSNorm / residual RMSNorm, LayerNorm and the static-scale
+FP8 variants, with the reference package's function names and schemas
+(flashrt-residual-norm-quant/torch-ext/flashrt_residual_norm_quant/__init__.py:97-175)."""
 from __future__ import annotations
 
 import torch
@@ -32,6 +31,54 @@ def _residual_add_rms_norm_fake(residual, x, weight, eps, out) -> None:
     return None
 
 
+@torch.library.register_fake(add_op_namespace_prefix("layer_norm_bf16"))
+def _layer_norm_fake(x, weight, bias, eps, out) -> None:
+    _check(x, out, "out")
+    if weight.shape != (x.shape[1],) or bias.shape != (x.shape[1],):
+        raise RuntimeError("weight and bias must have shape (x.shape[1],)")
+    return None
+
+
+@torch.library.register_fake(add_op_namespace_prefix("rms_norm_quant_fp8_static_bf16"))
+def _rms_norm_fp8_fake(x, weight, scale, eps, out) -> None:
+    _check(x, out, "out")
+    if weight.shape != (x.shape[1],):
+        raise RuntimeError("weight must have shape (x.shape[1],)")
+    return None
+
+
+@torch.library.register_fake(add_op_namespace_prefix("residual_add_rms_norm_quant_fp8_static_bf16"))
+def _residual_add_rms_norm_fp8_fake(residual, x, weight, scale, eps, out) -> None:
+    if residual.shape != x.shape:
+        raise RuntimeError("residual and x must have the same shape")
+    _check(x, out, "out")
+    return None
+
+
+def layer_norm_bf16(x, weight, bias, eps: float = 1e-5, out=None):
+    """BF16 LayerNorm with affine weight and bias."""
+    if out is None:
+        out = torch.empty_like(x, dtype=torch.bfloat16)
+    ops.layer_norm_bf16(x, weight, bias, float(eps), out)
+    return out
+
+
+def rms_norm_quant_fp8_static_bf16(x, weight, scale, eps: float = 1e-6, out=None):
+    """BF16 RMSNorm followed by static-scale FP8 E4M3 quantization."""
+    if out is None:
+        out = torch.empty_like(x, dtype=torch.float8_e4m3fn)
+    ops.rms_norm_quant_fp8_static_bf16(x, weight, scale, float(eps), out)
+    return out
+
+
+def residual_add_rms_norm_quant_fp8_static_bf16(residual, x, weight, scale, eps: float = 1e-6, out=None):
+    """In-place ``residual += x`` then RMSNorm and static FP8 quantization."""
+    if out is None:
+        out = torch.empty_like(x, dtype=torch.float8_e4m3fn)
+    ops.residual_add_rms_norm_quant_fp8_static_bf16(residual, x, weight, scale, float(eps), out)
+    return out
+
+
 def rms_norm_bf16(x, weight, eps: float = 1e-6, out=None):
     """BF16 RMSNorm with affine weight."""
     if out is None:
@@ -48,4 +95,5 @@ def residual_add_rms_norm_bf16(residual, x, weight, eps: float = 1e-6, out=None)
     return out
 
 
-__all__ = ["rms_norm_bf16", "residual_add_rms_norm_bf16"]
+__all__ = ["layer_norm_bf16", "residual_add_rms_norm_quant_fp8_static_bf16", "rms_norm_quant_fp8_static_bf16",
+           "rms_norm_bf16", "residual_add_rms_norm_bf16"]

@@ -250,6 +250,38 @@ void rms_norm_bf16(const Tensor& x, const Tensor& weight, double eps, Tensor& ou
   check_rc(frt_rms_norm_bf16(x.data_ptr(), weight.data_ptr(), out.data_ptr(), as_int(x.size(0), "rows"),
                              as_int(x.size(1), "dim"), static_cast<float>(eps), stream_of(x)), "rms_norm_bf16");
 }
+void layer_norm_bf16(const Tensor& x, const Tensor& weight, const Tensor& bias, double eps, Tensor& out) {
+  check_norm_inputs(x, &weight, &out, "out");
+  check_dtype(bias, torch::kBFloat16, "bias", "torch.bfloat16");
+  TORCH_CHECK(bias.dim() == 1 && bias.size(0) == x.size(1), "bias must have shape (dim,)");
+  check_same_device(x, bias, "x", "bias");
+  c10::cuda::CUDAGuard guard(x.device());
+  check_rc(frt_layer_norm_bf16(x.data_ptr(), weight.data_ptr(), bias.data_ptr(), out.data_ptr(),
+                               as_int(x.size(0), "rows"), as_int(x.size(1), "dim"), static_cast<float>(eps),
+                               stream_of(x)), "layer_norm_bf16");
+}
+void fp8_norm_call(Tensor* residual, const Tensor& x, const Tensor& weight, const Tensor& scale, double eps, Tensor& out,
+                   const char* op) {
+  check_norm_inputs(x, &weight, residual, "residual");
+  check_dtype(scale, torch::kFloat32, "scale", "torch.float32");
+  TORCH_CHECK(scale.numel() == 1, "scale must hold one float32 value");
+  check_cuda(out, "out");
+  TORCH_CHECK(out.scalar_type() == torch::kFloat8_e4m3fn, "out must be torch.float8_e4m3fn");
+  TORCH_CHECK(out.sizes() == x.sizes(), "out and x must have the same 2D shape");
+  check_same_device(x, scale, "x", "scale");
+  check_same_device(x, out, "x", "out");
+  c10::cuda::CUDAGuard guard(x.device());
+  check_rc(frt_rms_norm_quant_fp8(residual ? residual->data_ptr() : nullptr, x.data_ptr(), weight.data_ptr(),
+                                  scale.data_ptr(), out.data_ptr(), as_int(x.size(0), "rows"),
+                                  as_int(x.size(1), "dim"), static_cast<float>(eps), stream_of(x)), op);
+}
+void rms_norm_quant_fp8_static_bf16(const Tensor& x, const Tensor& weight, const Tensor& scale, double eps, Tensor& out) {
+  fp8_norm_call(nullptr, x, weight, scale, eps, out, "rms_norm_quant_fp8_static_bf16");
+}
+void residual_add_rms_norm_quant_fp8_static_bf16(Tensor& residual, const Tensor& x, const Tensor& weight,
+                                                 const Tensor& scale, double eps, Tensor& out) {
+  fp8_norm_call(&residual, x, weight, scale, eps, out, "residual_add_rms_norm_quant_fp8_static_bf16");
+}
 void residual_add_rms_norm_bf16(Tensor& residual, const Tensor& x, const Tensor& weight, double eps, Tensor& out) {
   check_norm_inputs(x, &weight, &out, "out");
   check_norm_inputs(x, nullptr, &residual, "residual");
@@ -501,6 +533,12 @@ TORCH_LIBRARY_EXPAND(flashrt_residual_norm_quant_b200, ops) {
   ops.def("residual_add_rms_norm_bf16(Tensor! residual, Tensor x, Tensor weight, float eps, Tensor! out) -> ()");
   ops.impl("rms_norm_bf16", torch::kCUDA, &rms_norm_bf16);
   ops.impl("residual_add_rms_norm_bf16", torch::kCUDA, &residual_add_rms_norm_bf16);
+  ops.def("layer_norm_bf16(Tensor x, Tensor weight, Tensor bias, float eps, Tensor! out) -> ()");
+  ops.def("rms_norm_quant_fp8_static_bf16(Tensor x, Tensor weight, Tensor scale, float eps, Tensor! out) -> ()");
+  ops.def("residual_add_rms_norm_quant_fp8_static_bf16(Tensor! residual, Tensor x, Tensor weight, Tensor scale, float eps, Tensor! out) -> ()");
+  ops.impl("layer_norm_bf16", torch::kCUDA, &layer_norm_bf16);
+  ops.impl("rms_norm_quant_fp8_static_bf16", torch::kCUDA, &rms_norm_quant_fp8_static_bf16);
+  ops.impl("residual_add_rms_norm_quant_fp8_static_bf16", torch::kCUDA, &residual_add_rms_norm_quant_fp8_static_bf16);
 }
 
 TORCH_LIBRARY_EXPAND(fp4_gemm_b200, ops) {

@@ -87,6 +87,20 @@ int frt_rms_norm_bf16(const void* x, const void* weight, void* out,
 int frt_residual_add_rms_norm_bf16(void* residual, const void* x, const void* weight, void* out,
                                    int rows, int dim, float eps, void* stream);
 
+/* LayerNorm, bf16 in / out, affine bf16 weight and bias [dim]:
+ *   out = bf16(((x - mean) * rsqrt(var + eps)) * w + b), fp32 statistics (two row reductions).
+ * replaces layer_norm_bf16, flashrt-residual-norm-quant/csrc/residual_norm_quant.cuh:18 */
+int frt_layer_norm_bf16(const void* x, const void* weight, const void* bias, void* out,
+                        int rows, int dim, float eps, void* stream);
+
+/* (residual-add +) RMSNorm -> FP8 E4M3 with a static per-tensor scale (device scalar `scale`):
+ *   residual (or null) <- bf16(residual + x);  v = (in * rstd) * w  (in = the rounded residual, or x);
+ *   out_fp8[rows, dim] = e4m3_rn(clamp(v * (1 / scale), +-448)).
+ * replaces rms_norm_quant_fp8_static_bf16 and residual_add_rms_norm_quant_fp8_static_bf16,
+ *   flashrt-residual-norm-quant/csrc/residual_norm_quant.cuh:28,38 */
+int frt_rms_norm_quant_fp8(void* residual, const void* x, const void* weight, const void* scale,
+                           void* out_fp8, int rows, int dim, float eps, void* stream);
+
 /* ---- fused (residual-add +) RMSNorm -> NVFP4 producer -------------------
  * One pass over HBM: reads x (and residual), writes residual in place,
  * packed e2m1, swizzled UE4M3 scales and, if `normed` is non-null, the bf16

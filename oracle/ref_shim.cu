@@ -71,6 +71,20 @@ int ref_residual_add_rms_norm_bf16(void* res, const void* x, const void* w, void
   flash_rt::residual_norm_quant::residual_add_rms_norm_bf16(res, x, w, out, rows, dim, eps, S(st));
   return 0;
 }
+int ref_layer_norm_bf16(const void* x, const void* w, const void* b, void* out, int rows, int dim, float eps, void* st) {
+  flash_rt::residual_norm_quant::layer_norm_bf16(x, w, b, out, rows, dim, eps, S(st));
+  return 0;
+}
+int ref_rms_norm_quant_fp8(void* res, const void* x, const void* w, void* out, int rows, int dim, float eps,
+                           const void* scale, void* st) {
+  if (res)
+    flash_rt::residual_norm_quant::residual_add_rms_norm_quant_fp8_static_bf16(
+        res, x, w, out, rows, dim, eps, static_cast<const float*>(scale), S(st));
+  else
+    flash_rt::residual_norm_quant::rms_norm_quant_fp8_static_bf16(x, w, out, rows, dim, eps,
+                                                                   static_cast<const float*>(scale), S(st));
+  return 0;
+}
 // K13
 int ref_rms_norm_quantize_bf16(const void* x, const void* w, float eps, void* normed, void* packed, void* sfa,
                                int rows, int dim, void* st) {

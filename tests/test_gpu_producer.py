@@ -287,3 +287,70 @@ def test_argument_errors():
     assert L.frt_norm_quant_nvfp4(None, P(x), None, 1e-6, 1.0, None, P(p), P(s), 4, 32768, 0, st()) == -4
     assert L.frt_nvfp4_sf_linear_to_swizzled(P(s), P(s), 0, 64, st()) == -2
     assert b"null" in L.frt_error_string(-1)
+
+
+@pytest.mark.parametrize("rows,dim", CASES)
+def test_layer_norm_bf16(rows, dim):
+    x, w, b = randn_bf16((rows, dim), 41 + rows, 1.0, 0.3), randn_bf16((dim,), 42, 0.1, 1.0), randn_bf16((dim,), 43, 0.2)
+    out = torch.empty(rows, dim, dtype=torch.bfloat16, device=DEV)
+    capi.check(capi.lib().frt_layer_norm_bf16(P(D(x)), P(D(w)), P(D(b)), P(out), rows, dim, 1e-5, st()))
+    np.testing.assert_array_equal(bits(out), O.layer_norm_bf16(bits(x), bits(w), bits(b), 1e-5))
+    want = torch.nn.functional.layer_norm(x.float(), (dim,), w.float(), b.float(), 1e-5)
+    assert (out.float().cpu() - want).abs().max() <= 2.0 ** -5        # bf16 rounding of values of a few units
+    ref = ref_lib()
+    if ref is not None:
+        ro = torch.empty_like(out)
+        ref.ref_layer_norm_bf16(P(D(x)), P(D(w)), P(D(b)), P(ro), rows, dim, C.c_float(1e-5), st())
+        torch.cuda.synchronize()
+        assert (ro.float() - out.float()).abs().max() <= 2.0 ** -5
+        assert (ro != out).float().mean() < 0.02
+
+
+@pytest.mark.parametrize("with_residual", [False, True])
+@pytest.mark.parametrize("rows,dim", [(1, 1024), (63, 2048), (257, 4096), (9, 8192)])
+def test_rms_norm_quant_fp8_static(rows, dim, with_residual):
+    x, r, w = randn_bf16((rows, dim), 51 + rows), randn_bf16((rows, dim), 52 + rows), randn_bf16((dim,), 53, 0.1, 1.0)
+    scale_v = 0.037
+    scale = torch.tensor([scale_v], dtype=torch.float32, device=DEV)
+    out = torch.empty(rows, dim, dtype=torch.uint8, device=DEV)
+    res = r.to(DEV).clone()
+    capi.check(capi.lib().frt_rms_norm_quant_fp8(P(res) if with_residual else None, P(D(x)), P(D(w)), P(scale), P(out),
+                                                 rows, dim, 1e-6, st()))
+    want_res, want = O.rms_norm_quant_fp8(bits(x), bits(w), scale_v, 1e-6, res_bits=bits(r) if with_residual else None)
+    np.testing.assert_array_equal(out.cpu().numpy(), want)
+    if with_residual:
+        np.testing.assert_array_equal(bits(res), want_res)
+    ref = ref_lib()
+    if ref is not None:
+        ro = torch.empty_like(out)
+        rres = r.to(DEV).clone()
+        ref.ref_rms_norm_quant_fp8(P(rres) if with_residual else None, P(D(x)), P(D(w)), P(ro), rows, dim,
+                                   C.c_float(1e-6), P(scale), st())
+        torch.cuda.synchronize()
+        if with_residual:
+            assert torch.equal(rres, res)
+        # other summation order and the approximate rsqrt: a sliver of values lands on the other side of an
+        # e4m3 rounding boundary, one code step away
+        assert (ro != out).float().mean() < 0.02
+        d = (ro.view(torch.float8_e4m3fn).float() - out.view(torch.float8_e4m3fn).float()).abs()
+        assert (d <= 0.13 * out.view(torch.float8_e4m3fn).float().abs() + 2.0 ** -9).all()
+
+
+def test_norm_package_torch_ops():
+    import flashrt_residual_norm_quant as pkg
+    rows, dim = 33, 1024
+    x, r, w, b = (randn_bf16((rows, dim), 61).to(DEV), randn_bf16((rows, dim), 62).to(DEV),
+                  randn_bf16((dim,), 63, 0.1, 1.0).to(DEV), randn_bf16((dim,), 64, 0.2).to(DEV))
+    scale = torch.tensor([0.05], dtype=torch.float32, device=DEV)
+    y = pkg.layer_norm_bf16(x, w, b)
+    np.testing.assert_array_equal(bits(y), O.layer_norm_bf16(bits(x), bits(w), bits(b), 1e-5))
+    q = pkg.rms_norm_quant_fp8_static_bf16(x, w, scale)
+    assert q.dtype == torch.float8_e4m3fn
+    np.testing.assert_array_equal(q.view(torch.uint8).cpu().numpy(), O.rms_norm_quant_fp8(bits(x), bits(w), 0.05, 1e-6)[1])
+    res = r.clone()
+    q2 = pkg.residual_add_rms_norm_quant_fp8_static_bf16(res, x, w, scale)
+    want_res, want = O.rms_norm_quant_fp8(bits(x), bits(w), 0.05, 1e-6, res_bits=bits(r))
+    np.testing.assert_array_equal(q2.view(torch.uint8).cpu().numpy(), want)
+    np.testing.assert_array_equal(bits(res), want_res)
+    with pytest.raises(RuntimeError, match="float8_e4m3fn"):
+        pkg.rms_norm_quant_fp8_static_bf16(x, w, scale, out=torch.empty_like(x))
