@@ -247,7 +247,39 @@ __device__ __forceinline__ void pack16_bf16(const float (&v)[16], uint4& o0, uin
   o1.z = pack_bf16x2(v[12], v[13]); o1.w = pack_bf16x2(v[14], v[15]);
 }
 
-template <int TPR, bool HAS_RES, bool QUANT, int ENC>
+// 8 packed 16-bit values <-> fp32, bf16 or (FP16) IEEE half
+template <bool FP16>
+__device__ __forceinline__ void unpack8(const uint4& raw, float* out) {
+  if (FP16) {
+    const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __half22float2(h[i]);
+      out[2 * i] = f.x;
+      out[2 * i + 1] = f.y;
+    }
+  } else {
+    unpack_bf16x8(raw, out);
+  }
+}
+template <bool FP16>
+__device__ __forceinline__ void pack16(const float (&v)[16], uint4& o0, uint4& o1) {
+  if (FP16) {
+    uint32_t w[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+      w[i] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    o0 = make_uint4(w[0], w[1], w[2], w[3]);
+    o1 = make_uint4(w[4], w[5], w[6], w[7]);
+  } else {
+    pack16_bf16(v, o0, o1);
+  }
+}
+
+// FP16: activations and residual are IEEE half instead of bf16 (the weight, when given, stays bf16).
+template <int TPR, bool HAS_RES, bool QUANT, int ENC, bool FP16 = false>
 __global__ void __launch_bounds__(TPR > 256 ? TPR : 256)
 norm_quant_kernel(const NormParams p) {
   pdl_launch_dependents();
@@ -273,17 +305,17 @@ norm_quant_kernel(const NormParams p) {
       r1 = __ldcs(p.residual + 2 * idx + 1);
     }
   }
-  unpack_bf16x8(x0, v);
-  unpack_bf16x8(x1, v + 8);
+  unpack8<FP16>(x0, v);
+  unpack8<FP16>(x1, v + 8);
   float part = 0.f;
   if (HAS_RES) {
     float r[16];
-    unpack_bf16x8(r0, r);
-    unpack_bf16x8(r1, r + 8);
+    unpack8<FP16>(r0, r);
+    unpack8<FP16>(r1, r + 8);
 #pragma unroll
     for (int j = 0; j < 16; ++j) v[j] = __fadd_rn(r[j], v[j]);
     uint4 o0, o1;
-    pack16_bf16(v, o0, o1);
+    pack16<FP16>(v, o0, o1);
     if (ok) {
       __stcs(p.residual + 2 * idx, o0);
       __stcs(p.residual + 2 * idx + 1, o1);
@@ -292,8 +324,8 @@ norm_quant_kernel(const NormParams p) {
 #pragma unroll
     for (int j = 0; j < 16; ++j) part = __fadd_rn(part, __fmul_rn(v[j], v[j]));
     if (p.flags & FRT_PRODUCER_NORM_FROM_BF16_RESIDUAL) {   // norm input = the rounded residual
-      unpack_bf16x8(o0, v);
-      unpack_bf16x8(o1, v + 8);
+      unpack8<FP16>(o0, v);
+      unpack8<FP16>(o1, v + 8);
     }
   } else {
 #pragma unroll
@@ -694,6 +726,17 @@ int dispatch_norm(NormParams& p, bool has_res, bool quant, cudaStream_t st) {
   return launch_norm<1024>(p, has_res, quant, st);
 }
 
+// fp16 activations / residual, no weight: residual_add_rms_norm_fp4_sfa_v2_fp16 of the reference
+template <int TPR>
+int launch_norm_fp16(const NormParams& p, cudaStream_t st) {
+  constexpr int CTA = TPR > 256 ? TPR : 256;
+  constexpr int rows_per_cta = CTA / TPR;
+  const dim3 grid((p.rows + rows_per_cta - 1) / rows_per_cta), block(CTA);
+  if (g_opt_quant_encoder == 1) launch_pdl(norm_quant_kernel<TPR, true, true, kEncChain, true>, grid, block, 0, st, p);
+  else launch_pdl(norm_quant_kernel<TPR, true, true, kEncHw, true>, grid, block, 0, st, p);
+  return launch_result();
+}
+
 int check_norm_args(const void* x, int rows, int dim) {
   if (!x) return FRT_E_NULL;
   if (rows <= 0 || dim <= 0 || dim % 16 != 0) return FRT_E_SHAPE;
@@ -840,6 +883,28 @@ int frt_norm_quant_nvfp4(void* residual, const void* x, const void* weight, floa
   p.eps = eps; p.inv_global_scale = inv_global_scale; p.dim_f = static_cast<float>(dim);
   p.flags = flags;
   return dispatch_norm(p, residual != nullptr, true, as_stream(stream));
+}
+
+int frt_residual_norm_quant_nvfp4_fp16(void* residual, const void* x, float eps, void* packed, void* sf, int rows,
+                                       int dim, void* stream) {
+  if (int rc = check_norm_args(x, rows, dim)) return rc;
+  if (!residual || !packed || !sf) return FRT_E_NULL;
+  if (!aligned(x, 16) || !aligned(residual, 16) || !aligned(packed, 8)) return FRT_E_ALIGN;
+  NormParams p{};
+  p.residual = static_cast<uint4*>(residual);
+  p.x = static_cast<const uint4*>(x);
+  p.packed = static_cast<uint2*>(packed);
+  p.sf = static_cast<uint8_t*>(sf);
+  p.rows = rows; p.nb = dim / 16; p.sf_cols = (dim + 63) / 64;
+  p.eps = eps; p.inv_global_scale = 1.0f; p.dim_f = static_cast<float>(dim);
+  cudaStream_t st = as_stream(stream);
+  const int nb = p.nb;
+  if (nb <= 32) return launch_norm_fp16<32>(p, st);
+  if (nb <= 64) return launch_norm_fp16<64>(p, st);
+  if (nb <= 128) return launch_norm_fp16<128>(p, st);
+  if (nb <= 256) return launch_norm_fp16<256>(p, st);
+  if (nb <= 512) return launch_norm_fp16<512>(p, st);
+  return launch_norm_fp16<1024>(p, st);
 }
 
 int frt_rms_norm_bf16(const void* x, const void* weight, void* out, int rows, int dim, float eps, void* stream) {

@@ -30,6 +30,7 @@ SIGNATURES = {
     "frt_moe_route_plan": (_I, [_P, _I, _I, _I, _P, _P, _P, _P]),
     "frt_moe_gather_nvfp4": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _P]),
     "frt_moe_weighted_sum_bf16": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _P]),
+    "frt_residual_norm_quant_nvfp4_fp16": (_I, [_P, _P, _F, _P, _P, _I, _I, _P]),
     "frt_layer_norm_bf16": (_I, [_P, _P, _P, _P, _I, _I, _F, _P]),
     "frt_rms_norm_quant_fp8": (_I, [_P, _P, _P, _P, _P, _I, _I, _F, _P]),
     "frt_silu_mul_quant_nvfp4": (_I, [_P, _P, _P, _I, _I, _P]),

@@ -26,6 +26,7 @@ _REPOS = {
     "flashrt/flashrt-residual-norm-quant": "flashrt_residual_norm_quant",
     "flashrt/grouped-moe-gemm": "grouped_moe_gemm",
     "flashrt/transformer-fused-ops": "transformer_fused_ops",
+    "flashrt/flashrt-smallm-gemm": "flashrt_smallm_gemm",
 }
 
 

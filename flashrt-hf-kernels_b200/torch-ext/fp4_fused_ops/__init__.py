@@ -141,6 +141,23 @@ def rms_norm_quant_nvfp4(x, weight, eps: float = 1e-6, *, one_plus_weight: bool 
     return packed, sfa
 
 
+@torch.library.register_fake(add_op_namespace_prefix("residual_add_rms_norm_fp4_sfa_v2_fp16"))
+def _residual_add_rms_norm_fp16_fake(residual, x, packed, sfa) -> None:
+    _check_producer(x, packed, sfa)
+    if residual.shape != x.shape:
+        raise RuntimeError("residual and x must have the same 2D shape")
+    return None
+
+
+def residual_add_rms_norm_fp4_sfa_v2_fp16(residual, x, *, packed=None, sfa=None):
+    """FP16 ``residual += x`` in place, unweighted RMSNorm (eps 1e-6) of the fp32 sum, NVFP4 with swizzled
+    scales (fp4-fused-ops/torch-ext/fp4_fused_ops/__init__.py: residual_add_rms_norm_fp4_sfa_v2_fp16)."""
+    if packed is None or sfa is None:
+        packed, sfa = _alloc_fp4(x.shape[0], x.shape[1], x.device)
+    ops.residual_add_rms_norm_fp4_sfa_v2_fp16(residual, x, packed, sfa)
+    return packed, sfa
+
+
 def dequantize_fp4_sfa_fp16(packed, sfa, out=None):
     if out is None:
         out = torch.empty((packed.shape[0], packed.shape[1] * 2), device=packed.device, dtype=torch.float16)
@@ -150,4 +167,4 @@ def dequantize_fp4_sfa_fp16(packed, sfa, out=None):
 
 __all__ = ["sfa_size_bytes", "rms_norm_quantize_fp4_sfa_bf16", "residual_add_rms_norm_nvfp4_bf16",
            "residual_add_rms_norm_quant_nvfp4_swizzled_bf16", "residual_add_rms_norm_quant_nvfp4",
-           "dequantize_fp4_sfa_fp16", "silu_mul_quantize_fp4_sfa_bf16", "rms_norm_quant_nvfp4"]
+           "dequantize_fp4_sfa_fp16", "silu_mul_quantize_fp4_sfa_bf16", "rms_norm_quant_nvfp4", "residual_add_rms_norm_fp4_sfa_v2_fp16"]

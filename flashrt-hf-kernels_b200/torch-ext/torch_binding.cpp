@@ -227,6 +227,37 @@ void fp4_w4a4_gemm_warpsplit_mrows_bf16(const Tensor& a, const Tensor& b, const 
   gemm_call(a, b, sfa, sfb, nullptr, nullptr, out, alpha, "fp4_w4a4_gemm_warpsplit_mrows_bf16");
 }
 
+// M = 1 decode matvec of the reference's small-M package (flashrt-smallm-gemm/torch-ext/torch_binding.cpp:55-108):
+// a_packed (K/2,) or (1, K/2), out (N,).  Any K % 32 == 0 is accepted (the reference kernel takes 4096 and 12288).
+void nvfp4_w4a4_decode_matvec_bf16out(const Tensor& a, const Tensor& b, const Tensor& sfa, const Tensor& sfb, Tensor& out,
+                                      double alpha) {
+  check_dtype(a, torch::kUInt8, "a_packed", "torch.uint8");
+  check_dtype(b, torch::kUInt8, "b_packed", "torch.uint8");
+  check_dtype(sfa, torch::kUInt8, "sfa", "torch.uint8");
+  check_dtype(sfb, torch::kUInt8, "sfb", "torch.uint8");
+  check_dtype(out, torch::kBFloat16, "out", "torch.bfloat16");
+  TORCH_CHECK(b.dim() == 2, "b_packed must have shape (N, K / 2)");
+  TORCH_CHECK(a.dim() == 1 || (a.dim() == 2 && a.size(0) == 1), "a_packed must have shape (K / 2,) or (1, K / 2)");
+  const int64_t n = b.size(0), k = b.size(1) * 2;
+  TORCH_CHECK(n > 0, "N must be positive");
+  TORCH_CHECK(k > 0, "K must be positive");
+  TORCH_CHECK(a.numel() * 2 == k, "a_packed must contain K / 2 bytes");
+  TORCH_CHECK(k % 32 == 0, "K must be divisible by 32 on this device (16-byte packed row pitch)");
+  TORCH_CHECK(n % 8 == 0, "N must be divisible by 8");
+  TORCH_CHECK(out.numel() >= n, "out must contain at least N BF16 values");
+  const int ni = as_int(n, "N"), ki = as_int(k, "K");
+  TORCH_CHECK(sfa.numel() >= frt_nvfp4_sf_swizzled_bytes(1, ki), "sfa must contain the swizzled bytes for one activation row");
+  TORCH_CHECK(sfb.numel() >= frt_nvfp4_sf_swizzled_bytes(ni, ki), "sfb must contain the swizzled bytes for N weight rows");
+  check_same_device(a, b, "a_packed", "b_packed");
+  check_same_device(a, sfa, "a_packed", "sfa");
+  check_same_device(a, sfb, "a_packed", "sfb");
+  check_same_device(a, out, "a_packed", "out");
+  c10::cuda::CUDAGuard guard(a.device());
+  check_rc(frt_nvfp4_gemm_bf16(a.data_ptr(), sfa.data_ptr(), b.data_ptr(), sfb.data_ptr(), nullptr, nullptr,
+                               out.data_ptr(), 1, ni, ki, static_cast<float>(alpha), 0.0f, stream_of(a)),
+           "nvfp4_w4a4_decode_matvec_bf16out");
+}
+
 // ------------------------------------------------------------------ norms
 void check_norm_inputs(const Tensor& x, const Tensor* weight, const Tensor* other, const char* other_name) {
   check_dtype(x, torch::kBFloat16, "x", "torch.bfloat16");
@@ -344,6 +375,22 @@ void residual_add_rms_norm_quant_nvfp4_ex(Tensor& residual, const Tensor& x, con
   Tensor n = normed.has_value() ? normed.value() : Tensor();
   producer_call(&residual, x, &weight, eps, inv_global_scale, normed.has_value() ? &n : nullptr, packed, sfa, 0u,
                 "residual_add_rms_norm_quant_nvfp4_ex");
+}
+// fp16 activations / residual, unweighted, eps = 1e-6 (fp4-fused-ops/torch-ext/torch_binding.cpp:269-296)
+void residual_add_rms_norm_fp4_sfa_v2_fp16(Tensor& residual, const Tensor& x, Tensor& packed, Tensor& sfa) {
+  check_dtype(residual, torch::kFloat16, "residual", "torch.float16");
+  check_dtype(x, torch::kFloat16, "x", "torch.float16");
+  TORCH_CHECK(x.dim() == 2 && residual.sizes() == x.sizes(), "residual and x must have the same shape");
+  TORCH_CHECK(x.size(1) <= 16384, "v2 residual path supports dim <= 16384");
+  TORCH_CHECK(x.size(1) % 16 == 0, "dim must be divisible by 16");
+  check_same_device(residual, x, "residual", "x");
+  check_packed_scales(packed, sfa, x.size(0), x.size(1), "packed", "sfa");
+  check_same_device(x, packed, "x", "packed");
+  check_same_device(x, sfa, "x", "sfa");
+  c10::cuda::CUDAGuard guard(x.device());
+  check_rc(frt_residual_norm_quant_nvfp4_fp16(residual.data_ptr(), x.data_ptr(), 1e-6f, packed.data_ptr(), sfa.data_ptr(),
+                                              as_int(x.size(0), "rows"), as_int(x.size(1), "dim"), stream_of(x)),
+           "residual_add_rms_norm_fp4_sfa_v2_fp16");
 }
 // Additive op: RMSNorm (plain or 1 + weight) -> NVFP4 without a residual, optional bf16 copy of
 // the normalised tensor (what transformers' decoder layers pass on to the projections).
@@ -514,6 +561,11 @@ void moe_gather_nvfp4(const Tensor& packed, const Tensor& sfa, const Tensor& tok
 
 }  // namespace
 
+TORCH_LIBRARY_EXPAND(flashrt_smallm_gemm_b200, ops) {
+  ops.def("nvfp4_w4a4_decode_matvec_bf16out(Tensor a_packed, Tensor b_packed, Tensor sfa, Tensor sfb, Tensor! out, float alpha=1.0) -> ()");
+  ops.impl("nvfp4_w4a4_decode_matvec_bf16out", torch::kCUDA, &nvfp4_w4a4_decode_matvec_bf16out);
+}
+
 TORCH_LIBRARY_EXPAND(transformer_fused_ops_b200, ops) {
   ops.def("nexn2_router_topk_bf16(Tensor logits, Tensor! out_idx, Tensor! out_val, int k) -> ()");
   ops.def("router_topk_bf16(Tensor logits, Tensor! out_idx, Tensor! out_val, int k) -> ()");
@@ -578,6 +630,8 @@ TORCH_LIBRARY_EXPAND(fp4_fused_ops_b200, ops) {
   ops.def("residual_add_rms_norm_quant_nvfp4_ex(Tensor! residual, Tensor x, Tensor weight, float eps, float inv_global_scale, Tensor!? normed, Tensor! packed, Tensor! sfa) -> ()");
   ops.def("dequantize_fp4_sfa_fp16(Tensor packed, Tensor sfa, Tensor! out) -> ()");
   ops.def("silu_mul_quantize_fp4_sfa_bf16(Tensor merged, Tensor! packed, Tensor! sfa) -> ()");
+  ops.def("residual_add_rms_norm_fp4_sfa_v2_fp16(Tensor! residual, Tensor x, Tensor! packed, Tensor! sfa) -> ()");
+  ops.impl("residual_add_rms_norm_fp4_sfa_v2_fp16", torch::kCUDA, &residual_add_rms_norm_fp4_sfa_v2_fp16);
   ops.def("rms_norm_quant_nvfp4_ex(Tensor x, Tensor weight, float eps, Tensor!? normed, Tensor! packed, Tensor! sfa, bool one_plus_weight=False, bool round_bf16=True) -> ()");
   ops.impl("rms_norm_quant_nvfp4_ex", torch::kCUDA, &rms_norm_quant_nvfp4_ex);
   ops.impl("silu_mul_quantize_fp4_sfa_bf16", torch::kCUDA, &silu_mul_quantize_fp4_sfa_bf16);

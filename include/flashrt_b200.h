@@ -87,6 +87,13 @@ int frt_rms_norm_bf16(const void* x, const void* weight, void* out,
 int frt_residual_add_rms_norm_bf16(void* residual, const void* x, const void* weight, void* out,
                                    int rows, int dim, float eps, void* stream);
 
+/* fp16 form of the fused producer, no weight: residual (fp16, in place) <- half(residual + x);
+ * v = (residual + x in fp32) * rsqrt(mean(v^2) + eps); rule-A NVFP4 of v.
+ * replaces residual_add_rms_norm_fp4_sfa_v2_fp16 (eps fixed at 1e-6 there),
+ *   fp4-fused-ops/csrc/fused_fp4/norm_silu_fp4_sfa.cuh:39 */
+int frt_residual_norm_quant_nvfp4_fp16(void* residual, const void* x, float eps, void* packed,
+                                       void* sf_swizzled, int rows, int dim, void* stream);
+
 /* LayerNorm, bf16 in / out, affine bf16 weight and bias [dim]:
  *   out = bf16(((x - mean) * rsqrt(var + eps)) * w + b), fp32 statistics (two row reductions).
  * replaces layer_norm_bf16, flashrt-residual-norm-quant/csrc/residual_norm_quant.cuh:18 */

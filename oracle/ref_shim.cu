@@ -19,6 +19,7 @@
 #ifdef REF_HAVE_CUTLASS
 #define FLASHRT_HAVE_COSMOS3_EDGE 1
 #include "fused_fp4/cosmos3_edge_fp4.cuh"       // fp4-fused-ops/csrc
+#include "fused_fp4/norm_silu_fp4_sfa.cuh"      // fp4-fused-ops/csrc
 #include "cutlass_nvfp4_w4a16_gemm_sm100.cuh"   // fp4-gemm/csrc/gemm/fp4
 #endif
 
@@ -112,6 +113,13 @@ int ref_res_rms_fp4_bf16(void* res, const void* x, const void* w, void* packed, 
   flash_rt::fused_fp4::cosmos3_edge_res_rms_fp4_sfa_bf16(
       static_cast<__nv_bfloat16*>(res), static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
       static_cast<uint8_t*>(packed), static_cast<uint8_t*>(sfa), rows, dim, eps, S(st));
+  return 0;
+}
+// fp16 residual + RMSNorm -> NVFP4 (v2: one thread per 16-element block)
+int ref_res_rms_fp4_v2_fp16(void* res, const void* x, void* packed, void* sfa, int rows, int dim, void* st) {
+  flash_rt::fused_fp4::residual_add_rms_norm_fp4_sfa_v2_fp16(static_cast<__half*>(res), static_cast<const __half*>(x),
+                                                             static_cast<uint8_t*>(packed), static_cast<uint8_t*>(sfa),
+                                                             rows, dim, S(st));
   return 0;
 }
 // K15 / K16: the reference's CUTLASS sm100 GEMM (cluster 1x1x1), bf16 out

@@ -354,3 +354,31 @@ def test_norm_package_torch_ops():
     np.testing.assert_array_equal(bits(res), want_res)
     with pytest.raises(RuntimeError, match="float8_e4m3fn"):
         pkg.rms_norm_quant_fp8_static_bf16(x, w, scale, out=torch.empty_like(x))
+
+
+@pytest.mark.parametrize("rows,dim", [(1, 1024), (63, 2048), (257, 4096), (9, 8192)])
+def test_fp16_residual_norm_quant(rows, dim):
+    """residual_add_rms_norm_fp4_sfa_v2_fp16: fp16 activations and residual, unweighted, eps 1e-6"""
+    g = torch.Generator().manual_seed(700 + rows)
+    x = torch.randn(rows, dim, generator=g).to(torch.float16)
+    r = torch.randn(rows, dim, generator=g).to(torch.float16)
+    res = r.to(DEV).clone()
+    packed, sf = alloc_fp4(rows, dim)
+    capi.check(capi.lib().frt_residual_norm_quant_nvfp4_fp16(P(res), P(D(x)), 1e-6, P(packed), P(sf), rows, dim, st()))
+    want = O.residual_norm_quant_fp16(r.numpy(), x.numpy(), 1e-6)
+    assert torch.equal(res.cpu(), torch.from_numpy(want["residual"]))
+    np.testing.assert_array_equal(sf.cpu().numpy(), O.sf_linear_to_swizzled(want["sf_linear"]))
+    np.testing.assert_array_equal(packed.cpu().numpy(), want["packed"])
+    ref = ref_lib()
+    if ref is not None and ref.ref_has_cutlass() and dim >= 512:
+        rres = r.to(DEV).clone()
+        rp, rs = alloc_fp4(rows, dim)
+        ref.ref_res_rms_fp4_v2_fp16(P(rres), P(D(x)), P(rp), P(rs), rows, dim, st())
+        torch.cuda.synchronize()
+        assert torch.equal(rres, res)
+        code_mismatch = (O.unpack_codes(rp.cpu().numpy()) != O.unpack_codes(packed.cpu().numpy())).mean()
+        assert code_mismatch < 2e-3 and (rs != sf).float().mean().item() < 2e-3
+    import fp4_fused_ops
+    res2 = r.to(DEV).clone()
+    p2, s2 = fp4_fused_ops.residual_add_rms_norm_fp4_sfa_v2_fp16(res2, x.to(DEV))
+    assert torch.equal(p2, packed) and torch.equal(res2, res)

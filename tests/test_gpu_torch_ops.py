@@ -217,3 +217,25 @@ def test_hub_and_layers():
     xa = torch.randn(66, 512, device=DEV, dtype=torch.bfloat16)
     oa, ob = fused(res, xa)
     assert oa.shape == (66, 256) and ob.shape == (66, 128)
+
+
+@pytest.mark.parametrize("K", [4096, 12288, 2048])
+def test_decode_matvec_known_answer(K):
+    """the reference's constant-input check of its M=1 matvec
+    (flashrt-smallm-gemm/tests/test_nvfp4_w4a4_decode_matvec.py:33-52): nibbles 0x11 (0.5), scales 0x38 (1.0)
+    give K * 0.25 * alpha in every output"""
+    import flashrt_nvfp4
+    import flashrt_smallm_gemm
+    N, alpha = 16, 0.5
+    a_packed = torch.full((K // 2,), 0x11, device=DEV, dtype=torch.uint8)
+    b_packed = torch.full((N, K // 2), 0x11, device=DEV, dtype=torch.uint8)
+    sfa = flashrt_nvfp4.nvfp4_sf_linear_to_swizzled(torch.full((1, K // 16), 0x38, dtype=torch.uint8, device=DEV))
+    sfb = flashrt_nvfp4.nvfp4_sf_linear_to_swizzled(torch.full((N, K // 16), 0x38, dtype=torch.uint8, device=DEV))
+    out = flashrt_smallm_gemm.nvfp4_w4a4_decode_matvec_bf16out(a_packed, b_packed, sfa, sfb, alpha=alpha)
+    expected = torch.full((N,), K * 0.25 * alpha, device=DEV, dtype=torch.bfloat16)
+    torch.testing.assert_close(out, expected)
+    again = flashrt_smallm_gemm.nvfp4_w4a4_decode_matvec_bf16out(a_packed.view(1, -1), b_packed, sfa, sfb, alpha=alpha,
+                                                                 out=out)
+    assert again.data_ptr() == out.data_ptr() and torch.equal(again, expected)
+    with pytest.raises(RuntimeError, match=r"\(K / 2,\) or \(1, K / 2\)"):
+        flashrt_smallm_gemm.nvfp4_w4a4_decode_matvec_bf16out(b_packed[:2], b_packed, sfa, sfb)
