@@ -107,6 +107,25 @@ def quantize_fp4_sfa_bf16(x, packed=None, sfa=None, is_sfb: bool = False):
     return packed, sfa
 
 
+@torch.library.register_fake(add_op_namespace_prefix("quantize_fp4_sfa_bf16_pdl"))
+def _quantize_bf16_pdl_fake(x, packed, sfa, is_sfb=False) -> None:
+    return None
+
+
+@torch.library.register_fake(add_op_namespace_prefix("fp4_w4a4_gemm_warpsplit_mrows_pdl_bf16"))
+def _mrows_pdl_fake(a, b, sfa, sfb, out, alpha=1.0, warps=2, stages=6) -> None:
+    _gemm_fake_check(a, b, out)
+    return None
+
+
+def quantize_fp4_sfa_bf16_pdl(x, packed=None, sfa=None, is_sfb: bool = False):
+    """PDL-enabled twin of :func:`quantize_fp4_sfa_bf16` (every launch of this build is one already)."""
+    if packed is None or sfa is None:
+        packed, sfa = _alloc_fp4(x.shape[0], x.shape[1], x.device)
+    ops.quantize_fp4_sfa_bf16_pdl(x, packed, sfa, bool(is_sfb))
+    return packed, sfa
+
+
 def dequantize_fp4_sfa_fp16(packed, sfa, out=None, is_sfb: bool = False):
     if out is None:
         out = torch.empty((packed.shape[0], packed.shape[1] * 2), device=packed.device, dtype=torch.float16)
@@ -307,4 +326,4 @@ __all__ = ["capabilities", "sfa_size_bytes", "quantize_fp4_sfa_fp16", "quantize_
            "nvfp4_gemm_bias_bf16",
            "nvfp4_gemm_bias_residual_bf16", "nvfp4_gemm_residual_bf16", "fp4_w4a4_gemv_warpsplit_bf16",
            "fp4_w4a4_gemm_warpsplit_mrows_bf16", "pack_nvfp4_weight_bf16", "quantize_fp4_sfa_mse_fp16",
-           "quantize_fp4_sfa_mse_bf16", "aligned_fp4_dim", "quantize_fp4_sfa_padded_bf16", "adopt_modelopt_nvfp4_weight"]
+           "quantize_fp4_sfa_mse_bf16", "quantize_fp4_sfa_bf16_pdl", "aligned_fp4_dim", "quantize_fp4_sfa_padded_bf16", "adopt_modelopt_nvfp4_weight"]

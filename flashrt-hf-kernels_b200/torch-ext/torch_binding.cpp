@@ -604,6 +604,11 @@ TORCH_LIBRARY_EXPAND(fp4_gemm_b200, ops) {
   ops.def("quantize_fp4_sfa_fp16(Tensor x, Tensor! packed, Tensor! sfa, bool is_sfb=False) -> ()");
   ops.def("quantize_fp4_sfa_bf16(Tensor x, Tensor! packed, Tensor! sfa, bool is_sfb=False) -> ()");
   ops.def("dequantize_fp4_sfa_fp16(Tensor packed, Tensor sfa, Tensor! out, bool is_sfb=False) -> ()");
+  // "_pdl" twins of the reference: every launch of this library is a programmatic dependent launch already
+  ops.def("quantize_fp4_sfa_bf16_pdl(Tensor x, Tensor! packed, Tensor! sfa, bool is_sfb=False) -> ()");
+  ops.def("fp4_w4a4_gemm_warpsplit_mrows_pdl_bf16(Tensor a_packed, Tensor b_packed, Tensor sfa, Tensor sfb, Tensor! out, float alpha=1.0, int warps=2, int stages=6) -> ()");
+  ops.impl("quantize_fp4_sfa_bf16_pdl", torch::kCUDA, &quantize_fp4_sfa_bf16);
+  ops.impl("fp4_w4a4_gemm_warpsplit_mrows_pdl_bf16", torch::kCUDA, &fp4_w4a4_gemm_warpsplit_mrows_bf16);
   ops.def("quantize_fp4_sfa_mse_fp16(Tensor x, Tensor! packed, Tensor! sfa, bool is_sfb=False) -> ()");
   ops.def("quantize_fp4_sfa_mse_bf16(Tensor x, Tensor! packed, Tensor! sfa, bool is_sfb=False) -> ()");
   ops.impl("quantize_fp4_sfa_mse_fp16", torch::kCUDA, &quantize_fp4_sfa_mse_fp16);

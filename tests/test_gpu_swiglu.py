@@ -132,3 +132,36 @@ def test_torch_ops_swiglu():
         fp4_gemm.nvfp4_gemm_swiglu_nvfp4_bf16(a, b[:384], sfa, sfb, out_packed=p2, out_sfa=s2)
     with pytest.raises(RuntimeError, match="divisible by 32"):
         fp4_fused_ops.silu_mul_quantize_fp4_sfa_bf16(merged[:, :48].contiguous(), packed=p1, sfa=s1)
+
+
+def test_swiglu_ops_compile_and_graph():
+    """the new ops trace under torch.compile(fullgraph=True) and replay bit-stably in a CUDA graph"""
+    import fp4_gemm
+    import transformer_fused_ops
+    M, hidden, K = 256, 256, 256
+    a, sfa, b, sfb = make_operands(M, 2 * hidden, K, 99)
+    p_eager, s_eager = fp4_gemm.nvfp4_gemm_swiglu_nvfp4_bf16(a, b, sfa, sfb)
+
+    def step(aa):
+        return fp4_gemm.nvfp4_gemm_swiglu_nvfp4_bf16(aa, b, sfa, sfb)
+
+    p_c, s_c = torch.compile(step, fullgraph=True)(a)
+    assert torch.equal(p_c, p_eager) and torch.equal(s_c, s_eager)
+    logits = randn_bf16((64, 128), 5).to(DEV)
+    idx_e, val_e = transformer_fused_ops.router_topk_bf16(logits, 8)
+    idx_c, val_c = torch.compile(lambda l: transformer_fused_ops.router_topk_bf16(l, 8), fullgraph=True)(logits)
+    assert torch.equal(idx_c, idx_e) and torch.equal(val_c, val_e)
+
+    op, osf = alloc_fp4(M, hidden)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        fp4_gemm.nvfp4_gemm_swiglu_nvfp4_bf16(a, b, sfa, sfb, out_packed=op, out_sfa=osf)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            fp4_gemm.nvfp4_gemm_swiglu_nvfp4_bf16(a, b, sfa, sfb, out_packed=op, out_sfa=osf)
+    torch.cuda.synchronize()
+    op.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(op, p_eager)
