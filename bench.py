@@ -42,6 +42,8 @@ import torch  # noqa: E402
 
 L2_BYTES = 126 << 20
 EPS = 1e-6
+# measured DRAM traffic per launch of the four Qwen3-8B M=4096 GEMMs (ncu, bytes)
+NCU_DRAM_TRAFFIC_BYTES = {"qkv": 29563904, "o": 19248896, "gate_up": 221514496, "down": 70588160}
 
 WORKLOADS = {
     # name: (tokens, hidden, [(layer, N, K, fed_by_producer)])
@@ -479,12 +481,10 @@ def run_ours(args, rank, world, local_rank):
                          "traffic": None},
             "detail": detail,
         }
-        traffic_file = ROOT / "profiles" / "gemm_dram_traffic.json"
-        if traffic_file.exists():
-            try:
-                line["roofline"]["traffic"] = json.loads(traffic_file.read_text()).get(dom_g["name"])
-            except Exception:
-                pass
+        # ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this workload
+        # (profiles/nvfp4_gemm_pair_and_producer_qwen3_8b_m4096.md); only meaningful for the unsharded default
+        if args.workload == "c2" and not args.tokens and dom_g["n_loc"] == dom_g["n"]:
+            line["roofline"]["traffic"] = NCU_DRAM_TRAFFIC_BYTES.get(dom_g["name"])
         if allgather:
             line["allgather_separate"] = allgather
         if column_sharded:
@@ -497,15 +497,24 @@ def run_ours(args, rank, world, local_rank):
 def run_moe(args, rank, world, local_rank):
     """Grouped NVFP4 GEMMs of one MoE layer (replicas only: every rank runs the whole workload)."""
     from flashrt_b200_core import capi, load
-    from oracle.nvfp4_oracle import route_topk       # routing of the synthetic workload (host, set-up only)
     load()
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
     L, P, st = capi.lib(), capi.ptr, capi.stream_ptr()
-    rng = np.random.default_rng(3)
-    _, offs = route_topk(rng.standard_normal((MOE["tokens"], MOE["experts"])).astype(np.float32), MOE["top_k"])
-    rows, experts = int(offs[-1]), MOE["experts"]
-    offs_d = torch.from_numpy(offs).to(dev)
+    # routing of the synthetic workload: top-8 of seeded N(0,1) logits (= top-8 of their softmax), sorted by
+    # expert into per-expert offsets, with this library's router and routing-plan kernels
+    experts = MOE["experts"]
+    g0 = torch.Generator(device=dev).manual_seed(3)
+    setup_logits = torch.randn(MOE["tokens"], experts, generator=g0, device=dev).to(torch.bfloat16)
+    s_idx = torch.empty(MOE["tokens"], MOE["top_k"], dtype=torch.int32, device=dev)
+    s_val = torch.empty(MOE["tokens"], MOE["top_k"], dtype=torch.float32, device=dev)
+    offs_d = torch.empty(experts + 1, dtype=torch.int32, device=dev)
+    s_rop = torch.empty(MOE["tokens"], MOE["top_k"], dtype=torch.int32, device=dev)
+    s_tor = torch.empty(MOE["tokens"] * MOE["top_k"], dtype=torch.int32, device=dev)
+    assert L.frt_router_topk_bf16(P(setup_logits), P(s_idx), P(s_val), MOE["tokens"], experts, MOE["top_k"], st) == 0
+    assert L.frt_moe_route_plan(P(s_idx), MOE["tokens"], MOE["top_k"], experts, P(offs_d), P(s_rop), P(s_tor), st) == 0
+    torch.cuda.synchronize()
+    rows = int(offs_d[-1].item())
     alpha = torch.ones(experts, device=dev)
     work = torch.empty(int(L.frt_nvfp4_grouped_gemm_workspace_bytes(rows, experts)), dtype=torch.uint8, device=dev)
     sfb = lambda r, k: int(L.frt_nvfp4_sf_swizzled_bytes(r, k))
