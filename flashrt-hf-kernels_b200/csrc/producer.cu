@@ -15,6 +15,15 @@ int g_opt_pdl = 1;
 
 namespace {
 
+// Stores the scale byte of block kb of `row`; the thread that owns the row's last block also zeroes the
+// (up to three) padding bytes that complete the row's last 64-element group when dim % 64 != 0: the tensor
+// cores read whole groups, and a NaN pattern left there would poison the (zero) padding products.
+__device__ __forceinline__ void store_scale(uint8_t* sf, int row, int kb, int nb, int sf_cols, uint8_t value) {
+  sf[sf_offset(row, kb, sf_cols)] = value;
+  if (kb == nb - 1)
+    for (int j = nb; j < 4 * sf_cols; ++j) sf[sf_offset(row, j, sf_cols)] = 0;
+}
+
 // ---------------------------------------------------------------------------
 // linear [rows, nb] -> swizzled.  One thread moves the 4 scale bytes of one
 // (row, 64-element group): a 4-byte read (or byte reads at a ragged edge) and
@@ -30,7 +39,7 @@ __global__ void sf_linear_to_swizzled_kernel(const uint8_t* __restrict__ src, ui
   if (vec_ok && 4 * g + 4 <= nb) {
     *reinterpret_cast<uint32_t*>(d) = *reinterpret_cast<const uint32_t*>(s);
   } else {
-    for (int j = 0; j < 4 && 4 * g + j < nb; ++j) d[j] = s[j];
+    for (int j = 0; j < 4; ++j) d[j] = 4 * g + j < nb ? s[j] : 0;   // padding of the last group: zero
   }
 }
 
@@ -68,7 +77,7 @@ quantize_kernel(const uint4* __restrict__ src, uint2* __restrict__ packed, uint8
   uint8_t sfb;
   const uint2 out = quantize_block16<ENC>(v, sfb, inv_scale_table());
   packed[idx] = out;
-  sf[sf_offset(row, kb, sf_cols)] = sfb;
+  store_scale(sf, row, kb, nb, sf_cols, sfb);
 }
 
 // ---------------------------------------------------------------------------
@@ -130,7 +139,7 @@ quantize_mse_kernel(const uint4* __restrict__ src, uint2* __restrict__ packed, u
   }
   const float inv = __fdiv_rn(1.f, ue4m3_to_float(best));
   packed[idx] = encode_block16<kEncChain, false>(v, inv);
-  sf[sf_offset(row, kb, sf_cols)] = best;
+  store_scale(sf, row, kb, nb, sf_cols, best);
 }
 
 // ---------------------------------------------------------------------------
@@ -161,7 +170,7 @@ silu_mul_quant_kernel(const uint4* __restrict__ merged, uint2* __restrict__ pack
   uint8_t sfb;
   const uint2 out = quantize_block16<ENC>(v, sfb, inv_scale_table());
   packed[idx] = out;
-  sf[sf_offset(row, kb, sf_cols)] = sfb;
+  store_scale(sf, row, kb, nb, sf_cols, sfb);
 }
 
 // ---------------------------------------------------------------------------
@@ -386,7 +395,7 @@ norm_quant_kernel(const NormParams p) {
     if (p.flags & FRT_PRODUCER_RNE_E2M1) out = quantize_block16<kEncRne>(v, sfb, inv_scale_table());
     else out = quantize_block16<ENC>(v, sfb, inv_scale_table());
     p.packed[idx] = out;
-    p.sf[sf_offset(row, s, p.sf_cols)] = sfb;
+    store_scale(p.sf, row, s, p.nb, p.sf_cols, sfb);
   }
 }
 
@@ -649,7 +658,7 @@ norm_quant_stream_kernel(const NormParams p, unsigned* status) {
         if (p.flags & FRT_PRODUCER_RNE_E2M1) out = quantize_block16<kEncRne>(v, sfb, inv_scale_table());
         else out = quantize_block16<ENC>(v, sfb, inv_scale_table());
         p.packed[idx] = out;
-        p.sf[sf_offset(row, s, p.sf_cols)] = sfb;
+        store_scale(p.sf, row, s, p.nb, p.sf_cols, sfb);
       }
     }
   }

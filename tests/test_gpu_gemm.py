@@ -205,3 +205,20 @@ def test_against_reference_cutlass_gemm():
     torch.cuda.synchronize()
     rel, cos = O.gemm_error_metrics(out.cpu(), rout.cpu())
     assert rel <= 1e-3 and cos >= 0.9999, (rel, cos)
+
+
+@pytest.mark.parametrize("m,n,k", [(64, 128, 96), (300, 256, 160), (16, 128, 32), (256, 512, 224)])
+def test_k_not_a_multiple_of_64(m, n, k):
+    """K % 64 != 0: the tensor cores read whole 64-element scale groups, so the scale bytes that pad the last
+    group must not hold NaN patterns.  The quantisers of this library write them as zero whatever the buffer
+    held before (here: 0x7F, the e4m3 NaN)."""
+    g = torch.Generator().manual_seed(5 + k)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(n, k, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    ap, sfa = alloc_fp4(m, k, fill=0x7F)
+    bp, sfb = alloc_fp4(n, k, fill=0x7F)
+    quantize(x, ap, sfa)
+    quantize(w, bp, sfb)
+    out = gemm(ap, sfa, bp, sfb, m, n, k)
+    assert not torch.isnan(out.float()).any()
+    assert_close(out, oracle_out(ap, sfa, bp, sfb, m, n, k))

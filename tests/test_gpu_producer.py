@@ -50,7 +50,15 @@ def test_sf_layout(rows, dim):
     np.testing.assert_array_equal(got[offs], want[offs])
     mask = np.ones(got.size, bool)
     mask[offs] = False
-    assert np.all(got[mask] == 0xAB)          # padding bytes are left alone
+    # bytes that complete a real row's last 64-element group are written as zero (the tensor cores read
+    # them); bytes of rows beyond `rows` are left alone
+    nb, groups = dim // 16, (dim + 63) // 64
+    k_pad = np.zeros(got.size, bool)
+    r = np.arange(rows)
+    for kb in range(nb, 4 * groups):
+        k_pad[((r >> 7) * groups + (kb >> 2)) * 512 + (r & 31) * 16 + ((r >> 5) & 3) * 4 + (kb & 3)] = True
+    assert np.all(got[k_pad] == 0)
+    assert np.all(got[mask & ~k_pad] == 0xAB)
 
 
 @pytest.mark.parametrize("encoder", [0, 1])
