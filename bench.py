@@ -567,20 +567,19 @@ def run_moe(args, rank, world, local_rank):
     hp = torch.empty(T * topk, k2 // 2, dtype=torch.uint8, device=dev)
     hs = torch.zeros(sfb(T * topk, k2), dtype=torch.uint8, device=dev)
     final = torch.empty(T, n2, dtype=torch.float32, device=dev)
+    weights = torch.empty(T, topk, dtype=torch.float32, device=dev)
     R = T * topk
 
     def routed_layer():
-        rcs = [L.frt_router_topk_bf16(P(logits), P(idx), P(val), T, E, topk, st)]
-        weights = torch.softmax(val, dim=-1)          # k values per token (torch; the reference does the same)
-        rcs += [L.frt_moe_route_plan(P(idx), T, topk, E, P(off), P(rop), P(tor), st),
-                L.frt_nvfp4_quantize(P(hidden), 0, P(xp), P(xs), T, k1, st),
-                L.frt_moe_gather_nvfp4(P(xp), P(xs), P(tor), P(gp), P(gs), R, T, k1, st),
-                L.frt_nvfp4_grouped_gemm_bf16(P(gp), P(gs), P(wp1), P(wsf1), P(alpha), P(off), None, 0, P(out1), R, n1,
-                                              k1, E, n1 * (k1 // 2), int(wsf1.shape[1]), P(work), st),
-                L.frt_silu_mul_quant_nvfp4(P(out1), P(hp), P(hs), R, n1 // 2, st),
-                L.frt_nvfp4_grouped_gemm_bf16(P(hp), P(hs), P(wp2), P(wsf2), P(alpha), P(off), None, 0, P(out2), R, n2,
-                                              k2, E, n2 * (k2 // 2), int(wsf2.shape[1]), P(work), st),
-                L.frt_moe_weighted_sum_bf16(P(out2), P(rop), P(weights), P(final), T, topk, n2, n2, st)]
+        rcs = [L.frt_router_topk_softmax_bf16(P(logits), P(idx), P(val), P(weights), T, E, topk, st),
+               L.frt_moe_route_plan(P(idx), T, topk, E, P(off), P(rop), P(tor), st),
+               L.frt_moe_quantize_scatter_nvfp4(P(hidden), P(rop), P(gp), P(gs), T, topk, k1, st),
+               L.frt_nvfp4_grouped_gemm_bf16(P(gp), P(gs), P(wp1), P(wsf1), P(alpha), P(off), None, 0, P(out1), R, n1,
+                                             k1, E, n1 * (k1 // 2), int(wsf1.shape[1]), P(work), st),
+               L.frt_silu_mul_quant_nvfp4(P(out1), P(hp), P(hs), R, n1 // 2, st),
+               L.frt_nvfp4_grouped_gemm_bf16(P(hp), P(hs), P(wp2), P(wsf2), P(alpha), P(off), None, 0, P(out2), R, n2,
+                                             k2, E, n2 * (k2 // 2), int(wsf2.shape[1]), P(work), st),
+               L.frt_moe_weighted_sum_bf16(P(out2), P(rop), P(weights), P(final), T, topk, n2, n2, st)]
         assert not any(rcs), rcs
 
     routed_us = None
@@ -605,8 +604,8 @@ def run_moe(args, rank, world, local_rank):
                        "layers": {l[0]: [l[1], l[2]] for l in layers},
                        "l2": "weights 340 MB + activations per step exceed the 126 MiB L2"},
             "detail": {"routed_layer_us": routed_us,
-                       "routed_layer": "router top-k, routing plan, quantise, gather, grouped gate/up, SwiGLU->NVFP4, "
-                                       "grouped down, weighted un-permute (12 launches of this library + one softmax)"},
+                       "routed_layer": "router top-k + softmax, routing plan, quantise into expert order, grouped gate/up, "
+                                       "SwiGLU->NVFP4, grouped down, weighted un-permute (11 launches of this library)"},
             "gpu_launches": launches, "clocks": clocks.summary()}), flush=True)
 
 

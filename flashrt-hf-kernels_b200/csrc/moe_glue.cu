@@ -25,7 +25,7 @@ __device__ __forceinline__ int tie_key(int i) {
 
 __global__ void __launch_bounds__(kRouterWarps * 32)
 router_topk_kernel(const __nv_bfloat16* __restrict__ logits, int* __restrict__ out_idx,
-                   float* __restrict__ out_val, int tokens, int n, int k) {
+                   float* __restrict__ out_val, float* __restrict__ out_weight, int tokens, int n, int k) {
   extern __shared__ float s_logits[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int token = blockIdx.x * kRouterWarps + warp;
@@ -54,6 +54,16 @@ router_topk_kernel(const __nv_bfloat16* __restrict__ logits, int* __restrict__ o
       if (bidx >= 0) mine[bidx] = -FLT_MAX;
     }
     __syncwarp();
+  }
+  // optional: softmax over the k selected logits (equal to re-normalising the top-k of the full softmax);
+  // lane j owns slot j, the maximum is slot 0
+  if (out_weight != nullptr) {
+    const float v0 = out_val[static_cast<int64_t>(token) * k];
+    const float e = lane < k ? expf(out_val[static_cast<int64_t>(token) * k + lane] - v0) : 0.f;
+    float sum = e;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (lane < k) out_weight[static_cast<int64_t>(token) * k + lane] = __fdiv_rn(e, sum);
   }
 }
 
@@ -183,6 +193,33 @@ gather_nvfp4_kernel(const uint4* __restrict__ packed_in, const uint8_t* __restri
 }
 
 // ---------------------------------------------------------------------------
+// Quantise bf16 token rows to NVFP4 straight into expert order: every 16-element block is quantised once
+// and its 8 packed bytes + scale byte are stored to each of the token's k expert-sorted rows (pairs with a
+// negative row are skipped).  Replaces quantise + gather (and their intermediate) in the routed layer.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+quantize_scatter_kernel(const uint4* __restrict__ x, const int* __restrict__ row_of_pair, uint2* __restrict__ packed,
+                        uint8_t* __restrict__ sf, int tokens, int k, int nb, int sf_cols) {
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<int64_t>(tokens) * nb) return;
+  const int t = static_cast<int>(idx / nb);
+  const int kb = static_cast<int>(idx - static_cast<int64_t>(t) * nb);
+  float v[16];
+  unpack_bf16x8(__ldcs(x + 2 * idx), v);
+  unpack_bf16x8(__ldcs(x + 2 * idx + 1), v + 8);
+  uint8_t sfb;
+  const uint2 out = quantize_block16<kEncHw>(v, sfb, inv_scale_table());
+  for (int j = 0; j < k; ++j) {
+    const int r = __ldg(row_of_pair + static_cast<int64_t>(t) * k + j);
+    if (r < 0) continue;
+    packed[static_cast<int64_t>(r) * nb + kb] = out;
+    sf[sf_offset(r, kb, sf_cols)] = sfb;
+    if (kb == nb - 1)
+      for (int q = nb; q < 4 * sf_cols; ++q) sf[sf_offset(r, q, sf_cols)] = 0;
+  }
+}
+
+// ---------------------------------------------------------------------------
 // Weighted un-permute: out[t, :] = sum_j w[t, j] * y[row[t, j], :] in fp32, slots in order
 // (one fused multiply-add per slot), pairs with a negative row skipped.  One CTA per token.
 // ---------------------------------------------------------------------------
@@ -235,16 +272,34 @@ using namespace frt;
 
 extern "C" {
 
-int frt_router_topk_bf16(const void* logits, void* out_idx, void* out_val, int tokens, int n_experts, int k,
-                         void* stream) {
+int frt_router_topk_softmax_bf16(const void* logits, void* out_idx, void* out_val, void* out_weight, int tokens,
+                                 int n_experts, int k, void* stream) {
   if (!logits || !out_idx || !out_val) return FRT_E_NULL;
   if (tokens <= 0 || n_experts <= 0 || k <= 0) return FRT_E_SHAPE;
   if (k > 32 || n_experts > 1024) return FRT_E_UNSUPPORTED;
   const int grid = (tokens + kRouterWarps - 1) / kRouterWarps;
   const size_t smem = static_cast<size_t>(kRouterWarps) * n_experts * sizeof(float);
   router_topk_kernel<<<grid, kRouterWarps * 32, smem, as_stream(stream)>>>(
-      static_cast<const __nv_bfloat16*>(logits), static_cast<int*>(out_idx), static_cast<float*>(out_val), tokens,
-      n_experts, k);
+      static_cast<const __nv_bfloat16*>(logits), static_cast<int*>(out_idx), static_cast<float*>(out_val),
+      static_cast<float*>(out_weight), tokens, n_experts, k);
+  return launch_result();
+}
+
+int frt_router_topk_bf16(const void* logits, void* out_idx, void* out_val, int tokens, int n_experts, int k,
+                         void* stream) {
+  return frt_router_topk_softmax_bf16(logits, out_idx, out_val, nullptr, tokens, n_experts, k, stream);
+}
+
+int frt_moe_quantize_scatter_nvfp4(const void* x, const void* row_of_pair, void* packed_out, void* sf_out, int tokens,
+                                   int k, int K, void* stream) {
+  if (!x || !row_of_pair || !packed_out || !sf_out) return FRT_E_NULL;
+  if (tokens <= 0 || k <= 0 || K <= 0 || K % 16 != 0) return FRT_E_SHAPE;
+  if (!aligned(x, 16) || !aligned(packed_out, 8)) return FRT_E_ALIGN;
+  const int nb = K / 16;
+  const int64_t total = static_cast<int64_t>(tokens) * nb;
+  quantize_scatter_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, as_stream(stream)>>>(
+      static_cast<const uint4*>(x), static_cast<const int*>(row_of_pair), static_cast<uint2*>(packed_out),
+      static_cast<uint8_t*>(sf_out), tokens, k, nb, (K + 63) / 64);
   return launch_result();
 }
 

@@ -27,6 +27,8 @@ SIGNATURES = {
     "frt_norm_quant_nvfp4": (_I, [_P, _P, _P, _F, _F, _P, _P, _P, _I, _I, _U, _P]),
     "frt_nvfp4_gemm_bf16": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _F, _F, _P]),
     "frt_router_topk_bf16": (_I, [_P, _P, _P, _I, _I, _I, _P]),
+    "frt_router_topk_softmax_bf16": (_I, [_P, _P, _P, _P, _I, _I, _I, _P]),
+    "frt_moe_quantize_scatter_nvfp4": (_I, [_P, _P, _P, _P, _I, _I, _I, _P]),
     "frt_moe_route_plan": (_I, [_P, _I, _I, _I, _P, _P, _P, _P]),
     "frt_moe_gather_nvfp4": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _P]),
     "frt_moe_weighted_sum_bf16": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _P]),

@@ -117,5 +117,21 @@ def moe_gather_nvfp4(packed, sfa, token_of_row, *, out_packed=None, out_sfa=None
     return out_packed, out_sfa
 
 
+@torch.library.register_fake(add_op_namespace_prefix("moe_quantize_scatter_nvfp4"))
+def _quantize_scatter_fake(x, row_of_pair, out_packed, out_sfa) -> None:
+    if x.dim() != 2 or row_of_pair.dim() != 2 or row_of_pair.shape[0] != x.shape[0]:
+        raise RuntimeError("x must be (tokens, K) and row_of_pair (tokens, topk)")
+    return None
+
+
+def moe_quantize_scatter_nvfp4(x, row_of_pair, *, out_packed=None, out_sfa=None):
+    """bf16 token rows quantised to NVFP4 straight into expert-sorted order (quantise + gather in one pass)."""
+    from flashrt_b200_core import alloc_fp4
+    if out_packed is None or out_sfa is None:
+        out_packed, out_sfa = alloc_fp4(row_of_pair.numel(), x.shape[1], x.device)
+    ops.moe_quantize_scatter_nvfp4(x, row_of_pair, out_packed, out_sfa)
+    return out_packed, out_sfa
+
+
 __all__ = ["grouped_nvfp4_gemm_bf16", "grouped_nvfp4_gemm_bf16_offsets", "grouped_workspace", "moe_route_plan",
-           "moe_gather_nvfp4"]
+           "moe_gather_nvfp4", "moe_quantize_scatter_nvfp4"]

@@ -499,6 +499,25 @@ void router_topk_bf16(const Tensor& logits, Tensor& out_idx, Tensor& out_val, in
   check_rc(frt_router_topk_bf16(logits.data_ptr(), out_idx.data_ptr(), out_val.data_ptr(), as_int(tokens, "tokens"),
                                 as_int(n, "n_experts"), as_int(k, "k"), stream_of(logits)), "router_topk_bf16");
 }
+// additive: top-k with the softmax of the selected logits as routing weights, in the same kernel
+void router_topk_softmax_bf16(const Tensor& logits, Tensor& out_idx, Tensor& out_val, Tensor& out_weight, int64_t k) {
+  check_dtype(out_weight, torch::kFloat32, "out_weight", "torch.float32");
+  TORCH_CHECK(out_weight.sizes() == out_val.sizes(), "out_weight must have the shape of out_val");
+  check_dtype(logits, torch::kBFloat16, "logits", "torch.bfloat16");
+  check_dtype(out_idx, torch::kInt32, "out_idx", "torch.int32");
+  check_dtype(out_val, torch::kFloat32, "out_val", "torch.float32");
+  TORCH_CHECK(logits.dim() == 2, "logits must have shape (tokens, n_experts)");
+  const int64_t tokens = logits.size(0), n = logits.size(1);
+  TORCH_CHECK(out_idx.sizes() == torch::IntArrayRef({tokens, k}) && out_val.sizes() == torch::IntArrayRef({tokens, k}),
+              "topk outputs must have shape (tokens, k)");
+  check_same_device(logits, out_idx, "logits", "out_idx");
+  check_same_device(logits, out_val, "logits", "out_val");
+  check_same_device(logits, out_weight, "logits", "out_weight");
+  c10::cuda::CUDAGuard guard(logits.device());
+  check_rc(frt_router_topk_softmax_bf16(logits.data_ptr(), out_idx.data_ptr(), out_val.data_ptr(), out_weight.data_ptr(),
+                                        as_int(tokens, "tokens"), as_int(n, "n_experts"), as_int(k, "k"),
+                                        stream_of(logits)), "router_topk_softmax_bf16");
+}
 void moe_weighted_sum_bf16_to_fp32(const Tensor& expert_output, const Tensor& row_indices, const Tensor& router_weight,
                                    Tensor& out) {
   check_dtype(expert_output, torch::kBFloat16, "expert_output", "torch.bfloat16");
@@ -539,6 +558,23 @@ void moe_route_plan(const Tensor& topk_idx, int64_t n_experts, Tensor& expert_of
                               as_int(n_experts, "n_experts"), expert_offsets.data_ptr(), row_of_pair.data_ptr(),
                               token_of_row.data_ptr(), stream_of(topk_idx)), "moe_route_plan");
 }
+void moe_quantize_scatter_nvfp4(const Tensor& x, const Tensor& row_of_pair, Tensor& out_packed, Tensor& out_sfa) {
+  check_dtype(x, torch::kBFloat16, "x", "torch.bfloat16");
+  check_dtype(row_of_pair, torch::kInt32, "row_of_pair", "torch.int32");
+  TORCH_CHECK(x.dim() == 2 && row_of_pair.dim() == 2 && row_of_pair.size(0) == x.size(0),
+              "x must be (tokens, K) and row_of_pair (tokens, topk)");
+  TORCH_CHECK(x.size(1) % 16 == 0, "K must be divisible by 16");
+  TORCH_CHECK(out_packed.dim() == 2 && out_packed.size(0) >= row_of_pair.numel(),
+              "out_packed must have a row for every (token, slot) pair");
+  check_packed_scales(out_packed, out_sfa, out_packed.size(0), x.size(1), "out_packed", "out_sfa");
+  check_same_device(x, row_of_pair, "x", "row_of_pair");
+  check_same_device(x, out_packed, "x", "out_packed");
+  check_same_device(x, out_sfa, "x", "out_sfa");
+  c10::cuda::CUDAGuard guard(x.device());
+  check_rc(frt_moe_quantize_scatter_nvfp4(x.data_ptr(), row_of_pair.data_ptr(), out_packed.data_ptr(), out_sfa.data_ptr(),
+                                          as_int(x.size(0), "tokens"), as_int(row_of_pair.size(1), "topk"),
+                                          as_int(x.size(1), "K"), stream_of(x)), "moe_quantize_scatter_nvfp4");
+}
 void moe_gather_nvfp4(const Tensor& packed, const Tensor& sfa, const Tensor& token_of_row, Tensor& out_packed,
                       Tensor& out_sfa) {
   check_dtype(token_of_row, torch::kInt32, "token_of_row", "torch.int32");
@@ -573,6 +609,8 @@ TORCH_LIBRARY_EXPAND(transformer_fused_ops_b200, ops) {
   ops.impl("nexn2_router_topk_bf16", torch::kCUDA, &router_topk_bf16);
   ops.impl("router_topk_bf16", torch::kCUDA, &router_topk_bf16);
   ops.impl("moe_weighted_sum_bf16_to_fp32", torch::kCUDA, &moe_weighted_sum_bf16_to_fp32);
+  ops.def("router_topk_softmax_bf16(Tensor logits, Tensor! out_idx, Tensor! out_val, Tensor! out_weight, int k) -> ()");
+  ops.impl("router_topk_softmax_bf16", torch::kCUDA, &router_topk_softmax_bf16);
 }
 
 TORCH_LIBRARY_EXPAND(flashrt_nvfp4_b200, ops) {
@@ -660,6 +698,8 @@ TORCH_LIBRARY_EXPAND(grouped_moe_gemm_b200, ops) {
   ops.def("moe_gather_nvfp4(Tensor packed, Tensor sfa, Tensor token_of_row, Tensor! out_packed, Tensor! out_sfa) -> ()");
   ops.impl("moe_route_plan", torch::kCUDA, &moe_route_plan);
   ops.impl("moe_gather_nvfp4", torch::kCUDA, &moe_gather_nvfp4);
+  ops.def("moe_quantize_scatter_nvfp4(Tensor x, Tensor row_of_pair, Tensor! out_packed, Tensor! out_sfa) -> ()");
+  ops.impl("moe_quantize_scatter_nvfp4", torch::kCUDA, &moe_quantize_scatter_nvfp4);
 }
 
 REGISTER_EXTENSION(TORCH_EXTENSION_NAME)

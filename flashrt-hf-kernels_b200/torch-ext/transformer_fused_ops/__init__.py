@@ -48,6 +48,22 @@ def router_topk_bf16(logits, k: int = 8, *, out_idx=None, out_val=None):
     return out_idx, out_val
 
 
+@torch.library.register_fake(add_op_namespace_prefix("router_topk_softmax_bf16"))
+def _topk_softmax_fake(logits, out_idx, out_val, out_weight, k) -> None:
+    if logits.dim() != 2 or tuple(out_idx.shape) != (logits.shape[0], k):
+        raise RuntimeError("logits must be (tokens, n_experts) and the outputs (tokens, k)")
+    return None
+
+
+def router_topk_softmax_bf16(logits, k: int = 8):
+    """Top-k router that also returns the routing weights (softmax over the k selected logits) from the same
+    kernel: ``(idx, val, weight)``, each (tokens, k)."""
+    idx, val = _alloc_topk(logits, k)
+    weight = torch.empty_like(val)
+    ops.router_topk_softmax_bf16(logits, idx, val, weight, int(k))
+    return idx, val, weight
+
+
 def nexn2_router_topk_bf16(logits, k: int = 8, *, out_idx=None, out_val=None):
     if out_idx is None or out_val is None:
         out_idx, out_val = _alloc_topk(logits, k)
@@ -65,4 +81,4 @@ def moe_weighted_sum_bf16_to_fp32(expert_output, row_indices, router_weight, *, 
     return out
 
 
-__all__ = ["router_topk_bf16", "nexn2_router_topk_bf16", "moe_weighted_sum_bf16_to_fp32"]
+__all__ = ["router_topk_bf16", "router_topk_softmax_bf16", "nexn2_router_topk_bf16", "moe_weighted_sum_bf16_to_fp32"]

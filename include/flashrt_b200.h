@@ -228,6 +228,11 @@ int frt_nvfp4_grouped_gemm_bf16_noalloc(const void* a_packed, const void* sfa,
 int frt_router_topk_bf16(const void* logits, void* out_idx, void* out_val,
                          int tokens, int n_experts, int k, void* stream);
 
+/* The same router with the routing weights as a fourth output: out_weight f32 [tokens, k] = softmax over
+ * the k selected logits (= the top-k of the full softmax, re-normalised); out_weight may be NULL. */
+int frt_router_topk_softmax_bf16(const void* logits, void* out_idx, void* out_val, void* out_weight,
+                                 int tokens, int n_experts, int k, void* stream);
+
 /* Routing plan = stable sort of the (token, slot) pairs by expert, on the device:
  *   expert_offsets i32 [n_experts + 1]  rows of expert e are [offsets[e], offsets[e+1])
  *   row_of_pair    i32 [tokens * k]     expert-sorted row of pair (t, j); -1 if its index is
@@ -243,6 +248,12 @@ int frt_moe_route_plan(const void* topk_idx, int tokens, int k, int n_experts,
  * out row r = in row token_of_row[r].  K % 64 == 0.  Same README passage. */
 int frt_moe_gather_nvfp4(const void* packed_in, const void* sf_in, const void* token_of_row,
                          void* packed_out, void* sf_out, int rows, int tokens, int K, void* stream);
+
+/* Quantise bf16 token rows [tokens, K] (rule A, as frt_nvfp4_quantize) straight into expert order:
+ * the NVFP4 form of token t is stored to rows row_of_pair[t, 0..k) of packed_out / sf_out (negative rows
+ * skipped).  Equal to frt_nvfp4_quantize followed by frt_moe_gather_nvfp4, in one pass. */
+int frt_moe_quantize_scatter_nvfp4(const void* x, const void* row_of_pair, void* packed_out, void* sf_out,
+                                   int tokens, int k, int K, void* stream);
 
 /* Weighted un-permute: out f32 [tokens, hidden] = sum_j weights[t, j] * expert_out[row[t, j], :hidden]
  * (bf16 rows of pitch `stride` elements), one fused multiply-add per slot in slot order,

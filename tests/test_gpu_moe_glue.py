@@ -176,3 +176,27 @@ def test_glue_argument_errors():
     assert L.frt_moe_route_plan(P(t), 0, 4, 8, P(t), P(t), P(t), st()) < 0
     assert L.frt_moe_gather_nvfp4(P(t), P(t), P(t), P(t), P(t), 4, 4, 48, st()) < 0
     assert L.frt_moe_weighted_sum_bf16(P(lg), P(t), P(f), P(f), 1, 2, 64, 32, st()) < 0  # stride < hidden
+
+
+def test_router_softmax_and_quantize_scatter():
+    """the fused forms equal the separate stages: softmax of the selected logits; quantise + gather"""
+    import grouped_moe_gemm
+    import fp4_gemm
+    import transformer_fused_ops
+    tokens, E, k, K = 300, 64, 4, 320
+    logits = randn_bf16((tokens, E), 801).to(DEV)
+    idx, val, weight = transformer_fused_ops.router_topk_softmax_bf16(logits, k)
+    idx2, val2 = transformer_fused_ops.router_topk_bf16(logits, k)
+    assert torch.equal(idx, idx2) and torch.equal(val, val2)
+    torch.testing.assert_close(weight, torch.softmax(val, dim=-1), rtol=1e-6, atol=1e-7)
+    idx[3, 1] = -1                                       # an unrouted pair is skipped
+    offsets, row_of_pair, token_of_row = grouped_moe_gemm.moe_route_plan(idx, E)
+    rows = int(offsets[-1].item())
+    x = randn_bf16((tokens, K), 802).to(DEV)
+    xp, xs = fp4_gemm.quantize_fp4_sfa_bf16(x)
+    gp, gs = grouped_moe_gemm.moe_gather_nvfp4(xp, xs, token_of_row[:rows].contiguous())
+    sp, ss = alloc_fp4(tokens * k, K, fill=0x7F)
+    grouped_moe_gemm.moe_quantize_scatter_nvfp4(x, row_of_pair, out_packed=sp, out_sfa=ss)
+    torch.cuda.synchronize()
+    assert torch.equal(sp[:rows], gp)
+    np.testing.assert_array_equal(sf_linear(ss, tokens * k, K)[:rows], sf_linear(gs, rows, K))
