@@ -17,7 +17,12 @@
 //            tcgen05.mma cta_group::2; tcgen05.commit multicast to both CTAs'
 //            `empty` / `acc_full` barriers.
 //   warps 2..9 epilogue of this CTA's 128 rows (TMEM -> registers -> swizzled staging in shared
-//            memory -> TMA store).
+//            memory -> TMA store); warps 2..17 in the SwiGLU form, whose epilogue computes
+//            bf16(silu(gate) * up), quantises it to NVFP4 and stores packed bytes + scales.
+//
+// Forms (template parameters): dense bf16 output (the last, partial wave of tiles cut into column
+// slices, see decode_unit), SWIGLU (gate/up tile pairs, NVFP4 output), GROUPED (one expert's weights
+// on the M axis, a window of its token rows on the N axis, transposed bf16 output).
 //
 // TMEM (512 columns per CTA): two 128 x BN fp32 accumulators and one scale
 // buffer.  For BN = 256 the accumulators overlap ([0,256) and [208,464), scales

@@ -197,14 +197,15 @@ __device__ __forceinline__ uint32_t mapa(uint32_t local_smem_addr, uint32_t rank
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_smem_addr), "r"(rank));
   return r;
 }
-// Arrive on an mbarrier of another CTA of the cluster.  Relaxed: the arrival only hands over
-// TMEM columns (ordered by tcgen05.fence), it publishes no generic-proxy memory, and a
-// cluster-scope release would first drain every earlier store of the thread.
+// fp32 load from the shared memory of another CTA of the cluster (address from mapa)
 __device__ __forceinline__ float ld_cluster_f32(uint32_t cluster_addr) {
   float v;
   asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(cluster_addr) : "memory");
   return v;
 }
+// Arrive on an mbarrier of another CTA of the cluster.  Relaxed: the arrival only hands over
+// TMEM columns (ordered by tcgen05.fence), it publishes no generic-proxy memory, and a
+// cluster-scope release would first drain every earlier store of the thread.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
