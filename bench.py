@@ -11,21 +11,32 @@ linears at M = 4096 tokens (synthetic data, random weights of that shape):
 divided by the step time including the two producer launches), inputs resident
 in HBM.  `e2e` is the same metric through the torch operator API with the
 step's bf16 inputs in pinned host memory and the step's result read back to
-the host inside the timed region.  With N > 1 ranks (torchrun) every rank runs
-the step on its own M tokens with replicated weights (token-sharded, no
-collective: weak scaling, `value` = N ranks' flops / max time); the same line
-carries `column_sharded`: the fixed M-token problem with the weights
-column-sharded over the ranks, activations replicated, outputs left sharded
-(strong scaling), and the NCCL all-gather of those outputs timed separately.
-`--sharding columns` makes that form the headline instead.
+the host inside the timed region.
+
+N > 1 (torchrun, one rank per GPU): the fixed M-token problem with the NVFP4
+weights column-sharded over the ranks, activations replicated, outputs left
+sharded (strong scaling; `--sharding columns`, the default); the NCCL
+all-gather of the largest output is timed separately.  The same line carries
+the Llama-3-70B FFN in the same split (`c5_column_sharded`), the step with a
+row-sharded producer whose NVFP4 rows are all-gathered inside the step
+(`row_sharded_producer`), and the token-sharded replicas (`token_sharded`:
+every rank runs the whole step on its own tokens, no collective).
+
+At N = 1 `detail` also holds: every GEMM timed back to back over rotating
+buffers, a >= 2 s sustained run, the reference's own CUDA kernels on the same
+buffers (`reference_cuda`, when oracle/_ref was built), the decode sweep on
+rotating weight sets (`c3`), the grouped MoE GEMMs (`c4`) and the Llama-3-70B
+FFN (`c5`).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c5|c4]
-                    [--sharding tokens|columns] [--tokens M --graph]
+                    [--sharding columns|tokens] [--tokens M --graph] [--quick]
 """
 from __future__ import annotations
 
 import argparse
+import ctypes
 import json
+import math
 import os
 import statistics
 import sys
@@ -42,8 +53,11 @@ import torch  # noqa: E402
 
 L2_BYTES = 126 << 20
 EPS = 1e-6
-# measured DRAM traffic per launch of the four Qwen3-8B M=4096 GEMMs (ncu, bytes)
-NCU_DRAM_TRAFFIC_BYTES = {"qkv": 29563904, "o": 19248896, "gate_up": 221514496, "down": 70588160}
+# ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch, captured on the unsharded Qwen3-8B M=4096
+# shapes (kernel -> bytes); reported as `traffic` only for a launch of exactly that shape
+NCU_DRAM_TRAFFIC_BYTES = {("gemm", 4096, 6144, 4096): 29563904, ("gemm", 4096, 4096, 4096): 19248896,
+                          ("gemm", 4096, 24576, 4096): 221514496, ("gemm", 4096, 4096, 12288): 70588160,
+                          ("producer", 4096, 4096): 69002240}
 
 WORKLOADS = {
     # name: (tokens, hidden, [(layer, N, K, fed_by_producer)])
@@ -59,19 +73,23 @@ MOE = dict(name="qwen3-30b-a3b-moe-4096tok", experts=128, top_k=8, tokens=4096,
 
 
 def measured_peaks():
+    """Roofline denominators.  MEASURED_PEAKS.json holds a copy bandwidth and a cuBLAS bf16 rate (burst and
+    sustained); it has no FP4 figure, so the FP4 tensor peak is ASSUMED to be 4 x the measured bf16 rate."""
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
         d = json.loads(p.read_text())
-        return dict(hbm_gbs=d["hbm_gbs"], fp4_tflops=4.0 * d["bf16_tflops_sustained"],
-                    fp4_tflops_burst=4.0 * d["bf16_tflops"], source="measured (MEASURED_PEAKS.json; FP4 = 4 x bf16)")
-    return dict(hbm_gbs=6650.0, fp4_tflops=4.0 * 1400.0, fp4_tflops_burst=4.0 * 1590.0, source="fallback")
+        return dict(hbm_gbs=d["hbm_gbs"], fp4_burst=4.0 * d["bf16_tflops"], fp4_sustained=4.0 * d["bf16_tflops_sustained"],
+                    source="of measured (MEASURED_PEAKS.json); FP4 peak assumed 4 x measured bf16")
+    return dict(hbm_gbs=6650.0, fp4_burst=4.0 * 1590.0, fp4_sustained=4.0 * 1400.0,
+                source="of fallback (6.65 TB/s, 1.59 PFLOP/s bf16); FP4 peak assumed 4 x bf16")
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+    """Samples SM clock, power and throttle reasons through NVML (read-only) while a timed region runs."""
 
-    def __init__(self, index: int):
-        self.samples, self.reasons, self.max_mhz = [], set(), None
+    def __init__(self, index: int, period=0.005):
+        self.samples, self.power, self.reasons, self.max_mhz = [], [], set(), None
+        self.period = period
         self._stop = threading.Event()
         self._thread = None
         try:
@@ -90,13 +108,14 @@ class ClockSampler:
         while not self._stop.is_set():
             try:
                 self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                self.power.append(nv.nvmlDeviceGetPowerUsage(self.h) / 1000.0)
                 r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
                 for k, bit in names.items():
                     if r & bit:
                         self.reasons.add(k)
             except Exception:
                 pass
-            time.sleep(0.005)
+            time.sleep(self.period)
 
     def __enter__(self):
         if self.nv is not None:
@@ -112,8 +131,30 @@ class ClockSampler:
     def summary(self):
         if not self.samples:
             return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["nvml unavailable"]}
-        return {"sm_mhz": int(statistics.median(self.samples)), "sm_max_mhz": self.max_mhz,
-                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+        out = {"sm_mhz": int(statistics.median(self.samples)), "sm_max_mhz": self.max_mhz,
+               "reasons": sorted(self.reasons), "samples": len(self.samples)}
+        if self.power:
+            out["power_w_max"] = round(max(self.power), 1)
+        return out
+
+
+def event_ms(fn, iters, warm=3):
+    """mean milliseconds of fn() over `iters` back-to-back calls (CUDA events on the current stream)"""
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def rotating_sets(bytes_per_call):
+    """how many distinct buffer sets make one round of calls touch more than 4 x L2"""
+    return max(1, min(8, math.ceil(4 * L2_BYTES / max(bytes_per_call, 1))))
 
 
 # ----------------------------------------------------------------------------
@@ -130,6 +171,7 @@ class Layer:
         self.name, self.M, self.H, layers = WORKLOADS[key]
         if tokens:
             self.name, self.M = f"{self.name.rsplit('-m', 1)[0]}-m{tokens}", tokens
+        self.rank, self.world = rank, world
         g = torch.Generator(device=dev).manual_seed(seed)
         ga = torch.Generator(device=dev).manual_seed(seed + 1 if act_seed is None else act_seed)
         rn = lambda *s, scale=1.0: (torch.randn(*s, generator=g, device=dev) * scale).to(torch.bfloat16)
@@ -143,7 +185,6 @@ class Layer:
         for lname, n, k, fed in layers:
             assert n % (world * 128) == 0, "column shard must keep whole 128-row scale groups"
             n_loc = n // world
-            # quantise the full-width weight in slabs so every rank derives the same bytes for its shard
             w = rn(n_loc, k, scale=0.02)
             wp, wsf = fp4_gemm.quantize_fp4_sfa_bf16(w, is_sfb=True)
             del w
@@ -157,9 +198,34 @@ class Layer:
             self.flops_total += 2.0 * self.M * n * k
         self.bytes_streamed = sum(g_["wp"].numel() + g_["wsf"].numel() + g_["out"].numel() * 2 +
                                   g_["a_p"].numel() for g_ in self.gemms) + 2 * 3 * self.M * self.H * 2
+        torch.cuda.synchronize()
 
-    def step_capi(self, capi, st, ev=None):
-        """one pass through the C ABI (resident inputs); optional (start,end) events per kernel"""
+    # -- the producer, whole or on this rank's row shard ------------------------------------------------
+    def row_shard(self, world, rank):
+        from flashrt_b200_core import sharding
+        r0, r1 = sharding.row_shard_bounds(self.M, world, rank)
+        per_group = ((self.H // 16 + 3) // 4) * 512
+        return r0, r1, (r0 // 128) * per_group, ((r1 + 127) // 128) * per_group
+
+    def producer_capi(self, capi, st, rows=None):
+        L, P = capi.lib(), capi.ptr
+        if rows is None:
+            return L.frt_norm_quant_nvfp4(P(self.residual), P(self.hidden), P(self.norm_w), EPS, 1.0, None,
+                                          P(self.act_packed), P(self.act_sf), self.M, self.H, 0, st)
+        r0, r1, s0, s1 = rows
+        return L.frt_norm_quant_nvfp4(P(self.residual[r0:r1]), P(self.hidden[r0:r1]), P(self.norm_w), EPS, 1.0, None,
+                                      P(self.act_packed[r0:r1]), P(self.act_sf[s0:s1]), r1 - r0, self.H, 0, st)
+
+    def gather_activations(self, dist, rows):
+        """all-gather of the NVFP4 rows every rank produced for its row shard (in place: this rank's slice is
+        already where the collective would put it)"""
+        r0, r1, s0, s1 = rows
+        dist.all_gather_into_tensor(self.act_packed, self.act_packed[r0:r1])
+        dist.all_gather_into_tensor(self.act_sf, self.act_sf[s0:s1])
+
+    def step_capi(self, capi, st, ev=None, dist=None, rows=None):
+        """one pass through the C ABI (resident inputs); optional (start,end) events per kernel; with `rows`
+        the producer runs on this rank's row shard and NCCL all-gathers the NVFP4 rows"""
         L = capi.lib()
         P = capi.ptr
         launches = 0
@@ -168,8 +234,9 @@ class Layer:
                 pe = ev.get(("producer", i)) if ev is not None else None
                 if pe:
                     pe[0].record()
-                rc = L.frt_norm_quant_nvfp4(P(self.residual), P(self.hidden), P(self.norm_w), EPS, 1.0, None,
-                                            P(self.act_packed), P(self.act_sf), self.M, self.H, 0, st)
+                rc = self.producer_capi(capi, st, rows)
+                if rows is not None:
+                    self.gather_activations(dist, rows)
                 if pe:
                     pe[1].record()
                 assert rc == 0, rc
@@ -185,17 +252,306 @@ class Layer:
             launches += 1
         return launches
 
-    def step_ops(self, hidden, residual):
-        """one pass through the torch operator API; returns the last GEMM's output"""
+    def step_ops(self, hidden, residual, dist=None, rows=None):
+        """one pass through the torch operator API; returns the last GEMM's output.  With `rows`, hidden and
+        residual are this rank's row shard and the NVFP4 rows are all-gathered."""
         import fp4_fused_ops
         import fp4_gemm
         out = None
         for g_ in self.gemms:
             if g_["fed"]:
-                fp4_fused_ops.residual_add_rms_norm_quant_nvfp4_swizzled_bf16(
-                    residual, hidden, self.norm_w, EPS, packed=self.act_packed, sfa=self.act_sf)
+                if rows is None:
+                    fp4_fused_ops.residual_add_rms_norm_quant_nvfp4_swizzled_bf16(
+                        residual, hidden, self.norm_w, EPS, packed=self.act_packed, sfa=self.act_sf)
+                else:
+                    r0, r1, s0, s1 = rows
+                    fp4_fused_ops.residual_add_rms_norm_quant_nvfp4_swizzled_bf16(
+                        residual, hidden, self.norm_w, EPS, packed=self.act_packed[r0:r1], sfa=self.act_sf[s0:s1])
+                    self.gather_activations(dist, rows)
             out = fp4_gemm.nvfp4_gemm_bf16(g_["a_p"], g_["wp"], g_["a_sf"], g_["wsf"], out=g_["out"])
         return out
+
+
+def gemm_back_to_back(layer, capi, st, peaks, iters=12):
+    """Every GEMM of the layer alone, back to back over enough distinct buffer sets that one round of calls
+    touches more than 4 x L2: no event inside the timed region, so no event cost in the number."""
+    L, P = capi.lib(), capi.ptr
+    out = {}
+    for g_ in layer.gemms:
+        per_call = g_["wp"].numel() + g_["wsf"].numel() + g_["a_p"].numel() + g_["a_sf"].numel() + g_["out"].numel() * 2
+        sets = [g_] + [dict(g_, wp=g_["wp"].clone(), wsf=g_["wsf"].clone(), a_p=g_["a_p"].clone(),
+                            a_sf=g_["a_sf"].clone(), out=torch.empty_like(g_["out"]))
+                       for _ in range(rotating_sets(per_call) - 1)]
+
+        def calls():
+            for s_ in sets:
+                L.frt_nvfp4_gemm_bf16(P(s_["a_p"]), P(s_["a_sf"]), P(s_["wp"]), P(s_["wsf"]), None, None, P(s_["out"]),
+                                      layer.M, s_["n_loc"], s_["k"], 1.0, 0.0, st)
+        ms = event_ms(calls, max(2, iters // len(sets))) / len(sets)
+        tf = 2.0 * layer.M * g_["n_loc"] * g_["k"] / (ms * 1e-3) / 1e12
+        out[g_["name"]] = {"shape": [layer.M, g_["n_loc"], g_["k"]], "us": round(ms * 1e3, 2), "tflops": round(tf, 1),
+                           "frac_of_fp4_peak": round(tf / peaks["fp4_burst"], 4), "buffer_sets": len(sets)}
+        del sets
+    return out
+
+
+def producer_back_to_back(layer, capi, st, peaks):
+    """the fused producer alone, back to back over four input sets (larger than L2 together)"""
+    from flashrt_b200_core import alloc_fp4
+    L, P = capi.lib(), capi.ptr
+    dev = layer.hidden.device
+    psets = []
+    for _ in range(4):
+        pk, sfp_ = alloc_fp4(layer.M, layer.H, dev)
+        psets.append((layer.hidden.clone(), layer.residual0.clone(), pk, sfp_))
+
+    def producers():
+        for hx, rx, pk, sfp_ in psets:
+            L.frt_norm_quant_nvfp4(P(rx), P(hx), P(layer.norm_w), EPS, 1.0, None, P(pk), P(sfp_), layer.M, layer.H, 0, st)
+    p_us = event_ms(producers, 10) / 4 * 1e3
+    prod_bytes = layer.M * layer.H * 6.5625
+    return psets, {"us": round(p_us, 2), "gbs": round(prod_bytes / p_us / 1e3, 1),
+                   "frac_of_hbm_measured": round(prod_bytes / p_us / 1e3 / peaks["hbm_gbs"], 3),
+                   "what": "fused residual+RMSNorm->NVFP4 on 4 rotating input sets, 40 launches"}
+
+
+def reference_cuda_leg(layer, psets, capi, st, peaks):
+    """The reference's own CUDA kernels, compiled unmodified into oracle/_ref (test infrastructure; this leg and
+    the CPU baseline are the only places the benchmark touches it), on the same shapes and rotating buffers:
+    its CUTLASS Sm100 NVFP4 GEMM with the default and the wide-N tile, its fused producer and its quantiser."""
+    path = ROOT / "oracle" / "_ref" / "libflashrt_ref.so"
+    if not path.exists():
+        return {"unavailable": "oracle/_ref/libflashrt_ref.so was not built (no reference checkout at build time)"}
+    ref = ctypes.CDLL(str(path))
+    P = capi.ptr
+    res = {}
+    if ref.ref_has_cutlass():
+        for g_ in layer.gemms:
+            per_call = g_["wp"].numel() + g_["a_p"].numel() + g_["out"].numel() * 2
+            sets = [g_] + [dict(g_, wp=g_["wp"].clone(), wsf=g_["wsf"].clone(), a_p=g_["a_p"].clone(),
+                                a_sf=g_["a_sf"].clone(), out=torch.empty_like(g_["out"]))
+                           for _ in range(rotating_sets(per_call) - 1)]
+            row = {}
+            for label, variant in (("default_tile_128x128x256", 0), ("widen_tile_128x256x128", 1)):
+                def calls():
+                    for s_ in sets:
+                        ref.ref_gemm_sm100_bf16(P(s_["a_p"]), P(s_["wp"]), P(s_["out"]), layer.M, s_["n_loc"], s_["k"],
+                                                P(s_["a_sf"]), P(s_["wsf"]), ctypes.c_float(1.0), variant, st)
+                ms = event_ms(calls, max(2, 12 // len(sets))) / len(sets)
+                row[label] = round(2.0 * layer.M * g_["n_loc"] * g_["k"] / (ms * 1e-3) / 1e12, 1)
+            row["best_tflops"] = max(row.values())
+            row["reference_selects"] = "widen" if g_["n_loc"] >= 4 * g_["k"] else "default"
+            res[g_["name"]] = row
+            del sets
+        hx, rx, pk, sfp_ = psets[0]
+
+        def k10():
+            for hx, rx, pk, sfp_ in psets:
+                ref.ref_res_rms_fp4_bf16(P(rx), P(hx), P(layer.norm_w), P(pk), P(sfp_), layer.M, layer.H,
+                                         ctypes.c_float(EPS), st)
+        us = event_ms(k10, 10) / 4 * 1e3
+        res["fused_producer"] = {"us": round(us, 2), "gbs": round(layer.M * layer.H * 6.5625 / us / 1e3, 1)}
+    else:
+        res["gemm"] = {"unavailable": "oracle/_ref was built without a CUTLASS header tree"}
+
+    def k4():
+        for hx, rx, pk, sfp_ in psets:
+            ref.ref_quantize_bf16_vec(P(hx), P(pk), P(sfp_), layer.M, layer.H, st)
+    us = event_ms(k4, 10) / 4 * 1e3
+    res["quantizer"] = {"us": round(us, 2), "gbs": round(layer.M * layer.H * 2.5625 / us / 1e3, 1)}
+    res["what"] = ("the reference's kernels compiled for sm_100a from its own sources (cluster 1x1x1 CUTLASS Sm100 GEMM, "
+                   "fused residual+RMSNorm->NVFP4, vectorised quantiser), same shapes, same rotating buffers, CUDA events")
+    return res
+
+
+def sustained_leg(layer, capi, st, local_rank, ms_step, peaks, seconds=2.0):
+    """the same step looped for >= `seconds`: clocks settle under the power cap, so this is the sustained figure"""
+    n = max(10, int(seconds * 1e3 / ms_step) + 1)
+    with ClockSampler(local_rank, period=0.02) as clocks:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(n):
+            layer.step_capi(capi, st)
+        e1.record()
+        torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / n
+    c = clocks.summary()
+    tf = layer.flops_total / (ms * 1e-3) / 1e12
+    return {"steps": n, "seconds": round(ms * n / 1e3, 2), "ms_per_step": round(ms, 5), "tflops": round(tf, 1),
+            "frac_of_fp4_sustained_peak": round(tf / peaks["fp4_sustained"], 4), "clocks": c,
+            "ms_x_median_sm_mhz": round(ms * c["sm_mhz"], 2) if c.get("sm_mhz") else None}
+
+
+def decode_leg(capi, dev, peaks, tokens=(1, 4, 16, 64), graph_replays=20):
+    """Decode sweep on the Qwen3-8B linears: four distinct weight sets (434 MB, 3.4 x L2) visited in turn, so
+    every weight byte comes from HBM; one CUDA graph holds the four steps; the weight stream is
+    0.5625 * N * K bytes per GEMM."""
+    import fp4_gemm
+    from flashrt_b200_core import alloc_fp4
+    L, P = capi.lib(), capi.ptr
+    name, _, H, layers = WORKLOADS["c2"]
+    g = torch.Generator(device=dev).manual_seed(77)
+    wsets = []
+    for _ in range(4):
+        ws = []
+        for lname, n, k, fed in layers:
+            w = (torch.randn(n, k, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+            ws.append(fp4_gemm.quantize_fp4_sfa_bf16(w, is_sfb=True))
+            del w
+        wsets.append(ws)
+    wbytes = sum(0.5625 * n * k for _, n, k, _ in layers)
+    norm_w = torch.ones(H, device=dev, dtype=torch.bfloat16)
+    out = {}
+    for M in tokens:
+        hidden = torch.randn(M, H, generator=g, device=dev).to(torch.bfloat16)
+        residual = torch.randn(M, H, generator=g, device=dev).to(torch.bfloat16)
+        act_p, act_sf = alloc_fp4(M, H, dev)
+        res_in = [None if fed else fp4_gemm.quantize_fp4_sfa_bf16(torch.randn(M, k, generator=g, device=dev).to(torch.bfloat16))
+                  for _, n, k, fed in layers]
+        outs = [torch.empty(M, n, device=dev, dtype=torch.bfloat16) for _, n, k, _ in layers]
+        torch.cuda.synchronize()
+
+        def steps(st):
+            n_l = 0
+            for ws in wsets:
+                for i, (lname, n, k, fed) in enumerate(layers):
+                    if fed:
+                        assert L.frt_norm_quant_nvfp4(P(residual), P(hidden), P(norm_w), EPS, 1.0, None, P(act_p), P(act_sf),
+                                                      M, H, 0, st) == 0
+                        n_l += 1
+                    a_p, a_sf = (act_p, act_sf) if fed else res_in[i]
+                    assert L.frt_nvfp4_gemm_bf16(P(a_p), P(a_sf), P(ws[i][0]), P(ws[i][1]), None, None, P(outs[i]),
+                                                 M, n, k, 1.0, 0.0, st) == 0
+                    n_l += 1
+            return n_l
+        steps(capi.stream_ptr())
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                steps(capi.stream_ptr())
+        torch.cuda.synchronize()
+        ms = event_ms(graph.replay, graph_replays) / len(wsets)
+        gbs = wbytes / (ms * 1e-3) / 1e9
+        out[f"m{M}"] = {"us_per_step": round(ms * 1e3, 2), "weight_stream_gbs": round(gbs, 1),
+                        "frac_of_hbm_measured": round(gbs / peaks["hbm_gbs"], 3)}
+        del graph
+    out["what"] = (f"{name.rsplit('-m', 1)[0]} linears + 2 fused producers per step, 4 rotating weight sets "
+                   f"({4 * wbytes / 1e6:.0f} MB), one CUDA graph of 4 steps replayed {graph_replays} times; "
+                   f"{wbytes / 1e6:.1f} MB of weights per step")
+    out["roofline"] = {"bound": "hbm", "kernel": "decode step (4 nvfp4_gemm_kernel + 2 norm_quant_kernel launches)",
+                       "achieved": out["m1"]["weight_stream_gbs"] if "m1" in out else None, "peak": peaks["hbm_gbs"],
+                       "unit": "GB/s", "frac": out["m1"]["frac_of_hbm_measured"] if "m1" in out else None}
+    return out
+
+
+def moe_setup(capi, dev):
+    """routing of the synthetic workload: top-8 of seeded N(0,1) logits (= top-8 of their softmax), sorted by
+    expert into per-expert offsets, with this library's router and routing-plan kernels"""
+    L, P, st = capi.lib(), capi.ptr, capi.stream_ptr()
+    experts = MOE["experts"]
+    g0 = torch.Generator(device=dev).manual_seed(3)
+    setup_logits = torch.randn(MOE["tokens"], experts, generator=g0, device=dev).to(torch.bfloat16)
+    s_idx = torch.empty(MOE["tokens"], MOE["top_k"], dtype=torch.int32, device=dev)
+    s_val = torch.empty(MOE["tokens"], MOE["top_k"], dtype=torch.float32, device=dev)
+    offs_d = torch.empty(experts + 1, dtype=torch.int32, device=dev)
+    s_rop = torch.empty(MOE["tokens"], MOE["top_k"], dtype=torch.int32, device=dev)
+    s_tor = torch.empty(MOE["tokens"] * MOE["top_k"], dtype=torch.int32, device=dev)
+    assert L.frt_router_topk_bf16(P(setup_logits), P(s_idx), P(s_val), MOE["tokens"], experts, MOE["top_k"], st) == 0
+    assert L.frt_moe_route_plan(P(s_idx), MOE["tokens"], MOE["top_k"], experts, P(offs_d), P(s_rop), P(s_tor), st) == 0
+    torch.cuda.synchronize()
+    rows = int(offs_d[-1].item())
+    alpha = torch.ones(experts, device=dev)
+    work = torch.empty(int(L.frt_nvfp4_grouped_gemm_workspace_bytes(rows, experts)), dtype=torch.uint8, device=dev)
+    sfb = lambda r, k: int(L.frt_nvfp4_sf_swizzled_bytes(r, k))
+    layers, flops = [], 0.0
+    for name, n, k in MOE["layers"]:
+        ap = torch.randint(0, 256, (rows, k // 2), dtype=torch.uint8, device=dev)
+        wp = torch.randint(0, 256, (experts, n, k // 2), dtype=torch.uint8, device=dev)
+        asf = torch.randint(32, 80, (sfb(rows, k),), dtype=torch.uint8, device=dev)
+        wsf = torch.randint(32, 80, (experts, sfb(n, k)), dtype=torch.uint8, device=dev)
+        out = torch.empty(rows, n, dtype=torch.bfloat16, device=dev)
+        layers.append((name, n, k, ap, wp, asf, wsf, out))
+        flops += 2.0 * rows * n * k
+    return dict(rows=rows, experts=experts, offs=offs_d, alpha=alpha, work=work, layers=layers, flops=flops, sfb=sfb)
+
+
+def moe_measure(capi, dev, peaks, steps, warmup):
+    L, P, st = capi.lib(), capi.ptr, capi.stream_ptr()
+    S = moe_setup(capi, dev)
+    rows, experts, layers = S["rows"], S["experts"], S["layers"]
+
+    def one(layer_):
+        name, n, k, ap, wp, asf, wsf, out = layer_
+        rc = L.frt_nvfp4_grouped_gemm_bf16(P(ap), P(asf), P(wp), P(wsf), P(S["alpha"]), P(S["offs"]), None, 0, P(out), rows,
+                                           n, k, experts, n * (k // 2), int(wsf.shape[1]), P(S["work"]), st)
+        assert rc == 0, rc
+
+    def step():
+        for l_ in layers:
+            one(l_)
+    l0 = L.frt_launch_count()
+    ms = event_ms(step, steps, warm=warmup)
+    launches = int(L.frt_launch_count() - l0)
+    per_layer = {}
+    for l_ in layers:
+        lms = event_ms(lambda: one(l_), max(5, steps // 2))
+        fl = 2.0 * rows * l_[1] * l_[2]
+        wb = experts * l_[1] * l_[2] * 0.5625
+        per_layer[l_[0]] = {"us": round(lms * 1e3, 1), "tflops": round(fl / (lms * 1e-3) / 1e12, 1),
+                            "frac_of_fp4_peak": round(fl / (lms * 1e-3) / 1e12 / peaks["fp4_burst"], 4),
+                            "weight_stream_gbs": round(wb / (lms * 1e-3) / 1e9, 1),
+                            "weight_stream_frac_of_hbm": round(wb / (lms * 1e-3) / 1e9 / peaks["hbm_gbs"], 3)}
+
+    # ---- the whole routed layer through the C ABI: router -> plan -> quantise -> gather ->
+    # grouped gate/up -> SwiGLU -> NVFP4 -> grouped down -> weighted un-permute
+    T, E, topk = MOE["tokens"], experts, MOE["top_k"]
+    (_, n1, k1, _, wp1, _, wsf1, out1), (_, n2, k2, _, wp2, _, wsf2, out2) = layers
+    sfb = S["sfb"]
+    g = torch.Generator(device=dev).manual_seed(11)
+    hidden = torch.randn(T, k1, generator=g, device=dev).to(torch.bfloat16)
+    logits = torch.randn(T, E, generator=g, device=dev).to(torch.bfloat16)
+    idx = torch.empty(T, topk, dtype=torch.int32, device=dev)
+    val = torch.empty(T, topk, dtype=torch.float32, device=dev)
+    off = torch.empty(E + 1, dtype=torch.int32, device=dev)
+    rop = torch.empty(T, topk, dtype=torch.int32, device=dev)
+    tor = torch.empty(T * topk, dtype=torch.int32, device=dev)
+    gp = torch.empty(T * topk, k1 // 2, dtype=torch.uint8, device=dev)
+    gs = torch.zeros(sfb(T * topk, k1), dtype=torch.uint8, device=dev)
+    hp = torch.empty(T * topk, k2 // 2, dtype=torch.uint8, device=dev)
+    hs = torch.zeros(sfb(T * topk, k2), dtype=torch.uint8, device=dev)
+    final = torch.empty(T, n2, dtype=torch.float32, device=dev)
+    weights = torch.empty(T, topk, dtype=torch.float32, device=dev)
+    R = T * topk
+    alpha, work = S["alpha"], S["work"]
+
+    def routed_layer():
+        rcs = [L.frt_router_topk_softmax_bf16(P(logits), P(idx), P(val), P(weights), T, E, topk, st),
+               L.frt_moe_route_plan(P(idx), T, topk, E, P(off), P(rop), P(tor), st),
+               L.frt_moe_quantize_scatter_nvfp4(P(hidden), P(rop), P(gp), P(gs), T, topk, k1, st),
+               L.frt_nvfp4_grouped_gemm_bf16(P(gp), P(gs), P(wp1), P(wsf1), P(alpha), P(off), None, 0, P(out1), R, n1,
+                                             k1, E, n1 * (k1 // 2), int(wsf1.shape[1]), P(work), st),
+               L.frt_silu_mul_quant_nvfp4(P(out1), P(hp), P(hs), R, n1 // 2, st),
+               L.frt_nvfp4_grouped_gemm_bf16(P(hp), P(hs), P(wp2), P(wsf2), P(alpha), P(off), None, 0, P(out2), R, n2,
+                                             k2, E, n2 * (k2 // 2), int(wsf2.shape[1]), P(work), st),
+               L.frt_moe_weighted_sum_bf16(P(out2), P(rop), P(weights), P(final), T, topk, n2, n2, st)]
+        assert not any(rcs), rcs
+
+    routed_us = None
+    if n1 // 2 == k2 and rows == R:
+        routed_us = round(event_ms(routed_layer, max(5, min(50, steps))) * 1e3, 1)
+    tf = S["flops"] / (ms * 1e-3) / 1e12
+    return {"tflops": round(tf, 2), "ms_per_step": round(ms, 5), "routed_rows": rows, "experts": experts,
+            "layers": per_layer, "routed_layer_us": routed_us, "gpu_launches": launches,
+            "roofline": {"bound": "tensor", "kernel": "nvfp4_gemm_pair_kernel<grouped> (gate/up + down)",
+                         "achieved": round(tf, 1), "peak": round(peaks["fp4_burst"], 1), "unit": "TFLOP/s",
+                         "frac": round(tf / peaks["fp4_burst"], 4),
+                         "peak_note": peaks["source"] + "; the workload sits near the ridge (340 MB of expert weights "
+                                      "for 309 GFLOP): weight-stream GB/s per layer is reported beside it"},
+            "what": "router top-k + softmax, routing plan, quantise into expert order, grouped gate/up, SwiGLU->NVFP4, "
+                    "grouped down, weighted un-permute = routed_layer_us (11 launches of this library)"}
 
 
 def run_ours(args, rank, world, local_rank):
@@ -207,20 +563,38 @@ def run_ours(args, rank, world, local_rank):
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
     peaks = measured_peaks()
-    # N > 1: by default every rank runs the whole step on its OWN tokens (weights replicated, no
-    # collective: weak scaling); --sharding columns runs the fixed problem with column-sharded weights
-    # and replicated activations (strong scaling), which the token-sharded run also reports beside it.
-    tokens_mode = world > 1 and args.sharding != "columns"
+    # N > 1: the fixed problem with column-sharded weights and replicated activations (strong scaling) unless
+    # --sharding tokens: every rank runs the whole step on its OWN tokens (weights replicated, no collective).
+    tokens_mode = world > 1 and args.sharding == "tokens"
     col_world = 1 if tokens_mode else world
     layer = Layer(args.workload, rank, col_world, dev, tokens=args.tokens,
                   act_seed=7000 + rank if tokens_mode else None)
     job_flops = layer.flops_total * (world if tokens_mode else 1)
     st = capi.stream_ptr()
+    L = capi.lib()
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+        return ms
+
+    def timed_steps(lay, n_steps, **kw):
+        """barrier, n steps, barrier; milliseconds per step, max over ranks"""
+        barrier()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(n_steps):
+            lay.step_capi(capi, st, **kw)
+        t1.record()
+        barrier()
+        return max_over_ranks(t0.elapsed_time(t1) / n_steps)
 
     for _ in range(args.warmup):
         layer.step_capi(capi, st)
@@ -250,7 +624,8 @@ def run_ours(args, rank, world, local_rank):
                 "metric": "nvfp4_linear_path_tflops", "value": round(job_flops / (ms * 1e-3) / 1e12, 3),
                 "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
                 "ms_per_step": round(ms, 5), "higher_is_better": True, "data": "synthetic", "timing": "cuda graph replay",
-                "config": {"workload": layer.name, "tokens": layer.M},
+                "config": {"workload": layer.name, "tokens": layer.M,
+                           "l2": "ONE weight set replayed: partly L2-resident; detail.c3 of the default run rotates four"},
                 "weight_stream_gbs_whole_step": round(wbytes / (ms * 1e-3) / 1e9, 1),
                 "weight_stream_frac_of_hbm_measured": round(wbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 3),
                 "gpu_launches": n_launch * args.steps, "clocks": clocks.summary()}), flush=True)
@@ -264,7 +639,7 @@ def run_ours(args, rank, world, local_rank):
     dom = (layer.gemms[dom_i]["name"], dom_i)
     events = [{dom: (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))}
               for _ in range(args.steps)]
-    launches0 = capi.lib().frt_launch_count()
+    launches0 = L.frt_launch_count()
     with ClockSampler(local_rank) as clocks:
         barrier()
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -274,12 +649,8 @@ def run_ours(args, rank, world, local_rank):
         t1.record()
         barrier()
     ms_total = t0.elapsed_time(t1)
-    launches = capi.lib().frt_launch_count() - launches0
-    if world > 1:
-        t = torch.tensor([ms_total], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total = float(t.item())
-    ms_step = ms_total / args.steps
+    launches = L.frt_launch_count() - launches0
+    ms_step = max_over_ranks(ms_total) / args.steps
     value = job_flops / (ms_step * 1e-3) / 1e12
 
     dom_ms = statistics.mean(e[dom][0].elapsed_time(e[dom][1]) for e in events)
@@ -299,56 +670,41 @@ def run_ours(args, rank, world, local_rank):
     dom_flops = 2.0 * layer.M * dom_g["n_loc"] * dom_g["k"]
     achieved = dom_flops / (dom_ms * 1e-3) / 1e12
     prod_bytes = layer.M * layer.H * 6.5625
+    timed_region_s = ms_total * 1e-3
     detail = {
-        "gemm_only_tflops": job_flops / (gemm_ms * 1e-3) / 1e12,
-        "per_kernel_us": {f"{k[0]}": round(v * 1e3, 2) for k, v in per_kernel.items()},
-        "per_gemm_tflops": {layer.gemms[k[1]]["name"]: round(2.0 * layer.M * layer.gemms[k[1]]["n_loc"] *
-                            layer.gemms[k[1]]["k"] / (v * 1e-3) / 1e12, 1) for k, v in per_kernel.items()
-                            if k[0] != "producer"},
-        "weight_stream_gbs": round(sum(0.5625 * g_["n_loc"] * g_["k"] for g_ in layer.gemms) / (gemm_ms * 1e-3) / 1e9 * world, 1),
-        "producer_gbs": round(prod_bytes / (statistics.mean(prod_ms) * 1e-3) / 1e9, 1) if prod_ms else None,
+        "gemm_only_tflops": round(job_flops / (gemm_ms * 1e-3) / 1e12, 1),
+        "in_step_us_with_event_overhead": {f"{k[0]}": round(v * 1e3, 2) for k, v in per_kernel.items()},
+        "producer_in_step_gbs": round(prod_bytes / (statistics.mean(prod_ms) * 1e-3) / 1e9, 1) if prod_ms else None,
         "producer_frac_of_hbm_measured": round(prod_bytes / (statistics.mean(prod_ms) * 1e-3) / 1e9 /
                                                peaks["hbm_gbs"], 3) if prod_ms else None,
     }
-
-    # ---- the producer alone, back to back over four input sets (292 MB: larger than L2) ----------------
-    if any(g_["fed"] for g_ in layer.gemms):
-        from flashrt_b200_core import alloc_fp4
-        Lp, Pp = capi.lib(), capi.ptr
-        psets = []
-        for _ in range(4):
-            pk, sfp_ = alloc_fp4(layer.M, layer.H, dev)
-            psets.append((layer.hidden.clone(), layer.residual0.clone(), pk, sfp_))
-
-        def producers():
-            for hx, rx, pk, sfp_ in psets:
-                Lp.frt_norm_quant_nvfp4(Pp(rx), Pp(hx), Pp(layer.norm_w), EPS, 1.0, None, Pp(pk), Pp(sfp_), layer.M,
-                                        layer.H, 0, st)
-        for _ in range(3):
-            producers()
-        torch.cuda.synchronize()
-        q0, q1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        q0.record()
-        for _ in range(10):
-            producers()
-        q1.record()
-        torch.cuda.synchronize()
-        p_us = q0.elapsed_time(q1) / 40 * 1e3
-        detail["producer_back_to_back"] = {"us": round(p_us, 2), "gbs": round(prod_bytes / p_us / 1e3, 1),
-                                           "frac_of_hbm_measured": round(prod_bytes / p_us / 1e3 / peaks["hbm_gbs"], 3),
-                                           "what": "fused residual+RMSNorm->NVFP4 on 4 rotating input sets, 40 launches"}
-        del psets
+    deep = world == 1 and not args.quick
+    # ---- every GEMM alone, back to back over rotating buffers; the producer likewise --------------------
+    psets = None
+    if world == 1:
+        detail["per_gemm"] = gemm_back_to_back(layer, capi, st, peaks)
+        all_ms = sum(v["us"] for v in detail["per_gemm"].values()) * 1e-3
+        detail["four_gemms_frac_of_fp4_peak" if len(layer.gemms) == 4 else "gemms_frac_of_fp4_peak"] = round(
+            layer.flops_total / (all_ms * 1e-3) / 1e12 / peaks["fp4_burst"], 4)
+    if any(g_["fed"] for g_ in layer.gemms) and world == 1:
+        psets, detail["producer_back_to_back"] = producer_back_to_back(layer, capi, st, peaks)
 
     # ---- end to end through the torch operator API with host buffers ----------
-    # the step's two bf16 inputs (hidden, residual) sit in ONE pinned buffer and travel as one copy
-    host_in = torch.empty(2, layer.M, layer.H, dtype=torch.bfloat16).pin_memory()
-    host_in[0].copy_(layer.hidden.cpu())
-    host_in[1].copy_(layer.residual0.cpu())
+    # N = 1: the step's two bf16 inputs (hidden, residual) sit in ONE pinned buffer and travel as one copy.
+    # N > 1, column-sharded: each rank copies only ITS row shard of the inputs, runs the producer on those rows,
+    # all-gathers the NVFP4 rows over NVLink (NCCL), runs its column shard of the GEMMs and reads back its
+    # shard of the result; summed over ranks the job moves the same input rows once and the whole output once.
+    rows = layer.row_shard(world, rank) if (world > 1 and not tokens_mode and layer.M % (128 * world) == 0) else None
+    m_loc = layer.M if rows is None else rows[1] - rows[0]
+    host_in = torch.empty(2, m_loc, layer.H, dtype=torch.bfloat16).pin_memory()
+    sl = slice(None) if rows is None else slice(rows[0], rows[1])
+    host_in[0].copy_(layer.hidden[sl].cpu())
+    host_in[1].copy_(layer.residual0[sl].cpu())
     last = layer.gemms[-1]["out"]
     host_out = [torch.empty(last.shape, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
-    dev_in = [torch.empty(2, layer.M, layer.H, dtype=torch.bfloat16, device=dev) for _ in range(2)]
+    dev_in = [torch.empty(2, m_loc, layer.H, dtype=torch.bfloat16, device=dev) for _ in range(2)]
     copy_s, comp_s, out_s = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
-    h2d = 2 * layer.M * layer.H * 2 * world          # whole job: every rank copies its step inputs
+    h2d = 2 * m_loc * layer.H * 2 * world            # whole job, every rank's copies
     d2h = last.numel() * 2 * world
 
     def e2e_steps(n):
@@ -366,7 +722,7 @@ def run_ours(args, rank, world, local_rank):
                 comp_s.wait_event(in_ready[b])
                 if s >= 1:
                     comp_s.wait_event(out_free)
-                out = layer.step_ops(dev_in[b][0], dev_in[b][1])
+                out = layer.step_ops(dev_in[b][0], dev_in[b][1], dist=dist, rows=rows)
                 in_free[b].record(comp_s)
                 out_ready.record(comp_s)
             with torch.cuda.stream(out_s):
@@ -383,11 +739,7 @@ def run_ours(args, rank, world, local_rank):
     w0 = time.perf_counter()
     e2e_steps(e2e_n)
     barrier()
-    e2e_ms = (time.perf_counter() - w0) * 1e3 / max(e2e_n, 1)
-    if world > 1:
-        t = torch.tensor([e2e_ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
+    e2e_ms = max_over_ranks((time.perf_counter() - w0) * 1e3 / max(e2e_n, 1))
     e2e_val = job_flops / (e2e_ms * 1e-3) / 1e12
 
     # ---- all-gather of the sharded outputs, timed separately -------------------
@@ -403,82 +755,118 @@ def run_ours(args, rank, world, local_rank):
             dist.all_gather_into_tensor(gathered, big["out"])
         a1.record()
         barrier()
-        ag_ms = a0.elapsed_time(a1) / 10
-        t = torch.tensor([ag_ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ag_ms = float(t.item())
+        ag_ms = max_over_ranks(a0.elapsed_time(a1) / 10)
         tot = gathered.numel() * 2
         del gathered
         return {"layer": big["name"], "ms": round(ag_ms, 4), "bytes_total": tot,
                 "bus_gbs": round(tot * (world - 1) / world / (ag_ms * 1e-3) / 1e9, 1), "backend": "nccl"}
 
-    # ---- all-gather of the column-sharded outputs, timed separately; in a token-sharded run the
-    # column-sharded form of the same (fixed-size) problem is measured here as well
-    allgather = column_sharded = None
+    def column_run(key, n_steps):
+        """the workload `key` column-sharded over the ranks: replicated producer, and row-sharded producer +
+        NCCL all-gather of the NVFP4 rows inside the step"""
+        col = layer if key == args.workload and not tokens_mode else Layer(key, rank, world, dev)
+        for _ in range(max(3, args.warmup // 2)):
+            col.step_capi(capi, st)
+        ms_rep = timed_steps(col, n_steps)
+        res = {"value": round(col.flops_total / (ms_rep * 1e-3) / 1e12, 2), "unit": "TFLOP/s",
+               "ms_per_step": round(ms_rep, 5), "scaling": "strong",
+               "what": f"{col.name}: fixed {col.M} tokens, weights column-sharded x{world}, activations replicated "
+                       "(every rank runs the whole producer), outputs left sharded"}
+        if col.M % (128 * world) == 0:
+            rws = col.row_shard(world, rank)
+            for _ in range(3):
+                col.step_capi(capi, st, dist=dist, rows=rws)
+            ms_row = timed_steps(col, n_steps, dist=dist, rows=rws)
+            res["row_sharded_producer"] = {
+                "value": round(col.flops_total / (ms_row * 1e-3) / 1e12, 2), "ms_per_step": round(ms_row, 5),
+                "what": "producer on this rank's rows, NCCL all-gather of packed + scale bytes inside the step"}
+        res["allgather_separate"] = time_allgather(col)
+        if col is not layer:
+            del col
+        return res
+
+    allgather = column_sharded = token_sharded = c5_col = row_sharded = None
     if world > 1 and not tokens_mode:
         allgather = time_allgather(layer)
+        if layer.M % (128 * world) == 0:
+            rws = layer.row_shard(world, rank)
+            for _ in range(3):
+                layer.step_capi(capi, st, dist=dist, rows=rws)
+            ms_row = timed_steps(layer, args.steps, dist=dist, rows=rws)
+            row_sharded = {"value": round(layer.flops_total / (ms_row * 1e-3) / 1e12, 2), "ms_per_step": round(ms_row, 5),
+                           "what": "the same step with the producer on this rank's rows and an NCCL all-gather of the "
+                                   "packed + scale bytes (M*K*0.5625 B per producer) inside the step"}
+        if args.workload == "c2" and not args.tokens and not args.quick:
+            # every rank runs the whole step on its own tokens: replicas, no collective (weak scaling)
+            tok = Layer("c2", rank, 1, dev, act_seed=7000 + rank)
+            for _ in range(3):
+                tok.step_capi(capi, st)
+            ms_tok = timed_steps(tok, args.steps)
+            token_sharded = {"value": round(tok.flops_total * world / (ms_tok * 1e-3) / 1e12, 2), "unit": "TFLOP/s",
+                             "ms_per_step": round(ms_tok, 5), "scaling": "weak",
+                             "what": f"every rank runs the whole step on its own {tok.M} tokens, weights replicated"}
+            del tok
+            torch.cuda.empty_cache()
+            c5_col = column_run("c5", max(5, args.steps // 4))
     elif world > 1:
-        col = Layer(args.workload, rank, world, dev, tokens=args.tokens)
-        for _ in range(args.warmup):
-            col.step_capi(capi, st)
-        barrier()
-        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        c0.record()
-        for _ in range(args.steps):
-            col.step_capi(capi, st)
-        c1.record()
-        barrier()
-        t = torch.tensor([c0.elapsed_time(c1) / args.steps], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        col_ms = float(t.item())
-        column_sharded = {"value": round(col.flops_total / (col_ms * 1e-3) / 1e12, 2), "unit": "TFLOP/s",
-                          "ms_per_step": round(col_ms, 5), "scaling": "strong",
-                          "what": f"the same workload at a fixed {col.M} tokens, weights column-sharded x{world}, "
-                                  "activations replicated, outputs left sharded",
-                          "allgather_separate": time_allgather(col)}
-        del col
-
+        column_sharded = column_run(args.workload, args.steps)
     # ---- the FFN as a connected chain: gate/up GEMM -> SwiGLU -> NVFP4 -> down GEMM ------
     # (not part of `value`: in the timed step above the down GEMM reads a resident NVFP4 input)
     names = [g_["name"] for g_ in layer.gemms]
     if world == 1 and "gate_up" in names and "down" in names:
         gu, dn = layer.gemms[names.index("gate_up")], layer.gemms[names.index("down")]
-        Lc, Pc = capi.lib(), capi.ptr
+        Pc = capi.ptr
         hid = gu["n_loc"] // 2
         if dn["k"] == hid and hid % 128 == 0:
             def plain():
-                Lc.frt_nvfp4_gemm_bf16(Pc(gu["a_p"]), Pc(gu["a_sf"]), Pc(gu["wp"]), Pc(gu["wsf"]), None, None,
-                                       Pc(gu["out"]), layer.M, gu["n_loc"], gu["k"], 1.0, 0.0, st)
-                Lc.frt_silu_mul_quant_nvfp4(Pc(gu["out"]), Pc(dn["a_p"]), Pc(dn["a_sf"]), layer.M, hid, st)
-                Lc.frt_nvfp4_gemm_bf16(Pc(dn["a_p"]), Pc(dn["a_sf"]), Pc(dn["wp"]), Pc(dn["wsf"]), None, None,
-                                       Pc(dn["out"]), layer.M, dn["n_loc"], dn["k"], 1.0, 0.0, st)
+                L.frt_nvfp4_gemm_bf16(Pc(gu["a_p"]), Pc(gu["a_sf"]), Pc(gu["wp"]), Pc(gu["wsf"]), None, None,
+                                      Pc(gu["out"]), layer.M, gu["n_loc"], gu["k"], 1.0, 0.0, st)
+                L.frt_silu_mul_quant_nvfp4(Pc(gu["out"]), Pc(dn["a_p"]), Pc(dn["a_sf"]), layer.M, hid, st)
+                L.frt_nvfp4_gemm_bf16(Pc(dn["a_p"]), Pc(dn["a_sf"]), Pc(dn["wp"]), Pc(dn["wsf"]), None, None,
+                                      Pc(dn["out"]), layer.M, dn["n_loc"], dn["k"], 1.0, 0.0, st)
 
             def fused():
-                Lc.frt_nvfp4_gemm_swiglu_nvfp4(Pc(gu["a_p"]), Pc(gu["a_sf"]), Pc(gu["wp"]), Pc(gu["wsf"]),
-                                               Pc(dn["a_p"]), Pc(dn["a_sf"]), layer.M, gu["n_loc"], gu["k"], 1.0, st)
-                Lc.frt_nvfp4_gemm_bf16(Pc(dn["a_p"]), Pc(dn["a_sf"]), Pc(dn["wp"]), Pc(dn["wsf"]), None, None,
-                                       Pc(dn["out"]), layer.M, dn["n_loc"], dn["k"], 1.0, 0.0, st)
-
-            chain = {}
+                L.frt_nvfp4_gemm_swiglu_nvfp4(Pc(gu["a_p"]), Pc(gu["a_sf"]), Pc(gu["wp"]), Pc(gu["wsf"]),
+                                              Pc(dn["a_p"]), Pc(dn["a_sf"]), layer.M, gu["n_loc"], gu["k"], 1.0, st)
+                L.frt_nvfp4_gemm_bf16(Pc(dn["a_p"]), Pc(dn["a_sf"]), Pc(dn["wp"]), Pc(dn["wsf"]), None, None,
+                                      Pc(dn["out"]), layer.M, dn["n_loc"], dn["k"], 1.0, 0.0, st)
             n_it = max(5, min(50, args.steps))
-            for label, fn in (("three_kernels_us", plain), ("swiglu_in_gemm_epilogue_us", fused)):
-                for _ in range(3):
-                    fn()
-                torch.cuda.synchronize()
-                c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                c0.record()
-                for _ in range(n_it):
-                    fn()
-                c1.record()
-                torch.cuda.synchronize()
-                chain[label] = round(c0.elapsed_time(c1) / n_it * 1e3, 1)
-            detail["ffn_chain"] = chain
+            detail["ffn_chain"] = {"three_kernels_us": round(event_ms(plain, n_it) * 1e3, 1),
+                                   "swiglu_in_gemm_epilogue_us": round(event_ms(fused, n_it) * 1e3, 1)}
+
+    if deep:
+        detail["sustained"] = sustained_leg(layer, capi, st, local_rank, ms_step, peaks)
+        if psets is not None and args.workload == "c2" and not args.tokens:
+            detail["reference_cuda"] = reference_cuda_leg(layer, psets, capi, st, peaks)
+    del psets
+    if deep and args.workload == "c2" and not args.tokens:
+        torch.cuda.empty_cache()
+        detail["c3"] = decode_leg(capi, dev, peaks)
+        torch.cuda.empty_cache()
+        detail["c4"] = moe_measure(capi, dev, peaks, steps=max(5, min(20, args.steps)), warmup=3)
+        torch.cuda.empty_cache()
+        c5 = Layer("c5", 0, 1, dev)
+        for _ in range(3):
+            c5.step_capi(capi, st)
+        c5_ms = event_ms(lambda: c5.step_capi(capi, st), 5, warm=1)
+        c5_tf = c5.flops_total / (c5_ms * 1e-3) / 1e12
+        detail["c5"] = {"tflops": round(c5_tf, 1), "ms_per_step": round(c5_ms, 4), "config": c5.name,
+                        "per_gemm": gemm_back_to_back(c5, capi, st, peaks, iters=4),
+                        "roofline": {"bound": "tensor", "kernel": "nvfp4_gemm_pair_kernel (Llama-3-70B FFN, 8192 tokens)",
+                                     "achieved": round(c5_tf, 1), "peak": round(peaks["fp4_burst"], 1), "unit": "TFLOP/s",
+                                     "frac": round(c5_tf / peaks["fp4_burst"], 4), "peak_note": peaks["source"]}}
+        del c5
+        torch.cuda.empty_cache()
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cpu_baseline = run_cpu_port(args, steps=1, sample_rows=32)
 
     if rank == 0:
+        # The timed region is a burst (milliseconds at boost clock) unless it runs for a second or more:
+        # the burst bf16 figure x 4 is the denominator then, the sustained one otherwise.
+        burst = timed_region_s < 1.0
+        peak = peaks["fp4_burst"] if burst else peaks["fp4_sustained"]
         line = {
             "metric": "nvfp4_linear_path_tflops", "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_step, 5), "higher_is_better": True,
@@ -490,44 +878,45 @@ def run_ours(args, rank, world, local_rank):
                        "global_tokens": layer.M * (world if tokens_mode else 1),
                        "parallelism": (f"token-sharded x{world}: every rank runs the step on its own {layer.M} tokens, "
                                        "weights replicated, no collective" if tokens_mode else
-                                       f"column-sharded x{world}, activations replicated" if world > 1 else "single GPU"),
+                                       f"column-sharded x{world}: NVFP4 weights partitioned by output columns, "
+                                       "activations replicated, outputs left sharded" if world > 1 else "single GPU"),
                        "l2": f"inputs larger than L2: each step streams {layer.bytes_streamed >> 20} MiB "
                              f"({L2_BYTES >> 20} MiB L2), every tensor touched once per step"},
             "e2e": {"value": round(e2e_val, 2), "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_ms, 4),
                     "api": "torch ops fp4_fused_ops.residual_add_rms_norm_quant_nvfp4_swizzled_bf16 + "
-                           "fp4_gemm.nvfp4_gemm_bf16; pinned host in/out, copies overlapped on side streams"},
+                           "fp4_gemm.nvfp4_gemm_bf16; pinned host in/out, copies overlapped on side streams" +
+                           ("; each rank copies its row shard of the inputs, the NVFP4 rows are all-gathered (NCCL)"
+                            if rows is not None else "")},
             "gpu_launches": int(launches),
             "clocks": clocks.summary(),
             "roofline": {"bound": "tensor", "kernel": f"nvfp4_gemm_pair_kernel ({dom_g['name']} "
                          f"{layer.M}x{dom_g['n_loc']}x{dom_g['k']})", "achieved": round(achieved, 1),
-                         "peak": round(peaks["fp4_tflops"], 1), "unit": "TFLOP/s",
-                         "frac": round(achieved / peaks["fp4_tflops"], 4),
-                         "peak_note": peaks["source"] + ", sustained figure (kernel timed inside a long step)",
-                         "frac_of_burst_peak": round(achieved / peaks["fp4_tflops_burst"], 4),
+                         "peak": round(peak, 1), "unit": "TFLOP/s",
+                         "frac": round(achieved / peak, 4),
+                         "peak_note": peaks["source"] + ("; burst figure: the timed region lasted "
+                                                         f"{timed_region_s * 1e3:.1f} ms" if burst else
+                                                         "; sustained figure: the timed region lasted "
+                                                         f"{timed_region_s:.1f} s"),
+                         "frac_of_sustained_peak": round(achieved / peaks["fp4_sustained"], 4),
                          "frac_of_nominal_9000": round(achieved / 9000.0, 4),
-                         "traffic": None},
+                         "algorithmic_flops_per_launch": dom_flops,
+                         "traffic": NCU_DRAM_TRAFFIC_BYTES.get(("gemm", layer.M, dom_g["n_loc"], dom_g["k"]))},
             "detail": detail,
         }
-        # ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this workload
-        # (profiles/nvfp4_gemm_pair_and_producer_qwen3_8b_m4096.md); only meaningful for the unsharded default
-        if args.workload == "c2" and not args.tokens and dom_g["n_loc"] == dom_g["n"]:
-            line["roofline"]["traffic"] = NCU_DRAM_TRAFFIC_BYTES.get(dom_g["name"])
         if "producer_back_to_back" in detail:
             pb = detail["producer_back_to_back"]
             line["roofline_producer"] = {
                 "bound": "hbm", "kernel": f"norm_quant_kernel ({layer.M}x{layer.H} residual+RMSNorm->NVFP4)",
                 "achieved": pb["gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": pb["frac_of_hbm_measured"],
                 "algorithmic_bytes": int(prod_bytes),
-                # ncu on this shape: 67.1 MB read + 1.9 MB written back by kernel end (the rest of the 46 MB of
-                # output is still dirty in L2 then)
-                "traffic": 69002240 if (layer.M, layer.H) == (4096, 4096) else None}
-        if allgather:
-            line["allgather_separate"] = allgather
-        if column_sharded:
-            line["column_sharded"] = column_sharded
-        if cpu_baseline:
-            line["cpu_baseline"] = cpu_baseline
+                # (at kernel end part of the output is still dirty in L2, so DRAM traffic is below the algorithmic bytes)
+                "traffic": NCU_DRAM_TRAFFIC_BYTES.get(("producer", layer.M, layer.H))}
+        for key, val in (("allgather_separate", allgather), ("row_sharded_producer", row_sharded),
+                         ("column_sharded", column_sharded), ("token_sharded", token_sharded),
+                         ("c5_column_sharded", c5_col), ("cpu_baseline", cpu_baseline)):
+            if val:
+                line[key] = val
         print(json.dumps(line), flush=True)
 
 
@@ -537,113 +926,20 @@ def run_moe(args, rank, world, local_rank):
     load()
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
-    L, P, st = capi.lib(), capi.ptr, capi.stream_ptr()
-    # routing of the synthetic workload: top-8 of seeded N(0,1) logits (= top-8 of their softmax), sorted by
-    # expert into per-expert offsets, with this library's router and routing-plan kernels
-    experts = MOE["experts"]
-    g0 = torch.Generator(device=dev).manual_seed(3)
-    setup_logits = torch.randn(MOE["tokens"], experts, generator=g0, device=dev).to(torch.bfloat16)
-    s_idx = torch.empty(MOE["tokens"], MOE["top_k"], dtype=torch.int32, device=dev)
-    s_val = torch.empty(MOE["tokens"], MOE["top_k"], dtype=torch.float32, device=dev)
-    offs_d = torch.empty(experts + 1, dtype=torch.int32, device=dev)
-    s_rop = torch.empty(MOE["tokens"], MOE["top_k"], dtype=torch.int32, device=dev)
-    s_tor = torch.empty(MOE["tokens"] * MOE["top_k"], dtype=torch.int32, device=dev)
-    assert L.frt_router_topk_bf16(P(setup_logits), P(s_idx), P(s_val), MOE["tokens"], experts, MOE["top_k"], st) == 0
-    assert L.frt_moe_route_plan(P(s_idx), MOE["tokens"], MOE["top_k"], experts, P(offs_d), P(s_rop), P(s_tor), st) == 0
-    torch.cuda.synchronize()
-    rows = int(offs_d[-1].item())
-    alpha = torch.ones(experts, device=dev)
-    work = torch.empty(int(L.frt_nvfp4_grouped_gemm_workspace_bytes(rows, experts)), dtype=torch.uint8, device=dev)
-    sfb = lambda r, k: int(L.frt_nvfp4_sf_swizzled_bytes(r, k))
-    layers, flops = [], 0.0
-    for name, n, k in MOE["layers"]:
-        ap = torch.randint(0, 256, (rows, k // 2), dtype=torch.uint8, device=dev)
-        wp = torch.randint(0, 256, (experts, n, k // 2), dtype=torch.uint8, device=dev)
-        asf = torch.randint(32, 80, (sfb(rows, k),), dtype=torch.uint8, device=dev)
-        wsf = torch.randint(32, 80, (experts, sfb(n, k)), dtype=torch.uint8, device=dev)
-        out = torch.empty(rows, n, dtype=torch.bfloat16, device=dev)
-        layers.append((name, n, k, ap, wp, asf, wsf, out))
-        flops += 2.0 * rows * n * k
-
-    def step():
-        for name, n, k, ap, wp, asf, wsf, out in layers:
-            rc = L.frt_nvfp4_grouped_gemm_bf16(P(ap), P(asf), P(wp), P(wsf), P(alpha), P(offs_d), None, 0, P(out), rows,
-                                               n, k, experts, n * (k // 2), int(wsf.shape[1]), P(work), st)
-            assert rc == 0, rc
-
-    for _ in range(args.warmup):
-        step()
-    torch.cuda.synchronize()
-    l0 = L.frt_launch_count()
+    peaks = measured_peaks()
     with ClockSampler(local_rank) as clocks:
-        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        t0.record()
-        for _ in range(args.steps):
-            step()
-        t1.record()
-        torch.cuda.synchronize()
-    ms = t0.elapsed_time(t1) / args.steps
-    launches = int(L.frt_launch_count() - l0)
-
-    # ---- the whole routed layer through the C ABI: router -> plan -> quantise -> gather ->
-    # grouped gate/up -> SwiGLU -> NVFP4 -> grouped down -> weighted un-permute
-    T, E, topk = MOE["tokens"], experts, MOE["top_k"]
-    (_, n1, k1, _, wp1, _, wsf1, out1), (_, n2, k2, _, wp2, _, wsf2, out2) = layers
-    g = torch.Generator(device=dev).manual_seed(11)
-    hidden = torch.randn(T, k1, generator=g, device=dev).to(torch.bfloat16)
-    logits = torch.randn(T, E, generator=g, device=dev).to(torch.bfloat16)
-    idx = torch.empty(T, topk, dtype=torch.int32, device=dev)
-    val = torch.empty(T, topk, dtype=torch.float32, device=dev)
-    off = torch.empty(E + 1, dtype=torch.int32, device=dev)
-    rop = torch.empty(T, topk, dtype=torch.int32, device=dev)
-    tor = torch.empty(T * topk, dtype=torch.int32, device=dev)
-    xp = torch.empty(T, k1 // 2, dtype=torch.uint8, device=dev)
-    xs = torch.zeros(sfb(T, k1), dtype=torch.uint8, device=dev)
-    gp = torch.empty(T * topk, k1 // 2, dtype=torch.uint8, device=dev)
-    gs = torch.zeros(sfb(T * topk, k1), dtype=torch.uint8, device=dev)
-    hp = torch.empty(T * topk, k2 // 2, dtype=torch.uint8, device=dev)
-    hs = torch.zeros(sfb(T * topk, k2), dtype=torch.uint8, device=dev)
-    final = torch.empty(T, n2, dtype=torch.float32, device=dev)
-    weights = torch.empty(T, topk, dtype=torch.float32, device=dev)
-    R = T * topk
-
-    def routed_layer():
-        rcs = [L.frt_router_topk_softmax_bf16(P(logits), P(idx), P(val), P(weights), T, E, topk, st),
-               L.frt_moe_route_plan(P(idx), T, topk, E, P(off), P(rop), P(tor), st),
-               L.frt_moe_quantize_scatter_nvfp4(P(hidden), P(rop), P(gp), P(gs), T, topk, k1, st),
-               L.frt_nvfp4_grouped_gemm_bf16(P(gp), P(gs), P(wp1), P(wsf1), P(alpha), P(off), None, 0, P(out1), R, n1,
-                                             k1, E, n1 * (k1 // 2), int(wsf1.shape[1]), P(work), st),
-               L.frt_silu_mul_quant_nvfp4(P(out1), P(hp), P(hs), R, n1 // 2, st),
-               L.frt_nvfp4_grouped_gemm_bf16(P(hp), P(hs), P(wp2), P(wsf2), P(alpha), P(off), None, 0, P(out2), R, n2,
-                                             k2, E, n2 * (k2 // 2), int(wsf2.shape[1]), P(work), st),
-               L.frt_moe_weighted_sum_bf16(P(out2), P(rop), P(weights), P(final), T, topk, n2, n2, st)]
-        assert not any(rcs), rcs
-
-    routed_us = None
-    if n1 // 2 == k2 and rows == R:
-        for _ in range(3):
-            routed_layer()
-        torch.cuda.synchronize()
-        r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        n_it = max(5, min(50, args.steps))
-        r0.record()
-        for _ in range(n_it):
-            routed_layer()
-        r1.record()
-        torch.cuda.synchronize()
-        routed_us = round(r0.elapsed_time(r1) / n_it * 1e3, 1)
+        r = moe_measure(capi, dev, peaks, args.steps, args.warmup)
     if rank == 0:
         print(json.dumps({
-            "metric": "nvfp4_grouped_moe_tflops", "value": round(flops / (ms * 1e-3) / 1e12, 2), "unit": "TFLOP/s",
-            "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 5),
+            "metric": "nvfp4_grouped_moe_tflops", "value": r["tflops"], "unit": "TFLOP/s",
+            "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_step"],
             "higher_is_better": True, "scaling": "replicas only", "vs_baseline": None, "dtype": "nvfp4", "data": "synthetic",
-            "config": {"workload": MOE["name"], "routed_rows": rows, "experts": experts,
-                       "layers": {l[0]: [l[1], l[2]] for l in layers},
+            "config": {"workload": MOE["name"], "routed_rows": r["routed_rows"], "experts": r["experts"],
+                       "layers": {l[0]: [l[1], l[2]] for l in MOE["layers"]},
                        "l2": "weights 340 MB + activations per step exceed the 126 MiB L2"},
-            "detail": {"routed_layer_us": routed_us,
-                       "routed_layer": "router top-k + softmax, routing plan, quantise into expert order, grouped gate/up, "
-                                       "SwiGLU->NVFP4, grouped down, weighted un-permute (11 launches of this library)"},
-            "gpu_launches": launches, "clocks": clocks.summary()}), flush=True)
+            "roofline": r["roofline"],
+            "detail": {"layers": r["layers"], "routed_layer_us": r["routed_layer_us"], "routed_layer": r["what"]},
+            "gpu_launches": r["gpu_launches"], "clocks": clocks.summary()}), flush=True)
 
 
 # ----------------------------------------------------------------------------
@@ -704,6 +1000,9 @@ def run_reference(args, rank, world):
     pure-torch oracle its tests use, restated under oracle/ (kind "port")."""
     if rank != 0:
         return
+    if args.workload not in WORKLOADS:
+        print(json.dumps({"impl": "reference", "unavailable": "the CPU arm covers the dense workloads (c2, c5)"}))
+        return
     rows = 64
     steps_run = max(1, min(args.steps, 3))       # bounded: each step is a 64-token sample of the workload
     res = run_cpu_port(args, steps=steps_run, sample_rows=rows, warmup=min(args.warmup, 1))
@@ -730,13 +1029,15 @@ def main():
     ap.add_argument("--tokens", type=int, default=0, help="override the token count M (decode sweep: 1, 4, 16, 64)")
     ap.add_argument("--graph", action="store_true",
                     help="time CUDA-graph replays of the step (launch-bound decode shapes); prints a short line")
-    ap.add_argument("--sharding", default="tokens", choices=["tokens", "columns"],
-                    help="N > 1: tokens = data-parallel over token rows (weak scaling, default); columns = "
-                         "column-sharded weights on the fixed problem (strong scaling)")
+    ap.add_argument("--sharding", default="columns", choices=["columns", "tokens"],
+                    help="N > 1: columns = column-sharded weights on the fixed problem (strong scaling, default); "
+                         "tokens = data-parallel replicas over token rows (weak scaling)")
     ap.add_argument("--no-pdl", action="store_true",
                     help="plain kernel launches instead of programmatic dependent launches (A/B)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--quick", action="store_true",
+                    help="only the step itself: no sustained / reference-kernel / decode / MoE / Llama-70B legs")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))

@@ -17,8 +17,13 @@ namespace frt {
 extern std::atomic<int64_t> g_launches;     // kernels launched by this library
 extern int g_opt_quant_encoder;             // FRT_OPT_QUANT_ENCODER
 extern int g_opt_gemm_config;               // FRT_OPT_GEMM_CONFIG
-extern int g_opt_gemm_debug;                // experiment switches of the GEMM kernel
 extern int g_opt_pdl;                       // FRT_OPT_PDL: programmatic dependent launch (default on)
+extern int g_opt_norm_form;                 // FRT_OPT_NORM_FORM: 0 automatic, 1 per-row-group, 2 streamed
+extern int g_opt_tail_split;                // FRT_OPT_GEMM_TAIL_SPLIT: slice the last wave of the dense pair GEMM
+extern int g_opt_split_k;                   // FRT_OPT_GEMM_SPLIT_K: cluster split-K of the small-M GEMM
+#ifdef FRT_DEBUG
+extern int g_opt_gemm_debug;                // experiment switches of the GEMM kernel (debug builds only)
+#endif
 
 // Status word written by kernels whose bounded waits ran out (one per device
 // context, lives in device global memory of this library).

@@ -35,7 +35,19 @@ namespace frt {
 namespace {
 
 __device__ unsigned g_status_word = 0;
+
+// Experiment hooks (skip the output stores, skip the scale copies, a clock64 timeline of one CTA
+// pair) exist only in a build with -DFRT_DEBUG; the shipped library has none of them.
+#ifdef FRT_DEBUG
 long long* g_trace = nullptr;   // set by frt_debug_set_trace
+#define FRT_DBG(p, bit) (((p).dbg & (bit)) != 0)
+#define FRT_TRACING(p) ((p).trace != nullptr)
+#define FRT_TRACE(p, slot) ((p).trace[slot] = clock64())
+#else
+#define FRT_DBG(p, bit) false
+#define FRT_TRACING(p) false
+#define FRT_TRACE(p, slot) ((void)0)
+#endif
 
 constexpr int BM = 128;            // UMMA M, rows of P per tile
 constexpr int BK = 256;            // elements of K per smem stage (128 bytes per row)
@@ -57,10 +69,14 @@ struct GemmParams {
   int ldd;                  // row stride of d and c, in elements
   float alpha, beta;
   int group_m;              // raster: tiles walk GROUP_M p-tiles before the next q-tile
-  int dbg;                  // experiment switches (0 in production)
   const float* alpha_stack; // grouped: per-expert alpha
+  int max_items;            // grouped: capacity of the work list (items beyond it were dropped by the plan)
   int splits;               // split-K cluster size (small-M form), 1 otherwise
-  long long* trace;         // clock64 timeline of pair 0, 8 slots per tile (null in production)
+  int p_interleaved;        // P is stored in the interleaved GEMV layout [rows/8][K/64][8][32 B] (4-D tensor map)
+#ifdef FRT_DEBUG
+  int dbg;                  // experiment switches
+  long long* trace;         // clock64 timeline of pair 0, 8 slots per tile
+#endif
   // SwiGLU -> NVFP4 epilogue: Q holds [gate ; up] (2 * hidden rows); outputs are hidden wide
   // dense 256-wide pair form: work units = tiles, those of the last partial wave cut in column slices
   int units, tail_first, tail_split;
@@ -88,6 +104,15 @@ __device__ __forceinline__ void tile_coords(int t, const GemmParams& p, int& pt,
   const int r = t - group * per_group;
   pt = first + r % gsize;
   qt = r / gsize;
+}
+
+// One stage of P: 128 rows x 128 bytes, 128B-swizzled.  The interleaved layout keeps, for each group of 8 rows and
+// each 64-element k-tile, the 8 rows' 32-byte pieces together; as a 4-D tensor (32 B, k-tile, row in group, group)
+// a box of (32, 4, 8, 16) lands in shared memory exactly as the plain 2-D box of 128 rows x 128 bytes does.
+__device__ __forceinline__ void load_p_stage(void* dst, const CUtensorMap* map, uint64_t* bar, int ks, int pt,
+                                             bool interleaved) {
+  if (interleaved) ptx::tma_load_4d(dst, map, bar, 0, ks * KT_PER_STAGE, 0, pt * (BM / 8));
+  else ptx::tma_load_2d(dst, map, bar, ks * 128, pt * BM);
 }
 
 // SPLITK (small token counts, SWAP form only): `p.splits` CTAs form a cluster on one tile of 128
@@ -173,7 +198,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
           uint8_t* st = smem + n_pre * L::STAGE_BYTES;
           const int kts = min(KT_PER_STAGE, p.k_tiles - ks * KT_PER_STAGE);
           ptx::mbar_expect_tx(&full[n_pre], L::A_BYTES + L::B_BYTES + kts * SF_TILE * (1 + nblk));
-          ptx::tma_load_2d(st, &map_p, &full[n_pre], ks * 128, pt * BM);
+          load_p_stage(st, &map_p, &full[n_pre], ks, pt, SWAP && p.p_interleaved);
           ptx::bulk_load(st + L::A_BYTES + L::B_BYTES,
                          p.sfp + (static_cast<int64_t>(pt) * p.sf_cols + ks * KT_PER_STAGE) * SF_TILE,
                          kts * SF_TILE, &full[n_pre]);
@@ -198,7 +223,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
             }
             const uint32_t bytes = L::A_BYTES + L::B_BYTES + kts * SF_TILE * (1 + nblk);
             ptx::mbar_expect_tx(&full[s], bytes);
-            ptx::tma_load_2d(st, &map_p, &full[s], ks * 128, pt * BM);
+            load_p_stage(st, &map_p, &full[s], ks, pt, SWAP && p.p_interleaved);
             ptx::bulk_load(st + L::A_BYTES + L::B_BYTES,
                            p.sfp + (static_cast<int64_t>(pt) * p.sf_cols + ks * KT_PER_STAGE) * SF_TILE,
                            kts * SF_TILE, &full[s]);
@@ -231,7 +256,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
       const uint64_t sf_desc = ptx::desc_sf_32x16(smem0 + L::A_BYTES + L::B_BYTES);
       const uint32_t op_hi = static_cast<uint32_t>(op_desc >> 32), op_lo0 = static_cast<uint32_t>(op_desc);
       const uint32_t sf_hi = static_cast<uint32_t>(sf_desc >> 32), sf_lo0 = static_cast<uint32_t>(sf_desc);
-      const bool copy_always = !(p.dbg & 2);
+      const bool copy_always = !FRT_DBG(p, 2);
       int s = 0, tl = 0;
       uint32_t ph = 0, sfbuf = 0;
       bool aborted = false;
@@ -350,7 +375,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
               uint4 o;
               o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
               o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
-              if (!(p.dbg & 1)) *reinterpret_cast<uint4*>(p.d + off + 8 * g) = o;
+              if (!FRT_DBG(p, 1)) *reinterpret_cast<uint4*>(p.d + off + 8 * g) = o;
             }
           }
         } else {
@@ -455,6 +480,22 @@ int make_operand_map(CUtensorMap* map, const void* base, int rows, int K, int bo
   return r == CUDA_SUCCESS ? FRT_OK : FRT_E_DRIVER;
 }
 
+// packed e2m1 weights in the interleaved GEMV layout [rows/8][K/64][8 rows][32 bytes]; box = one stage of 128
+// rows x 4 k-tiles, written to shared memory in (group, row, k-tile, byte) order = 128-byte rows, 128B swizzle
+int make_interleaved_map(CUtensorMap* map, const void* base, int rows, int K) {
+  auto enc = get_encode();
+  if (!enc) return FRT_E_DRIVER;
+  const cuuint64_t kt = static_cast<cuuint64_t>(K / 64);
+  const cuuint64_t dims[4] = {32, kt, 8, static_cast<cuuint64_t>(rows / 8)};
+  const cuuint64_t strides[3] = {256, 32, kt * 256};
+  const cuuint32_t box[4] = {32, KT_PER_STAGE, 8, BM / 8};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(base), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? FRT_OK : FRT_E_DRIVER;
+}
+
 // swizzled scale buffer as [row_blocks][sf_cols][512 bytes]; box = `blocks` row groups x 4 k-tiles
 int make_sf_map(CUtensorMap* map, const void* base, int rows, int sf_cols, int blocks) {
   auto enc = get_encode();
@@ -550,7 +591,7 @@ int launch_gemm_pair(const void* p_packed, const void* q_packed, GemmParams& p, 
   const int all_pairs = sms / 2;
   const int left = tiles % all_pairs;
   p.tail_split = 1;
-  if (BN == 256 && left > 0 && !(g_opt_gemm_debug & 8)) {
+  if (BN == 256 && left > 0 && g_opt_tail_split) {
     if (left * 4 <= all_pairs) p.tail_split = 4;
     else if (left * 2 <= all_pairs && p.K < 8192) p.tail_split = 2;
   }
@@ -633,6 +674,10 @@ __device__ __forceinline__ void emit_windows(GroupWork* work, int max_items, int
   const int first = lo & ~63;
   const int n_win = (hi - first + 255) / 256;
   int slot = atomicAdd(&work->count, n_win);
+  // A list that does not fit (overlapping or unsorted offsets: a sorted description always fits the
+  // documented workspace) is cut short, never overrun: the GEMM kernel clamps the count the same way,
+  // and the status word tells the host that rows were dropped.
+  if (slot + n_win > max_items) atomicOr(&g_status_word, 0x200u);
   for (int start = first; start < hi; start += 256, ++slot) {
     const int len = min(256, (hi - start + 31) & ~31);
     if (slot < max_items) {
@@ -695,7 +740,11 @@ int make_sf_stack_map(CUtensorMap* map, const void* base, int n, int sf_cols, in
 
 }  // namespace
 
-int64_t grouped_max_items(int rows, int experts) { return static_cast<int64_t>(rows) / 64 + 2ll * experts + 8; }
+// Capacity of the work list for `rows` expert-sorted rows.  Offsets form: an expert with r rows gives at most
+// r / 256 + 2 windows (its first window starts on the 64-row boundary below its first row).  tile_expert form:
+// a run of equal tiles gives at most as many windows as it has 16-row tiles, so rows / 16 covers any
+// interleaving of experts (the reference's test pattern `arange(tiles) % experts` makes every tile a run).
+int64_t grouped_max_items(int rows, int experts) { return static_cast<int64_t>(rows) / 16 + 2ll * experts + 8; }
 
 template <int STAGES>
 int run_grouped_impl(const void* a, const void* sfa, const void* b_stack, const void* sfb_stack, const void* alpha,
@@ -725,8 +774,11 @@ int run_grouped_impl(const void* a, const void* sfa, const void* b_stack, const 
   p.p_tiles = (N + 255) / 256;
   p.q_tiles = 0;
   p.group_m = 1;
+  p.max_items = static_cast<int>(grouped_max_items(rows, experts));
+#ifdef FRT_DEBUG
   p.dbg = g_opt_gemm_debug & 0xff;
   p.trace = g_trace;
+#endif
   PairMaps maps{};
   if (int rc = make_weight_stack_map(&maps.p, b_stack, N, K, experts, b_stride)) return rc;
   if (int rc = make_operand_map(&maps.q, a, rows, K, 32)) return rc;          // token windows load in 32-row boxes
@@ -734,7 +786,7 @@ int run_grouped_impl(const void* a, const void* sfa, const void* b_stack, const 
   if (int rc = make_sf_map(&maps.sfq, sfa, rows, p.sf_cols, 1)) return rc;      // one 128-row scale group per load
   if (int rc = make_output_map(&maps.d, out, rows, N, N)) return rc;
   auto* work = static_cast<GroupWork*>(workspace);
-  const int max_items = static_cast<int>(grouped_max_items(rows, experts));
+  const int max_items = p.max_items;
   if (cudaMemsetAsync(work, 0, 16, st) != cudaSuccess) return FRT_E_LAUNCH;
   const int num_tiles = tile_rows > 0 ? rows / tile_rows : 0;
   const int plan_threads = offsets ? experts : num_tiles;
@@ -765,10 +817,50 @@ unsigned* device_status_word() {
   return ptr;
 }
 
+// Picks the kernel configuration and, for the small-M form, the split-K cluster size.
+//   one CTA per tile: 1 = 128x128 (2 acc), 2 = 128x256 (1 acc), 3 = 128x192 (2 acc);
+//   CTA pair per tile: 4 = 256x256, 5 = 256x192, 6 = 256x128;
+//   swapped (small token counts): 11 = N16, 12 = N32, 13 = N64, 14 = N128
+void select_gemm_config(int P, int Q, int K, bool swap, int requested, int sms, int& cfg, int& splits) {
+  cfg = requested;
+  splits = 1;
+  if (cfg == 0) {
+    if (swap) cfg = Q <= 16 ? 11 : Q <= 32 ? 12 : Q <= 64 ? 13 : 14;
+    else if (P > 128) {
+      // CTA pairs.  Estimated time = waves x cost of one tile, with the measured relative
+      // tile costs 256-wide 1.0, 192-wide 0.878, 128-wide 0.665 (narrower tiles move more bytes
+      // per flop through the ~64 B/clk an SM takes in from L2).  256x256 wins at every full
+      // Qwen3-8B / Llama-70B shape; narrower tiles win when a column shard leaves fewer 256-wide
+      // tiles than CTA pairs.
+      const int pairs = sms / 2, p_tiles = (P + 255) / 256;
+      const int widths[3] = {256, 192, 128}, cfgs[3] = {4, 5, 6};
+      const float cost[3] = {1.0f, 0.878f, 0.665f};
+      float best = 0.f;
+      for (int i = 0; i < 3; ++i) {
+        const int tiles = p_tiles * ((Q + widths[i] - 1) / widths[i]);
+        const float t = static_cast<float>((tiles + pairs - 1) / pairs) * cost[i];
+        if (i == 0 || t < best * 0.97f) { best = t; cfg = cfgs[i]; }   // prefer the wider tile on near-ties
+      }
+    } else {
+      cfg = K >= 8192 ? 2 : 3;      // long K amortises the single-accumulator 128x256 tile
+    }
+  }
+  const int bn = cfg == 11 ? 16 : cfg == 12 ? 32 : cfg == 13 ? 64 : 0;
+  if (swap && bn && Q <= bn && g_opt_split_k) {
+    // few 128-row weight tiles: split K over a cluster so that every SM streams weights
+    const int tiles = (P + BM - 1) / BM, k_stages = ((K + 63) / 64 + KT_PER_STAGE - 1) / KT_PER_STAGE;
+    int want = (bn <= 32 ? 2 * sms : sms) / tiles;     // two CTAs of the 16/32-token forms fit an SM
+    if (want > 8) want = 8;
+    for (int s = want; s >= 2; --s)
+      if (k_stages % s == 0 && k_stages / s >= 2) { splits = s; break; }
+    if (bn == 64 && splits < 4) splits = 1;   // 64 token columns: the cross-CTA sum only pays off from 4-way
+  }
+}
+
 // Shared by the dense and the small-M entry: P/Q already in kernel orientation.
 int run_gemm(const void* p_packed, const void* sfp, int P, const void* q_packed, const void* sfq, int Q, int K,
              const void* bias, const void* c, void* d, int ldd, float alpha, float beta, bool swap,
-             int config, cudaStream_t st) {
+             int config, cudaStream_t st, bool p_interleaved = false) {
   const DeviceInfo di = device_info();
   if (!di.ok || di.cc_major != 10) return FRT_E_DEVICE;
   GemmParams p{};
@@ -784,34 +876,13 @@ int run_gemm(const void* p_packed, const void* sfp, int P, const void* q_packed,
   p.ldd = ldd;
   p.alpha = alpha; p.beta = beta;
   p.group_m = 16;
+#ifdef FRT_DEBUG
   p.dbg = g_opt_gemm_debug & 0xff;
   p.trace = g_trace;
+#endif
 
-  // configuration: one CTA per tile: 1 = 128x128 (2 acc), 2 = 128x256 (1 acc), 3 = 128x192 (2 acc);
-  // CTA pair per tile: 4 = 256x256, 5 = 256x192, 6 = 256x128;
-  // swapped (small token counts): 11 = N16, 12 = N32, 13 = N64, 14 = N128
-  int cfg = config;
-  if (cfg == 0) {
-    if (swap) cfg = Q <= 16 ? 11 : Q <= 32 ? 12 : Q <= 64 ? 13 : 14;
-    else if (P > 128) {
-      // CTA pairs.  Estimated time = waves x cost of one tile, with the measured relative
-      // tile costs 256-wide 1.0, 192-wide 0.878, 128-wide 0.665 (narrower tiles move more bytes
-      // per flop through the ~64 B/clk an SM takes in from L2).  256x256 wins at every full
-      // Qwen3-8B / Llama-70B shape; narrower tiles win when a column shard leaves fewer 256-wide
-      // tiles than CTA pairs.
-      const int pairs = di.sms / 2, p_tiles = (P + 255) / 256;
-      const int widths[3] = {256, 192, 128}, cfgs[3] = {4, 5, 6};
-      const float cost[3] = {1.0f, 0.878f, 0.665f};
-      float best = 0.f;
-      for (int i = 0; i < 3; ++i) {
-        const int tiles = p_tiles * ((Q + widths[i] - 1) / widths[i]);
-        const float t = static_cast<float>((tiles + pairs - 1) / pairs) * cost[i];
-        if (i == 0 || t < best * 0.97f) { best = t; cfg = cfgs[i]; }   // prefer the wider tile on near-ties
-      }
-    } else {
-      cfg = K >= 8192 ? 2 : 3;      // long K amortises the single-accumulator 128x256 tile
-    }
-  }
+  int cfg = 0, splits = 1;
+  select_gemm_config(P, Q, K, swap, config, di.sms, cfg, splits);
   if (cfg >= 4 && cfg <= 6) {
     if (swap) return FRT_E_UNSUPPORTED;
     switch (cfg) {
@@ -829,17 +900,16 @@ int run_gemm(const void* p_packed, const void* sfp, int P, const void* q_packed,
   if ((cfg >= 11) != swap) return FRT_E_UNSUPPORTED;
   if (bn < 32 && Q > bn) return FRT_E_UNSUPPORTED;   // a 16-row tile must start a 32-row scale group
   CUtensorMap mp, mq;
-  if (int rc = make_operand_map(&mp, p_packed, P, K, BM)) return rc;
+  if (p_interleaved) {
+    if (!swap) return FRT_E_UNSUPPORTED;
+    if (int rc = make_interleaved_map(&mp, p_packed, P, K)) return rc;
+  } else if (int rc = make_operand_map(&mp, p_packed, P, K, BM)) {
+    return rc;
+  }
   if (int rc = make_operand_map(&mq, q_packed, Q, K, bn)) return rc;
-  p.splits = 1;
-  if (swap && Q <= bn && cfg >= 11 && cfg <= 13 && !(g_opt_gemm_debug & 16)) {
-    // few 128-row weight tiles: split K over a cluster so that every SM streams weights
-    const int tiles = (P + BM - 1) / BM, k_stages = (p.k_tiles + KT_PER_STAGE - 1) / KT_PER_STAGE;
-    int want = (bn <= 32 ? 2 * di.sms : di.sms) / tiles;     // two CTAs of the 16/32-token forms fit an SM
-    if (want > 8) want = 8;
-    for (int s = want; s >= 2; --s)
-      if (k_stages % s == 0 && k_stages / s >= 2) { p.splits = s; break; }
-    if (bn == 64 && p.splits < 4) p.splits = 1;   // 64 token columns: the cross-CTA sum only pays off from 4-way
+  p.p_interleaved = p_interleaved ? 1 : 0;
+  p.splits = splits;
+  {
     if (p.splits > 1) {
       switch (cfg) {
         case 11: return launch_gemm_splitk<16, 5>(mp, mq, p, st);
@@ -860,13 +930,27 @@ int run_gemm(const void* p_packed, const void* sfp, int P, const void* q_packed,
   return FRT_E_UNSUPPORTED;
 }
 
+// [N, K/2] row-major -> [N/8][K/64][8][32 B]: one thread moves 16 bytes.
+__global__ void repack_interleaved_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, int n, int kt) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;     // 16-byte piece of dst
+  if (i >= static_cast<int64_t>(n) * kt * 2) return;
+  const int half = static_cast<int>(i & 1);
+  const int r8 = static_cast<int>((i >> 1) & 7);
+  const int64_t rest = i >> 4;
+  const int t = static_cast<int>(rest % kt);
+  const int64_t grp = rest / kt;
+  dst[i] = src[((grp * 8 + r8) * kt + t) * 2 + half];
+}
+
 }  // namespace frt
 
 using namespace frt;
 
 extern "C" {
 
+#ifdef FRT_DEBUG
 void frt_debug_set_trace(void* ptr) { g_trace = static_cast<long long*>(ptr); }
+#endif
 
 int frt_nvfp4_gemm_bf16(const void* a, const void* sfa, const void* b, const void* sfb, const void* bias,
                         const void* c, void* d, int M, int N, int K, float alpha, float beta, void* stream) {
@@ -881,6 +965,39 @@ int frt_nvfp4_gemm_bf16(const void* a, const void* sfa, const void* b, const voi
   const bool swap = cfg ? cfg >= 11 : (M <= 64);
   if (swap) return run_gemm(b, sfb, N, a, sfa, M, K, bias, cc, d, N, alpha, beta, true, cfg, as_stream(stream));
   return run_gemm(a, sfa, M, b, sfb, N, K, bias, cc, d, N, alpha, beta, false, cfg, as_stream(stream));
+}
+
+int frt_nvfp4_repack_interleaved(const void* b_packed, void* b_interleaved, int N, int K, void* stream) {
+  if (!b_packed || !b_interleaved) return FRT_E_NULL;
+  if (N <= 0 || K <= 0 || N % 8 != 0 || K % 64 != 0) return FRT_E_SHAPE;
+  if (!aligned(b_packed, 16) || !aligned(b_interleaved, 16)) return FRT_E_ALIGN;
+  const int kt = K / 64;
+  const int64_t pieces = static_cast<int64_t>(N) * kt * 2;
+  repack_interleaved_kernel<<<static_cast<unsigned>((pieces + 255) / 256), 256, 0, as_stream(stream)>>>(
+      static_cast<const uint4*>(b_packed), static_cast<uint4*>(b_interleaved), N, kt);
+  return launch_result();
+}
+
+int frt_nvfp4_gemv_interleaved_bf16(const void* a, const void* sfa, const void* b_interleaved, const void* sfb,
+                                    void* out, int N, int K, float alpha, void* stream) {
+  if (!a || !sfa || !b_interleaved || !sfb || !out) return FRT_E_NULL;
+  if (N <= 0 || K <= 0 || N % 8 != 0 || K % 64 != 0) return FRT_E_SHAPE;
+  if (!aligned(a, 16) || !aligned(b_interleaved, 16) || !aligned(sfa, 16) || !aligned(sfb, 16)) return FRT_E_ALIGN;
+  const int cfg = g_opt_gemm_config >= 11 && g_opt_gemm_config <= 13 ? g_opt_gemm_config : 0;
+  return run_gemm(b_interleaved, sfb, N, a, sfa, 1, K, nullptr, nullptr, out, N, alpha, 0.f, true, cfg,
+                  as_stream(stream), true);
+}
+
+int frt_nvfp4_gemm_plan(int M, int N, int K, int* config, int* split_k) {
+  if (!config || !split_k) return FRT_E_NULL;
+  if (M <= 0 || N <= 0 || K <= 0 || K % 32 != 0 || N % 8 != 0) return FRT_E_SHAPE;
+  const DeviceInfo di = device_info();
+  const int sms = di.ok ? di.sms : 148;                 // no device (a build machine): the B200 count
+  const int requested = g_opt_gemm_config;
+  const bool swap = requested ? requested >= 11 : (M <= 64);
+  if (swap) select_gemm_config(N, M, K, true, requested, sms, *config, *split_k);
+  else select_gemm_config(M, N, K, false, requested, sms, *config, *split_k);
+  return FRT_OK;
 }
 
 int frt_nvfp4_gemm_swiglu_nvfp4(const void* a, const void* sfa, const void* b, const void* sfb, void* out_packed,
@@ -902,8 +1019,10 @@ int frt_nvfp4_gemm_swiglu_nvfp4(const void* a, const void* sfa, const void* b, c
   p.sfq_row_blocks = (N2 + 127) / 128;
   p.alpha = alpha;
   p.group_m = 16;
+#ifdef FRT_DEBUG
   p.dbg = g_opt_gemm_debug & 0xff;
   p.trace = g_trace;
+#endif
   p.hidden = N2 / 2;
   p.out_packed = static_cast<uint8_t*>(out_packed);
   p.out_sf = static_cast<uint8_t*>(out_sf);

@@ -161,7 +161,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
   }
   pdl_wait();                 // everything above overlapped the previous kernel; global memory from here on
   if (GROUPED) {
-    total_tiles = work->count * p.p_tiles;
+    total_tiles = min(work->count, p.max_items) * p.p_tiles;   // the plan never stores beyond max_items
     // tile i of this pair is global tile pair_id + i * num_pairs; its item is items[tile / p_tiles]
     for (int i = threadIdx.x; i < L::ITEM_CACHE; i += blockDim.x) {
       const int t = pair_id + i * num_pairs;
@@ -277,13 +277,13 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
         const int a = tl & 1;
         // tile tl may start once the epilogues of tile tl-1 have drained the columns the two
         // accumulators share (which also means tile tl-2, same accumulator, is fully drained)
-        const bool tr = p.trace != nullptr && pair_id == 0 && tl < 32;
-        if (tr) p.trace[tl * 8 + 0] = clock64();
+        const bool tr = FRT_TRACING(p) && pair_id == 0 && tl < 32;
+        if (tr) FRT_TRACE(p, tl * 8 + 0);
         if (tl > 0 && !ptx::mbar_wait_bounded(acc_free, (tl - 1) & 1, WAIT_LIMIT)) {
           atomicOr(&g_status_word, 4u); *abort_flag = 1; break;
         }
         ptx::tc_fence_after();
-        if (tr) p.trace[tl * 8 + 1] = clock64();
+        if (tr) FRT_TRACE(p, tl * 8 + 1);
         const uint32_t d_tmem = tmem_base + (a ? L::ACC1 : 0);
         uint32_t qoff, idesc = IDESC;
         if (GROUPED) {
@@ -315,7 +315,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
             if (kt < kts) {
               const uint32_t sfp_t = sf_tmem + kt * 4;
               const uint32_t sfq_t = sf_tmem + KT_PER_STAGE * 4 + kt * SFQ_COLS_PER_KT;
-              if (!(p.dbg & 2) || (tl == 0 && ks == 0)) {
+              if (!FRT_DBG(p, 2) || (tl == 0 && ks == 0)) {
                 ptx::tc_cp_32x128b_warpx4_pair(sfp_t, sfp_lo + kt * (SF_TILE >> 4), sf_hi);
 #pragma unroll
                 for (int b = 0; b < L::SFQ_BLOCKS; ++b)
@@ -331,7 +331,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
         }
         if (aborted) break;
         ptx::tc_commit_pair(&acc_full[a], 3);
-        if (tr) p.trace[tl * 8 + 2] = clock64();
+        if (tr) FRT_TRACE(p, tl * 8 + 2);
       }
     }
   } else {
@@ -377,8 +377,8 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
       ptx::tc_fence_after();
       const int drain_rank = a ? half : PARTS - 1 - half;   // this warp owns drain positions [rank * NCH, +NCH)
       const bool first_half = drain_rank == 0;              // ... the first of which are the shared columns
-      const bool tr = p.trace != nullptr && pair_id == 0 && tl < 32 && leader && quarter == 0 && lane == 0;
-      if (tr) p.trace[tl * 8 + (first_half ? 3 : 6)] = clock64();
+      const bool tr = FRT_TRACING(p) && pair_id == 0 && tl < 32 && leader && quarter == 0 && lane == 0;
+      if (tr) FRT_TRACE(p, tl * 8 + (first_half ? 3 : 6));
       const int prow = pt * 256 + row_in_tile + lane;       // dense: output row; grouped: output column
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + (a ? L::ACC1 : 0);
       auto chunk_of = [&](int j) {                          // j-th chunk of this warp -> column chunk
@@ -412,7 +412,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
         ptx::tc_wait_ld(rg);
         ptx::tc_wait_ld(ru);
         if (owner) release();
-        if (tr && first_half) p.trace[tl * 8 + 4] = clock64();
+        if (tr && first_half) FRT_TRACE(p, tl * 8 + 4);
         const float* inv_table = inv_scale_table();
         uint32_t pk[4];
         uint32_t sfw = 0;
@@ -431,14 +431,14 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
           pk[2 * b + 1] = o.y;
           sfw |= static_cast<uint32_t>(sfb) << (8 * b);
         }
-        if (prow < p.P && !(p.dbg & 1)) {
+        if (prow < p.P && !FRT_DBG(p, 1)) {
           const int col = qt * 128 + 32 * c;                 // first of the 32 output columns
           uint8_t* dst = p.out_packed + static_cast<int64_t>(prow) * (p.hidden >> 1) + (col >> 1);
           *reinterpret_cast<uint4*>(dst) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
           *reinterpret_cast<uint16_t*>(p.out_sf + sf_offset(prow, col >> 4, p.hidden >> 6)) =
               static_cast<uint16_t>(sfw);
         }
-        if (tr) p.trace[tl * 8 + (first_half ? 5 : 7)] = clock64();
+        if (tr) FRT_TRACE(p, tl * 8 + (first_half ? 5 : 7));
         continue;
       }
       uint32_t r[2][32];
@@ -453,7 +453,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
       ptx::tc_wait_ld(r[0]);
       ptx::tc_wait_ld(r[1]);
       if (first_half && RELEASE_CHUNKS > 0) release();
-      if (tr && first_half) p.trace[tl * 8 + 4] = clock64();
+      if (tr && first_half) FRT_TRACE(p, tl * 8 + 4);
 #pragma unroll
       for (int j = 0; j < NCH; ++j) {
         const int cchunk = chunk_of(j);
@@ -483,7 +483,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
             ptx::fence_proxy_async();
             __syncwarp();
             if (lane == 0) {
-              if (!(p.dbg & 1)) ptx::tma_store_2d(&maps.d, buf, n0, tok0);
+              if (!FRT_DBG(p, 1)) ptx::tma_store_2d(&maps.d, buf, n0, tok0);
               ptx::bulk_commit_group();
             }
             ++nstore;
@@ -491,7 +491,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
 #pragma unroll
             for (int jj = 0; jj < 32; ++jj) {
               const int tok = tok0 + jj;
-              if (tok >= item.lo && tok < item.hi && !(p.dbg & 1))
+              if (tok >= item.lo && tok < item.hi && !FRT_DBG(p, 1))
                 p.d[static_cast<int64_t>(tok) * p.ldd + prow] = __float2bfloat16_rn(__uint_as_float(v32[jj]) * alpha);
             }
           }
@@ -533,7 +533,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
           ptx::fence_proxy_async();
           __syncwarp();
           if (lane == 0) {
-            if (!(p.dbg & 1)) ptx::tma_store_2d(&maps.d, buf, q_base, pt * 256 + row_in_tile);
+            if (!FRT_DBG(p, 1)) ptx::tma_store_2d(&maps.d, buf, q_base, pt * 256 + row_in_tile);
             ptx::bulk_commit_group();
           }
           ++nstore;
@@ -541,7 +541,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
         }   // live
         if (j + 2 < NCH && chunk_live(chunk_of(j + 2))) ptx::tc_ld_32x32b_x32(taddr + chunk_of(j + 2) * 32, r[j & 1]);
       }
-      if (tr) p.trace[tl * 8 + (first_half ? 5 : 7)] = clock64();
+      if (tr) FRT_TRACE(p, tl * 8 + (first_half ? 5 : 7));
     }
     if (lane == 0) ptx::bulk_wait_group_all();   // staging must outlive the stores that read it
   }

@@ -16,9 +16,9 @@ namespace {
 // Work-list storage for the entry point that allocates nothing.  It is part of
 // the library image: every GPU that loads the library carries these bytes until
 // the process exits.  Sized for FRT_GROUPED_STATIC_MAX_ROWS rows and
-// FRT_GROUPED_STATIC_MAX_EXPERTS experts (16 + 32 * (rows/64 + 2*experts + 8)).
+// FRT_GROUPED_STATIC_MAX_EXPERTS experts (16 + 32 * (rows/16 + 2*experts + 8) = 393,488 bytes).
 constexpr int64_t kStaticScratchBytes =
-    16 + 32 * (FRT_GROUPED_STATIC_MAX_ROWS / 64 + 2ll * FRT_GROUPED_STATIC_MAX_EXPERTS + 8);
+    16 + 32 * (FRT_GROUPED_STATIC_MAX_ROWS / 16 + 2ll * FRT_GROUPED_STATIC_MAX_EXPERTS + 8);
 static __device__ __align__(256) unsigned char g_grouped_static_scratch[kStaticScratchBytes];
 
 // In host code the array's name is only a handle for the runtime, not a device

@@ -10,8 +10,13 @@ namespace frt {
 std::atomic<int64_t> g_launches{0};
 int g_opt_quant_encoder = 0;
 int g_opt_gemm_config = 0;
-int g_opt_gemm_debug = 0;
 int g_opt_pdl = 1;
+int g_opt_norm_form = 0;
+int g_opt_tail_split = 1;
+int g_opt_split_k = 1;
+#ifdef FRT_DEBUG
+int g_opt_gemm_debug = 0;
+#endif
 
 namespace {
 
@@ -51,7 +56,9 @@ template <int ENC, bool FP16>
 __global__ void __launch_bounds__(256)
 quantize_kernel(const uint4* __restrict__ src, uint2* __restrict__ packed, uint8_t* __restrict__ sf,
                 int rows, int nb, int sf_cols) {
-  pdl_launch_dependents();
+  // No early griddepcontrol.launch_dependents here: this kernel also packs WEIGHTS, and the small-M GEMM
+  // loads its weight operand before it waits on the previous grid.  Without the trigger a dependent grid
+  // starts only when this one has completed, so a GEMM enqueued right after a weight pack sees whole weights.
   pdl_wait();
   const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= static_cast<int64_t>(rows) * nb) return;
@@ -695,9 +702,9 @@ int launch_norm(const NormParams& p, bool has_res, bool quant, cudaStream_t st) 
   // Measured on B200: one CTA per row group wins while a row fits 256 threads (64 resident
   // warps per SM hide the latency by themselves); for wider rows the CTA-wide barrier of a
   // 512/1024-thread CTA stalls the SM and the staged persistent form is 15-35 % faster.
-  // Debug bits 32 / 64 force one form or the other.
+  // FRT_OPT_NORM_FORM forces one form or the other (tests run every case on both).
   const bool stream = p.out_fp8 == nullptr &&
-                      ((g_opt_gemm_debug & 64) || (!(g_opt_gemm_debug & 32) && TPR > (quant ? 256 : 512)));
+                      (g_opt_norm_form == 2 || (g_opt_norm_form != 1 && TPR > (quant ? 256 : 512)));
   if (!stream) {
     constexpr int CTA = TPR > 256 ? TPR : 256;
     constexpr int rows_per_cta = CTA / TPR;
@@ -788,8 +795,13 @@ int frt_set_option(int key, int value) {
   int prev = -1;
   if (key == FRT_OPT_QUANT_ENCODER) { prev = g_opt_quant_encoder; g_opt_quant_encoder = value; }
   if (key == FRT_OPT_GEMM_CONFIG) { prev = g_opt_gemm_config; g_opt_gemm_config = value; }
-  if (key == 3) { prev = g_opt_gemm_debug; g_opt_gemm_debug = value; }
   if (key == FRT_OPT_PDL) { prev = g_opt_pdl; g_opt_pdl = value; }
+  if (key == FRT_OPT_NORM_FORM) { prev = g_opt_norm_form; g_opt_norm_form = value; }
+  if (key == FRT_OPT_GEMM_TAIL_SPLIT) { prev = g_opt_tail_split; g_opt_tail_split = value; }
+  if (key == FRT_OPT_GEMM_SPLIT_K) { prev = g_opt_split_k; g_opt_split_k = value; }
+#ifdef FRT_DEBUG
+  if (key == 3) { prev = g_opt_gemm_debug; g_opt_gemm_debug = value; }
+#endif
   return prev;
 }
 

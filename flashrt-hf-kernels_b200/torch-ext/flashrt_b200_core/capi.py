@@ -26,6 +26,9 @@ SIGNATURES = {
     "frt_residual_add_rms_norm_bf16": (_I, [_P, _P, _P, _P, _I, _I, _F, _P]),
     "frt_norm_quant_nvfp4": (_I, [_P, _P, _P, _F, _F, _P, _P, _P, _I, _I, _U, _P]),
     "frt_nvfp4_gemm_bf16": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _F, _F, _P]),
+    "frt_nvfp4_repack_interleaved": (_I, [_P, _P, _I, _I, _P]),
+    "frt_nvfp4_gemv_interleaved_bf16": (_I, [_P, _P, _P, _P, _P, _I, _I, _F, _P]),
+    "frt_nvfp4_gemm_plan": (_I, [_I, _I, _I, C.POINTER(_I), C.POINTER(_I)]),
     "frt_router_topk_bf16": (_I, [_P, _P, _P, _I, _I, _I, _P]),
     "frt_router_topk_softmax_bf16": (_I, [_P, _P, _P, _P, _I, _I, _I, _P]),
     "frt_moe_quantize_scatter_nvfp4": (_I, [_P, _P, _P, _P, _I, _I, _I, _P]),

@@ -207,6 +207,42 @@ def fp4_w4a4_gemv_warpsplit_bf16(a_packed, b_packed, sfa, sfb, *, alpha: float =
     return out
 
 
+@torch.library.register_fake(add_op_namespace_prefix("fp4_repack_b_interleaved_sm120"))
+def _repack_b_interleaved_fake(b_packed, b_interleaved) -> None:
+    if b_interleaved.shape != b_packed.shape:
+        raise RuntimeError("b_interleaved must have the same shape as b_packed")
+    return None
+
+
+@torch.library.register_fake(add_op_namespace_prefix("fp4_w4a4_gemv_warpsplit_interleaved_bf16"))
+def _gemv_warpsplit_interleaved_fake(a_packed, b_interleaved, sfa, sfb, out, alpha=1.0, warps=4, stages=4) -> None:
+    if a_packed.shape[0] != 1:
+        raise RuntimeError("interleaved warp-split GEMV serves M=1 only")
+    if out.shape != (1, b_interleaved.shape[0]):
+        raise RuntimeError("out must have shape (1, N)")
+    return None
+
+
+def fp4_repack_b_interleaved_sm120(b_packed: torch.Tensor, *, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Bind-time repack of a dense row-major packed weight into the M = 1 GEMV layout
+    ([N/8][K/64][8][32 B]; fp4-gemm/torch-ext/fp4_gemm/__init__.py:760-773).  The name is the reference's;
+    on B200 the layout is read through a 4-D tensor map by the same weight-streaming kernel."""
+    if out is None:
+        out = torch.empty_like(b_packed)
+    ops.fp4_repack_b_interleaved_sm120(b_packed, out)
+    return out
+
+
+def fp4_w4a4_gemv_warpsplit_interleaved_bf16(a_packed, b_interleaved, sfa, sfb, *, alpha: float = 1.0, warps: int = 8,
+                                             stages: int = 3, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """M = 1 GEMV over a weight repacked by fp4_repack_b_interleaved_sm120 (bit-equal to the plain-layout GEMV)."""
+    if out is None:
+        out = torch.empty((1, b_interleaved.shape[0]), device=a_packed.device, dtype=torch.bfloat16)
+    ops.fp4_w4a4_gemv_warpsplit_interleaved_bf16(a_packed, b_interleaved, sfa, sfb, out, float(alpha), int(warps),
+                                                 int(stages))
+    return out
+
+
 def fp4_w4a4_gemm_warpsplit_mrows_bf16(a_packed, b_packed, sfa, sfb, *, alpha: float = 1.0, warps: int = 2,
                                        stages: int = 6, out: Optional[torch.Tensor] = None):
     """1..16 rows riding one weight stream."""
@@ -325,5 +361,6 @@ __all__ = ["capabilities", "sfa_size_bytes", "quantize_fp4_sfa_fp16", "quantize_
            "dequantize_fp4_sfa_fp16", "nvfp4_gemm_bf16", "nvfp4_gemm_swiglu_nvfp4_bf16", "fp4_w4a16_linear_bf16",
            "nvfp4_gemm_bias_bf16",
            "nvfp4_gemm_bias_residual_bf16", "nvfp4_gemm_residual_bf16", "fp4_w4a4_gemv_warpsplit_bf16",
-           "fp4_w4a4_gemm_warpsplit_mrows_bf16", "pack_nvfp4_weight_bf16", "quantize_fp4_sfa_mse_fp16",
+           "fp4_w4a4_gemm_warpsplit_mrows_bf16", "fp4_repack_b_interleaved_sm120",
+           "fp4_w4a4_gemv_warpsplit_interleaved_bf16", "pack_nvfp4_weight_bf16", "quantize_fp4_sfa_mse_fp16",
            "quantize_fp4_sfa_mse_bf16", "quantize_fp4_sfa_bf16_pdl", "aligned_fp4_dim", "quantize_fp4_sfa_padded_bf16", "adopt_modelopt_nvfp4_weight"]

@@ -13,6 +13,8 @@
 //   transformer_fused_ops  transformer-fused-ops/torch-ext/torch_binding.cpp:735-737 (router, weighted sum only)
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
+#include <map>
+#include <mutex>
 #include <torch/all.h>
 #include <torch/library.h>
 
@@ -227,6 +229,35 @@ void fp4_w4a4_gemm_warpsplit_mrows_bf16(const Tensor& a, const Tensor& b, const 
   gemm_call(a, b, sfa, sfb, nullptr, nullptr, out, alpha, "fp4_w4a4_gemm_warpsplit_mrows_bf16");
 }
 
+// Bind-time interleaved weight layout of the M = 1 GEMV and the GEMV that reads it
+// (fp4-gemm/torch-ext/torch_binding.cpp:317-387): same checks and messages; `warps` / `stages` accepted and ignored.
+void fp4_repack_b_interleaved_sm120(const Tensor& b_packed, Tensor& b_interleaved) {
+  check_dtype(b_packed, torch::kUInt8, "b_packed", "torch.uint8");
+  check_dtype(b_interleaved, torch::kUInt8, "b_interleaved", "torch.uint8");
+  TORCH_CHECK(b_packed.dim() == 2, "b_packed must have shape (N, K / 2)");
+  TORCH_CHECK(b_interleaved.sizes() == b_packed.sizes(), "b_interleaved must have the same shape as b_packed");
+  const int64_t n = b_packed.size(0), k = b_packed.size(1) * 2;
+  TORCH_CHECK(n > 0 && n % 8 == 0, "N must be positive and divisible by 8");
+  TORCH_CHECK(k > 0 && k % 64 == 0, "K must be positive and divisible by 64");
+  check_same_device(b_packed, b_interleaved, "b_packed", "b_interleaved");
+  c10::cuda::CUDAGuard guard(b_packed.device());
+  check_rc(frt_nvfp4_repack_interleaved(b_packed.data_ptr(), b_interleaved.data_ptr(), as_int(n, "N"), as_int(k, "K"),
+                                        stream_of(b_packed)), "fp4_repack_b_interleaved_sm120");
+}
+void fp4_w4a4_gemv_warpsplit_interleaved_bf16(const Tensor& a, const Tensor& b_interleaved, const Tensor& sfa,
+                                              const Tensor& sfb, Tensor& out, double alpha, int64_t warps,
+                                              int64_t stages) {
+  const GemmShape s = check_gemm_inputs(a, b_interleaved, sfa, sfb, out);
+  TORCH_CHECK(s.m == 1, "interleaved warp-split GEMV serves M=1 only");
+  TORCH_CHECK(warps == 2 || warps == 4 || warps == 8, "warps must be 2, 4 or 8");
+  TORCH_CHECK(stages == 3 || stages == 4 || stages == 6, "stages must be 3, 4 or 6");
+  TORCH_CHECK(s.k % 64 == 0, "K/64 must be divisible by warps");
+  c10::cuda::CUDAGuard guard(a.device());
+  check_rc(frt_nvfp4_gemv_interleaved_bf16(a.data_ptr(), sfa.data_ptr(), b_interleaved.data_ptr(), sfb.data_ptr(),
+                                           out.data_ptr(), s.n, s.k, static_cast<float>(alpha), stream_of(a)),
+           "fp4_w4a4_gemv_warpsplit_interleaved_bf16");
+}
+
 // M = 1 decode matvec of the reference's small-M package (flashrt-smallm-gemm/torch-ext/torch_binding.cpp:55-108):
 // a_packed (K/2,) or (1, K/2), out (N,).  Any K % 32 == 0 is accepted (the reference kernel takes 4096 and 12288).
 void nvfp4_w4a4_decode_matvec_bf16out(const Tensor& a, const Tensor& b, const Tensor& sfa, const Tensor& sfb, Tensor& out,
@@ -424,9 +455,18 @@ void grouped_common(const Tensor& input, const Tensor& weight, const Tensor& inp
   TORCH_CHECK(N % 8 == 0, "N must be divisible by 8");
   TORCH_CHECK(input.get_device() == output.get_device(), "all tensors must share one device");
 }
-Tensor grouped_workspace(const Tensor& like, int rows, int experts) {
-  return torch::empty({frt_nvfp4_grouped_gemm_workspace_bytes(rows, experts)},
-                      torch::TensorOptions().dtype(torch::kUInt8).device(like.device()));
+// Work-list scratch of the reference-schema op, which has no workspace argument: one buffer per (device,
+// stream), allocated on the first call that needs it (or a larger one) and reused by every later call, so the
+// hot call allocates nothing.  Calls on one stream are ordered, so they may share it; another stream gets its own.
+Tensor grouped_workspace(const Tensor& like, int rows, int experts, void* stream) {
+  static std::mutex mu;
+  static std::map<std::pair<int, void*>, Tensor> cache;
+  const int64_t need = frt_nvfp4_grouped_gemm_workspace_bytes(rows, experts);
+  std::lock_guard<std::mutex> lock(mu);
+  Tensor& slot = cache[{static_cast<int>(like.get_device()), stream}];
+  if (!slot.defined() || slot.numel() < need)
+    slot = torch::empty({need}, torch::TensorOptions().dtype(torch::kUInt8).device(like.device()));
+  return slot;
 }
 void grouped_nvfp4_gemm_bf16_out(const Tensor& input, const Tensor& weight, const Tensor& input_scale,
                                  const Tensor& weight_scale, const Tensor& alpha, const Tensor& tile_expert,
@@ -440,7 +480,7 @@ void grouped_nvfp4_gemm_bf16_out(const Tensor& input, const Tensor& weight, cons
   TORCH_CHECK(input_scale_stride >= 0 && weight_stride > 0 && weight_scale_stride > 0, "invalid byte strides");
   const int rows = as_int(input.size(0), "rows"), experts = as_int(weight.size(0), "experts");
   c10::cuda::CUDAGuard guard(input.device());
-  Tensor work = workspace.has_value() ? workspace.value() : grouped_workspace(input, rows, experts);
+  Tensor work = workspace.has_value() ? workspace.value() : grouped_workspace(input, rows, experts, stream_of(input));
   TORCH_CHECK(work.is_cuda() && work.nbytes() >= static_cast<size_t>(frt_nvfp4_grouped_gemm_workspace_bytes(rows, experts)),
               "workspace is too small");
   check_rc(frt_nvfp4_grouped_gemm_bf16(input.data_ptr(), input_scale.data_ptr(), weight.data_ptr(),
@@ -638,6 +678,8 @@ TORCH_LIBRARY_EXPAND(fp4_gemm_b200, ops) {
   ops.def("nvfp4_gemm_bias_residual_bf16(Tensor a_packed, Tensor b_packed, Tensor sfa, Tensor sfb, Tensor bias, Tensor residual, Tensor! out) -> ()");
   ops.def("nvfp4_gemm_residual_bf16(Tensor a_packed, Tensor b_packed, Tensor sfa, Tensor sfb, Tensor residual, Tensor! out, float alpha=1.0) -> ()");
   ops.def("fp4_w4a4_gemv_warpsplit_bf16(Tensor a_packed, Tensor b_packed, Tensor sfa, Tensor sfb, Tensor! out, float alpha=1.0, int warps=4, int stages=4) -> ()");
+  ops.def("fp4_repack_b_interleaved_sm120(Tensor b_packed, Tensor! b_interleaved) -> ()");
+  ops.def("fp4_w4a4_gemv_warpsplit_interleaved_bf16(Tensor a_packed, Tensor b_interleaved, Tensor sfa, Tensor sfb, Tensor! out, float alpha=1.0, int warps=4, int stages=4) -> ()");
   ops.def("fp4_w4a4_gemm_warpsplit_mrows_bf16(Tensor a_packed, Tensor b_packed, Tensor sfa, Tensor sfb, Tensor! out, float alpha=1.0, int warps=2, int stages=6) -> ()");
   ops.def("quantize_fp4_sfa_fp16(Tensor x, Tensor! packed, Tensor! sfa, bool is_sfb=False) -> ()");
   ops.def("quantize_fp4_sfa_bf16(Tensor x, Tensor! packed, Tensor! sfa, bool is_sfb=False) -> ()");
@@ -659,6 +701,8 @@ TORCH_LIBRARY_EXPAND(fp4_gemm_b200, ops) {
   ops.impl("nvfp4_gemm_bias_residual_bf16", torch::kCUDA, &nvfp4_gemm_bias_residual_bf16);
   ops.impl("nvfp4_gemm_residual_bf16", torch::kCUDA, &nvfp4_gemm_residual_bf16);
   ops.impl("fp4_w4a4_gemv_warpsplit_bf16", torch::kCUDA, &fp4_w4a4_gemv_warpsplit_bf16);
+  ops.impl("fp4_repack_b_interleaved_sm120", torch::kCUDA, &fp4_repack_b_interleaved_sm120);
+  ops.impl("fp4_w4a4_gemv_warpsplit_interleaved_bf16", torch::kCUDA, &fp4_w4a4_gemv_warpsplit_interleaved_bf16);
   ops.impl("fp4_w4a4_gemm_warpsplit_mrows_bf16", torch::kCUDA, &fp4_w4a4_gemm_warpsplit_mrows_bf16);
   ops.impl("quantize_fp4_sfa_fp16", torch::kCUDA, &quantize_fp4_sfa_fp16);
   ops.impl("quantize_fp4_sfa_bf16", torch::kCUDA, &quantize_fp4_sfa_bf16);

@@ -47,7 +47,8 @@ int64_t frt_nvfp4_sf_swizzled_bytes(int rows, int dim);
  * replaces sfa_offset_128x64, fp4-gemm/csrc/sfa_layout.cuh:12 */
 int64_t frt_nvfp4_sf_offset(int row, int k, int dim);
 
-/* linear [rows, dim/16] u8 -> swizzled; padding bytes of dst are not written.
+/* linear [rows, dim/16] u8 -> swizzled.  The bytes that pad a row's last 64-element group
+ * (dim % 64 != 0) are written as zero; rows of dst beyond `rows` are not written.
  * replaces nvfp4_sf_linear_to_swizzled, flashrt-nvfp4/csrc/nvfp4_sf_reshape_sm120.cuh:33 */
 int frt_nvfp4_sf_linear_to_swizzled(const void* src_linear, void* dst_swizzled,
                                     int rows, int dim, void* stream);
@@ -57,7 +58,9 @@ int frt_nvfp4_sf_linear_to_swizzled(const void* src_linear, void* dst_swizzled,
  * packed [rows, dim/2] u8 (8-byte aligned) + swizzled UE4M3 scales.
  * Rule: d = max(amax/6, 1e-12); sf = e4m3_rn(d); q = v * (1/float(sf));
  * e2m1 code by thresholds {.25,.75,1.25,1.75,2.5,3.5,5} with ties to the
- * smaller magnitude; sign bit = q < 0.  Padding scale bytes are not written.
+ * smaller magnitude; sign bit = q < 0.  The scale bytes that pad a row's last 64-element
+ * group (dim % 64 != 0) are written as zero (the tensor cores read whole groups); scale
+ * bytes of rows beyond `rows` are not written.
  * replaces quantize_fp4_dynamic_sfa_bf16_vec, fp4-gemm/csrc/quantize/quantize_fp4_sfa_bf16.cuh:20
  * and quantize_fp4_dynamic_sfa_fp16/_bf16, fp4-gemm/csrc/quantize/quantize_fp4_sfa.cuh:8,24 */
 int frt_nvfp4_quantize(const void* src, int src_dtype, void* packed, void* sf_swizzled,
@@ -135,9 +138,18 @@ int frt_norm_quant_nvfp4(void* residual, const void* x, const void* weight, floa
  *               (+ bias[n]) (+ beta * C[m,n])),  fp32 accumulation in TMEM.
  * A [M,K/2] u8 row-major, B [N,K/2] u8 row-major, scales swizzled, bias bf16
  * [N] or null, C bf16 [M,N] or null (may alias D), beta in {0,1}.
- * K % 64 == 0, N % 8 == 0, A/B 16-byte aligned, D/C 16-byte aligned.
+ * K % 32 == 0, N % 8 == 0, A/B 16-byte aligned, D/C 16-byte aligned.
  * Scale buffers must hold frt_nvfp4_sf_swizzled_bytes() bytes; rows of the
- * last 128-row group beyond M / N may hold anything.
+ * last 128-row group beyond M / N may hold anything; when K % 64 != 0 the
+ * scale bytes that pad the last 64-element group must not be NaN patterns
+ * (this library's quantisers write zeros there).
+ * B / SFB are treated as constants of the stream: for M <= 64 the kernel starts
+ * loading them before it waits for the previous kernel of the stream (launches
+ * are programmatic dependents, see FRT_OPT_PDL).  Weights packed on the same
+ * stream by frt_nvfp4_quantize / _quantize_mse / _sf_linear_to_swizzled or by an
+ * ordinary kernel are complete by then (those never release their dependents
+ * early); weights written by a caller's kernel that triggers programmatic
+ * dependents before its last store need an event or a stream sync first.
  * replaces fp4_w4a16_gemm_sm100_bf16out (+ _widen, _pingpong),
  *   fp4-gemm/csrc/gemm/fp4/cutlass_nvfp4_w4a16_gemm_sm100.cuh, and
  *   cutlass_fp4_gemm_bias_bf16 / _bias_res_bf16,
@@ -148,6 +160,25 @@ int frt_norm_quant_nvfp4(void* residual, const void* x, const void* weight, floa
 int frt_nvfp4_gemm_bf16(const void* a_packed, const void* sfa, const void* b_packed, const void* sfb,
                         const void* bias, const void* c, void* d,
                         int M, int N, int K, float alpha, float beta, void* stream);
+
+/* The reference's bind-time weight layout of its M = 1 GEMV and the GEMV that consumes it.
+ * Layout: b_interleaved viewed as [N/8][K/64][8][32 bytes] holds b_packed [N/8][8][K/64][32 bytes]
+ * (groups of 8 rows x 64-element k-tiles x 8 rows x 32 B), N % 8 == 0, K % 64 == 0.
+ * The GEMV reads that layout through a 4-D tensor map into the same shared-memory tile as the plain
+ * layout and runs the same weight-streaming kernel: out[1, N] bit-equal to frt_nvfp4_gemm_bf16 at M = 1.
+ * replaces fp4_w4a4_repack_b_ilv_sm120 and fp4_w4a4_mma_sm120_warpsplit_ilv_bf16out,
+ *   fp4-gemm/csrc/gemm/fp4/fp4_w4a4_mma_warpsplit_ilv_sm120.cuh:15,21 */
+int frt_nvfp4_repack_interleaved(const void* b_packed, void* b_interleaved, int N, int K, void* stream);
+int frt_nvfp4_gemv_interleaved_bf16(const void* a_packed, const void* sfa, const void* b_interleaved,
+                                    const void* sfb, void* out, int N, int K, float alpha, void* stream);
+
+/* Which kernel configuration frt_nvfp4_gemm_bf16 would run for (M, N, K) on the current
+ * device, without launching anything (a host-side query; tests use it to prove which path a
+ * shape takes).  *config: 1-3 one CTA per 128-row tile (128 / 256 / 192 columns), 4-6 CTA pair
+ * per 256-row tile (256 / 192 / 128 columns), 11-14 weight-streaming form for M <= 64 (16 /
+ * 32 / 64 / 128 token columns); *split_k: CTAs of a cluster that share one tile's K (1 = none).
+ * replaces select_sm110_variant, fp4-gemm/torch-ext/torch_binding.cpp:169 */
+int frt_nvfp4_gemm_plan(int M, int N, int K, int* config, int* split_k);
 
 /* ---- SwiGLU -> NVFP4 (the step between the two FFN GEMMs) -----------------
  * merged [rows, 2*hidden] bf16 = [gate | up] (16-byte aligned, hidden % 16 == 0) ->
@@ -183,7 +214,11 @@ int frt_nvfp4_gemm_swiglu_nvfp4(const void* a_packed, const void* sfa, const voi
  *                    {16,64} rows) uses expert tile_expert[t]; negative = skip
  *                    (those output rows are left untouched).
  * K % 64 == 0, N % 8 == 0.  `work` is caller-owned scratch of
- * frt_nvfp4_grouped_gemm_workspace_bytes() bytes (device, 16-byte aligned).
+ * frt_nvfp4_grouped_gemm_workspace_bytes() bytes (device, 16-byte aligned): room for
+ * rows/16 + 2*num_experts + 8 row windows, which covers every sorted expert_offsets and every
+ * tile_expert pattern (16-row tiles of alternating experts included).  Offsets that overlap or
+ * decrease describe more rows than exist; windows that do not fit are dropped, never written past
+ * the buffer, and bit 0x200 of the status word (frt_device_status) reports it.
  * replaces moe_blocktile_mma_sm120_bf16 / moe_m64_mma_sm120_bf16 / moe_m16_mma_sm120_bf16,
  *   grouped-moe-gemm/csrc/moe_blocktile_mma_sm120.cuh */
 int64_t frt_nvfp4_grouped_gemm_workspace_bytes(int rows, int num_experts);
@@ -203,7 +238,7 @@ int frt_nvfp4_grouped_gemm_bf16(const void* a_packed, const void* sfa,
  * inputs and outputs are still the caller's.  No counterpart in the reference.
  *  - Limits: rows <= FRT_GROUPED_STATIC_MAX_ROWS and
  *    num_experts <= FRT_GROUPED_STATIC_MAX_EXPERTS, else FRT_E_TOO_LARGE.  The
- *    array (about 192 KiB) is resident on every GPU that loads the library.
+ *    array (about 384 KiB) is resident on every GPU that loads the library.
  *  - The first call on a device looks up the array's device address (no
  *    allocation); make that first call before starting a stream capture.
  *  - Every call uses the same array: two calls whose kernels can overlap on the
@@ -278,6 +313,12 @@ int64_t frt_launch_count(void);
 #define FRT_OPT_PDL             4   /* 1 = launch kernels with programmatic stream serialization
                                        (default): a kernel's prologue overlaps the tail of the
                                        previous kernel of the stream; 0 = plain launches      */
+#define FRT_OPT_NORM_FORM       5   /* norm kernels: 0 = by row width (default), 1 = one CTA per
+                                       row group, 2 = persistent CTAs fed by bulk copies       */
+#define FRT_OPT_GEMM_TAIL_SPLIT 6   /* dense CTA-pair GEMM: 1 = cut the last, partial wave of
+                                       tiles into column slices (default), 0 = whole tiles     */
+#define FRT_OPT_GEMM_SPLIT_K    7   /* small-M GEMM: 1 = split K over a cluster when there are
+                                       fewer weight tiles than SMs (default), 0 = never        */
 int frt_set_option(int key, int value);
 
 #ifdef __cplusplus

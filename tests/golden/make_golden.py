@@ -51,7 +51,7 @@ def bf16_bits(t: torch.Tensor) -> np.ndarray:
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the reference project")
     args = ap.parse_args()
     ref = Path(args.reference)
 

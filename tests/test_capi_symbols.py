@@ -28,6 +28,42 @@ def test_library_exports_every_declared_symbol():
         assert getattr(lib, name) is not None
 
 
+def test_library_exports_nothing_beyond_the_header():
+    """every extern "C" frt_* symbol of the shipped library is declared in the header: no undeclared
+    debug or experiment entry points"""
+    import shutil
+    import subprocess
+    from flashrt_b200_core import capi
+    nm = shutil.which("nm")
+    if nm is None:
+        pytest.skip("no nm")
+    out = subprocess.run([nm, "-D", "--defined-only", str(capi.LIB_PATH)], check=True, capture_output=True,
+                         text=True).stdout
+    exported = sorted({line.split()[-1] for line in out.splitlines() if line.split()[-1].startswith("frt_")})
+    assert exported == declared_symbols()
+
+
+def test_gemm_plan_query():
+    """the host-side configuration query: prefill shapes take the CTA-pair kernel, token counts <= 64 the
+    weight-streaming form, and the Qwen3-8B o / down projections at 33..64 tokens the cluster split-K"""
+    import ctypes as C
+    from flashrt_b200_core import capi
+    lib = capi.lib()
+
+    def plan(m, n, k):
+        cfg, split = C.c_int(0), C.c_int(0)
+        assert lib.frt_nvfp4_gemm_plan(m, n, k, C.byref(cfg), C.byref(split)) == 0
+        return cfg.value, split.value
+
+    assert plan(4096, 6144, 4096) == (4, 1)
+    assert plan(8192, 57344, 8192) == (4, 1)
+    assert plan(1, 4096, 4096)[0] == 11 and plan(16, 4096, 4096)[0] == 11
+    assert plan(17, 4096, 4096)[0] == 12 and plan(64, 24576, 4096) == (13, 1)
+    assert plan(64, 4096, 4096) == (13, 4) and plan(64, 4096, 12288) == (13, 4)
+    assert plan(64, 6144, 4096) == (13, 1)
+    assert lib.frt_nvfp4_gemm_plan(4, 100, 64, None, None) == -1
+
+
 def test_host_only_entry_points():
     from flashrt_b200_core import capi
     lib = capi.lib()

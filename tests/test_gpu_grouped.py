@@ -85,6 +85,56 @@ def test_skipped_tiles_and_runs_leave_output_untouched():
     assert torch.all(out.cpu()[~live] == 7.0)
 
 
+@pytest.mark.parametrize("with_skips", [False, True])
+def test_many_short_runs_fit_the_work_list(with_skips):
+    """16-row tiles of alternating experts make every tile its own window: 64 tiles give 64 work items
+    (grouped-moe-gemm/tests/test_grouped_moe_gemm.py:53-66 uses this `arange(tiles) % experts` pattern).
+    The documented workspace holds them, nothing is dropped (status word 0), skipped tiles stay untouched."""
+    tr, n, k, experts, tiles = 16, 264, 256, 3, 64
+    te = torch.arange(tiles, dtype=torch.int32) % experts
+    if with_skips:
+        te[1::5] = -1
+    rows = tr * tiles
+    ap, wp, al, wl, alpha, asw, wsw = make_inputs(rows, n, k, experts, 77)
+    out = torch.full((rows, n), 7.0, dtype=torch.bfloat16, device=DEV)
+    run_capi(ap.to(DEV), wp.to(DEV), asw.to(DEV), wsw.to(DEV), alpha.to(DEV), out, tile_expert=te.to(DEV), tile_rows=tr)
+    row_e = np.repeat(te.numpy(), tr)
+    want = O.grouped_gemm_bf16(ap.numpy(), al.numpy(), wp.numpy(), wl.numpy(), alpha.numpy(), row_e)
+    live = torch.from_numpy(row_e >= 0)
+    check(out, want, live)
+    assert torch.all(out.cpu()[~live] == 7.0)
+
+
+def test_overlapping_offsets_are_cut_short_not_overrun():
+    """Offsets that go back and forth describe more rows than exist: here 64 of 128 experts each claim all
+    4096 rows, 1024 row windows for a work list that holds 4096/16 + 2*128 + 8 = 520.  The windows that do not
+    fit are dropped (bit 0x200 of the status word), bytes beyond the workspace stay untouched, and the next,
+    well-formed call is clean."""
+    n, k, experts, rows = 128, 128, 128, 4096
+    ap, wp, al, wl, alpha, asw, wsw = make_inputs(rows, n, k, experts, 9)
+    offs = torch.zeros(experts + 1, dtype=torch.int32)
+    offs[1::2] = rows
+    L, P = capi.lib(), capi.ptr
+    need = int(L.frt_nvfp4_grouped_gemm_workspace_bytes(rows, experts))
+    assert need == 16 + 32 * 520
+    work = torch.full((need + 4096,), 0xAB, dtype=torch.uint8, device=DEV)
+    out = torch.zeros(rows, n, dtype=torch.bfloat16, device=DEV)
+    dev = [t.to(DEV) for t in (ap, asw, wp, wsw, alpha, offs)]
+    capi.check(L.frt_nvfp4_grouped_gemm_bf16(P(dev[0]), P(dev[1]), P(dev[2]), P(dev[3]), P(dev[4]), P(dev[5]), None, 0,
+                                             P(out), rows, n, k, experts, n * (k // 2), wsw.shape[1], P(work),
+                                             capi.stream_ptr()))
+    torch.cuda.synchronize()
+    assert device_status() & 0x200
+    assert torch.all(work[need:] == 0xAB)
+    assert torch.isfinite(out.float()).all()
+    # a sorted description on the same buffers afterwards
+    good = torch.arange(experts + 1, dtype=torch.int32) * (rows // experts)
+    out.zero_()
+    run_capi(dev[0], dev[2], dev[1], dev[3], dev[4], out, offsets=good.to(DEV))
+    row_e = np.repeat(np.arange(experts), rows // experts)
+    check(out, O.grouped_gemm_bf16(ap.numpy(), al.numpy(), wp.numpy(), wl.numpy(), alpha.numpy(), row_e))
+
+
 def test_golden_fixture_from_reference_helpers(golden_dir):
     g = np.load(golden_dir / "grouped_moe.npz")
     t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(DEV)

@@ -143,16 +143,16 @@ def test_dequantize_exact():
 CASES = [(1, 1024), (16, 128), (63, 2048), (128, 4096), (257, 4096), (33, 5120), (9, 8192), (5, 12288), (3, 16384)]
 
 # The norm kernels exist in two forms (one CTA per row group; persistent CTAs fed by bulk
-# copies); the library picks one by row width.  Debug bits 32 / 64 force each form, so
+# copies); the library picks one by row width.  FRT_OPT_NORM_FORM (key 5) forces each form, so
 # every case is checked on both.
-FORMS = [32, 64]
+FORMS = [1, 2]
 
 
 @pytest.fixture(params=FORMS, ids=["per_group", "streamed"])
 def form(request):
-    prev = capi.lib().frt_set_option(3, request.param)
+    prev = capi.lib().frt_set_option(5, request.param)
     yield request.param
-    capi.lib().frt_set_option(3, prev)
+    capi.lib().frt_set_option(5, prev)
 
 
 @pytest.mark.parametrize("rows,dim", CASES)
