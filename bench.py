@@ -15,12 +15,15 @@ the host inside the timed region.
 
 N > 1 (torchrun, one rank per GPU): the fixed M-token problem with the NVFP4
 weights column-sharded over the ranks, activations replicated, outputs left
-sharded (strong scaling; `--sharding columns`, the default); the NCCL
-all-gather of the largest output is timed separately.  The same line carries
-the Llama-3-70B FFN in the same split (`c5_column_sharded`), the step with a
-row-sharded producer whose NVFP4 rows are all-gathered inside the step
-(`row_sharded_producer`), and the token-sharded replicas (`token_sharded`:
-every rank runs the whole step on its own tokens, no collective).
+sharded (strong scaling; `--sharding columns`, the default).  The producer
+runs on each rank's row shard and stores its NVFP4 rows into every rank's
+activation buffer from inside the kernel (NVSwitch multicast stores over
+symmetric memory), timed inside the step; the NCCL all-gather of the largest
+output is timed separately.  The same line carries the step with every rank
+running the whole producer (`replicated_producer`), with an NCCL all-gather
+of the NVFP4 rows (`row_sharded_producer_nccl`), the Llama-3-70B FFN in the
+same split (`c5_column_sharded`) and the token-sharded replicas
+(`token_sharded`: every rank runs the whole step on its own tokens).
 
 At N = 1 `detail` also holds: every GEMM timed back to back over rotating
 buffers, a >= 2 s sustained run, the reference's own CUDA kernels on the same
@@ -28,7 +31,7 @@ buffers (`reference_cuda`, when oracle/_ref was built), the decode sweep on
 rotating weight sets (`c3`), the grouped MoE GEMMs (`c4`) and the Llama-3-70B
 FFN (`c5`).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c5|c4]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c5|c4|model]
                     [--sharding columns|tokens] [--tokens M --graph] [--quick]
 """
 from __future__ import annotations
@@ -223,20 +226,34 @@ class Layer:
         dist.all_gather_into_tensor(self.act_packed, self.act_packed[r0:r1])
         dist.all_gather_into_tensor(self.act_sf, self.act_sf[s0:s1])
 
-    def step_capi(self, capi, st, ev=None, dist=None, rows=None):
-        """one pass through the C ABI (resident inputs); optional (start,end) events per kernel; with `rows`
-        the producer runs on this rank's row shard and NCCL all-gathers the NVFP4 rows"""
+    def step_capi(self, capi, st, ev=None, dist=None, rows=None, shared=None):
+        """one pass through the C ABI (resident inputs); optional (start,end) events per kernel.  With `rows` the
+        producer runs on this rank's row shard and NCCL all-gathers the NVFP4 rows; with `shared` (a
+        SharedActivations) the row-shard producer stores its rows into every rank's buffer from inside the kernel
+        and a bounded wait kernel precedes the GEMM."""
         L = capi.lib()
         P = capi.ptr
         launches = 0
+        n_fed = 0
         for i, g_ in enumerate(self.gemms):
+            a_p, a_sf = g_["a_p"], g_["a_sf"]
             if g_["fed"]:
                 pe = ev.get(("producer", i)) if ev is not None else None
                 if pe:
                     pe[0].record()
-                rc = self.producer_capi(capi, st, rows)
-                if rows is not None:
-                    self.gather_activations(dist, rows)
+                if shared is not None:
+                    b = n_fed % shared.buffers
+                    n_fed += 1
+                    r0, r1 = shared.row0, shared.row0 + shared.rows_local
+                    shared.produce(b, self.residual[r0:r1], self.hidden[r0:r1], self.norm_w, EPS, st)
+                    shared.wait(b, st)
+                    a_p, a_sf = shared.packed[b], shared.sf[b]
+                    rc = 0
+                    launches += 1
+                else:
+                    rc = self.producer_capi(capi, st, rows)
+                    if rows is not None:
+                        self.gather_activations(dist, rows)
                 if pe:
                     pe[1].record()
                 assert rc == 0, rc
@@ -244,7 +261,7 @@ class Layer:
             ge = ev.get((g_["name"], i)) if ev is not None else None
             if ge:
                 ge[0].record()
-            rc = L.frt_nvfp4_gemm_bf16(P(g_["a_p"]), P(g_["a_sf"]), P(g_["wp"]), P(g_["wsf"]), None, None,
+            rc = L.frt_nvfp4_gemm_bf16(P(a_p), P(a_sf), P(g_["wp"]), P(g_["wsf"]), None, None,
                                        P(g_["out"]), self.M, g_["n_loc"], g_["k"], 1.0, 0.0, st)
             if ge:
                 ge[1].record()
@@ -252,13 +269,24 @@ class Layer:
             launches += 1
         return launches
 
-    def step_ops(self, hidden, residual, dist=None, rows=None):
+    def step_ops(self, hidden, residual, dist=None, rows=None, shared=None):
         """one pass through the torch operator API; returns the last GEMM's output.  With `rows`, hidden and
-        residual are this rank's row shard and the NVFP4 rows are all-gathered."""
+        residual are this rank's row shard and the NVFP4 rows are exchanged: by the producer kernel itself when
+        `shared` (a SharedActivations) is given, else by an NCCL all-gather."""
         import fp4_fused_ops
         import fp4_gemm
+        from flashrt_b200_core import capi
         out = None
+        n_fed = 0
         for g_ in self.gemms:
+            if g_["fed"] and shared is not None:
+                b = n_fed % shared.buffers
+                n_fed += 1
+                st = capi.stream_ptr()
+                shared.produce(b, residual, hidden, self.norm_w, EPS, st)
+                shared.wait(b, st)
+                out = fp4_gemm.nvfp4_gemm_bf16(shared.packed[b], g_["wp"], shared.sf[b], g_["wsf"], out=g_["out"])
+                continue
             if g_["fed"]:
                 if rows is None:
                     fp4_fused_ops.residual_add_rms_norm_quant_nvfp4_swizzled_bf16(
@@ -438,6 +466,28 @@ def decode_leg(capi, dev, peaks, tokens=(1, 4, 16, 64), graph_replays=20):
         out[f"m{M}"] = {"us_per_step": round(ms * 1e3, 2), "weight_stream_gbs": round(gbs, 1),
                         "frac_of_hbm_measured": round(gbs / peaks["hbm_gbs"], 3)}
         del graph
+        # every GEMM of the step alone: the same launch over the four weight sets, four times, in one graph
+        per = {}
+        for i, (lname, n, k, fed) in enumerate(layers):
+            a_p, a_sf = (act_p, act_sf) if fed else res_in[i]
+
+            def calls(st):
+                for _ in range(4):
+                    for ws in wsets:
+                        assert L.frt_nvfp4_gemm_bf16(P(a_p), P(a_sf), P(ws[i][0]), P(ws[i][1]), None, None, P(outs[i]),
+                                                     M, n, k, 1.0, 0.0, st) == 0
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                g1 = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g1, stream=side):
+                    calls(capi.stream_ptr())
+            torch.cuda.synchronize()
+            us = event_ms(g1.replay, 10) / 16 * 1e3
+            per[lname] = {"us": round(us, 2), "gbs": round(0.5625 * n * k / us / 1e3, 1),
+                          "frac_of_hbm_measured": round(0.5625 * n * k / us / 1e3 / peaks["hbm_gbs"], 3)}
+            del g1
+        out[f"m{M}"]["per_gemm_back_to_back"] = per
     out["what"] = (f"{name.rsplit('-m', 1)[0]} linears + 2 fused producers per step, 4 rotating weight sets "
                    f"({4 * wbytes / 1e6:.0f} MB), one CUDA graph of 4 steps replayed {graph_replays} times; "
                    f"{wbytes / 1e6:.1f} MB of weights per step")
@@ -596,8 +646,20 @@ def run_ours(args, rank, world, local_rank):
         barrier()
         return max_over_ranks(t0.elapsed_time(t1) / n_steps)
 
+    # N > 1, column-sharded: the producer runs on this rank's row shard and stores its NVFP4 rows into every
+    # rank's activation buffer from inside the kernel (symmetric memory, NVSwitch multicast stores); where the
+    # system has no symmetric memory every rank runs the whole producer instead.
+    shared, shared_note = None, None
+    if world > 1 and not tokens_mode and layer.M % (128 * world) == 0 and not args.graph and args.exchange != "none":
+        try:
+            from flashrt_b200_core.sharding import SharedActivations
+            shared = SharedActivations(layer.M, layer.H, dev, multicast=args.exchange == "multicast")
+        except Exception as e:
+            shared_note = "symmetric memory unavailable: " + repr(e)[:160]
+    step_kw = {"shared": shared} if shared is not None else {}
+
     for _ in range(args.warmup):
-        layer.step_capi(capi, st)
+        layer.step_capi(capi, st, **step_kw)
     barrier()
     if args.graph:
         side = torch.cuda.Stream()
@@ -645,7 +707,7 @@ def run_ours(args, rank, world, local_rank):
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         t0.record()
         for s in range(args.steps):
-            layer.step_capi(capi, st, events[s])
+            layer.step_capi(capi, st, events[s], **step_kw)
         t1.record()
         barrier()
     ms_total = t0.elapsed_time(t1)
@@ -659,7 +721,7 @@ def run_ours(args, rank, world, local_rank):
     ev2 = [{k: (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for k in keys}
            for _ in range(n_detail)]
     for s_ in range(n_detail):
-        layer.step_capi(capi, st, ev2[s_])
+        layer.step_capi(capi, st, ev2[s_], **step_kw)
     torch.cuda.synchronize()
     per_kernel = {}
     for k in keys:
@@ -722,7 +784,7 @@ def run_ours(args, rank, world, local_rank):
                 comp_s.wait_event(in_ready[b])
                 if s >= 1:
                     comp_s.wait_event(out_free)
-                out = layer.step_ops(dev_in[b][0], dev_in[b][1], dist=dist, rows=rows)
+                out = layer.step_ops(dev_in[b][0], dev_in[b][1], dist=dist, rows=rows, shared=shared)
                 in_free[b].record(comp_s)
                 out_ready.record(comp_s)
             with torch.cuda.stream(out_s):
@@ -777,17 +839,38 @@ def run_ours(args, rank, world, local_rank):
             for _ in range(3):
                 col.step_capi(capi, st, dist=dist, rows=rws)
             ms_row = timed_steps(col, n_steps, dist=dist, rows=rws)
-            res["row_sharded_producer"] = {
+            res["row_sharded_producer_nccl"] = {
                 "value": round(col.flops_total / (ms_row * 1e-3) / 1e12, 2), "ms_per_step": round(ms_row, 5),
                 "what": "producer on this rank's rows, NCCL all-gather of packed + scale bytes inside the step"}
+            try:
+                from flashrt_b200_core.sharding import SharedActivations
+                for label, mc in (("row_sharded_producer_peer_stores", False), ("row_sharded_producer_multicast", True)):
+                    sh = SharedActivations(col.M, col.H, dev, multicast=mc)
+                    for _ in range(3):
+                        col.step_capi(capi, st, shared=sh)
+                    ms_sh = timed_steps(col, n_steps, shared=sh)
+                    res[label] = {
+                        "value": round(col.flops_total / (ms_sh * 1e-3) / 1e12, 2), "ms_per_step": round(ms_sh, 5),
+                        "what": "producer on this rank's rows storing its NVFP4 rows into every rank's buffer from "
+                                "inside the kernel (" + ("NVSwitch multicast stores" if sh.uses_multicast else
+                                                         "peer stores over NVLink") + "), bounded flag wait before the GEMM"}
+                    del sh
+            except Exception as e:                          # no symmetric memory on this system
+                res["row_sharded_producer_peer_stores"] = {"unavailable": repr(e)[:200]}
         res["allgather_separate"] = time_allgather(col)
         if col is not layer:
             del col
         return res
 
-    allgather = column_sharded = token_sharded = c5_col = row_sharded = None
+    allgather = column_sharded = token_sharded = c5_col = row_sharded = replicated = None
     if world > 1 and not tokens_mode:
         allgather = time_allgather(layer)
+        if shared is not None:
+            for _ in range(3):
+                layer.step_capi(capi, st)
+            ms_rep = timed_steps(layer, args.steps)
+            replicated = {"value": round(layer.flops_total / (ms_rep * 1e-3) / 1e12, 2), "ms_per_step": round(ms_rep, 5),
+                          "what": "the same step with every rank running the whole producer (no exchange)"}
         if layer.M % (128 * world) == 0:
             rws = layer.row_shard(world, rank)
             for _ in range(3):
@@ -912,7 +995,14 @@ def run_ours(args, rank, world, local_rank):
                 "algorithmic_bytes": int(prod_bytes),
                 # (at kernel end part of the output is still dirty in L2, so DRAM traffic is below the algorithmic bytes)
                 "traffic": NCU_DRAM_TRAFFIC_BYTES.get(("producer", layer.M, layer.H))}
-        for key, val in (("allgather_separate", allgather), ("row_sharded_producer", row_sharded),
+        if world > 1 and not tokens_mode:
+            line["config"]["producer"] = (
+                "row-sharded, NVFP4 rows stored into every rank's buffer by the producer kernel itself ("
+                + ("NVSwitch multicast stores" if shared.uses_multicast else "peer stores") + "), bounded flag wait before "
+                "each consumer GEMM; timed inside the step" if shared is not None else
+                "replicated: every rank runs the whole producer" + (f" ({shared_note})" if shared_note else ""))
+        for key, val in (("allgather_separate", allgather), ("replicated_producer", replicated),
+                         ("row_sharded_producer_nccl", row_sharded),
                          ("column_sharded", column_sharded), ("token_sharded", token_sharded),
                          ("c5_column_sharded", c5_col), ("cpu_baseline", cpu_baseline)):
             if val:
@@ -940,6 +1030,80 @@ def run_moe(args, rank, world, local_rank):
             "roofline": r["roofline"],
             "detail": {"layers": r["layers"], "routed_layer_us": r["routed_layer_us"], "routed_layer": r["what"]},
             "gpu_launches": r["gpu_launches"], "clocks": clocks.summary()}), flush=True)
+
+
+def model_measure(dev, layers=36, tokens=4096, reps=3):
+    """A Qwen3-8B-shaped decoder (random weights, no checkpoint) through `transformers`: one prefill of `tokens`
+    tokens in bf16 eager, with every projection swapped for an NVFP4 linear (what the reference's quantizer does),
+    and with this library's fused conversion.  The attention kernel (torch SDPA) is the same in all three."""
+    import copy
+    import transformers
+    from flashrt_layers.transformers_backend import convert_decoder_model
+    cfg = transformers.Qwen3Config(hidden_size=4096, intermediate_size=12288, num_hidden_layers=layers,
+                                   num_attention_heads=32, num_key_value_heads=8, head_dim=128, vocab_size=151936,
+                                   max_position_embeddings=max(8192, tokens))
+    cfg._attn_implementation = "sdpa"
+    torch.manual_seed(0)
+    prev = torch.get_default_dtype()
+    torch.set_default_dtype(torch.bfloat16)
+    try:
+        with torch.device(dev):
+            model = transformers.Qwen3Model(cfg).eval()
+    finally:
+        torch.set_default_dtype(prev)
+    ids = torch.randint(0, cfg.vocab_size, (1, tokens), device=dev)
+
+    def prefill_ms(m):
+        with torch.no_grad():
+            for _ in range(2):
+                m(input_ids=ids, use_cache=False)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                out = m(input_ids=ids, use_cache=False).last_hidden_state
+            e1.record()
+            torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps, out
+
+    res = {"config": f"qwen3-8b-shaped decoder, {layers} layers, hidden 4096, 32/8 heads x 128, FFN 12288, {tokens} tokens, "
+                     "batch 1, random weights, transformers eager + SDPA attention"}
+    res["bf16_eager_ms"], ref = prefill_ms(model)
+    res["bf16_eager_ms"] = round(res["bf16_eager_ms"], 2)
+    per_linear = copy.deepcopy(model)
+    convert_decoder_model(per_linear, fuse=False)
+    ms, out = prefill_ms(per_linear)
+    res["nvfp4_per_linear_ms"] = round(ms, 2)
+    cos = lambda a, b: round(torch.nn.functional.cosine_similarity(a.float().flatten(), b.float().flatten(), dim=0).item(), 4)
+    res["cosine_vs_bf16_per_linear"] = cos(out, ref)
+    del per_linear, out
+    torch.cuda.empty_cache()
+    convert_decoder_model(model, fuse=True)
+    ms, out = prefill_ms(model)
+    res["nvfp4_fused_ms"] = round(ms, 2)
+    res["cosine_vs_bf16_fused"] = cos(out, ref)
+    res["speedup_vs_bf16_eager"] = round(res["bf16_eager_ms"] / ms, 2)
+    res["what"] = ("fused = norm + quantise in one kernel with the residual additions inside it, q/k/v as one GEMM, "
+                   "gate/up GEMM with the SwiGLU -> NVFP4 epilogue, down GEMM; per_linear = quantise + GEMM per nn.Linear")
+    del model
+    torch.cuda.empty_cache()
+    return res
+
+
+def run_model(args, rank, world, local_rank):
+    from flashrt_b200_core import load
+    load()
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    with ClockSampler(local_rank, period=0.02) as clocks:
+        r = model_measure(dev)
+    if rank == 0:
+        print(json.dumps({
+            "metric": "qwen3_8b_prefill_4096_ms", "value": r["nvfp4_fused_ms"], "unit": "ms", "n_gpus": 1,
+            "steps": 3, "warmup": 2, "ms_per_step": r["nvfp4_fused_ms"], "higher_is_better": False,
+            "scaling": "replicas only", "vs_baseline": None, "dtype": "nvfp4 linears, bf16 attention", "data": "synthetic",
+            "config": {"workload": "qwen3-8b-shaped-decoder-prefill-4096"}, "detail": {"model": r},
+            "clocks": clocks.summary()}), flush=True)
 
 
 # ----------------------------------------------------------------------------
@@ -1025,13 +1189,17 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["c4"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["c4", "model"])
     ap.add_argument("--tokens", type=int, default=0, help="override the token count M (decode sweep: 1, 4, 16, 64)")
     ap.add_argument("--graph", action="store_true",
                     help="time CUDA-graph replays of the step (launch-bound decode shapes); prints a short line")
     ap.add_argument("--sharding", default="columns", choices=["columns", "tokens"],
                     help="N > 1: columns = column-sharded weights on the fixed problem (strong scaling, default); "
                          "tokens = data-parallel replicas over token rows (weak scaling)")
+    ap.add_argument("--exchange", default="none", choices=["fused", "multicast", "none"],
+                    help="N > 1, columns: fused = row-sharded producer that stores its rows into every rank's buffer "
+                         "(peer stores; default); multicast = the same through NVSwitch multicast stores; "
+                         "none = every rank runs the whole producer")
     ap.add_argument("--no-pdl", action="store_true",
                     help="plain kernel launches instead of programmatic dependent launches (A/B)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -1055,6 +1223,8 @@ def main():
     try:
         if args.workload == "c4":
             run_moe(args, rank, world, local_rank)
+        elif args.workload == "model":
+            run_model(args, rank, world, local_rank)
         else:
             run_ours(args, rank, world, local_rank)
     finally:

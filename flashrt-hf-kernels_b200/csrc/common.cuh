@@ -21,6 +21,7 @@ extern int g_opt_pdl;                       // FRT_OPT_PDL: programmatic depende
 extern int g_opt_norm_form;                 // FRT_OPT_NORM_FORM: 0 automatic, 1 per-row-group, 2 streamed
 extern int g_opt_tail_split;                // FRT_OPT_GEMM_TAIL_SPLIT: slice the last wave of the dense pair GEMM
 extern int g_opt_split_k;                   // FRT_OPT_GEMM_SPLIT_K: cluster split-K of the small-M GEMM
+extern int g_opt_smallm_stages;             // FRT_OPT_SMALLM_STAGES: ring depth of the small-M GEMM (0 = default)
 #ifdef FRT_DEBUG
 extern int g_opt_gemm_debug;                // experiment switches of the GEMM kernel (debug builds only)
 #endif

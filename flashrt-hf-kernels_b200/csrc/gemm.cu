@@ -106,12 +106,14 @@ __device__ __forceinline__ void tile_coords(int t, const GemmParams& p, int& pt,
   qt = r / gsize;
 }
 
-// One stage of P: 128 rows x 128 bytes, 128B-swizzled.  The interleaved layout keeps, for each group of 8 rows and
-// each 64-element k-tile, the 8 rows' 32-byte pieces together; as a 4-D tensor (32 B, k-tile, row in group, group)
-// a box of (32, 4, 8, 16) lands in shared memory exactly as the plain 2-D box of 128 rows x 128 bytes does.
+// One stage of P: 128 rows x 128 bytes.  Plain layout: one 2-D box, 128B swizzle.  Interleaved GEMV layout
+// ([rows/8][K/64][8 rows][32 B], a dense 4-D tensor): a box of 16 row groups x 4 k-tiles x 8 rows x 32 B, stored
+// in that order with the 32-byte swizzle, so that every (row group, k-tile) is one 8-row x 32-byte swizzle atom
+// of 256 bytes; the MMA reads it with a SWIZZLE_32B descriptor whose 8-row-group pitch is 1024 bytes and which
+// advances 256 bytes per k-tile.
 __device__ __forceinline__ void load_p_stage(void* dst, const CUtensorMap* map, uint64_t* bar, int ks, int pt,
                                              bool interleaved) {
-  if (interleaved) ptx::tma_load_4d(dst, map, bar, 0, ks * KT_PER_STAGE, 0, pt * (BM / 8));
+  if (interleaved) ptx::tma_load_4d(dst, map, bar, 0, 0, ks * KT_PER_STAGE, pt * (BM / 8));
   else ptx::tma_load_2d(dst, map, bar, ks * 128, pt * BM);
 }
 
@@ -127,8 +129,27 @@ __device__ __forceinline__ void load_p_stage(void* dst, const CUtensorMap* map, 
 // are not written by any kernel of the stream) before it waits for the previous grid; only the
 // activation halves wait.  The weight stream of kernel n+1 thus overlaps kernel n, which is what a
 // chain of latency-bound decode GEMMs needs.
+// TMEM columns a CTA allocates: accumulators + two scale buffers, rounded up to a power of two (>= 32).
+template <int BN, int ACC>
+__host__ __device__ constexpr int tmem_cols() {
+  const int need = ACC * BN + 2 * KT_PER_STAGE * (4 + (BN <= 128 ? 1 : 2) * 4);
+  int c = 32;
+  while (c < need) c *= 2;
+  return c;
+}
+// CTAs of the small-M (swapped) form that share an SM: as many as fit its shared memory (228 KB, 1 KB reserved
+// per CTA) and TMEM (512 columns), at most 4.  Several small CTAs per SM let the CTAs of the NEXT kernel of the
+// stream become resident, and prefetch their weights, while this kernel still runs.
+template <int BN, int STAGES, int ACC, bool SWAP>
+__host__ __device__ constexpr int ctas_per_sm() {
+  if (!SWAP || BN > 64) return 1;
+  int n = (228 * 1024) / (SmemLayout<BN, STAGES>::TOTAL + 1024);
+  if (512 / tmem_cols<BN, ACC>() < n) n = 512 / tmem_cols<BN, ACC>();
+  return n > 4 ? 4 : (n < 1 ? 1 : n);
+}
+
 template <int BN, int STAGES, int ACC, bool SWAP, bool SPLITK = false>
-__global__ void __launch_bounds__(192, (SWAP && BN <= 32) ? 2 : 1)
+__global__ void __launch_bounds__(192, ctas_per_sm<BN, STAGES, ACC, SWAP>())
 nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
                   const GemmParams p) {
   using L = SmemLayout<BN, STAGES>;
@@ -136,7 +157,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
   constexpr int SF_COLS = KT_PER_STAGE * (4 + SFQ_COLS_PER_KT);    // per SF buffer
   constexpr int ACC_COLS = ACC * BN;
   static_assert(ACC_COLS + 2 * SF_COLS <= 512, "TMEM budget");
-  constexpr uint32_t TMEM_COLS = (ACC_COLS + 2 * SF_COLS <= 256) ? 256 : 512;
+  constexpr uint32_t TMEM_COLS = tmem_cols<BN, ACC>();
+  static_assert(ACC_COLS + 2 * SF_COLS <= static_cast<int>(TMEM_COLS), "TMEM allocation");
   constexpr uint32_t IDESC = ptx::idesc_nvf4(BM, BN);
 
   extern __shared__ uint8_t smem_raw[];
@@ -256,6 +278,10 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
       const uint64_t sf_desc = ptx::desc_sf_32x16(smem0 + L::A_BYTES + L::B_BYTES);
       const uint32_t op_hi = static_cast<uint32_t>(op_desc >> 32), op_lo0 = static_cast<uint32_t>(op_desc);
       const uint32_t sf_hi = static_cast<uint32_t>(sf_desc >> 32), sf_lo0 = static_cast<uint32_t>(sf_desc);
+      // P operand of the interleaved layout: layout type 6 (SWIZZLE_32B) in descriptor bits 61..63, 256 bytes per k-tile
+      const bool p_ilv = SWAP && p.p_interleaved;
+      const uint32_t p_hi = p_ilv ? ((op_hi & 0x1fffffffu) | (6u << 29)) : op_hi;
+      const uint32_t p_step = p_ilv ? 16u : 2u;
       const bool copy_always = !FRT_DBG(p, 2);
       int s = 0, tl = 0;
       uint32_t ph = 0, sfbuf = 0;
@@ -296,7 +322,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
                   ptx::tc_cp_32x128b_warpx4(sfq_t + 4 * b, sfq_lo + (b * KT_PER_STAGE + kt) * (SF_TILE >> 4), sf_hi);
               }
               // +2 per k-tile: 32 bytes (64 e2m1) along K inside the 128-byte swizzle span
-              ptx::tc_mma_nvf4(d_tmem, a_lo + 2 * kt, b_lo + 2 * kt, op_hi, IDESC, sfp_t, sfq_t + qoff,
+              ptx::tc_mma_nvf4(d_tmem, a_lo + p_step * kt, b_lo + 2 * kt, p_hi, op_hi, IDESC, sfp_t, sfq_t + qoff,
                                ks != ks_begin || kt != 0);
             }
           } else {
@@ -306,7 +332,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
               ptx::tc_cp_32x128b_warpx4(sfp_t, sfp_lo + kt * (SF_TILE >> 4), sf_hi);
               for (int b = 0; b < L::SFQ_BLOCKS; ++b)
                 ptx::tc_cp_32x128b_warpx4(sfq_t + 4 * b, sfq_lo + (b * KT_PER_STAGE + kt) * (SF_TILE >> 4), sf_hi);
-              ptx::tc_mma_nvf4(d_tmem, a_lo + 2 * kt, b_lo + 2 * kt, op_hi, IDESC, sfp_t, sfq_t + qoff,
+              ptx::tc_mma_nvf4(d_tmem, a_lo + p_step * kt, b_lo + 2 * kt, p_hi, op_hi, IDESC, sfp_t, sfq_t + qoff,
                                ks != ks_begin || kt != 0);
             }
           }
@@ -480,18 +506,18 @@ int make_operand_map(CUtensorMap* map, const void* base, int rows, int K, int bo
   return r == CUDA_SUCCESS ? FRT_OK : FRT_E_DRIVER;
 }
 
-// packed e2m1 weights in the interleaved GEMV layout [rows/8][K/64][8 rows][32 bytes]; box = one stage of 128
-// rows x 4 k-tiles, written to shared memory in (group, row, k-tile, byte) order = 128-byte rows, 128B swizzle
+// packed e2m1 weights in the interleaved GEMV layout: the dense 4-D tensor [rows/8][K/64][8 rows][32 bytes];
+// box = 16 row groups x 4 k-tiles x 8 rows x 32 bytes (one stage), 32-byte swizzle
 int make_interleaved_map(CUtensorMap* map, const void* base, int rows, int K) {
   auto enc = get_encode();
   if (!enc) return FRT_E_DRIVER;
   const cuuint64_t kt = static_cast<cuuint64_t>(K / 64);
-  const cuuint64_t dims[4] = {32, kt, 8, static_cast<cuuint64_t>(rows / 8)};
-  const cuuint64_t strides[3] = {256, 32, kt * 256};
-  const cuuint32_t box[4] = {32, KT_PER_STAGE, 8, BM / 8};
+  const cuuint64_t dims[4] = {32, 8, kt, static_cast<cuuint64_t>(rows / 8)};
+  const cuuint64_t strides[3] = {32, 256, kt * 256};
+  const cuuint32_t box[4] = {32, 8, KT_PER_STAGE, BM / 8};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
   const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(base), dims, strides, box, estr,
-                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? FRT_OK : FRT_E_DRIVER;
 }
@@ -555,7 +581,7 @@ int launch_gemm(const CUtensorMap& mp, const CUtensorMap& mq, GemmParams& p, int
   p.q_tiles = (p.Q + BN - 1) / BN;
   p.p_tiles = (p.P + BM - 1) / BM;
   const int tiles = p.p_tiles * p.q_tiles;
-  const int slots = (SWAP && BN <= 32) ? 2 * sms : sms;      // two small CTAs fit an SM
+  const int slots = ctas_per_sm<BN, STAGES, ACC, SWAP>() * sms;
   const int grid = tiles < slots ? tiles : slots;
   launch_pdl(kern, dim3(grid), dim3(192), L::TOTAL, st, mp, mq, p);
   return launch_result();
@@ -849,6 +875,10 @@ void select_gemm_config(int P, int Q, int K, bool swap, int requested, int sms, 
   if (swap && bn && Q <= bn && g_opt_split_k) {
     // few 128-row weight tiles: split K over a cluster so that every SM streams weights
     const int tiles = (P + BM - 1) / BM, k_stages = ((K + 63) / 64 + KT_PER_STAGE - 1) / KT_PER_STAGE;
+    if (g_opt_split_k >= 2) {                              // forced (measurements): taken when it divides the K stages
+      if (g_opt_split_k <= 8 && k_stages % g_opt_split_k == 0) splits = g_opt_split_k;
+      return;
+    }
     int want = (bn <= 32 ? 2 * sms : sms) / tiles;     // two CTAs of the 16/32-token forms fit an SM
     if (want > 8) want = 8;
     for (int s = want; s >= 2; --s)
@@ -909,22 +939,29 @@ int run_gemm(const void* p_packed, const void* sfp, int P, const void* q_packed,
   if (int rc = make_operand_map(&mq, q_packed, Q, K, bn)) return rc;
   p.p_interleaved = p_interleaved ? 1 : 0;
   p.splits = splits;
-  {
-    if (p.splits > 1) {
-      switch (cfg) {
-        case 11: return launch_gemm_splitk<16, 5>(mp, mq, p, st);
-        case 12: return launch_gemm_splitk<32, 4>(mp, mq, p, st);
-        default: return launch_gemm_splitk<64, 8>(mp, mq, p, st);
-      }
+  // ring depth of the small-M forms: FRT_OPT_SMALLM_STAGES overrides the default (0) for measurements
+  const int depth = g_opt_smallm_stages;
+  if (p.splits > 1) {
+    switch (cfg) {
+      case 11: return depth == 2 ? launch_gemm_splitk<16, 2>(mp, mq, p, st)
+                    : depth == 3 ? launch_gemm_splitk<16, 3>(mp, mq, p, st) : launch_gemm_splitk<16, 5>(mp, mq, p, st);
+      case 12: return depth == 2 ? launch_gemm_splitk<32, 2>(mp, mq, p, st)
+                    : depth == 3 ? launch_gemm_splitk<32, 3>(mp, mq, p, st) : launch_gemm_splitk<32, 4>(mp, mq, p, st);
+      default: return depth == 3 ? launch_gemm_splitk<64, 3>(mp, mq, p, st) : launch_gemm_splitk<64, 8>(mp, mq, p, st);
     }
   }
   switch (cfg) {
     case 1: return launch_gemm<128, 6, 2, false>(mp, mq, p, di.sms, st);
     case 2: return launch_gemm<256, 4, 1, false>(mp, mq, p, di.sms, st);
     case 3: return launch_gemm<192, 4, 2, false>(mp, mq, p, di.sms, st);
-    case 11: return launch_gemm<16, 5, 2, true>(mp, mq, p, di.sms, st);
-    case 12: return launch_gemm<32, 4, 2, true>(mp, mq, p, di.sms, st);
-    case 13: return launch_gemm<64, 8, 2, true>(mp, mq, p, di.sms, st);
+    case 11: return depth == 2 ? launch_gemm<16, 2, 2, true>(mp, mq, p, di.sms, st)
+                  : depth == 3 ? launch_gemm<16, 3, 2, true>(mp, mq, p, di.sms, st)
+                               : launch_gemm<16, 5, 2, true>(mp, mq, p, di.sms, st);
+    case 12: return depth == 2 ? launch_gemm<32, 2, 2, true>(mp, mq, p, di.sms, st)
+                  : depth == 3 ? launch_gemm<32, 3, 2, true>(mp, mq, p, di.sms, st)
+                               : launch_gemm<32, 4, 2, true>(mp, mq, p, di.sms, st);
+    case 13: return depth == 3 ? launch_gemm<64, 3, 2, true>(mp, mq, p, di.sms, st)
+                               : launch_gemm<64, 8, 2, true>(mp, mq, p, di.sms, st);
     case 14: return launch_gemm<128, 6, 2, true>(mp, mq, p, di.sms, st);
   }
   return FRT_E_UNSUPPORTED;

@@ -14,6 +14,7 @@ int g_opt_pdl = 1;
 int g_opt_norm_form = 0;
 int g_opt_tail_split = 1;
 int g_opt_split_k = 1;
+int g_opt_smallm_stages = 0;
 #ifdef FRT_DEBUG
 int g_opt_gemm_debug = 0;
 #endif
@@ -799,6 +800,7 @@ int frt_set_option(int key, int value) {
   if (key == FRT_OPT_NORM_FORM) { prev = g_opt_norm_form; g_opt_norm_form = value; }
   if (key == FRT_OPT_GEMM_TAIL_SPLIT) { prev = g_opt_tail_split; g_opt_tail_split = value; }
   if (key == FRT_OPT_GEMM_SPLIT_K) { prev = g_opt_split_k; g_opt_split_k = value; }
+  if (key == FRT_OPT_SMALLM_STAGES) { prev = g_opt_smallm_stages; g_opt_smallm_stages = value; }
 #ifdef FRT_DEBUG
   if (key == 3) { prev = g_opt_gemm_debug; g_opt_gemm_debug = value; }
 #endif

@@ -142,17 +142,19 @@ __device__ __forceinline__ void tc_cp_32x128b_warpx4(uint32_t taddr, uint32_t de
 }
 
 // D[tmem] (+)= A[smem] * B[smem], e2m1 x e2m1 with UE4M3 scales per 16 elements.
+// (the two operand descriptors may differ in their high words: the A operand of the interleaved GEMV layout uses
+// another swizzle mode than B)
 __device__ __forceinline__ void tc_mma_nvf4(uint32_t d_tmem, uint32_t a_desc_lo, uint32_t b_desc_lo,
-                                            uint32_t desc_hi, uint32_t idesc, uint32_t sfa_tmem,
+                                            uint32_t a_desc_hi, uint32_t b_desc_hi, uint32_t idesc, uint32_t sfa_tmem,
                                             uint32_t sfb_tmem, uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
       "mov.b64 da, {%1, %3};\n\t"
-      "mov.b64 db, {%2, %3};\n\t"
-      "setp.ne.b32 p, %7, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], da, db, %4, [%5], [%6], p;\n\t}"
-      ::"r"(d_tmem), "r"(a_desc_lo), "r"(b_desc_lo), "r"(desc_hi), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem),
-        "r"(accumulate)
+      "mov.b64 db, {%2, %4};\n\t"
+      "setp.ne.b32 p, %8, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], da, db, %5, [%6], [%7], p;\n\t}"
+      ::"r"(d_tmem), "r"(a_desc_lo), "r"(b_desc_lo), "r"(a_desc_hi), "r"(b_desc_hi), "r"(idesc), "r"(sfa_tmem),
+        "r"(sfb_tmem), "r"(accumulate)
       : "memory");
 }
 

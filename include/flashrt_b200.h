@@ -133,6 +133,31 @@ int frt_norm_quant_nvfp4(void* residual, const void* x, const void* weight, floa
                          float inv_global_scale, void* normed, void* packed, void* sf_swizzled,
                          int rows, int dim, unsigned flags, void* stream);
 
+/* ---- the same producer on a row shard, fused with its exchange (one node, up to 8 GPUs) ---------------
+ * For column-parallel GEMMs every GPU needs the NVFP4 activations of all M token rows.  Each rank calls this on
+ * ITS rows (residual / x point at the rank's first row, `row0` is that row's index in the whole tensor) and the
+ * kernel stores the packed codes and swizzled scale bytes of those rows straight into every GPU's copy of the
+ * whole [M, dim/2] + scale buffers:
+ *   mc_packed / mc_sf non-null : NVSwitch multicast addresses of the two buffers (one multimem.st reaches all GPUs);
+ *   else dst_packed[i] / dst_sf[i], i < n_dst : each GPU's copy as mapped into this process (peer stores), this
+ *     rank's own copy included.
+ * When the grid has finished, the kernel writes `epoch` to element `rank` of every rank's flag array
+ * (peer_flags[r] = rank r's array of n_ranks uint32, as mapped into this process).  `counter` is one zeroed uint32
+ * of local device memory per buffer (the kernel leaves it zero).  Epochs of one buffer must increase call by call.
+ * frt_peer_wait enqueues a kernel that returns once every rank's flag in the LOCAL array has reached `epoch`
+ * (bounded: after about a second it sets bit 0x400 of the status word and returns); enqueue it between this call
+ * and the first consumer of the buffer.  A buffer may be refilled once every rank has passed the wait of ANOTHER
+ * buffer filled later (two buffers used alternately are enough for producer -> GEMMs -> producer -> GEMMs chains).
+ * All buffers are the caller's (symmetric allocations, e.g. torch.distributed._symmetric_memory); nothing allocates.
+ * Bytes written are those frt_norm_quant_nvfp4 writes for the same rows.  No `normed` output.  n_ranks <= 8.
+ * The reference has no multi-GPU code; this entry point has no counterpart there. */
+int frt_norm_quant_nvfp4_bcast(void* residual, const void* x, const void* weight, float eps,
+                               float inv_global_scale, void* mc_packed, void* mc_sf,
+                               void* const* dst_packed, void* const* dst_sf, int n_dst,
+                               int row0, int rows, int dim, unsigned flags, void* counter,
+                               void* const* peer_flags, int n_ranks, int rank, unsigned epoch, void* stream);
+int frt_peer_wait(const void* flags, int n_ranks, unsigned epoch, void* stream);
+
 /* ---- dense NVFP4 A4W4 GEMM, bf16 out ------------------------------------
  * D[M,N] = bf16(alpha * sum_k A[m,k]*SFA[m,k/16] * B[n,k]*SFB[n,k/16]
  *               (+ bias[n]) (+ beta * C[m,n])),  fp32 accumulation in TMEM.
@@ -164,8 +189,8 @@ int frt_nvfp4_gemm_bf16(const void* a_packed, const void* sfa, const void* b_pac
 /* The reference's bind-time weight layout of its M = 1 GEMV and the GEMV that consumes it.
  * Layout: b_interleaved viewed as [N/8][K/64][8][32 bytes] holds b_packed [N/8][8][K/64][32 bytes]
  * (groups of 8 rows x 64-element k-tiles x 8 rows x 32 B), N % 8 == 0, K % 64 == 0.
- * The GEMV reads that layout through a 4-D tensor map into the same shared-memory tile as the plain
- * layout and runs the same weight-streaming kernel: out[1, N] bit-equal to frt_nvfp4_gemm_bf16 at M = 1.
+ * The GEMV reads that layout as a dense 4-D tensor (32-byte-swizzled 8-row x 32-byte atoms in shared
+ * memory) and runs the same weight-streaming kernel: out[1, N] bit-equal to frt_nvfp4_gemm_bf16 at M = 1.
  * replaces fp4_w4a4_repack_b_ilv_sm120 and fp4_w4a4_mma_sm120_warpsplit_ilv_bf16out,
  *   fp4-gemm/csrc/gemm/fp4/fp4_w4a4_mma_warpsplit_ilv_sm120.cuh:15,21 */
 int frt_nvfp4_repack_interleaved(const void* b_packed, void* b_interleaved, int N, int K, void* stream);
@@ -318,7 +343,10 @@ int64_t frt_launch_count(void);
 #define FRT_OPT_GEMM_TAIL_SPLIT 6   /* dense CTA-pair GEMM: 1 = cut the last, partial wave of
                                        tiles into column slices (default), 0 = whole tiles     */
 #define FRT_OPT_GEMM_SPLIT_K    7   /* small-M GEMM: 1 = split K over a cluster when there are
-                                       fewer weight tiles than SMs (default), 0 = never        */
+                                       fewer weight tiles than SMs (default), 0 = never,
+                                       2..8 = that many CTAs per tile when it divides K / 256   */
+#define FRT_OPT_SMALLM_STAGES   8   /* small-M GEMM: shared-memory ring depth, 0 = default, 2 or 3 =
+                                       shallower rings (more CTAs per SM); for measurements      */
 int frt_set_option(int key, int value);
 
 #ifdef __cplusplus

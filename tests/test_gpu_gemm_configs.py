@@ -212,5 +212,6 @@ def test_interleaved_repack_and_gemv(n, k):
     want = O.gemm_bf16(a.cpu().numpy(), sf_linear(sfa, 1, k), b.cpu().numpy(), sf_linear(sfb, n, k), alpha=2.0 ** -6)
     check(got, want)
     with pytest.raises(RuntimeError, match="M=1 only"):
-        fp4_gemm.fp4_w4a4_gemv_warpsplit_interleaved_bf16(torch.cat([a, a]), b_ilv, sfa, sfb)
+        fp4_gemm.fp4_w4a4_gemv_warpsplit_interleaved_bf16(torch.cat([a, a]), b_ilv, sfa, sfb,
+                                                          out=torch.empty((2, n), device=DEV, dtype=torch.bfloat16))
     assert device_status() == 0

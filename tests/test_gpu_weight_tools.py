@@ -106,10 +106,12 @@ def test_adopt_modelopt_two_level_weight():
 
 def test_transformers_decoder_conversion():
     """A small random Qwen3 through `convert_decoder_model`: the fused conversion (norm+quant in one kernel, shared
-    activations, SwiGLU epilogue) agrees with the per-linear conversion, and both stay close to the bf16 model."""
+    activations, one q/k/v GEMM, SwiGLU epilogue, residual additions inside the norm kernels) agrees with the
+    per-linear conversion, and both stay close to the bf16 model."""
     transformers = pytest.importorskip("transformers")
-    from flashrt_layers.transformers_backend import NormQuant, SharedInputFFN, convert_decoder_model
-    cfg = transformers.Qwen3Config(hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4,
+    from flashrt_layers.transformers_backend import (FinalNorm, NormQuant, ProjectionSlice, SharedInputFFN,
+                                                     StackedProjection, convert_decoder_model)
+    cfg = transformers.Qwen3Config(hidden_size=256, intermediate_size=512, num_hidden_layers=3, num_attention_heads=4,
                                    num_key_value_heads=2, head_dim=64, vocab_size=512, max_position_embeddings=256)
     torch.manual_seed(0)
     base = transformers.Qwen3ForCausalLM(cfg).to(DEV, torch.bfloat16).eval()
@@ -118,18 +120,65 @@ def test_transformers_decoder_conversion():
     with torch.no_grad():
         ref = base(ids).logits.float()
         plain = copy.deepcopy(base)
-        assert convert_decoder_model(plain, fuse=False) == 14
+        assert convert_decoder_model(plain, fuse=False) == 21
         fused = copy.deepcopy(base)
-        assert convert_decoder_model(fused, fuse=True) == 14
-        assert isinstance(fused.model.layers[0].mlp, SharedInputFFN)
-        assert isinstance(fused.model.layers[0].input_layernorm, NormQuant)
+        assert convert_decoder_model(fused, fuse=True, fuse_residual=False) == 21
+        carried = copy.deepcopy(base)
+        assert convert_decoder_model(carried, fuse=True) == 21
+        layer = fused.model.layers[0]
+        assert isinstance(layer.mlp, SharedInputFFN) and isinstance(layer.input_layernorm, NormQuant)
+        assert isinstance(layer.self_attn.q_proj, StackedProjection) and isinstance(layer.self_attn.k_proj, ProjectionSlice)
+        assert isinstance(carried.model.norm, FinalNorm) and not isinstance(fused.model.norm, FinalNorm)
         out_plain = plain(ids).logits.float()
         out_fused = fused(ids).logits.float()
+        out_carried = carried(ids).logits.float()
+        again = carried(ids).logits.float()                 # a second pass starts from a clean residual carry
     cos = lambda a, b: torch.nn.functional.cosine_similarity(a.flatten(), b.flatten(), dim=0).item()
     # A4W4 on every projection of a random-weight model: about 0.95 against bf16 (each linear alone is ~0.99)
-    assert cos(out_plain, ref) > 0.9 and cos(out_fused, ref) > 0.9, (cos(out_plain, ref), cos(out_fused, ref))
+    for out in (out_plain, out_fused, out_carried):
+        assert cos(out, ref) > 0.9, cos(out, ref)
     # the fused norm multiplies by the weight in fp32 (transformers rounds to bf16 first): a few codes flip
-    assert cos(out_fused, out_plain) > 0.99, cos(out_fused, out_plain)
+    assert cos(out_fused, out_plain) > 0.98, cos(out_fused, out_plain)
+    # residual additions inside the norm kernels: the norm sees the fp32 sum instead of its bf16 rounding
+    assert cos(out_carried, out_fused) > 0.98, cos(out_carried, out_fused)
+    assert torch.equal(again, out_carried)
+    assert carried.model.layers[0]._frt_carry.deferred is None
     # the shared quantisation was used: one producer call per norm, no per-linear quantise of that tensor
-    layer = fused.model.layers[0]
     assert layer.self_attn.q_proj.source is layer.input_layernorm.produced
+
+
+def test_conversion_skip_names_and_norm_detection():
+    """`skip` matches qualified module names; a norm that scales by (1 + weight) is detected by running it, and a
+    norm of another form is left alone"""
+    transformers = pytest.importorskip("transformers")
+    from torch import nn
+    from flashrt_layers.transformers_backend import SharedInputLinear, _norm_semantics, convert_decoder_model
+    cfg = transformers.Qwen3Config(hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4,
+                                   num_key_value_heads=2, head_dim=64, vocab_size=512, max_position_embeddings=256)
+    torch.manual_seed(1)
+    model = transformers.Qwen3ForCausalLM(cfg).to(DEV, torch.bfloat16).eval()
+    n = convert_decoder_model(model, fuse=True, skip=("lm_head", "model.layers.1.mlp", "layers.0.self_attn.o_proj"))
+    assert n == 6 + 4                                        # layer 0 keeps its o_proj, layer 1 its MLP
+    assert isinstance(model.model.layers[0].self_attn.o_proj, nn.Linear)
+    assert isinstance(model.model.layers[1].self_attn.o_proj, SharedInputLinear)
+    assert isinstance(model.model.layers[1].mlp.gate_proj, nn.Linear)
+    with torch.no_grad():
+        assert torch.isfinite(model(torch.randint(0, 512, (1, 16), device=DEV)).logits.float()).all()
+
+    class OnePlus(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.weight = nn.Parameter(torch.randn(256, device=DEV) * 0.1)
+            self.eps = 1e-6
+
+        def forward(self, x):
+            xf = x.float()
+            return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + self.eps) * (1 + self.weight.float())).to(x.dtype)
+
+    class Shifted(OnePlus):
+        def forward(self, x):
+            return super().forward(x) + 1.0
+
+    assert _norm_semantics(OnePlus()) == "one_plus"
+    assert _norm_semantics(Shifted()) is None
+    assert _norm_semantics(transformers.models.qwen3.modeling_qwen3.Qwen3RMSNorm(256).to(DEV)) == "plain"
