@@ -18,7 +18,6 @@ namespace frt {
 namespace {
 
 constexpr int kMaxRanks = 8;
-constexpr long long kPeerWaitLimit = 1ll << 31;     // SM clocks (about a second) before the wait gives up
 
 struct BcastParams {
   uint4* residual;            // this rank's rows, bf16 [rows, dim], in/out (or null)
@@ -202,14 +201,15 @@ norm_quant_bcast_kernel(const BcastParams p) {
 }
 
 // Polls this GPU's flag array until every rank has published `epoch` (flags only grow).  One warp; bounded.
-__global__ void peer_wait_kernel(const unsigned* flags, int n_ranks, unsigned epoch, unsigned* status) {
+__global__ void peer_wait_kernel(const unsigned* flags, int n_ranks, unsigned epoch, unsigned* status,
+                                 long long wait_limit) {
   pdl_launch_dependents();
   pdl_wait();
   const int r = threadIdx.x;
   if (r >= n_ranks) return;
   const long long t0 = clock64();
   while (static_cast<int>(ld_acquire_sys(flags + r) - epoch) < 0) {
-    if (clock64() - t0 > kPeerWaitLimit) {
+    if (clock64() - t0 > wait_limit) {
       atomicOr(status, 0x400u);
       return;
     }
@@ -289,7 +289,7 @@ int frt_peer_wait(const void* flags, int n_ranks, unsigned epoch, void* stream) 
   unsigned* status = device_status_word();
   if (!status) return FRT_E_LAUNCH;
   launch_pdl(peer_wait_kernel, dim3(1), dim3(32), 0, as_stream(stream), static_cast<const unsigned*>(flags), n_ranks,
-             epoch, status);
+             epoch, status, wait_limit_clocks());
   return launch_result();
 }
 

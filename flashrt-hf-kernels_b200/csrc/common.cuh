@@ -21,6 +21,8 @@ extern int g_opt_pdl;                       // FRT_OPT_PDL: programmatic depende
 extern int g_opt_norm_form;                 // FRT_OPT_NORM_FORM: 0 automatic, 1 per-row-group, 2 streamed
 extern int g_opt_tail_split;                // FRT_OPT_GEMM_TAIL_SPLIT: slice the last wave of the dense pair GEMM
 extern int g_opt_split_k;                   // FRT_OPT_GEMM_SPLIT_K: cluster split-K of the small-M GEMM
+extern int g_opt_wait_limit_log2;            // FRT_OPT_WAIT_LIMIT_LOG2: log2 of the SM-clock budget of device-side waits
+extern int g_opt_grouped_form;               // FRT_OPT_GROUPED_FORM: 0 automatic, 1 weight-major, 2 token-major
 extern int g_opt_smallm_stages;             // FRT_OPT_SMALLM_STAGES: ring depth of the small-M GEMM (0 = default)
 #ifdef FRT_DEBUG
 extern int g_opt_gemm_debug;                // experiment switches of the GEMM kernel (debug builds only)
@@ -29,6 +31,9 @@ extern int g_opt_gemm_debug;                // experiment switches of the GEMM k
 // Status word written by kernels whose bounded waits ran out (one per device
 // context, lives in device global memory of this library).
 unsigned* device_status_word();
+
+// SM clocks a device-side wait (mbarrier, peer flag) may spin before it gives up and reports through the status word
+inline long long wait_limit_clocks() { return 1ll << g_opt_wait_limit_log2; }
 
 inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
 

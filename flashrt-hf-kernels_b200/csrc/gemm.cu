@@ -53,7 +53,7 @@ constexpr int BM = 128;            // UMMA M, rows of P per tile
 constexpr int BK = 256;            // elements of K per smem stage (128 bytes per row)
 constexpr int KT_PER_STAGE = 4;    // UMMA K = 64 elements
 constexpr int SF_TILE = 512;       // bytes of scales for 128 rows x 64 elements
-constexpr long long WAIT_LIMIT = 1ll << 31;   // SM clocks (~1 s) before a wait gives up
+#define WAIT_LIMIT p.wait_limit   // SM clocks before a wait gives up (GemmParams::wait_limit, about a second by default)
 
 struct GemmParams {
   int P, Q, K;              // extents on the M axis, N axis, reduction
@@ -72,6 +72,7 @@ struct GemmParams {
   const float* alpha_stack; // grouped: per-expert alpha
   int max_items;            // grouped: capacity of the work list (items beyond it were dropped by the plan)
   int splits;               // split-K cluster size (small-M form), 1 otherwise
+  long long wait_limit;     // SM clocks a wait on an mbarrier may take before the CTA gives up
   int p_interleaved;        // P is stored in the interleaved GEMV layout [rows/8][K/64][8][32 B] (4-D tensor map)
 #ifdef FRT_DEBUG
   int dbg;                  // experiment switches
@@ -716,24 +717,48 @@ __device__ __forceinline__ void emit_windows(GroupWork* work, int max_items, int
   }
 }
 
+// Token-major items: the 128-row blocks an expert's rows touch, two per item (one per CTA of a pair; -1 = none).
+__device__ __forceinline__ void emit_block_pairs(GroupWork* work, int max_items, int lo, int hi, int expert) {
+  const int b0 = lo >> 7, b1 = (hi - 1) >> 7;
+  const int n_items = (b1 - b0 + 2) / 2;
+  int slot = atomicAdd(&work->count, n_items);
+  if (slot + n_items > max_items) atomicOr(&g_status_word, 0x200u);
+  for (int b = b0; b <= b1; b += 2, ++slot) {
+    if (slot < max_items) {
+      GroupItem it{};
+      it.q_row0 = b;                          // block of CTA 0
+      it.n_tokens = b + 1 <= b1 ? b + 1 : -1; // block of CTA 1
+      it.lo = lo; it.hi = hi;
+      it.expert = expert;
+      work->items[slot] = it;
+    }
+  }
+}
+
 // Turns either description of "which expert owns which rows" into windows of
-// at most 256 rows that start on a multiple of 64.
+// at most 256 rows that start on a multiple of 64 (weight-major form), or into pairs of 128-row blocks
+// (token-major form).
 __global__ void group_plan_kernel(const int* __restrict__ offsets, const int* __restrict__ tile_expert, int tile_rows,
-                                  int rows, int num_experts, int num_tiles, GroupWork* work, int max_items) {
+                                  int rows, int num_experts, int num_tiles, GroupWork* work, int max_items,
+                                  int token_major) {
   pdl_launch_dependents();
   pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (offsets != nullptr) {
     if (i >= num_experts) return;
     const int lo = max(0, min(offsets[i], rows)), hi = max(0, min(offsets[i + 1], rows));
-    if (hi > lo) emit_windows(work, max_items, lo, hi, i);
+    if (hi > lo) {
+      if (token_major) emit_block_pairs(work, max_items, lo, hi, i);
+      else emit_windows(work, max_items, lo, hi, i);
+    }
   } else {
     if (i >= num_tiles) return;
     const int e = tile_expert[i];
     if (e < 0 || e >= num_experts || (i > 0 && tile_expert[i - 1] == e)) return;   // not the first tile of a run
     int j = i + 1;
     while (j < num_tiles && tile_expert[j] == e) ++j;
-    emit_windows(work, max_items, i * tile_rows, j * tile_rows, e);
+    if (token_major) emit_block_pairs(work, max_items, i * tile_rows, j * tile_rows, e);
+    else emit_windows(work, max_items, i * tile_rows, j * tile_rows, e);
   }
 }
 
@@ -750,13 +775,14 @@ int make_weight_stack_map(CUtensorMap* map, const void* base, int n, int K, int 
   return r == CUDA_SUCCESS ? FRT_OK : FRT_E_DRIVER;
 }
 
-int make_sf_stack_map(CUtensorMap* map, const void* base, int n, int sf_cols, int experts, int64_t stride) {
+int make_sf_stack_map(CUtensorMap* map, const void* base, int n, int sf_cols, int experts, int64_t stride,
+                      int blocks = 1) {
   auto enc = get_encode();
   if (!enc) return FRT_E_DRIVER;
   const cuuint64_t dims[4] = {128, static_cast<cuuint64_t>(sf_cols), static_cast<cuuint64_t>((n + 127) / 128),
                               static_cast<cuuint64_t>(experts)};
   const cuuint64_t strides[3] = {512, static_cast<cuuint64_t>(sf_cols) * 512, static_cast<cuuint64_t>(stride)};
-  const cuuint32_t box[4] = {128, KT_PER_STAGE, 1, 1};
+  const cuuint32_t box[4] = {128, KT_PER_STAGE, static_cast<cuuint32_t>(blocks), 1};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
   const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, const_cast<void*>(base), dims, strides, box, estr,
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -800,6 +826,7 @@ int run_grouped_impl(const void* a, const void* sfa, const void* b_stack, const 
   p.p_tiles = (N + 255) / 256;
   p.q_tiles = 0;
   p.group_m = 1;
+  p.wait_limit = wait_limit_clocks();
   p.max_items = static_cast<int>(grouped_max_items(rows, experts));
 #ifdef FRT_DEBUG
   p.dbg = g_opt_gemm_debug & 0xff;
@@ -817,7 +844,59 @@ int run_grouped_impl(const void* a, const void* sfa, const void* b_stack, const 
   const int num_tiles = tile_rows > 0 ? rows / tile_rows : 0;
   const int plan_threads = offsets ? experts : num_tiles;
   launch_pdl(group_plan_kernel, dim3((plan_threads + 255) / 256), dim3(256), 0, st, static_cast<const int*>(offsets),
-             static_cast<const int*>(tile_expert), tile_rows, rows, experts, num_tiles, work, max_items);
+             static_cast<const int*>(tile_expert), tile_rows, rows, experts, num_tiles, work, max_items, 0);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  launch_pdl(kern, dim3(2 * (di.sms / 2)), dim3(320), L::TOTAL, st, maps, p, static_cast<const GroupWork*>(work));
+  return launch_result();
+}
+
+// Token-major grouped form: token blocks on the 256-row M axis, 256 output columns of the expert's weights on N.
+int run_grouped_token_major(const void* a, const void* sfa, const void* b_stack, const void* sfb_stack,
+                            const void* alpha, const void* offsets, const void* tile_expert, int tile_rows, void* out,
+                            int rows, int N, int K, int experts, int64_t b_stride, int64_t sfb_stride, void* workspace,
+                            cudaStream_t st) {
+  const DeviceInfo di = device_info();
+  if (!di.ok || di.cc_major != 10) return FRT_E_DEVICE;
+  constexpr int BN = 256, STAGES = 5;
+  using L = PairLayout<BN, STAGES, true, true>;
+  auto kern = nvfp4_gemm_pair_kernel<BN, STAGES, true, false, true>;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_set[dev & 63]) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL) != cudaSuccess)
+      return FRT_E_LAUNCH;
+    attr_set[dev & 63] = true;
+  }
+  GemmParams p{};
+  p.P = rows; p.Q = N; p.K = K;
+  p.k_tiles = (K + 63) / 64;
+  p.sf_cols = p.k_tiles;
+  p.d = static_cast<__nv_bfloat16*>(out);
+  p.ldd = N;
+  p.alpha = 1.f;
+  p.alpha_stack = static_cast<const float*>(alpha);
+  p.p_tiles = 0;
+  p.q_tiles = (N + BN - 1) / BN;
+  p.group_m = 1;
+  p.wait_limit = wait_limit_clocks();
+  p.max_items = static_cast<int>(grouped_max_items(rows, experts));
+#ifdef FRT_DEBUG
+  p.dbg = g_opt_gemm_debug & 0xff;
+  p.trace = g_trace;
+#endif
+  PairMaps maps{};
+  if (int rc = make_operand_map(&maps.p, a, rows, K, 128)) return rc;
+  if (int rc = make_sf_map(&maps.sfp, sfa, rows, p.sf_cols, 1)) return rc;
+  if (int rc = make_weight_stack_map(&maps.q, b_stack, N, K, experts, b_stride)) return rc;      // box: 128 rows = BN / 2
+  if (int rc = make_sf_stack_map(&maps.sfq, sfb_stack, N, p.sf_cols, experts, sfb_stride, L::SFQ_BLOCKS)) return rc;
+  if (int rc = make_output_map(&maps.d, out, rows, N, N)) return rc;
+  auto* work = static_cast<GroupWork*>(workspace);
+  if (cudaMemsetAsync(work, 0, 16, st) != cudaSuccess) return FRT_E_LAUNCH;
+  const int num_tiles = tile_rows > 0 ? rows / tile_rows : 0;
+  const int plan_threads = offsets ? experts : num_tiles;
+  launch_pdl(group_plan_kernel, dim3((plan_threads + 255) / 256), dim3(256), 0, st, static_cast<const int*>(offsets),
+             static_cast<const int*>(tile_expert), tile_rows, rows, experts, num_tiles, work, p.max_items, 1);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   launch_pdl(kern, dim3(2 * (di.sms / 2)), dim3(320), L::TOTAL, st, maps, p, static_cast<const GroupWork*>(work));
   return launch_result();
@@ -830,6 +909,14 @@ int run_grouped_impl(const void* a, const void* sfa, const void* b_stack, const 
 int run_grouped(const void* a, const void* sfa, const void* b_stack, const void* sfb_stack, const void* alpha,
                 const void* offsets, const void* tile_expert, int tile_rows, void* out, int rows, int N, int K,
                 int experts, int64_t b_stride, int64_t sfb_stride, void* workspace, cudaStream_t st) {
+  // The weight-major form is the default: on the Qwen3-30B-A3B-shaped layer (128 experts, ~256 rows each) it
+  // measured 88 / 77 us for gate/up / down against 101 / 84 us for the token-major form, whose tiles always
+  // contract full 128-row blocks (an unaligned expert touches three of them) while a weight-major window is as
+  // long as the expert's rows.  FRT_OPT_GROUPED_FORM = 2 selects the token-major form.
+  const bool token_major = g_opt_grouped_form == 2;
+  if (token_major)
+    return run_grouped_token_major(a, sfa, b_stack, sfb_stack, alpha, offsets, tile_expert, tile_rows, out, rows, N, K,
+                                   experts, b_stride, sfb_stride, workspace, st);
   if (K >= 1536)
     return run_grouped_impl<5>(a, sfa, b_stack, sfb_stack, alpha, offsets, tile_expert, tile_rows, out, rows, N, K,
                                experts, b_stride, sfb_stride, workspace, st);
@@ -906,6 +993,7 @@ int run_gemm(const void* p_packed, const void* sfp, int P, const void* q_packed,
   p.ldd = ldd;
   p.alpha = alpha; p.beta = beta;
   p.group_m = 16;
+  p.wait_limit = wait_limit_clocks();
 #ifdef FRT_DEBUG
   p.dbg = g_opt_gemm_debug & 0xff;
   p.trace = g_trace;
@@ -1056,6 +1144,7 @@ int frt_nvfp4_gemm_swiglu_nvfp4(const void* a, const void* sfa, const void* b, c
   p.sfq_row_blocks = (N2 + 127) / 128;
   p.alpha = alpha;
   p.group_m = 16;
+  p.wait_limit = wait_limit_clocks();
 #ifdef FRT_DEBUG
   p.dbg = g_opt_gemm_debug & 0xff;
   p.trace = g_trace;

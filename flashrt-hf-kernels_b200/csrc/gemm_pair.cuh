@@ -67,20 +67,20 @@ __device__ __forceinline__ void decode_unit(int u, const GemmParams& p, int& pt,
   tile_coords(t, p, pt, qt);
 }
 
-template <int BN, int STAGES, bool GROUPED = false>
+template <int BN, int STAGES, bool GROUPED = false, bool TM = false>
 struct PairLayout {
 
   static constexpr int A_BYTES = 128 * 128;              // this CTA's 128 rows of P
   static constexpr int B_BYTES = (BN / 2) * 128;         // this CTA's half of the Q tile
   // 128-row scale groups a Q tile can touch (a grouped window starts at any multiple of 64)
-  static constexpr int SFQ_BLOCKS = GROUPED ? 3 : (BN <= 128 ? 1 : 2);
+  static constexpr int SFQ_BLOCKS = (GROUPED && !TM) ? 3 : (BN <= 128 ? 1 : 2);
   static constexpr int SFP_BYTES = KT_PER_STAGE * SF_TILE;
   static constexpr int SFQ_BYTES = SFQ_BLOCKS * KT_PER_STAGE * SF_TILE;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFP_BYTES + SFQ_BYTES;
   // epilogue staging: 4 warps x 4 buffers of 32 rows x 64 bytes, written by TMA store
   // store staging: buffers of 32 rows x 64 B per epilogue warp (8 warps stage stores; the 5-stage
   // grouped form has room for one buffer each, the others for two)
-  static constexpr int SBUFS = (GROUPED && STAGES >= 5) ? 1 : 2;
+  static constexpr int SBUFS = (GROUPED && !TM && STAGES >= 5) ? 1 : 2;
   static constexpr int STAGING_BYTES = 8 * SBUFS * 2048;
   static constexpr int ITEM_CACHE = GROUPED ? 96 : 0;    // this pair's first work items, copied to smem
   static constexpr int TOTAL = STAGES * STAGE_BYTES + STAGING_BYTES + ITEM_CACHE * 32 + 1024 + 256;
@@ -97,6 +97,13 @@ struct PairLayout {
 // outer coordinate), Q = a window of token rows; the output tile is written
 // transposed (out[token, weight_row]) and masked to the rows of that expert.
 //
+// GROUPED + TM (token-major): P = two 128-row blocks of token rows (one per CTA; blocks are aligned to the
+// 128-row groups of the scale layout, so an expert's first and last block may be shared with its neighbours and
+// are masked row by row in the epilogue), Q = 256 output columns of that expert's weights.  The output tile is
+// row-major like the dense form's: TMA stores where a warp's 32 rows all belong to the expert, masked 16-byte
+// stores at its edges.  No transpose: this is the form for experts with many rows, where the transposing
+// epilogue of the weight-major form costs more than the mainloop (K = 768: three stages per tile).
+//
 // SWIGLU (BN = 256, dense): Q = [gate ; up] weights stacked along N (2H rows).  A tile is 128
 // gate columns and the 128 matching up columns: CTA 0 stages gate rows [128 qt, +128), CTA 1
 // up rows [H + 128 qt, +128), so accumulator columns [0,128) are gate and [128,256) up for the
@@ -107,12 +114,14 @@ struct PairLayout {
 // The SwiGLU form runs 16 epilogue warps (one lane quarter x one group of 32 outputs each):
 // its epilogue is an exponential and a division per output, and only that many warps issue
 // it in less time than the tile's mainloop takes.
-template <int BN, int STAGES, bool GROUPED, bool SWIGLU = false>
+template <int BN, int STAGES, bool GROUPED_ANY, bool SWIGLU = false, bool TM = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(SWIGLU ? 576 : 320, 1)
 nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p,
                        const GroupWork* __restrict__ work) {
-  using L = PairLayout<BN, STAGES, GROUPED>;
-  static_assert(!SWIGLU || (BN == 256 && !GROUPED), "the SwiGLU epilogue is a 256-wide dense tile");
+  using L = PairLayout<BN, STAGES, GROUPED_ANY, TM>;
+  constexpr bool GROUPED = GROUPED_ANY && !TM;     // the weight-major (transposed-output) grouped form
+  static_assert(!TM || GROUPED_ANY, "token-major is a grouped form");
+  static_assert(!SWIGLU || (BN == 256 && !GROUPED_ANY), "the SwiGLU epilogue is a 256-wide dense tile");
   constexpr int SFQ_COLS_PER_KT = L::SFQ_BLOCKS * 4;
   constexpr uint32_t IDESC = ptx::idesc_nvf4(256, BN);
   constexpr int CHUNKS = BN / 32;
@@ -138,8 +147,9 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
   const int num_pairs = gridDim.x >> 1;
   pdl_launch_dependents();
   // work units: grouped: read from the plan after the wait below; dense: tiles, the last wave sliced
-  int total_tiles = GROUPED ? 0 : (SWIGLU || BN != 256) ? p.p_tiles * p.q_tiles : p.units;
-  constexpr bool SLICED = !GROUPED && !SWIGLU && BN == 256;
+  int total_tiles = GROUPED_ANY ? 0 : (SWIGLU || BN != 256) ? p.p_tiles * p.q_tiles : p.units;
+  constexpr bool SLICED = !GROUPED_ANY && !SWIGLU && BN == 256;
+  const int per_item = TM ? p.q_tiles : p.p_tiles;          // tiles of one grouped work item
   const int k_stages = (p.k_tiles + KT_PER_STAGE - 1) / KT_PER_STAGE;
 
   if (threadIdx.x == 0) {
@@ -160,12 +170,12 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
     ptx::tmem_relinquish_pair();
   }
   pdl_wait();                 // everything above overlapped the previous kernel; global memory from here on
-  if (GROUPED) {
-    total_tiles = min(work->count, p.max_items) * p.p_tiles;   // the plan never stores beyond max_items
-    // tile i of this pair is global tile pair_id + i * num_pairs; its item is items[tile / p_tiles]
+  if (GROUPED_ANY) {
+    total_tiles = min(work->count, p.max_items) * per_item;   // the plan never stores beyond max_items
+    // tile i of this pair is global tile pair_id + i * num_pairs; its item is items[tile / per_item]
     for (int i = threadIdx.x; i < L::ITEM_CACHE; i += blockDim.x) {
       const int t = pair_id + i * num_pairs;
-      if (t < total_tiles) item_cache[i] = work->items[t / p.p_tiles];
+      if (t < total_tiles) item_cache[i] = work->items[t / per_item];
     }
   }
   ptx::tc_fence_before();
@@ -187,7 +197,17 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
       for (int t = pair_id; t < total_tiles && !*abort_flag; t += num_pairs, ++ti) {
         int pt, qt, q_row, q_blk, expert = 0;
         int nq = 0, nsf = 0;       // grouped: 32-row Q boxes per CTA, 128-row scale groups the window touches
-        if (GROUPED) {
+        int tm_p_row = 0;
+        if (TM) {
+          const GroupItem item = ti < L::ITEM_CACHE ? item_cache[ti] : work->items[t / per_item];
+          qt = t % per_item;
+          const int blk = (rank && item.n_tokens >= 0) ? item.n_tokens : item.q_row0;   // this CTA's 128-row block
+          tm_p_row = blk * 128;
+          q_row = qt * BN + static_cast<int>(rank) * (BN / 2);
+          q_blk = (qt * BN) >> 7;
+          expert = item.expert;
+          pt = 0;
+        } else if (GROUPED) {
           const GroupItem item = ti < L::ITEM_CACHE ? item_cache[ti] : work->items[t / p.p_tiles];
           pt = t % p.p_tiles;
           q_row = item.q_row0 + static_cast<int>(rank) * (item.n_tokens >> 1);
@@ -211,7 +231,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
             q_blk = (qt * BN) >> 7;
           }
         }
-        const int p_row = pt * 256 + static_cast<int>(rank) * 128;
+        const int p_row = TM ? tm_p_row : pt * 256 + static_cast<int>(rank) * 128;
         const int p_blk = p_row >> 7;
         for (int ks = 0; ks < k_stages; ++ks, ++it) {
           if (!ptx::mbar_wait_bounded(&empty[s], ph ^ 1, WAIT_LIMIT)) {
@@ -219,6 +239,18 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
           }
           const uint32_t st = smem0 + s * L::STAGE_BYTES;
           const uint32_t bar = full0 + s * 8;
+          if (TM) {
+            // tokens and their scales through the plain 2-D / 3-D maps, the expert's weights and weight scales
+            // through the stacked maps (expert = outer coordinate); boxes past the tensors' ends are zero-filled
+            if (leader) ptx::mbar_expect_tx(&full[s], 2 * L::STAGE_BYTES);
+            ptx::tma_load_2d_pair(st, &maps.p, bar, ks * 128, p_row);
+            ptx::tma_load_3d_pair(st + L::A_BYTES + L::B_BYTES, &maps.sfp, bar, 0, ks * KT_PER_STAGE, p_blk);
+            ptx::tma_load_3d_pair(st + L::A_BYTES, &maps.q, bar, ks * 128, q_row, expert);
+            ptx::tma_load_4d_pair(st + L::A_BYTES + L::B_BYTES + L::SFP_BYTES, &maps.sfq, bar, 0, ks * KT_PER_STAGE,
+                                  q_blk, expert);
+            if (++s == STAGES) { s = 0; ph ^= 1u; }
+            continue;
+          }
           if (GROUPED) {
             // the token window is loaded at its size: 32-row boxes of Q and only the scale groups it touches
             if (leader)
@@ -286,7 +318,9 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
         if (tr) FRT_TRACE(p, tl * 8 + 1);
         const uint32_t d_tmem = tmem_base + (a ? L::ACC1 : 0);
         uint32_t qoff, idesc = IDESC;
-        if (GROUPED) {
+        if (TM) {
+          qoff = (static_cast<uint32_t>((t % per_item) * BN) & 127u) >> 5;
+        } else if (GROUPED) {
           const GroupItem item = tl < L::ITEM_CACHE ? item_cache[tl] : work->items[t / p.p_tiles];
           qoff = (static_cast<uint32_t>(item.q_row0) & 127u) >> 5;
           idesc = ptx::idesc_nvf4(256, item.n_tokens);
@@ -360,7 +394,18 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
       int pt, qt = 0, col0 = 0, width = BN;
       GroupItem item{};
       float alpha = p.alpha;
-      if (GROUPED) {
+      int tm_row0 = 0;                      // TM: first token row of this warp's 32 TMEM lanes
+      bool tm_any = false, tm_all = false;  // TM: some / all of those rows belong to the item's expert
+      if (TM) {
+        item = tl < L::ITEM_CACHE ? item_cache[tl] : work->items[t / per_item];
+        qt = t % per_item;
+        pt = 0;
+        alpha = p.alpha_stack[item.expert];
+        const int blk = rank ? item.n_tokens : item.q_row0;      // CTA 1 of an odd last block: nothing to write
+        tm_row0 = blk * 128 + quarter * 32;
+        tm_any = blk >= 0 && tm_row0 < item.hi && tm_row0 + 32 > item.lo;
+        tm_all = blk >= 0 && tm_row0 >= item.lo && tm_row0 + 32 <= item.hi;
+      } else if (GROUPED) {
         item = tl < L::ITEM_CACHE ? item_cache[tl] : work->items[t / p.p_tiles];
         pt = t % p.p_tiles;
         alpha = p.alpha_stack[item.expert];
@@ -379,7 +424,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
       const bool first_half = drain_rank == 0;              // ... the first of which are the shared columns
       const bool tr = FRT_TRACING(p) && pair_id == 0 && tl < 32 && leader && quarter == 0 && lane == 0;
       if (tr) FRT_TRACE(p, tl * 8 + (first_half ? 3 : 6));
-      const int prow = pt * 256 + row_in_tile + lane;       // dense: output row; grouped: output column
+      const int prow = TM ? tm_row0 + lane : pt * 256 + row_in_tile + lane;   // dense / TM: output row; grouped: output column
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + (a ? L::ACC1 : 0);
       auto chunk_of = [&](int j) {                          // j-th chunk of this warp -> column chunk
         const int pos = drain_rank * NCH + j;
@@ -390,6 +435,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
           const int tok0 = item.q_row0 + cchunk * 32;
           return cchunk * 32 < item.n_tokens && tok0 < item.hi && tok0 + 32 > item.lo;
         }
+        if (TM) return tm_any && qt * BN + cchunk * 32 < p.Q;
         return cchunk * 32 < width && qt * BN + col0 + cchunk * 32 < p.Q;
       };
       auto release = [&]() {
@@ -499,6 +545,23 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
           // this lane's 32 outputs of row prow -> 64 bytes of bf16 in a staging buffer laid out
           // as the 64-byte TMA swizzle expects (16-byte piece index ^ ((row >> 1) & 3))
           const int q_base = qt * BN + col0 + cchunk * 32;
+          if (TM && !tm_all) {
+            // an edge of the expert's rows: each lane writes its own row if it belongs to the expert
+            if (prow >= item.lo && prow < item.hi) {
+              __nv_bfloat16* dst = p.d + static_cast<int64_t>(prow) * p.ldd + q_base;
+#pragma unroll
+              for (int g = 0; g < 4; ++g) {
+                if (q_base + 8 * g < p.Q && !FRT_DBG(p, 1)) {
+                  uint4 o;
+                  o.x = pack_bf16x2(__uint_as_float(v32[8 * g + 0]) * alpha, __uint_as_float(v32[8 * g + 1]) * alpha);
+                  o.y = pack_bf16x2(__uint_as_float(v32[8 * g + 2]) * alpha, __uint_as_float(v32[8 * g + 3]) * alpha);
+                  o.z = pack_bf16x2(__uint_as_float(v32[8 * g + 4]) * alpha, __uint_as_float(v32[8 * g + 5]) * alpha);
+                  o.w = pack_bf16x2(__uint_as_float(v32[8 * g + 6]) * alpha, __uint_as_float(v32[8 * g + 7]) * alpha);
+                  *reinterpret_cast<uint4*>(dst + 8 * g) = o;
+                }
+              }
+            }
+          } else {
           if (nstore >= WARP_BUFS) {                         // the store that last read this buffer is done
             if (lane == 0) ptx::bulk_wait_group_read<WARP_BUFS - 1>();
             __syncwarp();
@@ -533,10 +596,11 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
           ptx::fence_proxy_async();
           __syncwarp();
           if (lane == 0) {
-            if (!FRT_DBG(p, 1)) ptx::tma_store_2d(&maps.d, buf, q_base, pt * 256 + row_in_tile);
+            if (!FRT_DBG(p, 1)) ptx::tma_store_2d(&maps.d, buf, q_base, TM ? tm_row0 : pt * 256 + row_in_tile);
             ptx::bulk_commit_group();
           }
           ++nstore;
+          }   // whole-warp store
         }
         }   // live
         if (j + 2 < NCH && chunk_live(chunk_of(j + 2))) ptx::tc_ld_32x32b_x32(taddr + chunk_of(j + 2) * 32, r[j & 1]);

@@ -15,6 +15,8 @@ int g_opt_norm_form = 0;
 int g_opt_tail_split = 1;
 int g_opt_split_k = 1;
 int g_opt_smallm_stages = 0;
+int g_opt_wait_limit_log2 = 31;
+int g_opt_grouped_form = 0;
 #ifdef FRT_DEBUG
 int g_opt_gemm_debug = 0;
 #endif
@@ -505,7 +507,6 @@ int launch_layer_norm(const uint4* x, const uint4* w, const uint4* b, uint4* out
 // norm_quant_kernel.
 // ---------------------------------------------------------------------------
 constexpr int kStreamStages = 3;
-constexpr long long kStreamWaitLimit = 1ll << 31;   // SM clocks, about a second
 
 __device__ __forceinline__ void st_global_v8(void* dst, const uint4& a, const uint4& b) {
   asm volatile("st.global.cs.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
@@ -515,7 +516,7 @@ __device__ __forceinline__ void st_global_v8(void* dst, const uint4& a, const ui
 
 template <int TPR, bool HAS_RES, bool QUANT, int ENC>
 __global__ void __launch_bounds__(TPR > 256 ? TPR : 256, TPR > 256 ? 1024 / TPR : 4)
-norm_quant_stream_kernel(const NormParams p, unsigned* status) {
+norm_quant_stream_kernel(const NormParams p, unsigned* status, long long wait_limit) {
   constexpr int CTA = TPR > 256 ? TPR : 256;
   constexpr int RPC = CTA / TPR;                      // rows per group
   constexpr int WPR = TPR / 32;                       // warps per row
@@ -578,7 +579,7 @@ norm_quant_stream_kernel(const NormParams p, unsigned* status) {
   for (int group = blockIdx.x; group < n_groups; group += gridDim.x, ++it) {
     const int stage = it % kStreamStages;
     const uint32_t parity = (it / kStreamStages) & 1;
-    if (!ptx::mbar_wait_bounded(&full[stage], parity, kStreamWaitLimit)) atomicOr(status, 0x100u);
+    if (!ptx::mbar_wait_bounded(&full[stage], parity, wait_limit)) atomicOr(status, 0x100u);
     const int row = group * RPC + local_row;
     const bool ok = row < p.rows && s < p.nb;
     const int64_t idx = static_cast<int64_t>(row) * p.nb + s;
@@ -693,7 +694,7 @@ int launch_norm_stream(const NormParams& p, cudaStream_t st) {
   }
   const int n_groups = (p.rows + RPC - 1) / RPC;
   const int grid = n_groups < ctas_per_sm[dev] ? n_groups : ctas_per_sm[dev];
-  launch_pdl(kernel, dim3(grid), dim3(CTA), smem, st, p, device_status_word());
+  launch_pdl(kernel, dim3(grid), dim3(CTA), smem, st, p, device_status_word(), wait_limit_clocks());
   return launch_result();
 }
 
@@ -801,6 +802,11 @@ int frt_set_option(int key, int value) {
   if (key == FRT_OPT_GEMM_TAIL_SPLIT) { prev = g_opt_tail_split; g_opt_tail_split = value; }
   if (key == FRT_OPT_GEMM_SPLIT_K) { prev = g_opt_split_k; g_opt_split_k = value; }
   if (key == FRT_OPT_SMALLM_STAGES) { prev = g_opt_smallm_stages; g_opt_smallm_stages = value; }
+  if (key == FRT_OPT_GROUPED_FORM) { prev = g_opt_grouped_form; g_opt_grouped_form = value; }
+  if (key == FRT_OPT_WAIT_LIMIT_LOG2) {
+    prev = g_opt_wait_limit_log2;
+    g_opt_wait_limit_log2 = value < 20 ? 20 : value > 40 ? 40 : value;
+  }
 #ifdef FRT_DEBUG
   if (key == 3) { prev = g_opt_gemm_debug; g_opt_gemm_debug = value; }
 #endif

@@ -347,6 +347,12 @@ int64_t frt_launch_count(void);
                                        2..8 = that many CTAs per tile when it divides K / 256   */
 #define FRT_OPT_SMALLM_STAGES   8   /* small-M GEMM: shared-memory ring depth, 0 = default, 2 or 3 =
                                        shallower rings (more CTAs per SM); for measurements      */
+#define FRT_OPT_WAIT_LIMIT_LOG2 9   /* log2 of the SM clocks a device-side wait (mbarrier, peer flag) may
+                                       spin before the kernel gives up, sets its status bit and returns:
+                                       default 31 (about a second), accepted range 20..40            */
+#define FRT_OPT_GROUPED_FORM   10   /* grouped GEMM: 0 / 1 = weight-major (expert weights on the 256-row axis,
+                                       transposed output tile; default, the faster one measured),
+                                       2 = token-major (128-row token blocks on the 256-row axis)     */
 int frt_set_option(int key, int value);
 
 #ifdef __cplusplus

@@ -215,3 +215,48 @@ def test_interleaved_repack_and_gemv(n, k):
         fp4_gemm.fp4_w4a4_gemv_warpsplit_interleaved_bf16(torch.cat([a, a]), b_ilv, sfa, sfb,
                                                           out=torch.empty((2, n), device=DEV, dtype=torch.bfloat16))
     assert device_status() == 0
+
+
+# ---- tuning overrides of the small-M form keep the result --------------------------------------------------
+@pytest.mark.parametrize("m,depth,split", [(1, 2, 0), (1, 3, 8), (16, 2, 4), (24, 3, 0), (24, 2, 2), (64, 3, 0), (64, 3, 4)])
+def test_small_m_ring_depth_and_split_overrides(m, depth, split):
+    """FRT_OPT_SMALLM_STAGES (shallower shared-memory rings, more CTAs per SM) and a forced FRT_OPT_GEMM_SPLIT_K run
+    other instantiations of the weight-streaming kernel; every one must give the oracle's result."""
+    n, k = 1024, 4096
+    g = torch.Generator().manual_seed(m * 7 + depth)
+    ap, sfa = quantize((torch.randn(m, k, generator=g) * 0.5).to(torch.bfloat16).to(DEV))
+    bp, sfb = quantize((torch.randn(n, k, generator=g) * 0.05).to(torch.bfloat16).to(DEV))
+    L = capi.lib()
+    prev = L.frt_set_option(8, depth), L.frt_set_option(7, split)
+    try:
+        assert plan(m, n, k)[1] == max(split, 1)         # 0 = never split, >= 2 = that many CTAs per tile
+        out = gemm(ap, sfa, bp, sfb, m, n, k)
+    finally:
+        L.frt_set_option(8, prev[0]); L.frt_set_option(7, prev[1])
+    check(out, O.gemm_bf16(ap.cpu().numpy(), sf_linear(sfa, m, k), bp.cpu().numpy(), sf_linear(sfb, n, k)))
+    assert device_status() == 0
+
+
+def test_bounded_wait_runs_out_and_the_context_stays_usable():
+    """A device-side wait that nothing satisfies gives up after its clock budget, reports through the status word
+    and returns: here the wait for a peer flag of an epoch that no rank ever publishes, with the budget lowered to
+    2^20 clocks.  The stream stays usable: the next GEMM on it is correct and the status word is clean again."""
+    L, P = capi.lib(), capi.ptr
+    flags = torch.zeros(8, dtype=torch.int32, device=DEV)
+    prev = L.frt_set_option(9, 20)                       # FRT_OPT_WAIT_LIMIT_LOG2
+    try:
+        capi.check(L.frt_peer_wait(P(flags), 2, 1, capi.stream_ptr()))
+        torch.cuda.synchronize()
+    finally:
+        L.frt_set_option(9, prev)
+    assert device_status() == 0x400
+    assert device_status() == 0                          # reading the word clears it
+    flags[:2] = 5                                        # published epochs: the same wait now returns at once
+    capi.check(L.frt_peer_wait(P(flags), 2, 5, capi.stream_ptr()))
+    m, n, k = 64, 256, 512
+    g = torch.Generator().manual_seed(3)
+    ap, sfa = quantize((torch.randn(m, k, generator=g) * 0.5).to(torch.bfloat16).to(DEV))
+    bp, sfb = quantize((torch.randn(n, k, generator=g) * 0.05).to(torch.bfloat16).to(DEV))
+    out = gemm(ap, sfa, bp, sfb, m, n, k)
+    check(out, O.gemm_bf16(ap.cpu().numpy(), sf_linear(sfa, m, k), bp.cpu().numpy(), sf_linear(sfb, n, k)))
+    assert device_status() == 0

@@ -17,6 +17,15 @@ ROOT = Path(__file__).resolve().parent.parent
 sys.path.insert(0, str(ROOT / "flashrt-hf-kernels_b200" / "torch-ext"))
 
 
+@pytest.fixture(autouse=True, params=[1, 2], ids=["weight_major", "token_major"])
+def grouped_form(request):
+    """every case runs on both forms of the grouped kernel (FRT_OPT_GROUPED_FORM, key 10): expert weights on the
+    256-row axis with a transposed output tile, and token rows on the 256-row axis"""
+    prev = capi.lib().frt_set_option(10, request.param)
+    yield request.param
+    capi.lib().frt_set_option(10, prev)
+
+
 def make_inputs(rows, n, k, experts, seed):
     g = torch.Generator().manual_seed(seed)
     ap = torch.randint(0, 256, (rows, k // 2), generator=g, dtype=torch.uint8)
