@@ -1050,7 +1050,7 @@ def model_measure(dev, layers=36, tokens=4096, reps=3):
     from flashrt_layers.transformers_backend import convert_decoder_model
     cfg = transformers.Qwen3Config(hidden_size=4096, intermediate_size=12288, num_hidden_layers=layers,
                                    num_attention_heads=32, num_key_value_heads=8, head_dim=128, vocab_size=151936,
-                                   max_position_embeddings=max(8192, tokens))
+                                   max_position_embeddings=max(8192, tokens), initializer_range=0.006)
     cfg._attn_implementation = "sdpa"
     torch.manual_seed(0)
     prev = torch.get_default_dtype()
@@ -1076,7 +1076,8 @@ def model_measure(dev, layers=36, tokens=4096, reps=3):
         return e0.elapsed_time(e1) / reps, out
 
     res = {"config": f"qwen3-8b-shaped decoder, {layers} layers, hidden 4096, 32/8 heads x 128, FFN 12288, {tokens} tokens, "
-                     "batch 1, random weights, transformers eager + SDPA attention"}
+                     "batch 1, random N(0, 0.006) weights (a projection then has gain ~0.4, so that 36 random layers do "
+                     "not amplify rounding noise), transformers eager + SDPA attention"}
     res["bf16_eager_ms"], ref = prefill_ms(model)
     res["bf16_eager_ms"] = round(res["bf16_eager_ms"], 2)
     per_linear = copy.deepcopy(model)
@@ -1085,12 +1086,14 @@ def model_measure(dev, layers=36, tokens=4096, reps=3):
     res["nvfp4_per_linear_ms"] = round(ms, 2)
     cos = lambda a, b: round(torch.nn.functional.cosine_similarity(a.float().flatten(), b.float().flatten(), dim=0).item(), 4)
     res["cosine_vs_bf16_per_linear"] = cos(out, ref)
+    out_per_linear = out
     del per_linear, out
     torch.cuda.empty_cache()
     convert_decoder_model(model, fuse=True)
     ms, out = prefill_ms(model)
     res["nvfp4_fused_ms"] = round(ms, 2)
     res["cosine_vs_bf16_fused"] = cos(out, ref)
+    res["cosine_fused_vs_per_linear"] = cos(out, out_per_linear)
     res["speedup_vs_bf16_eager"] = round(res["bf16_eager_ms"] / ms, 2)
     res["what"] = ("fused = norm + quantise in one kernel with the residual additions inside it, q/k/v as one GEMM, "
                    "gate/up GEMM with the SwiGLU -> NVFP4 epilogue, down GEMM; per_linear = quantise + GEMM per nn.Linear")
