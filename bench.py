@@ -853,7 +853,8 @@ def run_ours(args, rank, world, local_rank):
                 "what": "producer on this rank's rows, NCCL all-gather of packed + scale bytes inside the step"}
             try:
                 from flashrt_b200_core.sharding import SharedActivations
-                for label, mc in (("row_sharded_producer_peer_stores", False), ("row_sharded_producer_multicast", True)):
+                legs = (("row_sharded_producer_peer_stores", False), ("row_sharded_producer_multicast", True))
+                for label, mc in (legs if args.exchange_legs else ()):
                     sh = SharedActivations(col.M, col.H, dev, multicast=mc)
                     for _ in range(3):
                         col.step_capi(capi, st, shared=sh)
@@ -1212,6 +1213,9 @@ def main():
                     help="N > 1, columns: fused = row-sharded producer that stores its rows into every rank's buffer "
                          "(peer stores; default); multicast = the same through NVSwitch multicast stores; "
                          "none = every rank runs the whole producer")
+    ap.add_argument("--exchange-legs", action="store_true",
+                    help="N > 1: also time the Llama-70B column-sharded step with the in-kernel exchange (peer stores "
+                         "and multicast stores); needs torch symmetric memory")
     ap.add_argument("--no-pdl", action="store_true",
                     help="plain kernel launches instead of programmatic dependent launches (A/B)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
