@@ -141,18 +141,24 @@ class ClockSampler:
         return out
 
 
-def event_ms(fn, iters, warm=3):
-    """mean milliseconds of fn() over `iters` back-to-back calls (CUDA events on the current stream)"""
+def event_ms(fn, iters, warm=3, best_of=1):
+    """mean milliseconds of fn() over `iters` back-to-back calls (CUDA events on the current stream); with
+    best_of > 1 the region is timed that many times and the fastest is returned (the burst figure: the same
+    convention as the measured bf16 / copy peaks the fractions are taken against)"""
     for _ in range(warm):
         fn()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(iters):
-        fn()
-    e1.record()
-    torch.cuda.synchronize()
-    return e0.elapsed_time(e1) / iters
+    best = None
+    for _ in range(best_of):
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / iters
+        best = ms if best is None else min(best, ms)
+    return best
 
 
 def rotating_sets(bytes_per_call):
@@ -315,10 +321,11 @@ def gemm_back_to_back(layer, capi, st, peaks, iters=12):
             for s_ in sets:
                 L.frt_nvfp4_gemm_bf16(P(s_["a_p"]), P(s_["a_sf"]), P(s_["wp"]), P(s_["wsf"]), None, None, P(s_["out"]),
                                       layer.M, s_["n_loc"], s_["k"], 1.0, 0.0, st)
-        ms = event_ms(calls, max(2, iters // len(sets))) / len(sets)
+        ms = event_ms(calls, max(2, iters // len(sets)), best_of=3) / len(sets)
         tf = 2.0 * layer.M * g_["n_loc"] * g_["k"] / (ms * 1e-3) / 1e12
         out[g_["name"]] = {"shape": [layer.M, g_["n_loc"], g_["k"]], "us": round(ms * 1e3, 2), "tflops": round(tf, 1),
-                           "frac_of_fp4_peak": round(tf / peaks["fp4_burst"], 4), "buffer_sets": len(sets)}
+                           "frac_of_fp4_peak": round(tf / peaks["fp4_burst"], 4), "buffer_sets": len(sets),
+                           "timing": "best of 3 regions"}
         del sets
     return out
 
@@ -336,11 +343,11 @@ def producer_back_to_back(layer, capi, st, peaks):
     def producers():
         for hx, rx, pk, sfp_ in psets:
             L.frt_norm_quant_nvfp4(P(rx), P(hx), P(layer.norm_w), EPS, 1.0, None, P(pk), P(sfp_), layer.M, layer.H, 0, st)
-    p_us = event_ms(producers, 10) / 4 * 1e3
+    p_us = event_ms(producers, 10, best_of=3) / 4 * 1e3
     prod_bytes = layer.M * layer.H * 6.5625
     return psets, {"us": round(p_us, 2), "gbs": round(prod_bytes / p_us / 1e3, 1),
                    "frac_of_hbm_measured": round(prod_bytes / p_us / 1e3 / peaks["hbm_gbs"], 3),
-                   "what": "fused residual+RMSNorm->NVFP4 on 4 rotating input sets, 40 launches"}
+                   "what": "fused residual+RMSNorm->NVFP4 on 4 rotating input sets, 40 launches, best of 3 regions"}
 
 
 def reference_cuda_leg(layer, psets, capi, st, peaks):
@@ -365,7 +372,7 @@ def reference_cuda_leg(layer, psets, capi, st, peaks):
                     for s_ in sets:
                         ref.ref_gemm_sm100_bf16(P(s_["a_p"]), P(s_["wp"]), P(s_["out"]), layer.M, s_["n_loc"], s_["k"],
                                                 P(s_["a_sf"]), P(s_["wsf"]), ctypes.c_float(1.0), variant, st)
-                ms = event_ms(calls, max(2, 12 // len(sets))) / len(sets)
+                ms = event_ms(calls, max(2, 12 // len(sets)), best_of=3) / len(sets)
                 row[label] = round(2.0 * layer.M * g_["n_loc"] * g_["k"] / (ms * 1e-3) / 1e12, 1)
             row["best_tflops"] = max(row.values())
             row["reference_selects"] = "widen" if g_["n_loc"] >= 4 * g_["k"] else "default"
@@ -377,7 +384,7 @@ def reference_cuda_leg(layer, psets, capi, st, peaks):
             for hx, rx, pk, sfp_ in psets:
                 ref.ref_res_rms_fp4_bf16(P(rx), P(hx), P(layer.norm_w), P(pk), P(sfp_), layer.M, layer.H,
                                          ctypes.c_float(EPS), st)
-        us = event_ms(k10, 10) / 4 * 1e3
+        us = event_ms(k10, 10, best_of=3) / 4 * 1e3
         res["fused_producer"] = {"us": round(us, 2), "gbs": round(layer.M * layer.H * 6.5625 / us / 1e3, 1)}
     else:
         res["gemm"] = {"unavailable": "oracle/_ref was built without a CUTLASS header tree"}
@@ -385,10 +392,10 @@ def reference_cuda_leg(layer, psets, capi, st, peaks):
     def k4():
         for hx, rx, pk, sfp_ in psets:
             ref.ref_quantize_bf16_vec(P(hx), P(pk), P(sfp_), layer.M, layer.H, st)
-    us = event_ms(k4, 10) / 4 * 1e3
+    us = event_ms(k4, 10, best_of=3) / 4 * 1e3
     res["quantizer"] = {"us": round(us, 2), "gbs": round(layer.M * layer.H * 2.5625 / us / 1e3, 1)}
     res["what"] = ("the reference's kernels compiled for sm_100a from its own sources (cluster 1x1x1 CUTLASS Sm100 GEMM, "
-                   "fused residual+RMSNorm->NVFP4, vectorised quantiser), same shapes, same rotating buffers, CUDA events")
+                   "fused residual+RMSNorm->NVFP4, vectorised quantiser), same shapes, same rotating buffers, CUDA events, best of 3 regions")
     return res
 
 
