@@ -312,6 +312,8 @@ def gemm_back_to_back(layer, capi, st, peaks, iters=12):
     L, P = capi.lib(), capi.ptr
     out = {}
     for g_ in layer.gemms:
+        torch.cuda.synchronize()
+        time.sleep(0.5)            # each kernel is timed alone, from an idle GPU (the burst peaks are measured that way)
         per_call = g_["wp"].numel() + g_["wsf"].numel() + g_["a_p"].numel() + g_["a_sf"].numel() + g_["out"].numel() * 2
         sets = [g_] + [dict(g_, wp=g_["wp"].clone(), wsf=g_["wsf"].clone(), a_p=g_["a_p"].clone(),
                             a_sf=g_["a_sf"].clone(), out=torch.empty_like(g_["out"]))
@@ -368,6 +370,8 @@ def reference_cuda_leg(layer, psets, capi, st, peaks):
                            for _ in range(rotating_sets(per_call) - 1)]
             row = {}
             for label, variant in (("default_tile_128x128x256", 0), ("widen_tile_128x256x128", 1)):
+                torch.cuda.synchronize()
+                time.sleep(0.5)    # same idle start as the per-GEMM leg of this library
                 def calls():
                     for s_ in sets:
                         ref.ref_gemm_sm100_bf16(P(s_["a_p"]), P(s_["wp"]), P(s_["out"]), layer.M, s_["n_loc"], s_["k"],

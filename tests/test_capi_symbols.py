@@ -89,3 +89,31 @@ def test_header_is_plain_c(tmp_path):
     src.write_text('#include "flashrt_b200.h"\nint main(void) { return frt_error_string(0) == 0; }\n')
     root = Path(__file__).resolve().parent.parent
     subprocess.run([cc, "-std=c99", "-Wall", "-Werror", f"-I{root / 'include'}", "-fsyntax-only", str(src)], check=True)
+
+
+def test_host_side_checks_of_the_newer_entry_points():
+    """argument checks that return before any device work: workspace size formula, option round trip, the
+    exchange producer's null / shape / rank checks, the interleaved layout's shape rule"""
+    import ctypes as C
+    from flashrt_b200_core import capi
+    lib = capi.lib()
+    assert lib.frt_nvfp4_grouped_gemm_workspace_bytes(4096, 128) == 16 + 32 * (4096 // 16 + 2 * 128 + 8)
+    assert lib.frt_nvfp4_grouped_gemm_workspace_bytes(0, 4) == 0
+    for key, value in ((5, 2), (6, 0), (7, 4), (8, 3), (10, 2)):
+        prev = lib.frt_set_option(key, value)
+        assert lib.frt_set_option(key, prev) == value
+    assert lib.frt_set_option(9, 5) == 31 and lib.frt_set_option(9, 31) == 20      # clamped to its floor
+    assert lib.frt_set_option(3, 1) == -1                                          # no such key in the shipped library
+    nul = (C.c_void_p * 8)()
+    one = C.c_void_p(256)
+    some = (C.c_void_p * 8)(*([256] * 8))
+    f = lib.frt_norm_quant_nvfp4_bcast
+    assert f(None, None, None, 1e-6, 1.0, None, None, some, some, 2, 0, 128, 1024, 0, one, some, 2, 0, 1, None) == -1
+    assert f(None, one, None, 1e-6, 1.0, one, None, some, some, 2, 0, 128, 1024, 0, one, some, 2, 0, 1, None) == -1
+    assert f(None, one, None, 1e-6, 1.0, None, None, some, some, 2, 0, 128, 1000, 0, one, some, 2, 0, 1, None) == -2
+    assert f(None, one, None, 1e-6, 1.0, None, None, some, some, 2, 0, 128, 1024, 0, one, some, 9, 0, 1, None) == -4
+    assert f(None, one, None, 1e-6, 1.0, None, None, some, some, 2, 0, 128, 1024, 0, one, some, 2, 2, 1, None) == -4
+    assert f(None, one, None, 1e-6, 1.0, None, None, nul, some, 2, 0, 128, 1024, 0, one, some, 2, 0, 1, None) == -1
+    assert lib.frt_peer_wait(None, 2, 1, None) == -1 and lib.frt_peer_wait(one, 9, 1, None) == -4
+    assert lib.frt_nvfp4_repack_interleaved(one, one, 12, 64, None) == -2          # N % 8
+    assert lib.frt_nvfp4_repack_interleaved(one, one, 16, 96, None) == -2          # K % 64
