@@ -251,8 +251,7 @@ class Layer:
                     b = n_fed % shared.buffers
                     n_fed += 1
                     r0, r1 = shared.row0, shared.row0 + shared.rows_local
-                    shared.produce(b, self.residual[r0:r1], self.hidden[r0:r1], self.norm_w, EPS, st)
-                    shared.wait(b, st)
+                    shared.produce(b, self.residual[r0:r1], self.hidden[r0:r1], self.norm_w, EPS, st)   # waits for the peers too
                     a_p, a_sf = shared.packed[b], shared.sf[b]
                     rc = 0
                     launches += 1
@@ -290,7 +289,6 @@ class Layer:
                 n_fed += 1
                 st = capi.stream_ptr()
                 shared.produce(b, residual, hidden, self.norm_w, EPS, st)
-                shared.wait(b, st)
                 out = fp4_gemm.nvfp4_gemm_bf16(shared.packed[b], g_["wp"], shared.sf[b], g_["wsf"], out=g_["out"])
                 continue
             if g_["fed"]:

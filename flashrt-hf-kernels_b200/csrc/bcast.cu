@@ -6,9 +6,14 @@
 // into every GPU's copy of the activation buffer, in the same kernel:
 //   * through one NVSwitch multicast address (`multimem.st`: the switch replicates each store to all GPUs), or
 //   * with plain stores to each GPU's mapped address (peer stores over NVLink), when no multicast mapping exists.
-// When the last CTA of the grid has finished, it publishes this rank's epoch number in every GPU's flag array
-// (release stores at system scope).  `peer_wait_kernel`, enqueued before the consumer GEMM, polls the local flag
-// array until every rank's flag has reached the epoch; the wait is bounded and reports through the status word.
+// The producer kernel itself sends only the packed codes (8 contiguous bytes per thread, merged to 16-byte
+// multicast stores) and writes the scale bytes into this GPU's own copy; a second, small kernel then copies the
+// shard's scale bytes - one contiguous range of the swizzled layout, since shards are whole 128-row groups - to
+// the other GPUs with 16-byte stores (one row's scale bytes are scattered over 64 tiles, and 4-byte remote stores
+// cost an NVLink request each) and publishes this rank's epoch number in every GPU's flag array (release stores at
+// system scope; the kernel boundary orders them after all of the producer's stores, so no CTA of the producer
+// has to wait for its remote stores).  `peer_wait_kernel`, enqueued before the consumer GEMM, polls the local
+// flag array until every rank's flag has reached the epoch; the wait is bounded and reports through the status word.
 //
 // Arithmetic, summation order and bytes are those of norm_quant_kernel (producer.cu) on the same rows.
 // The buffers are owned by the caller (symmetric allocations mapped into every process); nothing here allocates.
@@ -32,7 +37,9 @@ struct BcastParams {
   int rows, nb, sf_cols;
   float eps, inv_global_scale, dim_f;
   unsigned flags;
-  unsigned* counter;          // CTAs of this grid that are done (local scratch word, zero between calls)
+  uint8_t* local_sf;          // this GPU's own copy of the scale buffer (the producer kernel writes scales only here)
+  int64_t sf_lo, sf_bytes;    // byte range of this rank's rows in the swizzled scale buffer
+  unsigned* counter;          // CTAs of the finishing grid that are done (local scratch word, zero between calls)
   unsigned* peer_flags[kMaxRanks];  // every rank's flag array, as mapped into this process
   int n_ranks, rank;
   unsigned epoch;
@@ -46,9 +53,6 @@ __device__ __forceinline__ void multimem_st_v4(void* addr, uint32_t a, uint32_t 
   asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
                ::"l"(addr), "f"(__uint_as_float(a)), "f"(__uint_as_float(b)), "f"(__uint_as_float(c)),
                  "f"(__uint_as_float(d)) : "memory");
-}
-__device__ __forceinline__ void multimem_st_b32(void* addr, uint32_t v) {
-  asm volatile("multimem.st.relaxed.sys.global.b32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
 }
 __device__ __forceinline__ void st_release_sys(unsigned* addr, unsigned v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
@@ -160,42 +164,72 @@ norm_quant_bcast_kernel(const BcastParams p) {
     else packed = quantize_block16<kEncHw>(v, sfb, inv_scale_table());
     sf_byte = sfb;
   }
-  // The four scale bytes of a row's 64-element group are adjacent in the swizzled layout and belong to four
-  // adjacent lanes: the first of them gathers the word (blocks past the row's end contribute zero, which is what
-  // the padding of the last group must hold) and stores 4 bytes, the smallest unit a multicast store moves.
-  uint32_t word = sf_byte;
-  word |= __shfl_down_sync(0xffffffffu, sf_byte, 1) << 8;
-  word |= __shfl_down_sync(0xffffffffu, sf_byte, 2) << 16;
-  word |= __shfl_down_sync(0xffffffffu, sf_byte, 3) << 24;
   // multicast stores travel as separate requests: even lanes send their own 8 packed bytes and their odd
-  // neighbour's as one 16-byte store (an odd row length leaves the last block on its own 8-byte store)
+  // neighbour's as one 16-byte store (rows of an odd number of blocks keep 8-byte stores)
   const uint32_t nx = __shfl_down_sync(0xffffffffu, packed.x, 1), ny = __shfl_down_sync(0xffffffffu, packed.y, 1);
   if (ok) {
     const int grow = p.row0 + row;
     const int64_t packed_off = (static_cast<int64_t>(grow) * p.nb + s) * 8;
-    const int64_t sf_off = sf_offset(grow, s, p.sf_cols);
+    // scale byte into this GPU's copy (the padding of a row's last 64-element group is zeroed by the owner of
+    // the row's last block); the finishing kernel forwards the whole range
+    p.local_sf[sf_offset(grow, s, p.sf_cols)] = static_cast<uint8_t>(sf_byte);
+    if (s == p.nb - 1)
+      for (int j = p.nb; j < 4 * p.sf_cols; ++j) p.local_sf[sf_offset(grow, j, p.sf_cols)] = 0;
     if (p.mc_packed != nullptr) {
-      if ((s & 1) == 0) {
-        if (s + 1 < p.nb) multimem_st_v4(p.mc_packed + packed_off, packed.x, packed.y, nx, ny);
-        else multimem_st_b64(p.mc_packed + packed_off, packed);
+      if (p.nb & 1) {                        // rows of an odd number of blocks start 8-byte aligned only
+        multimem_st_b64(p.mc_packed + packed_off, packed);
+      } else if ((s & 1) == 0) {
+        multimem_st_v4(p.mc_packed + packed_off, packed.x, packed.y, nx, ny);
       }
-      if ((s & 3) == 0) multimem_st_b32(p.mc_sf + sf_off, word);
     } else {
-      for (int d = 0; d < p.n_dst; ++d) {
-        *reinterpret_cast<uint2*>(p.dst_packed[d] + packed_off) = packed;
-        if ((s & 3) == 0) *reinterpret_cast<uint32_t*>(p.dst_sf[d] + sf_off) = word;
-      }
+      for (int d = 0; d < p.n_dst; ++d) *reinterpret_cast<uint2*>(p.dst_packed[d] + packed_off) = packed;
     }
   }
-  // ---- publish: the last CTA to finish tells every rank that this rank's rows of epoch `epoch` have landed ----
+}
+
+// Forwards this rank's scale bytes (a contiguous range) to the other GPUs and publishes the epoch.  Runs after the
+// producer grid has completed (programmatic dependency + griddepcontrol.wait), so its flag stores are ordered after
+// every store of that grid.
+__global__ void __launch_bounds__(256)
+exchange_finish_kernel(const BcastParams p, unsigned* status, long long wait_limit) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t n16 = p.sf_bytes >> 4;
+  const uint4* src = reinterpret_cast<const uint4*>(p.local_sf + p.sf_lo);
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n16;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const uint4 v = src[i];
+    if (p.mc_sf != nullptr) {
+      multimem_st_v4(p.mc_sf + p.sf_lo + i * 16, v.x, v.y, v.z, v.w);
+    } else {
+      for (int d = 0; d < p.n_dst; ++d)
+        if (d != p.rank) *reinterpret_cast<uint4*>(p.dst_sf[d] + p.sf_lo + i * 16) = v;
+    }
+  }
+  __shared__ int is_last;
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence_system();
     const unsigned done = atomicAdd(p.counter, 1u) + 1u;
-    if (done == gridDim.x) {
+    is_last = done == gridDim.x;
+    if (is_last) {
       *p.counter = 0;                                   // ready for the next call on this stream
       __threadfence_system();
       for (int r = 0; r < p.n_ranks; ++r) st_release_sys(p.peer_flags[r] + p.rank, p.epoch);
+    }
+  }
+  __syncthreads();
+  // FRT_PRODUCER_WAIT_PEERS: the CTA that published also waits (bounded) until every rank's rows of this epoch
+  // have landed here, so the next kernel of the stream may consume the buffer without a separate wait kernel.
+  if ((p.flags & FRT_PRODUCER_WAIT_PEERS) && is_last && threadIdx.x < p.n_ranks) {
+    const unsigned* mine = p.peer_flags[p.rank] + threadIdx.x;
+    const long long t0 = clock64();
+    while (static_cast<int>(ld_acquire_sys(mine) - p.epoch) < 0) {
+      if (clock64() - t0 > wait_limit) {
+        atomicOr(status, 0x400u);
+        break;
+      }
+      __nanosleep(64);
     }
   }
 }
@@ -224,6 +258,10 @@ int launch_bcast(const BcastParams& p, bool has_res, cudaStream_t st) {
   const dim3 grid((p.rows + rows_per_cta - 1) / rows_per_cta), block(CTA);
   if (has_res) launch_pdl(norm_quant_bcast_kernel<TPR, true>, grid, block, 0, st, p);
   else launch_pdl(norm_quant_bcast_kernel<TPR, false>, grid, block, 0, st, p);
+  if (int rc = launch_result()) return rc;
+  const int64_t n16 = p.sf_bytes >> 4;
+  const int blocks = static_cast<int>(n16 / 256 < 1 ? 1 : n16 / 256 > 64 ? 64 : n16 / 256);
+  launch_pdl(exchange_finish_kernel, dim3(blocks), dim3(256), 0, st, p, device_status_word(), wait_limit_clocks());
   return launch_result();
 }
 
@@ -240,12 +278,14 @@ int frt_norm_quant_nvfp4_bcast(void* residual, const void* x, const void* weight
                                int n_ranks, int rank, unsigned epoch, void* stream) {
   if (!x || !counter || !peer_flags) return FRT_E_NULL;
   if ((mc_packed == nullptr) != (mc_sf == nullptr)) return FRT_E_NULL;
-  if (mc_packed == nullptr && (!dst_packed || !dst_sf || n_dst <= 0)) return FRT_E_NULL;
   if (rows <= 0 || dim <= 0 || dim % 16 != 0 || row0 < 0) return FRT_E_SHAPE;
+  if (row0 % 128 != 0 || rows % 128 != 0) return FRT_E_SHAPE;       // a shard is whole 128-row scale groups
   if (dim > 16384 || n_ranks < 1 || n_ranks > kMaxRanks || rank < 0 || rank >= n_ranks || n_dst > kMaxRanks)
     return FRT_E_UNSUPPORTED;
-  if (!aligned(x, 16) || !aligned(residual, 16) || !aligned(weight, 16) || !aligned(mc_packed, 8) ||
-      !aligned(mc_sf, 4) || !aligned(counter, 4))
+  if (!dst_sf || n_dst <= rank || !dst_sf[rank]) return FRT_E_NULL;   // this GPU's own copy of the scale buffer
+  if (mc_packed == nullptr && (!dst_packed || n_dst != n_ranks)) return FRT_E_NULL;
+  if (!aligned(x, 16) || !aligned(residual, 16) || !aligned(weight, 16) || !aligned(mc_packed, 16) ||
+      !aligned(counter, 4))
     return FRT_E_ALIGN;
   BcastParams p{};
   p.residual = static_cast<uint4*>(residual);
@@ -256,18 +296,22 @@ int frt_norm_quant_nvfp4_bcast(void* residual, const void* x, const void* weight
   if (mc_packed == nullptr) {
     for (int d = 0; d < n_dst; ++d) {
       if (!dst_packed[d] || !dst_sf[d]) return FRT_E_NULL;
-      if (!aligned(dst_packed[d], 8) || !aligned(dst_sf[d], 4)) return FRT_E_ALIGN;
+      if (!aligned(dst_packed[d], 8) || !aligned(dst_sf[d], 16)) return FRT_E_ALIGN;
       p.dst_packed[d] = static_cast<uint8_t*>(dst_packed[d]);
       p.dst_sf[d] = static_cast<uint8_t*>(dst_sf[d]);
     }
     p.n_dst = n_dst;
   }
+  if (!aligned(dst_sf[rank], 16) || !aligned(mc_sf, 16)) return FRT_E_ALIGN;
+  p.local_sf = static_cast<uint8_t*>(dst_sf[rank]);
   for (int r = 0; r < n_ranks; ++r) {
     if (!peer_flags[r]) return FRT_E_NULL;
     p.peer_flags[r] = static_cast<unsigned*>(peer_flags[r]);
   }
   p.row0 = row0;
   p.rows = rows; p.nb = dim / 16; p.sf_cols = (dim + 63) / 64;
+  p.sf_lo = static_cast<int64_t>(row0 / 128) * p.sf_cols * 512;
+  p.sf_bytes = static_cast<int64_t>(rows / 128) * p.sf_cols * 512;
   p.eps = eps; p.inv_global_scale = inv_global_scale; p.dim_f = static_cast<float>(dim);
   p.flags = flags;
   p.counter = static_cast<unsigned*>(counter);

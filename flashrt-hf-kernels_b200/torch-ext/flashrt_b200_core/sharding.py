@@ -98,11 +98,18 @@ class SharedActivations:
     def uses_multicast(self) -> bool:
         return bool(self._mc)
 
-    def produce(self, b: int, residual, x, weight, eps: float, stream, inv_global_scale: float = 1.0, flags: int = 0):
+    WAIT_PEERS = 0x100                                    # FRT_PRODUCER_WAIT_PEERS
+
+    def produce(self, b: int, residual, x, weight, eps: float, stream, inv_global_scale: float = 1.0, flags: int = 0,
+                wait: bool = True):
         """residual / x: THIS rank's rows (rows_local, dim) bf16; fills rows [row0, row0 + rows_local) of buffer b on
-        every rank and publishes the new epoch of the buffer."""
+        every rank and publishes the new epoch of the buffer.  With `wait` (default) the call also waits, on the
+        stream, until every rank's rows have landed in this rank's copy: the buffer may be consumed by the next
+        kernel of the stream.  With wait=False enqueue `wait(b, stream)` before the first consumer."""
         capi, C = self.capi, self.C
         self.epoch[b] += 1
+        if wait:
+            flags |= self.WAIT_PEERS
         mc_pk = C.c_void_p(self._mc + self._pk_off[b]) if self._mc else None
         mc_sf = C.c_void_p(self._mc + self._sf_off[b]) if self._mc else None
         local = self._bases[self.rank]

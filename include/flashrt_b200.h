@@ -129,24 +129,27 @@ int frt_rms_norm_quant_fp8(void* residual, const void* x, const void* weight, co
 #define FRT_PRODUCER_ROUND_BF16               2u
 #define FRT_PRODUCER_RNE_E2M1                 4u
 #define FRT_PRODUCER_NORM_FROM_BF16_RESIDUAL  8u
+#define FRT_PRODUCER_WAIT_PEERS           0x100u   /* frt_norm_quant_nvfp4_bcast only: also wait for every rank's rows */
 int frt_norm_quant_nvfp4(void* residual, const void* x, const void* weight, float eps,
                          float inv_global_scale, void* normed, void* packed, void* sf_swizzled,
                          int rows, int dim, unsigned flags, void* stream);
 
 /* ---- the same producer on a row shard, fused with its exchange (one node, up to 8 GPUs) ---------------
  * For column-parallel GEMMs every GPU needs the NVFP4 activations of all M token rows.  Each rank calls this on
- * ITS rows (residual / x point at the rank's first row, `row0` is that row's index in the whole tensor) and the
- * kernel stores the packed codes and swizzled scale bytes of those rows straight into every GPU's copy of the
- * whole [M, dim/2] + scale buffers:
+ * ITS rows (residual / x point at the rank's first row, `row0` is that row's index in the whole tensor; row0 and
+ * rows are multiples of 128, so that a shard's scale bytes are one contiguous range) and the producer kernel
+ * stores the packed codes of those rows straight into every GPU's copy of the whole [M, dim/2] buffer; a small
+ * second kernel forwards the shard's scale bytes and publishes the epoch:
  *   mc_packed / mc_sf non-null : NVSwitch multicast addresses of the two buffers (one multimem.st reaches all GPUs);
- *   else dst_packed[i] / dst_sf[i], i < n_dst : each GPU's copy as mapped into this process (peer stores), this
- *     rank's own copy included.
+ *   else dst_packed[i] / dst_sf[i], i < n_dst = n_ranks : each GPU's copy as mapped into this process (peer
+ *     stores), this rank's own copy included.  dst_sf[rank] (this GPU's own copy) is needed in both modes.
  * When the grid has finished, the kernel writes `epoch` to element `rank` of every rank's flag array
  * (peer_flags[r] = rank r's array of n_ranks uint32, as mapped into this process).  `counter` is one zeroed uint32
  * of local device memory per buffer (the kernel leaves it zero).  Epochs of one buffer must increase call by call.
  * frt_peer_wait enqueues a kernel that returns once every rank's flag in the LOCAL array has reached `epoch`
  * (bounded: after about a second it sets bit 0x400 of the status word and returns); enqueue it between this call
- * and the first consumer of the buffer.  A buffer may be refilled once every rank has passed the wait of ANOTHER
+ * and the first consumer of the buffer - or pass FRT_PRODUCER_WAIT_PEERS in `flags`, and the kernel that
+ * publishes this rank's epoch performs the same bounded wait before it ends (one kernel less in the chain).  A buffer may be refilled once every rank has passed the wait of ANOTHER
  * buffer filled later (two buffers used alternately are enough for producer -> GEMMs -> producer -> GEMMs chains).
  * All buffers are the caller's (symmetric allocations, e.g. torch.distributed._symmetric_memory); nothing allocates.
  * Bytes written are those frt_norm_quant_nvfp4 writes for the same rows.  No `normed` output.  n_ranks <= 8.

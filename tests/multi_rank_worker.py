@@ -54,8 +54,11 @@ def main():
                 sh.sf[b].fill_(0xEE)
                 torch.cuda.synchronize()
                 dist.barrier()                                       # nobody's poison lands after a peer's rows
-                sh.produce(b, res[r0:r1], hidden[r0:r1], norm_w, 1e-6, st)
-                sh.wait(b, st)
+                if epoch == 1:                                       # separate wait kernel
+                    sh.produce(b, res[r0:r1], hidden[r0:r1], norm_w, 1e-6, st, wait=False)
+                    sh.wait(b, st)
+                else:                                                # wait inside the finishing kernel
+                    sh.produce(b, res[r0:r1], hidden[r0:r1], norm_w, 1e-6, st)
                 n_loc = N // world
                 wp_loc, wsf_loc = shard_weight(wp, wsf, N, H, world, rank)
                 out = torch.empty(M, n_loc, device=dev, dtype=torch.bfloat16)
