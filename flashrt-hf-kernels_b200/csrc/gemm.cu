@@ -693,20 +693,31 @@ int launch_gemm_splitk(const CUtensorMap& mp, const CUtensorMap& mq, GemmParams&
 // Windows start on a multiple of 64 rows: the scales of a window are addressed in
 // TMEM as a column offset (one column per 32 rows) from a 128-row group, and the
 // MMA takes that scale address only at even columns.
+// Rows of the window that starts at `start` when the expert's rows end at `hi`: what is left, rounded up to
+// 32, if that is at most 320; else 256.
+__device__ __forceinline__ int window_rows(int start, int hi) {
+  const int rem = hi - start;
+  return rem <= 320 ? (rem + 31) & ~31 : 256;
+}
+
 __device__ __forceinline__ void emit_windows(GroupWork* work, int max_items, int lo, int hi, int expert) {
   // All windows of one expert take consecutive slots: their tiles then run at about the same
   // time on neighbouring CTA pairs and the expert's weights leave HBM once (with one slot per
   // atomic the windows of an expert ended up hundreds of tiles apart and the weights, long
   // evicted from L2, were streamed again for each).
+  // A window is 256 rows, or up to 320 when that takes in the expert's last rows: the rows beyond 256 are
+  // contracted by a second MMA against the weights already staged, so an expert with a few rows more than a
+  // full window does not stream its weights a second time for them.
   const int first = lo & ~63;
-  const int n_win = (hi - first + 255) / 256;
+  int n_win = 0;
+  for (int start = first; start < hi; start += window_rows(start, hi)) ++n_win;
   int slot = atomicAdd(&work->count, n_win);
   // A list that does not fit (overlapping or unsorted offsets: a sorted description always fits the
   // documented workspace) is cut short, never overrun: the GEMM kernel clamps the count the same way,
   // and the status word tells the host that rows were dropped.
   if (slot + n_win > max_items) atomicOr(&g_status_word, 0x200u);
-  for (int start = first; start < hi; start += 256, ++slot) {
-    const int len = min(256, (hi - start + 31) & ~31);
+  for (int start = first; start < hi; ++slot) {
+    const int len = window_rows(start, hi);
     if (slot < max_items) {
       GroupItem it{};
       it.q_row0 = start; it.n_tokens = len;
@@ -714,6 +725,7 @@ __device__ __forceinline__ void emit_windows(GroupWork* work, int max_items, int
       it.expert = expert;
       work->items[slot] = it;
     }
+    start += len;
   }
 }
 
@@ -903,9 +915,8 @@ int run_grouped_token_major(const void* a, const void* sfa, const void* b_stack,
 }
 
 
-// Long K: the tile is bound by streaming the expert's weights, so the fifth pipeline stage (more
-// bytes in flight per SM) matters; short K: the tile is bound by its epilogue, so the shared memory
-// goes to a second store-staging buffer per warp instead.
+// Four pipeline stages (a stage holds 128 weight rows, up to 160 token rows and their scales) and two
+// store-staging buffers per epilogue warp fill the shared memory of an SM.
 int run_grouped(const void* a, const void* sfa, const void* b_stack, const void* sfb_stack, const void* alpha,
                 const void* offsets, const void* tile_expert, int tile_rows, void* out, int rows, int N, int K,
                 int experts, int64_t b_stride, int64_t sfb_stride, void* workspace, cudaStream_t st) {
@@ -917,9 +928,6 @@ int run_grouped(const void* a, const void* sfa, const void* b_stack, const void*
   if (token_major)
     return run_grouped_token_major(a, sfa, b_stack, sfb_stack, alpha, offsets, tile_expert, tile_rows, out, rows, N, K,
                                    experts, b_stride, sfb_stride, workspace, st);
-  if (K >= 1536)
-    return run_grouped_impl<5>(a, sfa, b_stack, sfb_stack, alpha, offsets, tile_expert, tile_rows, out, rows, N, K,
-                               experts, b_stride, sfb_stride, workspace, st);
   return run_grouped_impl<4>(a, sfa, b_stack, sfb_stack, alpha, offsets, tile_expert, tile_rows, out, rows, N, K,
                              experts, b_stride, sfb_stride, workspace, st);
 }

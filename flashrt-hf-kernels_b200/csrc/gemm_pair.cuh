@@ -28,6 +28,8 @@
 // buffer.  For BN = 256 the accumulators overlap ([0,256) and [208,464), scales
 // at [464,512)): the epilogue of tile t drains the shared columns first and
 // releases them, so the mainloop of tile t+1 runs under the rest of the drain.
+// The weight-major grouped form places an item's accumulator by its width: even
+// tiles of a pair at [0, n), odd tiles at [448 - n, 448), scales at [448, 512).
 #pragma once
 
 struct PairMaps {
@@ -38,9 +40,12 @@ struct PairMaps {
 
 // One unit of grouped work: a window of expert-sorted token rows that one
 // expert's weights are applied to.  Built on the device by group_plan_kernel.
+// Weight-major form: a window longer than 256 rows is contracted by two MMAs per K block against the same
+// staged weights: rows [0, 256) and the rest (<= 64 rows), which is how an expert with a few rows more than
+// one full window costs one pass over its weights instead of two.
 struct GroupItem {
   int q_row0;      // first token row of the window (multiple of 64)
-  int n_tokens;    // window length, multiple of 32, <= 256 (the UMMA N of the tile)
+  int n_tokens;    // window length, multiple of 32, <= 320 (weight-major) 
   int lo, hi;      // token rows [lo, hi) of the window that belong to `expert`
   int expert;
   int pad[3];
@@ -71,16 +76,17 @@ template <int BN, int STAGES, bool GROUPED = false, bool TM = false>
 struct PairLayout {
 
   static constexpr int A_BYTES = 128 * 128;              // this CTA's 128 rows of P
-  static constexpr int B_BYTES = (BN / 2) * 128;         // this CTA's half of the Q tile
+  static constexpr int B_MAIN = (BN / 2) * 128;          // this CTA's half of the Q tile
+  // weight-major grouped form: one more 32-row box for this CTA's half of the rows beyond 256
+  static constexpr int B_BYTES = B_MAIN + ((GROUPED && !TM) ? 4096 : 0);
   // 128-row scale groups a Q tile can touch (a grouped window starts at any multiple of 64)
   static constexpr int SFQ_BLOCKS = (GROUPED && !TM) ? 3 : (BN <= 128 ? 1 : 2);
   static constexpr int SFP_BYTES = KT_PER_STAGE * SF_TILE;
   static constexpr int SFQ_BYTES = SFQ_BLOCKS * KT_PER_STAGE * SF_TILE;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFP_BYTES + SFQ_BYTES;
   // epilogue staging: 4 warps x 4 buffers of 32 rows x 64 bytes, written by TMA store
-  // store staging: buffers of 32 rows x 64 B per epilogue warp (8 warps stage stores; the 5-stage
-  // grouped form has room for one buffer each, the others for two)
-  static constexpr int SBUFS = (GROUPED && !TM && STAGES >= 5) ? 1 : 2;
+  // store staging: two buffers of 32 rows x 64 B per epilogue warp (8 warps stage stores)
+  static constexpr int SBUFS = 2;
   static constexpr int STAGING_BYTES = 8 * SBUFS * 2048;
   static constexpr int ITEM_CACHE = GROUPED ? 96 : 0;    // this pair's first work items, copied to smem
   static constexpr int TOTAL = STAGES * STAGE_BYTES + STAGING_BYTES + ITEM_CACHE * 32 + 1024 + 256;
@@ -89,13 +95,22 @@ struct PairLayout {
   static constexpr int ACC1 = (2 * BN + SF_COLS <= 512) ? BN : 512 - SF_COLS - BN;
   static constexpr int OVERLAP = BN - ACC1;              // 0 when disjoint
   static constexpr int SF_BASE = ACC1 + BN;
+  // weight-major grouped form: an item's accumulator is n_tokens columns wide; even tiles of a pair grow up
+  // from column 0, odd tiles down from ACC_COLS, and what two consecutive tiles share is drained first
+  static constexpr int ACC_COLS = SF_BASE;
   static_assert(SF_BASE + SF_COLS <= 512, "TMEM budget");
   static_assert(BN % 32 == 0 && OVERLAP >= 0, "tile shape");
 };
 
 // GROUPED: P = one expert's weights (3-D / 4-D tensor maps with the expert as the
-// outer coordinate), Q = a window of token rows; the output tile is written
-// transposed (out[token, weight_row]) and masked to the rows of that expert.
+// outer coordinate), Q = a window of up to 320 token rows (two MMAs per K block when it is
+// longer than 256: the staged weights serve both); the output tile is written
+// transposed (out[token, weight_row]) and masked to the rows of that expert.  The
+// epilogue reads the accumulator as 8 x 8 block fragments (tcgen05.ld 16x256b), which
+// stmatrix stores transposed into the staging buffer a TMA store (whole chunks) or
+// per-row 16-byte stores (the expert's first and last rows) write out.  Measured on the
+// Qwen3-30B-A3B layer: a stage is bound by what an SM takes in from L2 (~43 KB per
+// CTA and K stage at ~57 B/clk); prefetching the next tile's weights into L2 changed nothing.
 //
 // GROUPED + TM (token-major): P = two 128-row blocks of token rows (one per CTA; blocks are aligned to the
 // 128-row groups of the scale layout, so an expert's first and last block may be shared with its neighbours and
@@ -197,6 +212,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
       for (int t = pair_id; t < total_tiles && !*abort_flag; t += num_pairs, ++ti) {
         int pt, qt, q_row, q_blk, expert = 0;
         int nq = 0, nsf = 0;       // grouped: 32-row Q boxes per CTA, 128-row scale groups the window touches
+        int q_row2 = -1;           // grouped: this CTA's first row of the window's rows beyond 256 (-1: none)
         int tm_p_row = 0;
         if (TM) {
           const GroupItem item = ti < L::ITEM_CACHE ? item_cache[ti] : work->items[t / per_item];
@@ -210,11 +226,13 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
         } else if (GROUPED) {
           const GroupItem item = ti < L::ITEM_CACHE ? item_cache[ti] : work->items[t / p.p_tiles];
           pt = t % p.p_tiles;
-          q_row = item.q_row0 + static_cast<int>(rank) * (item.n_tokens >> 1);
+          const int main_n = min(item.n_tokens, 256), extra_n = item.n_tokens - main_n;
+          q_row = item.q_row0 + static_cast<int>(rank) * (main_n >> 1);
           q_blk = item.q_row0 >> 7;
           expert = item.expert;
-          nq = ((item.n_tokens >> 1) + 31) >> 5;
+          nq = ((main_n >> 1) + 31) >> 5;
           nsf = ((item.q_row0 + item.n_tokens - 1) >> 7) - q_blk + 1;
+          q_row2 = extra_n ? item.q_row0 + 256 + static_cast<int>(rank) * (extra_n >> 1) : -1;
         } else if (SLICED) {
           int col0, width;
           decode_unit(t, p, pt, qt, col0, width);
@@ -254,11 +272,13 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
           if (GROUPED) {
             // the token window is loaded at its size: 32-row boxes of Q and only the scale groups it touches
             if (leader)
-              ptx::mbar_expect_tx(&full[s], 2 * (L::A_BYTES + L::SFP_BYTES + nq * 4096 + nsf * KT_PER_STAGE * SF_TILE));
+              ptx::mbar_expect_tx(&full[s], 2 * (L::A_BYTES + L::SFP_BYTES + (nq + (q_row2 >= 0 ? 1 : 0)) * 4096 +
+                                                 nsf * KT_PER_STAGE * SF_TILE));
             ptx::tma_load_3d_pair(st, &maps.p, bar, ks * 128, p_row, expert);
             ptx::tma_load_4d_pair(st + L::A_BYTES + L::B_BYTES, &maps.sfp, bar, 0, ks * KT_PER_STAGE, p_blk, expert);
             for (int i = 0; i < nq; ++i)
               ptx::tma_load_2d_pair(st + L::A_BYTES + i * 4096, &maps.q, bar, ks * 128, q_row + 32 * i);
+            if (q_row2 >= 0) ptx::tma_load_2d_pair(st + L::A_BYTES + L::B_MAIN, &maps.q, bar, ks * 128, q_row2);
             for (int b = 0; b < nsf; ++b)
               ptx::tma_load_3d_pair(st + L::A_BYTES + L::B_BYTES + L::SFP_BYTES + b * KT_PER_STAGE * SF_TILE, &maps.sfq,
                                     bar, 0, ks * KT_PER_STAGE, q_blk + b);
@@ -316,14 +336,17 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
         }
         ptx::tc_fence_after();
         if (tr) FRT_TRACE(p, tl * 8 + 1);
-        const uint32_t d_tmem = tmem_base + (a ? L::ACC1 : 0);
-        uint32_t qoff, idesc = IDESC;
+        uint32_t d_tmem = tmem_base + (a ? L::ACC1 : 0);
+        uint32_t qoff, idesc = IDESC, idesc2 = 0;          // idesc2: the MMA over a grouped window's rows beyond 256
         if (TM) {
           qoff = (static_cast<uint32_t>((t % per_item) * BN) & 127u) >> 5;
         } else if (GROUPED) {
           const GroupItem item = tl < L::ITEM_CACHE ? item_cache[tl] : work->items[t / p.p_tiles];
           qoff = (static_cast<uint32_t>(item.q_row0) & 127u) >> 5;
-          idesc = ptx::idesc_nvf4(256, item.n_tokens);
+          const int main_n = min(item.n_tokens, 256);
+          idesc = ptx::idesc_nvf4(256, main_n);
+          if (item.n_tokens > 256) idesc2 = ptx::idesc_nvf4(256, item.n_tokens - 256);
+          d_tmem = tmem_base + (a ? L::ACC_COLS - item.n_tokens : 0);
         } else if (SLICED) {
           int pt, qt, col0, width;
           decode_unit(t, p, pt, qt, col0, width);
@@ -358,6 +381,9 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
               }
               ptx::tc_mma_nvf4_pair(d_tmem, a_lo + 2 * kt, b_lo + 2 * kt, op_hi, idesc, sfp_t, sfq_t + qoff,
                                     (ks | kt) != 0);
+              if (GROUPED && idesc2)     // same weights, the window's rows beyond 256: columns after the first 256
+                ptx::tc_mma_nvf4_pair(d_tmem + 256, a_lo + 2 * kt, b_lo + (L::B_MAIN >> 4) + 2 * kt, op_hi, idesc2, sfp_t,
+                                      sfq_t + qoff + 8, (ks | kt) != 0);
             }
           }
           ptx::tc_commit_pair(&empty[s], 3);
@@ -431,10 +457,6 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
         return a ? pos : CHUNKS - 1 - pos;
       };
       auto chunk_live = [&](int cchunk) {                   // warp-uniform: anything to write?
-        if (GROUPED) {
-          const int tok0 = item.q_row0 + cchunk * 32;
-          return cchunk * 32 < item.n_tokens && tok0 < item.hi && tok0 + 32 > item.lo;
-        }
         if (TM) return tm_any && qt * BN + cchunk * 32 < p.Q;
         return cchunk * 32 < width && qt * BN + col0 + cchunk * 32 < p.Q;
       };
@@ -487,6 +509,114 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
         if (tr) FRT_TRACE(p, tl * 8 + (first_half ? 5 : 7));
         continue;
       }
+      if constexpr (GROUPED) {
+        // The item's accumulator is n_tokens columns: [0, n) for even tiles of this pair, [ACC_COLS - n, ACC_COLS)
+        // for odd ones, so consecutive tiles share max(0, n + n_next - ACC_COLS) columns: the top chunks of an
+        // even tile, the bottom chunks of an odd one.  Chunks are drained from the shared end; the two groups of
+        // four warps take alternate drain positions, so the shared chunks are split between them, and a warp
+        // arrives on acc_free once its shared chunks are in registers (two register buffers: immediately after
+        // the prologue loads when it owns at most two of them).
+        const int nch = item.n_tokens >> 5;
+        int shared = 0;
+        if (t + num_pairs < total_tiles) {
+          const int n_next = (tl + 1 < L::ITEM_CACHE ? item_cache[tl + 1] : work->items[(t + num_pairs) / p.p_tiles]).n_tokens;
+          shared = max(0, (item.n_tokens + n_next - L::ACC_COLS) >> 5);
+        }
+        const int my_n = (nch - half + 1) >> 1;                       // drain positions half, half + 2, ...
+        const int my_shared = shared > half ? (shared - half + 1) >> 1 : 0;
+        const uint32_t gaddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                               (a ? L::ACC_COLS - item.n_tokens : 0);
+        auto chunk_at = [&](int j) { const int pos = half + 2 * j; return a ? pos : nch - 1 - pos; };
+        auto live_at = [&](int j) {                                   // warp-uniform: anything to write?
+          if (j >= my_n) return false;
+          const int tok0 = item.q_row0 + chunk_at(j) * 32;
+          return tok0 < item.hi && tok0 + 32 > item.lo;
+        };
+        const int n0 = pt * 256 + row_in_tile;                        // first output column of this warp
+        uint32_t r[2][32];
+        if (my_shared == 0) release();
+        // a chunk (this warp's 32 weight rows x 32 tokens) is loaded as 8 x 8 block fragments: registers
+        // [0,16) lanes 0..15, [16,32) lanes 16..31 of the warp's quarter
+        auto load_chunk = [&](int j, uint32_t (&dst)[32]) {
+          const uint32_t ad = gaddr + chunk_at(j) * 32;
+          ptx::tc_ld_16x256b_x4<0>(ad, dst);
+          ptx::tc_ld_16x256b_x4<16>(ad + (16u << 16), dst);
+        };
+        if (live_at(0)) load_chunk(0, r[0]);
+        if (live_at(1)) load_chunk(1, r[1]);
+        ptx::tc_wait_ld(r[0]);
+        ptx::tc_wait_ld(r[1]);
+        if (my_shared == 1 || my_shared == 2) release();
+        if (tr && first_half) FRT_TRACE(p, tl * 8 + 4);
+        constexpr int MAX_MINE = 5;                                   // a warp's share of an item's <= 10 chunks
+#pragma unroll
+        for (int j = 0; j < MAX_MINE; ++j) {
+          if (j < my_n) {
+            if (j >= 2) ptx::tc_wait_ld(r[j & 1]);
+            if (my_shared > 2 && j == my_shared - 1) release();
+            if (live_at(j)) {
+              const uint32_t (&v32)[32] = r[j & 1];
+              const int tok0 = item.q_row0 + chunk_at(j) * 32;
+              const uint32_t buf = stage_base + (nstore % WARP_BUFS) * 2048u;
+              if (nstore >= WARP_BUFS) {                     // the TMA store that last read this buffer is done
+                if (lane == 0) ptx::bulk_wait_group_read<WARP_BUFS - 1>();
+                __syncwarp();
+              }
+              // transpose through shared memory: [token][weight row], 64 bytes per token, 64-byte TMA swizzle.
+              // One stmatrix per 8 tokens: its four blocks are the four groups of 8 weight rows, stored
+              // transposed (thread 8m + i addresses token 8q + i, 16-byte piece m of the row).
+              const uint32_t piece = static_cast<uint32_t>(lane) >> 3;
+#pragma unroll
+              for (uint32_t q = 0; q < 4; ++q) {
+                const uint32_t token = 8u * q + (static_cast<uint32_t>(lane) & 7u);
+                auto pk = [&](int i) { return pack_bf16x2(__uint_as_float(v32[i]) * alpha, __uint_as_float(v32[i + 1]) * alpha); };
+                ptx::stmatrix_x4_trans(buf + token * 64u + ((piece ^ ((token >> 1) & 3u)) * 16u), pk(4 * q), pk(4 * q + 2),
+                                       pk(16 + 4 * q), pk(16 + 4 * q + 2));
+              }
+              if (tok0 >= item.lo && tok0 + 32 <= item.hi) {
+                // all 32 token rows belong to the expert: TMA writes (and clips) the box
+                ptx::fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) {
+                  if (!FRT_DBG(p, 1)) ptx::tma_store_2d(&maps.d, buf, n0, tok0);
+                  ptx::bulk_commit_group();
+                }
+                ++nstore;
+              } else {
+                // an edge of the expert's rows: each lane writes the 64 bytes of one token row, if the row is
+                // the expert's (rows are 16-byte aligned: the output map of the TMA path demands the same)
+                __syncwarp();
+                const int tok = tok0 + lane;
+                if (tok >= item.lo && tok < item.hi && !FRT_DBG(p, 1)) {
+                  __nv_bfloat16* dst = p.d + static_cast<int64_t>(tok) * p.ldd + n0;
+#pragma unroll
+                  for (uint32_t g = 0; g < 4; ++g) {
+                    uint4 o;
+                    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                                 : "=r"(o.x), "=r"(o.y), "=r"(o.z), "=r"(o.w)
+                                 : "r"(buf + lane * 64u + ((g ^ ((static_cast<uint32_t>(lane) >> 1) & 3u)) * 16u))
+                                 : "memory");
+                    const int col = n0 + 8 * static_cast<int>(g);
+                    if (col + 8 <= p.P) {
+                      *reinterpret_cast<uint4*>(dst + 8 * g) = o;
+                    } else {
+                      const uint32_t w[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+                      for (int e = 0; e < 8; ++e)
+                        if (col + e < p.P)
+                          reinterpret_cast<uint16_t*>(dst + 8 * g)[e] = static_cast<uint16_t>(w[e >> 1] >> (16 * (e & 1)));
+                    }
+                  }
+                }
+                __syncwarp();                                 // the buffer may be rewritten by the next chunk
+              }
+            }
+            if (live_at(j + 2)) load_chunk(j + 2, r[j & 1]);
+          }
+        }
+        if (tr) FRT_TRACE(p, tl * 8 + (first_half ? 5 : 7));
+        continue;
+      }
       uint32_t r[2][32];
       // every warp vouches that it is done with tile tl-1; the warps that own the shared columns
       // of this tile only after those columns are in their registers
@@ -509,39 +639,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
         if (live) {
         const uint32_t (&v32)[32] = r[j & 1];
         const uint32_t buf = stage_base + (nstore % WARP_BUFS) * 2048u;
-        if (GROUPED) {
-          const int tok0 = item.q_row0 + cchunk * 32;
-          const int n0 = pt * 256 + row_in_tile;            // first output column of this warp
-          if (tok0 >= item.lo && tok0 + 32 <= item.hi) {
-            // all 32 token rows belong to the expert: transpose through shared memory
-            // ([token][weight row], 64-byte TMA swizzle) and let TMA write (and clip) the box
-            if (nstore >= WARP_BUFS) {
-              if (lane == 0) ptx::bulk_wait_group_read<WARP_BUFS - 1>();
-              __syncwarp();
-            }
-            const uint32_t piece = static_cast<uint32_t>(lane) >> 3, within = (static_cast<uint32_t>(lane) & 7u) * 2u;
-#pragma unroll
-            for (int jj = 0; jj < 32; ++jj) {
-              const __nv_bfloat16 h = __float2bfloat16_rn(__uint_as_float(v32[jj]) * alpha);
-              const uint32_t addr = buf + jj * 64u + ((piece ^ ((static_cast<uint32_t>(jj) >> 1) & 3u)) * 16u) + within;
-              asm volatile("st.shared.b16 [%0], %1;" ::"r"(addr), "h"(*reinterpret_cast<const uint16_t*>(&h)) : "memory");
-            }
-            ptx::fence_proxy_async();
-            __syncwarp();
-            if (lane == 0) {
-              if (!FRT_DBG(p, 1)) ptx::tma_store_2d(&maps.d, buf, n0, tok0);
-              ptx::bulk_commit_group();
-            }
-            ++nstore;
-          } else if (prow < p.P) {
-#pragma unroll
-            for (int jj = 0; jj < 32; ++jj) {
-              const int tok = tok0 + jj;
-              if (tok >= item.lo && tok < item.hi && !FRT_DBG(p, 1))
-                p.d[static_cast<int64_t>(tok) * p.ldd + prow] = __float2bfloat16_rn(__uint_as_float(v32[jj]) * alpha);
-            }
-          }
-        } else {
+        {
           // this lane's 32 outputs of row prow -> 64 bytes of bf16 in a staging buffer laid out
           // as the 64-byte TMA swizzle expects (16-byte piece index ^ ((row >> 1) & 3))
           const int q_base = qt * BN + col0 + cchunk * 32;

@@ -180,6 +180,26 @@ __device__ __forceinline__ void tc_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[1
       : "r"(taddr)
       : "memory");
 }
+// 16 lanes x 8 columns x 4: registers 4q, 4q+1 = lane t/4, columns 8q + 2(t%4), +1; registers 4q+2, 4q+3 = lane
+// 8 + t/4, same columns (t = thread of the warp): pairs of registers are mma-style fragments of 8 x 8 blocks,
+// which is what stmatrix takes.  The lane field of taddr selects the 16 lanes (a multiple of 16 inside the
+// warp's quarter).  Fills r[OFF .. OFF + 16).
+template <int OFF>
+__device__ __forceinline__ void tc_ld_16x256b_x4(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.16x256b.x4.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[OFF + 0]), "=r"(r[OFF + 1]), "=r"(r[OFF + 2]), "=r"(r[OFF + 3]), "=r"(r[OFF + 4]), "=r"(r[OFF + 5]),
+        "=r"(r[OFF + 6]), "=r"(r[OFF + 7]), "=r"(r[OFF + 8]), "=r"(r[OFF + 9]), "=r"(r[OFF + 10]), "=r"(r[OFF + 11]),
+        "=r"(r[OFF + 12]), "=r"(r[OFF + 13]), "=r"(r[OFF + 14]), "=r"(r[OFF + 15])
+      : "r"(taddr)
+      : "memory");
+}
+// Four 8 x 8 b16 blocks, each stored transposed: thread 8m + i gives the shared-memory address of the 16 bytes
+// that receive column i of block m (register m of every thread holds that thread's fragment of block m).
+__device__ __forceinline__ void stmatrix_x4_trans(uint32_t smem_addr, uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3) {
+  asm volatile("stmatrix.sync.aligned.m8n8.x4.trans.shared.b16 [%0], {%1, %2, %3, %4};"
+               ::"r"(smem_addr), "r"(r0), "r"(r1), "r"(r2), "r"(r3) : "memory");
+}
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 // Same wait, tied to the destination registers of an earlier tcgen05.ld: the compiler may not
 // move arithmetic on those registers above the wait (the load fills them asynchronously).

@@ -155,7 +155,10 @@ def test_golden_fixture_from_reference_helpers(golden_dir):
 
 
 @pytest.mark.parametrize("sizes", [[5, 0, 300, 1, 31, 33, 64, 0, 257, 100], [1000], [0, 0, 17], [32, 32, 32, 32],
-                                   [255, 257, 256, 1, 1, 1, 511]])
+                                   [255, 257, 256, 1, 1, 1, 511],
+                                   # windows of 257..320 rows (one pass over the weights, two MMAs) at every start
+                                   # offset, next to windows just past 320 and short ones
+                                   [7, 300, 13, 320, 20, 289, 45, 321, 3, 260, 60, 600, 31, 288, 288, 288]])
 def test_offsets_signature_ragged(sizes):
     n, k = 264, 512
     experts = len(sizes)
