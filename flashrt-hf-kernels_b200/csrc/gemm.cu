@@ -43,10 +43,19 @@ long long* g_trace = nullptr;   // set by frt_debug_set_trace
 #define FRT_DBG(p, bit) (((p).dbg & (bit)) != 0)
 #define FRT_TRACING(p) ((p).trace != nullptr)
 #define FRT_TRACE(p, slot) ((p).trace[slot] = clock64())
+// wall-clock (globaltimer, ns) phase stamps of the small-M kernel: one 16-word record per CTA, slots handed out
+// by an atomic counter in word 0 of the trace buffer
+__device__ __forceinline__ long long frt_globaltimer() { long long v; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(v)); return v; }
+#define FRT_GT_DECL __shared__ long long gt_ts[12]
+#define FRT_GT_ZERO do { for (int i_ = 0; i_ < 12; ++i_) gt_ts[i_] = 0; } while (0)
+#define FRT_GT(p, slot) do { if ((p).trace) gt_ts[slot] = frt_globaltimer(); } while (0)
 #else
 #define FRT_DBG(p, bit) false
 #define FRT_TRACING(p) false
 #define FRT_TRACE(p, slot) ((void)0)
+#define FRT_GT_DECL
+#define FRT_GT_ZERO ((void)0)
+#define FRT_GT(p, slot) ((void)0)
 #endif
 
 constexpr int BM = 128;            // UMMA M, rows of P per tile
@@ -95,6 +104,9 @@ struct SmemLayout {
   static constexpr int SFQ_BYTES = SFQ_BLOCKS * KT_PER_STAGE * SF_TILE;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFP_BYTES + SFQ_BYTES;
   static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+  // split-K form: fp32 partials received from the cluster, [token slot][source rank][128 rows]
+  static constexpr int RECV_BYTES = (BN + 8) * BM * 4;
+  static constexpr int TOTAL_SPLITK = TOTAL + RECV_BYTES;
 };
 
 __device__ __forceinline__ void tile_coords(int t, const GemmParams& p, int& pt, int& qt) {
@@ -119,10 +131,14 @@ __device__ __forceinline__ void load_p_stage(void* dst, const CUtensorMap* map, 
 }
 
 // SPLITK (small token counts, SWAP form only): `p.splits` CTAs form a cluster on one tile of 128
-// weight rows; CTA r contracts its share of K, leaves its fp32 partial tile in its own shared
-// memory, and after a cluster barrier every CTA sums a slice of the columns over all ranks
-// through distributed shared memory, in rank order (deterministic), and writes it out.  This is
-// what lets a layer with few 128-row tiles pull weights through every SM.
+// weight rows; CTA r contracts its share of K and PUSHES its fp32 partials into the shared memory of
+// the CTA that owns the token column (token j belongs to rank j % splits): one asynchronous store through
+// distributed shared memory per value (st.async), which credits its bytes to the owner's mbarrier when it
+// lands.  The owner expects splits x 128 x 4 bytes per column it owns, sums the partials in rank order
+// (deterministic) and writes the column out; a CTA that owns no live token exits right after its pushes,
+// and nobody reads another CTA's memory, so no barrier holds the cluster together at the end.  (A pull
+// form - partials left in place, two cluster barriers around remote loads - took longer per launch.)
+// This is what lets a layer with few 128-row tiles pull weights through every SM.
 //
 // Small token counts (SWAP, BN <= 32): two CTAs fit an SM (4 stages of ~22 KB, 256 TMEM columns
 // each), and the kernel is launched as a programmatic dependent: its CTAs become resident beside
@@ -141,16 +157,16 @@ __host__ __device__ constexpr int tmem_cols() {
 // CTAs of the small-M (swapped) form that share an SM: as many as fit its shared memory (228 KB, 1 KB reserved
 // per CTA) and TMEM (512 columns), at most 4.  Several small CTAs per SM let the CTAs of the NEXT kernel of the
 // stream become resident, and prefetch their weights, while this kernel still runs.
-template <int BN, int STAGES, int ACC, bool SWAP>
+template <int BN, int STAGES, int ACC, bool SWAP, bool SPLITK = false>
 __host__ __device__ constexpr int ctas_per_sm() {
   if (!SWAP || BN > 64) return 1;
-  int n = (228 * 1024) / (SmemLayout<BN, STAGES>::TOTAL + 1024);
+  int n = (228 * 1024) / ((SPLITK ? SmemLayout<BN, STAGES>::TOTAL_SPLITK : SmemLayout<BN, STAGES>::TOTAL) + 1024);
   if (512 / tmem_cols<BN, ACC>() < n) n = 512 / tmem_cols<BN, ACC>();
   return n > 4 ? 4 : (n < 1 ? 1 : n);
 }
 
 template <int BN, int STAGES, int ACC, bool SWAP, bool SPLITK = false>
-__global__ void __launch_bounds__(192, ctas_per_sm<BN, STAGES, ACC, SWAP>())
+__global__ void __launch_bounds__(192, ctas_per_sm<BN, STAGES, ACC, SWAP, SPLITK>())
 nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
                   const GemmParams p) {
   using L = SmemLayout<BN, STAGES>;
@@ -171,8 +187,13 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
   uint64_t* acc_empty = acc_full + ACC;     // [ACC]    epilogue -> MMA
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + ACC);
   volatile uint32_t* abort_flag = tmem_slot + 1;
+  uint64_t* recv_bar = bars + 30;                                        // split-K: partials have arrived (last 16 bytes of the 256)
+  float* recv = reinterpret_cast<float*>(smem + STAGES * L::STAGE_BYTES + 256);   // split-K: [slot][rank][BM]
+  static_assert((2 * STAGES + 2 * ACC + 1) * 8 <= 240, "barrier area");
 
   pdl_launch_dependents();
+  FRT_GT_DECL;
+  if (threadIdx.x == 0) { FRT_GT_ZERO; FRT_GT(p, 0); }
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int total_tiles = p.p_tiles * p.q_tiles;
@@ -188,8 +209,15 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
   if (threadIdx.x == 0) {
     for (int i = 0; i < STAGES; ++i) { ptx::mbar_init(&full[i], 1); ptx::mbar_init(&empty[i], 1); }
     for (int i = 0; i < ACC; ++i) { ptx::mbar_init(&acc_full[i], 1); ptx::mbar_init(&acc_empty[i], 4); }
+    if (SPLITK) ptx::mbar_init(recv_bar, 1);
     *abort_flag = 0;
     ptx::fence_barrier_init();
+    if (SPLITK) {
+      // this rank owns token columns krank, krank + splits, ... of the tile: it expects every rank's 128-row
+      // partial of each (the single arrival of the phase is this one; the bytes come from the peers' stores)
+      const int live = min(BN, p.Q), owned = krank < live ? (live - krank + p.splits - 1) / p.splits : 0;
+      if (owned) ptx::mbar_expect_tx(recv_bar, static_cast<uint32_t>(owned * p.splits * BM * 4));
+    }
     ptx::prefetch_tensormap(&map_p);
     ptx::prefetch_tensormap(&map_q);
   }
@@ -200,6 +228,9 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
   ptx::tc_fence_before();
   __syncthreads();
   ptx::tc_fence_after();
+  // split-K: every CTA's receive barrier exists before anybody pushes: all threads arrive here (no
+  // waiting), the epilogue warps complete the cluster barrier just before their first push
+  if (SPLITK) ptx::cluster_arrive();
   const uint32_t tmem_base = *tmem_slot;
   // Everything above overlapped the previous kernel of the stream.  From here on global memory:
   // all warps wait for the previous grid, except the TMA thread, which first issues the loads
@@ -227,7 +258,9 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
                          kts * SF_TILE, &full[n_pre]);
         }
       }
+      FRT_GT(p, 1);
       pdl_wait();
+      FRT_GT(p, 2);
       for (int t = tile_first; t < total_tiles && !*abort_flag; t += tile_step) {
         int pt, qt;
         tile_coords(t, p, pt, qt);
@@ -304,6 +337,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
             atomicOr(&g_status_word, 8u); *abort_flag = 1; aborted = true; break;
           }
           ptx::tc_fence_after();
+          if (tl == 0 && ks == ks_begin) FRT_GT(p, 3);
           const uint32_t a_lo = op_lo0 + s * (L::STAGE_BYTES >> 4);
           const uint32_t b_lo = a_lo + (L::A_BYTES >> 4);
           const uint32_t sfp_lo = sf_lo0 + s * (L::STAGE_BYTES >> 4);
@@ -343,6 +377,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
         }
         if (aborted) break;
         ptx::tc_commit(&acc_full[a]);
+        FRT_GT(p, 4);
       }
     }
   } else {
@@ -359,6 +394,11 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
         break;
       }
       ptx::tc_fence_after();
+      if (warp == 2 && lane == 0) FRT_GT(p, 5);
+      if (SPLITK) {                                            // every rank's receive barrier is initialised
+        __syncwarp();
+        ptx::cluster_wait();
+      }
       const int prow = pt * BM + quarter * 32 + lane;          // index on the P axis
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + a * BN;
 #pragma unroll 1
@@ -407,11 +447,17 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
           }
         } else {
           if (SPLITK) {
-            // fp32 partial of this CTA's K share: part[token][weight row in tile], in the (idle) stage ring
-            float* part = reinterpret_cast<float*>(smem);
+            // fp32 partial of this CTA's K share: token jt goes to rank jt % splits, slot jt / splits, source krank
+            const uint32_t mine = ptx::smem_u32(recv) + static_cast<uint32_t>(quarter * 32 + lane) * 4u;
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (cchunk * 32 + j < BN) part[(cchunk * 32 + j) * BM + quarter * 32 + lane] = __uint_as_float(r[j]);
+            for (int j = 0; j < 32; ++j) {
+              const int jt = cchunk * 32 + j;
+              if (jt < BN && q_base + j < p.Q) {
+                const uint32_t owner = static_cast<uint32_t>(jt % p.splits), slot = static_cast<uint32_t>(jt / p.splits);
+                ptx::st_async_cluster_f32(ptx::mapa(mine + (slot * p.splits + krank) * (BM * 4u), owner), __uint_as_float(r[j]),
+                                          ptx::mapa(ptx::smem_u32(recv_bar), owner));
+              }
+            }
             continue;
           }
           // thread = output column prow (a weight row), columns of the tile = tokens
@@ -431,48 +477,63 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
       ptx::tc_fence_before();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&acc_empty[a]);
-    }
-  }
-
-  ptx::tc_fence_before();
-  __syncthreads();
-  if (SPLITK) {
-    ptx::cluster_arrive();
-    ptx::cluster_wait();                                  // every rank's partial tile is in its shared memory
-    if (warp >= 2 && tile_first < total_tiles && !*abort_flag) {
-      int pt, qt;
-      tile_coords(tile_first, p, pt, qt);
-      const int row = (warp & 3) * 32 + lane;
-      const int prow = pt * BM + row;
-      const uint32_t part0 = ptx::smem_u32(smem);
-      const float bias = (p.bias != nullptr && prow < p.P) ? __bfloat162float(p.bias[prow]) : 0.f;
-      // this rank's slice of the token columns; all remote loads of a column are issued
-      // before the first is used, and summed in rank order
-      uint32_t remote[8];
+      if (SPLITK) {
+        const int live = min(BN, p.Q - qt * BN), owners = min(live, p.splits);
+        if (warp == 2 && lane == 0) FRT_GT(p, 6);
+        if (krank < owners) {
+          // this rank owns token columns krank, krank + splits, ...: all ranks' partials, summed in rank order
+          if (!ptx::mbar_wait_bounded_acquire_cluster(recv_bar, 0, WAIT_LIMIT)) {
+            if (lane == 0) { atomicOr(&g_status_word, 16u); *abort_flag = 1; }
+            break;
+          }
+          if (warp == 2 && lane == 0) FRT_GT(p, 8);
+          const int row = quarter * 32 + lane;
+          const float bias = (p.bias != nullptr && prow < p.P) ? __bfloat162float(p.bias[prow]) : 0.f;
+          for (int jt = krank; jt < live; jt += p.splits) {
+            const float* src = recv + static_cast<size_t>((jt / p.splits) * p.splits) * BM + row;
+            float part[8];
 #pragma unroll
-      for (int r = 0; r < 8; ++r) remote[r] = ptx::mapa(part0 + static_cast<uint32_t>(row) * 4u, r < p.splits ? r : 0);
-      for (int j = krank; j < BN; j += p.splits) {
-        const int tok = qt * BN + j;
-        if (tok >= p.Q) break;
-        float part[8];
+            for (int r = 0; r < 8; ++r) part[r] = r < p.splits ? src[r * BM] : 0.f;
+            float acc = part[0];
 #pragma unroll
-        for (int r = 0; r < 8; ++r)
-          part[r] = r < p.splits ? ptx::ld_cluster_f32(remote[r] + static_cast<uint32_t>(j * BM) * 4u) : 0.f;
-        float acc = part[0];
-#pragma unroll
-        for (int r = 1; r < 8; ++r) acc += part[r];
-        if (prow < p.P) {
-          const int64_t off = static_cast<int64_t>(tok) * p.ldd + prow;
-          float v = acc * p.alpha + bias;
-          if (p.c != nullptr) v += p.beta * __bfloat162float(p.c[off]);
-          p.d[off] = __float2bfloat16_rn(v);
+            for (int r = 1; r < 8; ++r) acc += part[r];
+            if (prow < p.P) {
+              const int64_t off = static_cast<int64_t>(qt * BN + jt) * p.ldd + prow;
+              float v = acc * p.alpha + bias;
+              if (p.c != nullptr) v += p.beta * __bfloat162float(p.c[off]);
+              p.d[off] = __float2bfloat16_rn(v);
+            }
+          }
+          if (warp == 2 && lane == 0) FRT_GT(p, 9);
         }
       }
     }
-    ptx::cluster_arrive();
-    ptx::cluster_wait();                                  // nobody leaves while its partial may still be read
   }
+
+  if (SPLITK && warp < 2) {                       // completes the cluster barrier every thread arrived on at the start
+    __syncwarp();
+    ptx::cluster_wait();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0) FRT_GT(p, 7);
   if (warp == 1) ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+#ifdef FRT_DEBUG
+  if (p.trace) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const long long rec = atomicAdd(reinterpret_cast<unsigned long long*>(p.trace), 1ull);
+      if (rec < 4000) {
+        long long* o = p.trace + 16 + rec * 16;
+        unsigned smid; asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        o[0] = (static_cast<long long>(p.P) << 32) | static_cast<unsigned>(p.K);
+        o[1] = (static_cast<long long>(blockIdx.x) << 32) | (smid << 8) | static_cast<unsigned>(p.splits);
+        for (int i = 0; i < 10; ++i) o[2 + i] = gt_ts[i];
+        o[12] = frt_globaltimer();
+      }
+    }
+  }
+#endif
 }
 
 #include "gemm_pair.cuh"
@@ -662,7 +723,7 @@ int launch_gemm_splitk(const CUtensorMap& mp, const CUtensorMap& mq, GemmParams&
   int dev = 0;
   cudaGetDevice(&dev);
   if (!attr_set[dev & 63]) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL) != cudaSuccess)
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL_SPLITK) != cudaSuccess)
       return FRT_E_LAUNCH;
     attr_set[dev & 63] = true;
   }
@@ -671,7 +732,7 @@ int launch_gemm_splitk(const CUtensorMap& mp, const CUtensorMap& mq, GemmParams&
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(static_cast<unsigned>(p.p_tiles * p.splits));
   cfg.blockDim = dim3(192);
-  cfg.dynamicSmemBytes = L::TOTAL;
+  cfg.dynamicSmemBytes = L::TOTAL_SPLITK;
   cfg.stream = st;
   cudaLaunchAttribute attr[2] = {};
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -1039,11 +1100,11 @@ int run_gemm(const void* p_packed, const void* sfp, int P, const void* q_packed,
   const int depth = g_opt_smallm_stages;
   if (p.splits > 1) {
     switch (cfg) {
+      // (the receive buffer of the split-K form takes the place of one ring stage)
       case 11: return depth == 2 ? launch_gemm_splitk<16, 2>(mp, mq, p, st)
-                    : depth == 3 ? launch_gemm_splitk<16, 3>(mp, mq, p, st) : launch_gemm_splitk<16, 5>(mp, mq, p, st);
-      case 12: return depth == 2 ? launch_gemm_splitk<32, 2>(mp, mq, p, st)
-                    : depth == 3 ? launch_gemm_splitk<32, 3>(mp, mq, p, st) : launch_gemm_splitk<32, 4>(mp, mq, p, st);
-      default: return depth == 3 ? launch_gemm_splitk<64, 3>(mp, mq, p, st) : launch_gemm_splitk<64, 8>(mp, mq, p, st);
+                    : depth == 3 ? launch_gemm_splitk<16, 3>(mp, mq, p, st) : launch_gemm_splitk<16, 4>(mp, mq, p, st);
+      case 12: return depth == 2 ? launch_gemm_splitk<32, 2>(mp, mq, p, st) : launch_gemm_splitk<32, 3>(mp, mq, p, st);
+      default: return depth == 3 ? launch_gemm_splitk<64, 3>(mp, mq, p, st) : launch_gemm_splitk<64, 6>(mp, mq, p, st);
     }
   }
   switch (cfg) {

@@ -241,6 +241,33 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 
+// Split-K exchange: an asynchronous fp32 store into the shared memory of another CTA of the cluster that
+// credits its 4 bytes to an mbarrier of that CTA when it has landed (no fence, no separate arrival; the
+// issuing CTA may exit), and the wait the receiver uses.
+__device__ __forceinline__ void st_async_cluster_f32(uint32_t cluster_addr, float v, uint32_t cluster_bar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];"
+               ::"r"(cluster_addr), "r"(__float_as_uint(v)), "r"(cluster_bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_acquire_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 P, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, P;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_bounded_acquire_cluster(uint64_t* bar, uint32_t parity, long long limit_cycles) {
+  if (mbar_try_wait_acquire_cluster(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!mbar_try_wait_acquire_cluster(bar, parity)) {
+    if (clock64() - t0 > limit_cycles) return false;
+  }
+  return true;
+}
+
 // Tiled loads issued by either CTA of a pair; the completion bytes are
 // credited to the mbarrier at `bar_addr`, which may live in the pair's other CTA.
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const CUtensorMap* map, uint32_t bar_addr,
