@@ -105,7 +105,7 @@ struct SmemLayout {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFP_BYTES + SFQ_BYTES;
   static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
   // split-K form: fp32 partials received from the cluster, [token slot][source rank][128 rows]
-  static constexpr int RECV_BYTES = (BN + 8) * BM * 4;
+  static constexpr int RECV_BYTES = BN <= 16 ? (BN + 8) * BM * 4 : 0;   // (wider tiles reduce by remote loads)
   static constexpr int TOTAL_SPLITK = TOTAL + RECV_BYTES;
 };
 
@@ -133,11 +133,13 @@ __device__ __forceinline__ void load_p_stage(void* dst, const CUtensorMap* map, 
 // SPLITK (small token counts, SWAP form only): `p.splits` CTAs form a cluster on one tile of 128
 // weight rows; CTA r contracts its share of K and PUSHES its fp32 partials into the shared memory of
 // the CTA that owns the token column (token j belongs to rank j % splits): one asynchronous store through
-// distributed shared memory per value (st.async), which credits its bytes to the owner's mbarrier when it
-// lands.  The owner expects splits x 128 x 4 bytes per column it owns, sums the partials in rank order
+// distributed shared memory per value (st.async), which credits its bytes to the owner's mbarrier as it lands.  The owner expects splits x 128 x 4 bytes per column it owns, sums the partials in rank order
 // (deterministic) and writes the column out; a CTA that owns no live token exits right after its pushes,
-// and nobody reads another CTA's memory, so no barrier holds the cluster together at the end.  (A pull
-// form - partials left in place, two cluster barriers around remote loads - took longer per launch.)
+// and nobody reads another CTA's memory, so no barrier holds the cluster together at the end.  That is
+// the form for up to 16 token columns (-1.2 us per launch at one token against the pull form).  Wider
+// tiles keep the pull form: partials stay in place, and between two cluster barriers every rank reads its
+// columns from all ranks' shared memory (pushing 64 columns, by remote stores or by bulk copies from a
+// staging area, measured 3 us slower per launch).
 // This is what lets a layer with few 128-row tiles pull weights through every SM.
 //
 // Small token counts (SWAP, BN <= 32): two CTAs fit an SM (4 stages of ~22 KB, 256 TMEM columns
@@ -177,6 +179,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
   constexpr uint32_t TMEM_COLS = tmem_cols<BN, ACC>();
   static_assert(ACC_COLS + 2 * SF_COLS <= static_cast<int>(TMEM_COLS), "TMEM allocation");
   constexpr uint32_t IDESC = ptx::idesc_nvf4(BM, BN);
+  constexpr bool SPLITK_PUSH = SPLITK && BN <= 16;   // how split-K partials travel (see the comment above the kernel)
+  static_assert(!SPLITK || STAGES * L::STAGE_BYTES >= BN * BM * 4, "the ring holds a partial tile");
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -206,13 +210,14 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
   const int tile_first = SPLITK ? static_cast<int>(blockIdx.x) / p.splits : static_cast<int>(blockIdx.x);
   const int tile_step = SPLITK ? static_cast<int>(gridDim.x) / p.splits : static_cast<int>(gridDim.x);
 
+  int n_pre = 0;          // thread 0: leading stages whose weight half was requested before the wait
   if (threadIdx.x == 0) {
     for (int i = 0; i < STAGES; ++i) { ptx::mbar_init(&full[i], 1); ptx::mbar_init(&empty[i], 1); }
     for (int i = 0; i < ACC; ++i) { ptx::mbar_init(&acc_full[i], 1); ptx::mbar_init(&acc_empty[i], 4); }
-    if (SPLITK) ptx::mbar_init(recv_bar, 1);
+    if (SPLITK_PUSH) ptx::mbar_init(recv_bar, 1);
     *abort_flag = 0;
     ptx::fence_barrier_init();
-    if (SPLITK) {
+    if (SPLITK_PUSH) {
       // this rank owns token columns krank, krank + splits, ... of the tile: it expects every rank's 128-row
       // partial of each (the single arrival of the phase is this one; the bytes come from the peers' stores)
       const int live = min(BN, p.Q), owned = krank < live ? (live - krank + p.splits - 1) / p.splits : 0;
@@ -220,6 +225,27 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
     }
     ptx::prefetch_tensormap(&map_p);
     ptx::prefetch_tensormap(&map_q);
+    // Small token counts: the WEIGHT halves of the first stages are requested right here, before the TMEM
+    // allocation, the CTA barrier and the wait for the previous grid: weights are constants of the stream,
+    // and a CTA that became resident late (its predecessor's CTAs held the SM) has no other way to hide
+    // the first trip to HBM.  This thread is also the TMA producer below.
+    if (SWAP && tile_first < total_tiles) {
+      int pt, qt;
+      tile_coords(tile_first, p, pt, qt);
+      const int qblk0 = (qt * BN) >> 7;
+      int nblk = 0;
+      for (int b = 0; b < L::SFQ_BLOCKS; ++b) nblk += (qblk0 + b < p.sfq_row_blocks) ? 1 : 0;
+      for (int ks = ks_begin; ks < k_stages && n_pre < STAGES; ++ks, ++n_pre) {
+        uint8_t* st = smem + n_pre * L::STAGE_BYTES;
+        const int kts = min(KT_PER_STAGE, p.k_tiles - ks * KT_PER_STAGE);
+        ptx::mbar_expect_tx(&full[n_pre], L::A_BYTES + L::B_BYTES + kts * SF_TILE * (1 + nblk));
+        load_p_stage(st, &map_p, &full[n_pre], ks, pt, SWAP && p.p_interleaved);
+        ptx::bulk_load(st + L::A_BYTES + L::B_BYTES,
+                       p.sfp + (static_cast<int64_t>(pt) * p.sf_cols + ks * KT_PER_STAGE) * SF_TILE,
+                       kts * SF_TILE, &full[n_pre]);
+      }
+    }
+    FRT_GT(p, 1);
   }
   if (warp == 1) {
     ptx::tmem_alloc(tmem_slot, TMEM_COLS);
@@ -230,7 +256,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
   ptx::tc_fence_after();
   // split-K: every CTA's receive barrier exists before anybody pushes: all threads arrive here (no
   // waiting), the epilogue warps complete the cluster barrier just before their first push
-  if (SPLITK) ptx::cluster_arrive();
+  if (SPLITK_PUSH) ptx::cluster_arrive();
   const uint32_t tmem_base = *tmem_slot;
   // Everything above overlapped the previous kernel of the stream.  From here on global memory:
   // all warps wait for the previous grid, except the TMA thread, which first issues the loads
@@ -239,26 +265,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
 
   if (warp == 0) {
     // ===================== TMA producer =====================
-    if (ptx::elect_one()) {
+    if (lane == 0) {        // (thread 0: it issued the early weight loads above)
       int it = 0;
-      int n_pre = 0;          // leading stages whose weight half was loaded before the wait
-      if (SWAP && tile_first < total_tiles) {
-        int pt, qt;
-        tile_coords(tile_first, p, pt, qt);
-        const int qblk0 = (qt * BN) >> 7;
-        int nblk = 0;
-        for (int b = 0; b < L::SFQ_BLOCKS; ++b) nblk += (qblk0 + b < p.sfq_row_blocks) ? 1 : 0;
-        for (int ks = ks_begin; ks < k_stages && n_pre < STAGES; ++ks, ++n_pre) {
-          uint8_t* st = smem + n_pre * L::STAGE_BYTES;
-          const int kts = min(KT_PER_STAGE, p.k_tiles - ks * KT_PER_STAGE);
-          ptx::mbar_expect_tx(&full[n_pre], L::A_BYTES + L::B_BYTES + kts * SF_TILE * (1 + nblk));
-          load_p_stage(st, &map_p, &full[n_pre], ks, pt, SWAP && p.p_interleaved);
-          ptx::bulk_load(st + L::A_BYTES + L::B_BYTES,
-                         p.sfp + (static_cast<int64_t>(pt) * p.sf_cols + ks * KT_PER_STAGE) * SF_TILE,
-                         kts * SF_TILE, &full[n_pre]);
-        }
-      }
-      FRT_GT(p, 1);
       pdl_wait();
       FRT_GT(p, 2);
       for (int t = tile_first; t < total_tiles && !*abort_flag; t += tile_step) {
@@ -395,7 +403,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
       }
       ptx::tc_fence_after();
       if (warp == 2 && lane == 0) FRT_GT(p, 5);
-      if (SPLITK) {                                            // every rank's receive barrier is initialised
+      if (SPLITK_PUSH) {                                       // every rank's receive barrier is initialised
         __syncwarp();
         ptx::cluster_wait();
       }
@@ -446,16 +454,26 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
             }
           }
         } else {
-          if (SPLITK) {
-            // fp32 partial of this CTA's K share: token jt goes to rank jt % splits, slot jt / splits, source krank
-            const uint32_t mine = ptx::smem_u32(recv) + static_cast<uint32_t>(quarter * 32 + lane) * 4u;
+          if (SPLITK && !SPLITK_PUSH) {
+            // fp32 partial of this CTA's K share: part[token][weight row in tile], in the (idle) stage ring
+            float* part = reinterpret_cast<float*>(smem);
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (cchunk * 32 + j < BN) part[(cchunk * 32 + j) * BM + quarter * 32 + lane] = __uint_as_float(r[j]);
+            continue;
+          }
+          if (SPLITK_PUSH) {
+            // fp32 partial of this CTA's K share: token jt goes to rank jt % splits, where it is slot jt / splits
+            // of source krank: one asynchronous remote store per value
+            const uint32_t row4 = static_cast<uint32_t>(quarter * 32 + lane) * 4u;
+            const uint32_t slots = static_cast<uint32_t>((BN + p.splits - 1) / p.splits);
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               const int jt = cchunk * 32 + j;
               if (jt < BN && q_base + j < p.Q) {
                 const uint32_t owner = static_cast<uint32_t>(jt % p.splits), slot = static_cast<uint32_t>(jt / p.splits);
-                ptx::st_async_cluster_f32(ptx::mapa(mine + (slot * p.splits + krank) * (BM * 4u), owner), __uint_as_float(r[j]),
-                                          ptx::mapa(ptx::smem_u32(recv_bar), owner));
+                ptx::st_async_cluster_f32(ptx::mapa(ptx::smem_u32(recv) + row4 + (krank * slots + slot) * (BM * 4u), owner),
+                                          __uint_as_float(r[j]), ptx::mapa(ptx::smem_u32(recv_bar), owner));
               }
             }
             continue;
@@ -477,8 +495,9 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
       ptx::tc_fence_before();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&acc_empty[a]);
-      if (SPLITK) {
+      if (SPLITK_PUSH) {
         const int live = min(BN, p.Q - qt * BN), owners = min(live, p.splits);
+        const int slots = (BN + p.splits - 1) / p.splits;
         if (warp == 2 && lane == 0) FRT_GT(p, 6);
         if (krank < owners) {
           // this rank owns token columns krank, krank + splits, ...: all ranks' partials, summed in rank order
@@ -490,10 +509,10 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
           const int row = quarter * 32 + lane;
           const float bias = (p.bias != nullptr && prow < p.P) ? __bfloat162float(p.bias[prow]) : 0.f;
           for (int jt = krank; jt < live; jt += p.splits) {
-            const float* src = recv + static_cast<size_t>((jt / p.splits) * p.splits) * BM + row;
+            const float* src = recv + static_cast<size_t>(jt / p.splits) * BM + row;     // [source rank][slot][row]
             float part[8];
 #pragma unroll
-            for (int r = 0; r < 8; ++r) part[r] = r < p.splits ? src[r * BM] : 0.f;
+            for (int r = 0; r < 8; ++r) part[r] = r < p.splits ? src[static_cast<size_t>(r * slots) * BM] : 0.f;
             float acc = part[0];
 #pragma unroll
             for (int r = 1; r < 8; ++r) acc += part[r];
@@ -510,13 +529,51 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
     }
   }
 
-  if (SPLITK && warp < 2) {                       // completes the cluster barrier every thread arrived on at the start
+  if (SPLITK_PUSH && warp < 2) {                  // completes the cluster barrier every thread arrived on at the start
     __syncwarp();
     ptx::cluster_wait();
   }
   ptx::tc_fence_before();
   __syncthreads();
   if (threadIdx.x == 0) FRT_GT(p, 7);
+  if (SPLITK && !SPLITK_PUSH) {
+    // more than 16 token columns: partials stay in this CTA's (idle) stage ring, and after a cluster barrier
+    // every rank sums its token columns over all ranks through distributed shared memory, in rank order
+    ptx::cluster_arrive();
+    ptx::cluster_wait();                                  // every rank's partial tile is in its shared memory
+    if (warp >= 2 && tile_first < total_tiles && !*abort_flag) {
+      int pt, qt;
+      tile_coords(tile_first, p, pt, qt);
+      const int row = (warp & 3) * 32 + lane;
+      const int prow = pt * BM + row;
+      const uint32_t part0 = ptx::smem_u32(smem);
+      const float bias = (p.bias != nullptr && prow < p.P) ? __bfloat162float(p.bias[prow]) : 0.f;
+      // this rank's slice of the token columns; all remote loads of a column are issued
+      // before the first is used, and summed in rank order
+      uint32_t remote[8];
+#pragma unroll
+      for (int r = 0; r < 8; ++r) remote[r] = ptx::mapa(part0 + static_cast<uint32_t>(row) * 4u, r < p.splits ? r : 0);
+      for (int j = krank; j < BN; j += p.splits) {
+        const int tok = qt * BN + j;
+        if (tok >= p.Q) break;
+        float part[8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+          part[r] = r < p.splits ? ptx::ld_cluster_f32(remote[r] + static_cast<uint32_t>(j * BM) * 4u) : 0.f;
+        float acc = part[0];
+#pragma unroll
+        for (int r = 1; r < 8; ++r) acc += part[r];
+        if (prow < p.P) {
+          const int64_t off = static_cast<int64_t>(tok) * p.ldd + prow;
+          float v = acc * p.alpha + bias;
+          if (p.c != nullptr) v += p.beta * __bfloat162float(p.c[off]);
+          p.d[off] = __float2bfloat16_rn(v);
+        }
+      }
+    }
+    ptx::cluster_arrive();
+    ptx::cluster_wait();                                  // nobody leaves while its partial may still be read
+  }
   if (warp == 1) ptx::tmem_dealloc(tmem_base, TMEM_COLS);
 #ifdef FRT_DEBUG
   if (p.trace) {
@@ -1100,11 +1157,12 @@ int run_gemm(const void* p_packed, const void* sfp, int P, const void* q_packed,
   const int depth = g_opt_smallm_stages;
   if (p.splits > 1) {
     switch (cfg) {
-      // (the receive buffer of the split-K form takes the place of one ring stage)
+      // (up to 16 token columns: the receive buffer of the split-K form takes the place of one ring stage)
       case 11: return depth == 2 ? launch_gemm_splitk<16, 2>(mp, mq, p, st)
                     : depth == 3 ? launch_gemm_splitk<16, 3>(mp, mq, p, st) : launch_gemm_splitk<16, 4>(mp, mq, p, st);
-      case 12: return depth == 2 ? launch_gemm_splitk<32, 2>(mp, mq, p, st) : launch_gemm_splitk<32, 3>(mp, mq, p, st);
-      default: return depth == 3 ? launch_gemm_splitk<64, 3>(mp, mq, p, st) : launch_gemm_splitk<64, 6>(mp, mq, p, st);
+      case 12: return depth == 2 ? launch_gemm_splitk<32, 2>(mp, mq, p, st)
+                    : depth == 3 ? launch_gemm_splitk<32, 3>(mp, mq, p, st) : launch_gemm_splitk<32, 4>(mp, mq, p, st);
+      default: return depth == 3 ? launch_gemm_splitk<64, 3>(mp, mq, p, st) : launch_gemm_splitk<64, 8>(mp, mq, p, st);
     }
   }
   switch (cfg) {
