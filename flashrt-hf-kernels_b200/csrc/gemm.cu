@@ -83,14 +83,6 @@ struct GemmParams {
   int splits;               // split-K cluster size (small-M form), 1 otherwise
   long long wait_limit;     // SM clocks a wait on an mbarrier may take before the CTA gives up
   int p_interleaved;        // P is stored in the interleaved GEMV layout [rows/8][K/64][8][32 B] (4-D tensor map)
-  // fused producer (small-M form, FUSED): Q = NVFP4 of RMSNorm(residual + x) * weight, computed in the kernel
-  const uint4* nx;          // bf16 [Q, K]
-  const uint4* nres_in;     // bf16 [Q, K] or null
-  uint4* nres_out;          // bf16 [Q, K]: residual + x, written by CTA 0 (never aliases nres_in: every CTA reads that)
-  const uint4* nweight;     // bf16 [K] or null
-  float neps, ndim_f;
-  unsigned nflags;          // FRT_PRODUCER_* (ONE_PLUS_W, ROUND_BF16, RNE_E2M1, NORM_FROM_BF16_RESIDUAL)
-  int n_nb, n_wpr;          // 16-element blocks per row; warps per row of the stand-alone producer (its sum order)
 #ifdef FRT_DEBUG
   int dbg;                  // experiment switches
   long long* trace;         // clock64 timeline of pair 0, 8 slots per tile
@@ -175,7 +167,7 @@ __host__ __device__ constexpr int ctas_per_sm() {
   return n > 4 ? 4 : (n < 1 ? 1 : n);
 }
 
-template <int BN, int STAGES, int ACC, bool SWAP, bool SPLITK = false, bool FUSED = false>
+template <int BN, int STAGES, int ACC, bool SWAP, bool SPLITK = false>
 __global__ void __launch_bounds__(192, ctas_per_sm<BN, STAGES, ACC, SWAP, SPLITK>())
 nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
                   const GemmParams p) {
@@ -188,8 +180,6 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
   static_assert(ACC_COLS + 2 * SF_COLS <= static_cast<int>(TMEM_COLS), "TMEM allocation");
   constexpr uint32_t IDESC = ptx::idesc_nvf4(BM, BN);
   constexpr bool SPLITK_PUSH = SPLITK && BN <= 16;   // how split-K partials travel (see the comment above the kernel)
-  static_assert(!FUSED || (SWAP && BN == 16), "the fused producer feeds the 16-token form");
-  __shared__ float norm_ws[32];                      // FUSED: warp totals of a row's sum of squares
   static_assert(!SPLITK || STAGES * L::STAGE_BYTES >= BN * BM * 4, "the ring holds a partial tile");
 
   extern __shared__ uint8_t smem_raw[];
@@ -222,8 +212,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
 
   int n_pre = 0;          // thread 0: leading stages whose weight half was requested before the wait
   if (threadIdx.x == 0) {
-    // FUSED: a stage is full when the weights have landed AND the warp that owns its activation blocks has written them
-    for (int i = 0; i < STAGES; ++i) { ptx::mbar_init(&full[i], FUSED ? 2 : 1); ptx::mbar_init(&empty[i], 1); }
+    for (int i = 0; i < STAGES; ++i) { ptx::mbar_init(&full[i], 1); ptx::mbar_init(&empty[i], 1); }
     for (int i = 0; i < ACC; ++i) { ptx::mbar_init(&acc_full[i], 1); ptx::mbar_init(&acc_empty[i], 4); }
     if (SPLITK_PUSH) ptx::mbar_init(recv_bar, 1);
     *abort_flag = 0;
@@ -249,8 +238,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
       for (int ks = ks_begin; ks < k_stages && n_pre < STAGES; ++ks, ++n_pre) {
         uint8_t* st = smem + n_pre * L::STAGE_BYTES;
         const int kts = min(KT_PER_STAGE, p.k_tiles - ks * KT_PER_STAGE);
-        ptx::mbar_expect_tx(&full[n_pre], FUSED ? L::A_BYTES + kts * SF_TILE
-                                                 : L::A_BYTES + L::B_BYTES + kts * SF_TILE * (1 + nblk));
+        ptx::mbar_expect_tx(&full[n_pre], L::A_BYTES + L::B_BYTES + kts * SF_TILE * (1 + nblk));
         load_p_stage(st, &map_p, &full[n_pre], ks, pt, SWAP && p.p_interleaved);
         ptx::bulk_load(st + L::A_BYTES + L::B_BYTES,
                        p.sfp + (static_cast<int64_t>(pt) * p.sf_cols + ks * KT_PER_STAGE) * SF_TILE,
@@ -297,14 +285,13 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
             if (!ptx::mbar_wait_bounded(&empty[s], ph ^ 1, WAIT_LIMIT)) {
               atomicOr(&g_status_word, 1u); *abort_flag = 1; break;
             }
-            const uint32_t bytes = FUSED ? L::A_BYTES + kts * SF_TILE : L::A_BYTES + L::B_BYTES + kts * SF_TILE * (1 + nblk);
+            const uint32_t bytes = L::A_BYTES + L::B_BYTES + kts * SF_TILE * (1 + nblk);
             ptx::mbar_expect_tx(&full[s], bytes);
             load_p_stage(st, &map_p, &full[s], ks, pt, SWAP && p.p_interleaved);
             ptx::bulk_load(st + L::A_BYTES + L::B_BYTES,
                            p.sfp + (static_cast<int64_t>(pt) * p.sf_cols + ks * KT_PER_STAGE) * SF_TILE,
                            kts * SF_TILE, &full[s]);
           }
-          if (FUSED) continue;            // the activation half of the stage is written by the epilogue warps
           ptx::tma_load_2d(st + L::A_BYTES, &map_q, &full[s], ks * 128, q0);
           for (int b = 0; b < nblk; ++b)
             ptx::bulk_load(st + L::A_BYTES + L::B_BYTES + L::SFP_BYTES + b * KT_PER_STAGE * SF_TILE,
@@ -404,168 +391,6 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_consta
   } else {
     // ===================== epilogue (warps 2..5) =====================
     const int quarter = warp & 3;      // TMEM lanes [32*quarter, +32)
-    if constexpr (FUSED) {
-      // ---- fused producer: Q = NVFP4(RMSNorm(residual + x) * weight) for up to 4 token rows --------------
-      // Every CTA redoes the rows' norm (a row is 2 x K bytes, L2-resident after the first CTA) with the
-      // arithmetic AND the summation order of norm_quant_kernel, so the bytes are the ones that kernel would
-      // have stored: a virtual thread per 16-element block, n_wpr virtual warps per row, the row total added
-      // in virtual-warp order.  The four epilogue warps carry the virtual warps: real warp e the virtual
-      // warps [e * vpw, (e + 1) * vpw).  The packed blocks and scale bytes stay in registers, and the warp that
-      // owns a K stage's 16 blocks writes them into the stage's activation area (the layouts TMA would have
-      // produced: 128-byte swizzle rows, 512-byte scale tiles) each time the ring slot is free.
-      const int e = warp - 2;
-      const int et = e * 32 + lane;
-      const int nb = p.n_nb, wpr = p.n_wpr, vpw = wpr >= 4 ? wpr / 4 : 1;
-      constexpr int ZERO16 = (L::B_BYTES + L::SFQ_BYTES) / 16;
-      for (int i = et; i < STAGES * ZERO16; i += 128) {
-        uint8_t* base = smem + (i / ZERO16) * L::STAGE_BYTES + L::A_BYTES;
-        const int o = i % ZERO16;
-        uint4* dst = o < L::B_BYTES / 16 ? reinterpret_cast<uint4*>(base) + o
-                                         : reinterpret_cast<uint4*>(base + L::B_BYTES + L::SFP_BYTES) + (o - L::B_BYTES / 16);
-        *dst = make_uint4(0, 0, 0, 0);
-      }
-      uint2 pk[4][2];
-      uint32_t sfv[4][2];
-#pragma unroll
-      for (int m = 0; m < 4; ++m) { pk[m][0] = pk[m][1] = make_uint2(0, 0); sfv[m][0] = sfv[m][1] = 0; }
-      const bool has_res = p.nres_in != nullptr;
-      uint4 raw[2][2][4];                 // [row parity][virtual thread][x0, x1, r0, r1]
-      auto load_row = [&](int m, uint4 (&dst)[2][4]) {
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          const int vw = e * vpw + i, s = vw * 32 + lane;
-          const bool ok = i < vpw && vw < wpr && s < nb;
-          dst[i][0] = dst[i][1] = dst[i][2] = dst[i][3] = make_uint4(0, 0, 0, 0);
-          if (ok) {
-            const int64_t idx = static_cast<int64_t>(m) * nb + s;
-            dst[i][0] = __ldg(p.nx + 2 * idx);
-            dst[i][1] = __ldg(p.nx + 2 * idx + 1);
-            if (has_res) {
-              dst[i][2] = __ldg(p.nres_in + 2 * idx);
-              dst[i][3] = __ldg(p.nres_in + 2 * idx + 1);
-            }
-          }
-        }
-      };
-      load_row(0, raw[0]);
-#pragma unroll
-      for (int m = 0; m < 4; ++m) {
-        if (m < p.Q) {
-          if (m + 1 < p.Q) load_row(m + 1, raw[(m + 1) & 1]);
-          float v[2][16];
-#pragma unroll
-          for (int i = 0; i < 2; ++i) {
-            const int vw = e * vpw + i, s = vw * 32 + lane;
-            const bool ok = i < vpw && vw < wpr && s < nb;
-            unpack_bf16x8(raw[m & 1][i][0], v[i]);
-            unpack_bf16x8(raw[m & 1][i][1], v[i] + 8);
-            float part = 0.f;
-            if (has_res) {
-              float r[16];
-              unpack_bf16x8(raw[m & 1][i][2], r);
-              unpack_bf16x8(raw[m & 1][i][3], r + 8);
-#pragma unroll
-              for (int j = 0; j < 16; ++j) v[i][j] = __fadd_rn(r[j], v[i][j]);
-              uint4 o0, o1;
-              o0.x = pack_bf16x2(v[i][0], v[i][1]);   o0.y = pack_bf16x2(v[i][2], v[i][3]);
-              o0.z = pack_bf16x2(v[i][4], v[i][5]);   o0.w = pack_bf16x2(v[i][6], v[i][7]);
-              o1.x = pack_bf16x2(v[i][8], v[i][9]);   o1.y = pack_bf16x2(v[i][10], v[i][11]);
-              o1.z = pack_bf16x2(v[i][12], v[i][13]); o1.w = pack_bf16x2(v[i][14], v[i][15]);
-              if (ok && blockIdx.x == 0) {
-                const int64_t idx = static_cast<int64_t>(m) * nb + s;
-                p.nres_out[2 * idx] = o0;
-                p.nres_out[2 * idx + 1] = o1;
-              }
-#pragma unroll
-              for (int j = 0; j < 16; ++j) part = __fadd_rn(part, __fmul_rn(v[i][j], v[i][j]));
-              if (p.nflags & FRT_PRODUCER_NORM_FROM_BF16_RESIDUAL) {
-                unpack_bf16x8(o0, v[i]);
-                unpack_bf16x8(o1, v[i] + 8);
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 16; ++j) part = __fadd_rn(part, __fmul_rn(v[i][j], v[i][j]));
-            }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) part = __fadd_rn(part, __shfl_xor_sync(0xffffffffu, part, o));
-            if (lane == 0 && i < vpw && vw < wpr) norm_ws[vw] = part;
-          }
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-          float ssq = norm_ws[0];
-          for (int w = 1; w < wpr; ++w) ssq = __fadd_rn(ssq, norm_ws[w]);
-          asm volatile("bar.sync 1, 128;" ::: "memory");       // the next row overwrites the warp totals
-          const float rstd = __frsqrt_rn(__fadd_rn(__fdiv_rn(ssq, p.ndim_f), p.neps));
-#pragma unroll
-          for (int i = 0; i < 2; ++i) {
-            const int vw = e * vpw + i, s = vw * 32 + lane;
-            const bool ok = i < vpw && vw < wpr && s < nb;
-            if (ok) {
-              if (p.nweight != nullptr) {
-                float gw[16];
-                unpack_bf16x8(__ldg(p.nweight + 2 * s), gw);
-                unpack_bf16x8(__ldg(p.nweight + 2 * s + 1), gw + 8);
-                if (p.nflags & FRT_PRODUCER_ONE_PLUS_W) {
-#pragma unroll
-                  for (int j = 0; j < 16; ++j) gw[j] = __fadd_rn(1.f, gw[j]);
-                }
-#pragma unroll
-                for (int j = 0; j < 16; ++j) v[i][j] = __fmul_rn(__fmul_rn(v[i][j], rstd), gw[j]);
-              } else {
-#pragma unroll
-                for (int j = 0; j < 16; ++j) v[i][j] = __fmul_rn(v[i][j], rstd);
-              }
-              if (p.nflags & FRT_PRODUCER_ROUND_BF16) {
-#pragma unroll
-                for (int j = 0; j < 16; j += 2) {
-                  const uint32_t w2 = pack_bf16x2(v[i][j], v[i][j + 1]);
-                  v[i][j] = __uint_as_float(w2 << 16);
-                  v[i][j + 1] = __uint_as_float(w2 & 0xffff0000u);
-                }
-              }
-              uint8_t sfb;
-              if (p.nflags & FRT_PRODUCER_RNE_E2M1) pk[m][i] = quantize_block16<kEncRne>(v[i], sfb, inv_scale_table());
-              else pk[m][i] = quantize_block16<kEncHw>(v[i], sfb, inv_scale_table());
-              sfv[m][i] = sfb;
-            }
-          }
-        }
-      }
-      // (the zeroed areas are complete in every warp's view: the row barriers above came after the zero loop)
-      int it = 0;
-      bool stop = false;
-      for (int t = tile_first; t < total_tiles && !stop && !*abort_flag; t += tile_step) {
-        for (int ks = ks_begin; ks < k_stages; ++ks, ++it) {
-          // Every warp walks every stage and waits for its ring slot, like the TMA thread: a parity wait is only
-          // meaningful to a waiter that has seen the previous phase complete (a warp that jumped straight to its
-          // own later stages would take "slot free" from a barrier still two phases behind).
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
-          if (!ptx::mbar_wait_bounded(&empty[s], ph ^ 1, WAIT_LIMIT)) {
-            if (lane == 0) { atomicOr(&g_status_word, 1u); *abort_flag = 1; }
-            stop = true;
-            break;
-          }
-          const int vw = ks >> 1;                         // the virtual warp that holds blocks 16 ks .. 16 ks + 15
-          if (vw / vpw != e || vw >= wpr) continue;
-          const int i = vw % vpw;
-          if ((lane >> 4) == (ks & 1)) {
-            const int j = lane & 15;                      // block inside the stage
-            uint8_t* q = smem + s * L::STAGE_BYTES + L::A_BYTES;
-            uint8_t* sfq = q + L::B_BYTES + L::SFP_BYTES + (j >> 2) * SF_TILE + (j & 3);
-#pragma unroll
-            for (int m = 0; m < 4; ++m) {
-              if (m < p.Q) {
-                *reinterpret_cast<uint2*>(q + m * 128 + (((j >> 1) ^ (m & 7)) << 4) + ((j & 1) << 3)) = i ? pk[m][1] : pk[m][0];
-                sfq[m * 16] = static_cast<uint8_t>(i ? sfv[m][1] : sfv[m][0]);
-              }
-            }
-          }
-          ptx::fence_proxy_async();
-          __syncwarp();
-          if (lane == 0) ptx::mbar_arrive(&full[s]);
-        }
-      }
-    }
     int tl = 0;
     for (int t = tile_first; t < total_tiles && !*abort_flag; t += tile_step, ++tl) {
       int pt, qt;
@@ -860,10 +685,10 @@ DeviceInfo device_info() {
   return cache[dev];
 }
 
-template <int BN, int STAGES, int ACC, bool SWAP, bool FUSED = false>
+template <int BN, int STAGES, int ACC, bool SWAP>
 int launch_gemm(const CUtensorMap& mp, const CUtensorMap& mq, GemmParams& p, int sms, cudaStream_t st) {
   using L = SmemLayout<BN, STAGES>;
-  auto kern = nvfp4_gemm_kernel<BN, STAGES, ACC, SWAP, false, FUSED>;
+  auto kern = nvfp4_gemm_kernel<BN, STAGES, ACC, SWAP>;
   static bool attr_set[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -947,10 +772,10 @@ int launch_gemm_swiglu(const void* p_packed, const void* q_packed, GemmParams& p
   return launch_result();
 }
 
-template <int BN, int STAGES, bool FUSED = false>
+template <int BN, int STAGES>
 int launch_gemm_splitk(const CUtensorMap& mp, const CUtensorMap& mq, GemmParams& p, cudaStream_t st) {
   using L = SmemLayout<BN, STAGES>;
-  auto kern = nvfp4_gemm_kernel<BN, STAGES, 1, true, true, FUSED>;
+  auto kern = nvfp4_gemm_kernel<BN, STAGES, 1, true, true>;
   static bool attr_set[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -1357,48 +1182,6 @@ int run_gemm(const void* p_packed, const void* sfp, int P, const void* q_packed,
   return FRT_E_UNSUPPORTED;
 }
 
-// Fused producer + small-M GEMM: d[M, N] = NVFP4(RMSNorm(residual + x) * weight) @ W^T, M <= 4 token rows.
-int run_gemm_fused(const void* residual_in, void* residual_out, const void* x, const void* weight, float eps,
-                   unsigned flags, const void* w_packed, const void* sfw, const void* bias, void* d, int M, int N, int K,
-                   float alpha, cudaStream_t st) {
-  const DeviceInfo di = device_info();
-  if (!di.ok || di.cc_major != 10) return FRT_E_DEVICE;
-  GemmParams p{};
-  p.P = N; p.Q = M; p.K = K;
-  p.k_tiles = (K + 63) / 64;
-  p.sf_cols = p.k_tiles;
-  p.sfp = static_cast<const uint8_t*>(sfw);
-  p.sfq = nullptr;
-  p.sfq_row_blocks = 1;
-  p.d = static_cast<__nv_bfloat16*>(d);
-  p.bias = static_cast<const __nv_bfloat16*>(bias);
-  p.ldd = N;
-  p.alpha = alpha; p.beta = 0.f;
-  p.group_m = 16;
-  p.wait_limit = wait_limit_clocks();
-  p.nx = static_cast<const uint4*>(x);
-  p.nres_in = static_cast<const uint4*>(residual_in);
-  p.nres_out = static_cast<uint4*>(residual_out);
-  p.nweight = static_cast<const uint4*>(weight);
-  p.neps = eps; p.ndim_f = static_cast<float>(K);
-  p.nflags = flags;
-  p.n_nb = K / 16;
-  int tpr = 32;
-  while (tpr < p.n_nb) tpr *= 2;
-  p.n_wpr = tpr / 32;
-#ifdef FRT_DEBUG
-  p.dbg = g_opt_gemm_debug & 0xff;
-  p.trace = g_trace;
-#endif
-  int cfg = 0, splits = 1;
-  select_gemm_config(N, M, K, true, 11, di.sms, cfg, splits);
-  CUtensorMap mp;
-  if (int rc = make_operand_map(&mp, w_packed, N, K, BM)) return rc;
-  p.splits = splits;
-  if (splits > 1) return launch_gemm_splitk<16, 4, true>(mp, mp, p, st);
-  return launch_gemm<16, 5, 2, true, true>(mp, mp, p, di.sms, st);
-}
-
 // [N, K/2] row-major -> [N/8][K/64][8][32 B]: one thread moves 16 bytes.
 __global__ void repack_interleaved_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, int n, int kt) {
   const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;     // 16-byte piece of dst
@@ -1434,24 +1217,6 @@ int frt_nvfp4_gemm_bf16(const void* a, const void* sfa, const void* b, const voi
   const bool swap = cfg ? cfg >= 11 : (M <= 64);
   if (swap) return run_gemm(b, sfb, N, a, sfa, M, K, bias, cc, d, N, alpha, beta, true, cfg, as_stream(stream));
   return run_gemm(a, sfa, M, b, sfb, N, K, bias, cc, d, N, alpha, beta, false, cfg, as_stream(stream));
-}
-
-int frt_norm_quant_gemm_bf16(const void* residual_in, void* residual_out, const void* x, const void* weight, float eps,
-                             unsigned flags, const void* b, const void* sfb, const void* bias, void* d, int M, int N,
-                             int K, float alpha, void* stream) {
-  if (!x || !b || !sfb || !d) return FRT_E_NULL;
-  if ((residual_in == nullptr) != (residual_out == nullptr)) return FRT_E_NULL;
-  if (M <= 0 || N <= 0 || K <= 0 || K % 64 != 0 || N % 8 != 0) return FRT_E_SHAPE;
-  if (M > 4 || K > 4096) return FRT_E_UNSUPPORTED;     // run the producer and the GEMM as two calls
-  if (flags & ~(FRT_PRODUCER_ONE_PLUS_W | FRT_PRODUCER_ROUND_BF16 | FRT_PRODUCER_RNE_E2M1 |
-                FRT_PRODUCER_NORM_FROM_BF16_RESIDUAL))
-    return FRT_E_UNSUPPORTED;
-  if (residual_in != nullptr && residual_in == residual_out) return FRT_E_UNSUPPORTED;   // every CTA reads the input
-  if (!aligned(x, 16) || !aligned(b, 16) || !aligned(d, 16) || !aligned(bias, 16) || !aligned(sfb, 16) ||
-      !aligned(residual_in, 16) || !aligned(residual_out, 16) || !aligned(weight, 16))
-    return FRT_E_ALIGN;
-  return run_gemm_fused(residual_in, residual_out, x, weight, eps, flags, b, sfb, bias, d, M, N, K, alpha,
-                        as_stream(stream));
 }
 
 int frt_nvfp4_repack_interleaved(const void* b_packed, void* b_interleaved, int N, int K, void* stream) {

@@ -32,7 +32,6 @@ SIGNATURES = {
     "frt_nvfp4_repack_interleaved": (_I, [_P, _P, _I, _I, _P]),
     "frt_nvfp4_gemv_interleaved_bf16": (_I, [_P, _P, _P, _P, _P, _I, _I, _F, _P]),
     "frt_nvfp4_gemm_plan": (_I, [_I, _I, _I, C.POINTER(_I), C.POINTER(_I)]),
-    "frt_norm_quant_gemm_bf16": (_I, [_P, _P, _P, _P, _F, _U, _P, _P, _P, _P, _I, _I, _I, _F, _P]),
     "frt_router_topk_bf16": (_I, [_P, _P, _P, _I, _I, _I, _P]),
     "frt_router_topk_softmax_bf16": (_I, [_P, _P, _P, _P, _I, _I, _I, _P]),
     "frt_moe_quantize_scatter_nvfp4": (_I, [_P, _P, _P, _P, _I, _I, _I, _P]),

@@ -200,20 +200,6 @@ int frt_nvfp4_repack_interleaved(const void* b_packed, void* b_interleaved, int 
 int frt_nvfp4_gemv_interleaved_bf16(const void* a_packed, const void* sfa, const void* b_interleaved,
                                     const void* sfb, void* out, int N, int K, float alpha, void* stream);
 
-/* Decode fusion: d[M, N] = alpha * NVFP4(RMSNorm(residual_in + x) * weight) @ B^T (+ bias) in ONE launch, for
- * M <= 4 token rows and K <= 4096 (FRT_E_UNSUPPORTED otherwise: call the producer and the GEMM).  Every CTA of
- * the weight-streaming GEMM recomputes the rows' norm (arithmetic and summation order of frt_norm_quant_nvfp4,
- * so the activation bytes, and with them d, are the ones the two calls give) and writes its K stages' packed
- * blocks and scale bytes straight into shared memory; the NVFP4 activations never exist in global memory.
- * residual_in / residual_out: both NULL (plain RMSNorm of x) or both given and DISTINCT buffers; residual_out
- * receives bf16(residual_in + x).  weight bf16 [K] or NULL; flags: FRT_PRODUCER_ONE_PLUS_W, _ROUND_BF16,
- * _RNE_E2M1, _NORM_FROM_BF16_RESIDUAL with their meaning in frt_norm_quant_nvfp4.  B, sfb, bias as in
- * frt_nvfp4_gemm_bf16.  Saves a kernel boundary and the activation round trip per norm + linear pair of a
- * decode step.  No reference counterpart (its ops are separate: fp4_fused_ops + fp4_gemm). */
-int frt_norm_quant_gemm_bf16(const void* residual_in, void* residual_out, const void* x, const void* weight, float eps,
-                             unsigned flags, const void* b_packed, const void* sfb, const void* bias, void* d,
-                             int M, int N, int K, float alpha, void* stream);
-
 /* Which kernel configuration frt_nvfp4_gemm_bf16 would run for (M, N, K) on the current
  * device, without launching anything (a host-side query; tests use it to prove which path a
  * shape takes).  *config: 1-3 one CTA per 128-row tile (128 / 256 / 192 columns), 4-6 CTA pair
