@@ -349,7 +349,8 @@ int64_t frt_launch_count(void);
                                        fewer weight tiles than SMs (default), 0 = never,
                                        2..8 = that many CTAs per tile when it divides K / 256   */
 #define FRT_OPT_SMALLM_STAGES   8   /* small-M GEMM: shared-memory ring depth, 0 = default, 2 or 3 =
-                                       shallower rings (more CTAs per SM); for measurements      */
+                                       shallower rings (more CTAs per SM), 8 = the deep ring of the
+                                       64-token form (one CTA per SM); for measurements           */
 #define FRT_OPT_WAIT_LIMIT_LOG2 9   /* log2 of the SM clocks a device-side wait (mbarrier, peer flag) may
                                        spin before the kernel gives up, sets its status bit and returns:
                                        default 31 (about a second), accepted range 20..40            */

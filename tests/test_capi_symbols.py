@@ -59,8 +59,8 @@ def test_gemm_plan_query():
     assert plan(8192, 57344, 8192) == (4, 1)
     assert plan(1, 4096, 4096)[0] == 11 and plan(16, 4096, 4096)[0] == 11
     assert plan(17, 4096, 4096)[0] == 12 and plan(64, 24576, 4096) == (13, 1)
-    assert plan(64, 4096, 4096) == (13, 4) and plan(64, 4096, 12288) == (13, 4)
-    assert plan(64, 6144, 4096) == (13, 1)
+    assert plan(64, 4096, 4096) == (13, 8) and plan(64, 4096, 12288) == (13, 8)
+    assert plan(64, 6144, 4096) == (13, 4)
     assert lib.frt_nvfp4_gemm_plan(4, 100, 64, None, None) == -1
 
 

@@ -67,13 +67,14 @@ def test_decode_sweep_full_layer_shapes(layer, m):
 
 
 def test_64_token_split_k_path(layer):
-    """The 64-token o and down projections (32 weight tiles for 148 SMs) run as clusters of four CTAs that
-    share a tile's K and sum their partials through distributed shared memory; qkv and gate/up run unsplit.
-    The split result is checked against the oracle and against the same kernel with the split turned off."""
+    """The 64-token o and down projections (32 weight tiles for 148 SMs, two CTAs per SM) run as clusters of
+    eight CTAs that share a tile's K and sum their partials through distributed shared memory, qkv (48 tiles)
+    as clusters of four; gate/up runs unsplit.  The split result is checked against the oracle and against the
+    same kernel with the split turned off."""
     n, k, m = layer["n"], layer["k"], 64
     cfg, split = plan(m, n, k)
     assert cfg == 13
-    assert split == (4 if layer["name"] in ("o", "down") else 1)
+    assert split == {"o": 8, "down": 8, "qkv": 4, "gate_up": 1}[layer["name"]]
     ap, sfa = activations(m, k, 77)
     out = gemm(ap, sfa, layer["bp"], layer["sfb"], m, n, k)
     adq = O.dequantize_nvfp4(ap.cpu().numpy(), sf_linear(sfa, m, k))
@@ -218,7 +219,7 @@ def test_interleaved_repack_and_gemv(n, k):
 
 
 # ---- tuning overrides of the small-M form keep the result --------------------------------------------------
-@pytest.mark.parametrize("m,depth,split", [(1, 2, 0), (1, 3, 8), (16, 2, 4), (24, 3, 0), (24, 2, 2), (64, 3, 0), (64, 3, 4)])
+@pytest.mark.parametrize("m,depth,split", [(1, 2, 0), (1, 3, 8), (16, 2, 4), (24, 3, 0), (24, 2, 2), (64, 3, 0), (64, 3, 4), (64, 8, 0), (64, 8, 4)])
 def test_small_m_ring_depth_and_split_overrides(m, depth, split):
     """FRT_OPT_SMALLM_STAGES (shallower shared-memory rings, more CTAs per SM) and a forced FRT_OPT_GEMM_SPLIT_K run
     other instantiations of the weight-streaming kernel; every one must give the oracle's result."""
