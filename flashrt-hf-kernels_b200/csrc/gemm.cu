@@ -1094,8 +1094,11 @@ void select_gemm_config(int P, int Q, int K, bool swap, int requested, int sms, 
     }
     int want = 2 * sms / tiles;                        // two CTAs of these forms fit an SM
     if (want > 8) want = 8;
+    // up to 16 token columns a CTA keeps at least four K stages (o-proj of Qwen3-8B at one token: 4-way
+    // 4.2 us, 8-way 4.8 us); wider tiles at least two (64 tokens: 8-way 8.4 us, 4-way 9.2 us)
+    const int min_stages = bn == 16 ? 4 : 2;
     for (int s = want; s >= 2; --s)
-      if (k_stages % s == 0 && k_stages / s >= 2) { splits = s; break; }
+      if (k_stages % s == 0 && k_stages / s >= min_stages) { splits = s; break; }
     if (bn == 64 && splits < 4) splits = 1;   // 64 token columns: the cross-CTA sum only pays off from 4-way
   }
 }
