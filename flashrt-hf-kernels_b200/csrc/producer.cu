@@ -315,13 +315,21 @@ norm_quant_kernel(const NormParams p) {
   const int64_t idx = static_cast<int64_t>(row) * p.nb + s;
 
   float v[16];
-  uint4 x0 = make_uint4(0, 0, 0, 0), x1 = x0, r0 = x0, r1 = x0;
+  uint4 x0 = make_uint4(0, 0, 0, 0), x1 = x0, r0 = x0, r1 = x0, g0 = x0, g1 = x0;
+  // A few rows (decode): the kernel is a chain of dependent trips to L2, so the norm weight travels with the
+  // activations instead of after the row reduction, and the quantiser divides instead of looking its
+  // reciprocal scale up in a table in global memory (the same IEEE division: identical bytes).
+  const bool few_rows = p.rows <= 16;
   if (ok) {
     x0 = __ldcs(p.x + 2 * idx);
     x1 = __ldcs(p.x + 2 * idx + 1);
     if (HAS_RES) {
       r0 = __ldcs(p.residual + 2 * idx);
       r1 = __ldcs(p.residual + 2 * idx + 1);
+    }
+    if (few_rows && p.weight != nullptr) {
+      g0 = __ldg(p.weight + 2 * s);
+      g1 = __ldg(p.weight + 2 * s + 1);
     }
   }
   unpack8<FP16>(x0, v);
@@ -369,8 +377,12 @@ norm_quant_kernel(const NormParams p) {
   // ---- scale, (round,) quantise, store -------------------------------------
   if (p.weight != nullptr) {
     float g[16];
-    unpack_bf16x8(__ldg(p.weight + 2 * s), g);
-    unpack_bf16x8(__ldg(p.weight + 2 * s + 1), g + 8);
+    if (!few_rows) {
+      g0 = __ldg(p.weight + 2 * s);
+      g1 = __ldg(p.weight + 2 * s + 1);
+    }
+    unpack_bf16x8(g0, g);
+    unpack_bf16x8(g1, g + 8);
     if (p.flags & FRT_PRODUCER_ONE_PLUS_W) {
 #pragma unroll
       for (int j = 0; j < 16; ++j) g[j] = __fadd_rn(1.f, g[j]);
@@ -402,8 +414,9 @@ norm_quant_kernel(const NormParams p) {
   if (QUANT) {
     uint8_t sfb;
     uint2 out;
-    if (p.flags & FRT_PRODUCER_RNE_E2M1) out = quantize_block16<kEncRne>(v, sfb, inv_scale_table());
-    else out = quantize_block16<ENC>(v, sfb, inv_scale_table());
+    const float* lut = few_rows ? nullptr : inv_scale_table();
+    if (p.flags & FRT_PRODUCER_RNE_E2M1) out = quantize_block16<kEncRne>(v, sfb, lut);
+    else out = quantize_block16<ENC>(v, sfb, lut);
     p.packed[idx] = out;
     store_scale(p.sf, row, s, p.nb, p.sf_cols, sfb);
   }
