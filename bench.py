@@ -608,6 +608,7 @@ def moe_measure(capi, dev, peaks, steps, warmup):
     tf = S["flops"] / (ms * 1e-3) / 1e12
     return {"tflops": round(tf, 2), "ms_per_step": round(ms, 5), "routed_rows": rows, "experts": experts,
             "layers": per_layer, "routed_layer_us": routed_us, "gpu_launches": launches,
+            "decode": moe_decode_leg(capi, dev, peaks, S),
             # 309 GFLOP over 620 MB of algorithmic traffic = 500 flop/byte, below the ridge of this GPU
             # (4 x measured bf16 / measured copy bandwidth = 1012 flop/byte): the bound is HBM
             "roofline": {"bound": "hbm", "kernel": "nvfp4_gemm_pair_kernel<grouped> (gate/up + down)",
@@ -620,6 +621,62 @@ def moe_measure(capi, dev, peaks, steps, warmup):
                                          "frac": round(tf / peaks["fp4_burst"], 4)}},
             "what": "router top-k + softmax, routing plan, quantise into expert order, grouped gate/up, SwiGLU->NVFP4, "
                     "grouped down, weighted un-permute = routed_layer_us (11 launches of this library)"}
+
+
+def moe_decode_leg(capi, dev, peaks, S, tokens=(1, 4, 16)):
+    """The two grouped GEMMs at decode sizes: T tokens -> 8 T routed rows, a few rows per expert, so the job is a
+    stream of the chosen experts' weights (the reference's decode-side counterpart is grouped-moe-gemv).  Several
+    routings (different seeds) run in turn inside one CUDA graph so that the experts they touch exceed L2."""
+    L, P = capi.lib(), capi.ptr
+    experts, top_k = S["experts"], MOE["top_k"]
+    out = {}
+    for T in tokens:
+        n_routes = max(4, 16 // T)
+        rows = T * top_k
+        routes = []
+        for r in range(n_routes):
+            g0 = torch.Generator(device=dev).manual_seed(100 + 17 * r + T)
+            logits = torch.randn(T, experts, generator=g0, device=dev).to(torch.bfloat16)
+            idx = torch.empty(T, top_k, dtype=torch.int32, device=dev)
+            val = torch.empty(T, top_k, dtype=torch.float32, device=dev)
+            offs = torch.empty(experts + 1, dtype=torch.int32, device=dev)
+            rop = torch.empty(T, top_k, dtype=torch.int32, device=dev)
+            tor = torch.empty(rows, dtype=torch.int32, device=dev)
+            st = capi.stream_ptr()
+            assert L.frt_router_topk_bf16(P(logits), P(idx), P(val), T, experts, top_k, st) == 0
+            assert L.frt_moe_route_plan(P(idx), T, top_k, experts, P(offs), P(rop), P(tor), st) == 0
+            routes.append(offs)
+        torch.cuda.synchronize()
+        touched = sum(int((o[1:] > o[:-1]).sum().item()) for o in routes) / n_routes     # experts with rows, per step
+        work = torch.empty(int(L.frt_nvfp4_grouped_gemm_workspace_bytes(rows, experts)), dtype=torch.uint8, device=dev)
+        bufs = []
+        for name, n, k, _ap, wp, _asf, wsf, _out in S["layers"]:
+            ap = torch.randint(0, 256, (rows, k // 2), dtype=torch.uint8, device=dev)
+            asf = torch.randint(32, 80, (S["sfb"](rows, k),), dtype=torch.uint8, device=dev)
+            bufs.append((n, k, ap, asf, wp, wsf, torch.empty(rows, n, dtype=torch.bfloat16, device=dev)))
+
+        def steps(st):
+            for offs in routes:
+                for n, k, ap, asf, wp, wsf, o in bufs:
+                    assert L.frt_nvfp4_grouped_gemm_bf16(P(ap), P(asf), P(wp), P(wsf), P(S["alpha"]), P(offs), None, 0, P(o), rows,
+                                                         n, k, experts, n * (k // 2), int(wsf.shape[1]), P(work), st) == 0
+        steps(capi.stream_ptr())
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                steps(capi.stream_ptr())
+        torch.cuda.synchronize()
+        us = event_ms(graph.replay, 20) / n_routes * 1e3
+        wbytes = touched * sum(0.5625 * n * k for n, k, *_ in bufs)
+        out[f"t{T}"] = {"routed_rows": rows, "experts_touched": round(touched, 1), "us_per_step": round(us, 2),
+                        "weight_mb": round(wbytes / 1e6, 1), "weight_stream_gbs": round(wbytes / us / 1e3, 1),
+                        "frac_of_hbm_measured": round(wbytes / us / 1e3 / peaks["hbm_gbs"], 3)}
+        del graph
+    out["what"] = ("grouped gate/up + down (plan + GEMM launches) for T tokens x top-8, several routings per CUDA graph so "
+                   "that the touched experts' weights come from HBM; bytes = weights of the experts that have rows")
+    return out
 
 
 def run_ours(args, rank, world, local_rank):
@@ -1047,7 +1104,8 @@ def run_moe(args, rank, world, local_rank):
                        "layers": {l[0]: [l[1], l[2]] for l in MOE["layers"]},
                        "l2": "weights 340 MB + activations per step exceed the 126 MiB L2"},
             "roofline": r["roofline"],
-            "detail": {"layers": r["layers"], "routed_layer_us": r["routed_layer_us"], "routed_layer": r["what"]},
+            "detail": {"layers": r["layers"], "routed_layer_us": r["routed_layer_us"], "routed_layer": r["what"],
+                       "decode": r.get("decode")},
             "gpu_launches": r["gpu_launches"], "clocks": clocks.summary()}), flush=True)
 
 

@@ -873,6 +873,10 @@ __global__ void group_plan_kernel(const int* __restrict__ offsets, const int* __
                                   int token_major) {
   pdl_launch_dependents();
   pdl_wait();
+  if (gridDim.x == 1) {            // a single CTA resets the list itself (the host skips its memset)
+    if (threadIdx.x == 0) work->count = 0;
+    __syncthreads();
+  }
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (offsets != nullptr) {
     if (i >= num_experts) return;
@@ -970,9 +974,9 @@ int run_grouped_impl(const void* a, const void* sfa, const void* b_stack, const 
   if (int rc = make_output_map(&maps.d, out, rows, N, N)) return rc;
   auto* work = static_cast<GroupWork*>(workspace);
   const int max_items = p.max_items;
-  if (cudaMemsetAsync(work, 0, 16, st) != cudaSuccess) return FRT_E_LAUNCH;
   const int num_tiles = tile_rows > 0 ? rows / tile_rows : 0;
   const int plan_threads = offsets ? experts : num_tiles;
+  if (plan_threads > 256 && cudaMemsetAsync(work, 0, 16, st) != cudaSuccess) return FRT_E_LAUNCH;   // (else the plan's one CTA does it)
   launch_pdl(group_plan_kernel, dim3((plan_threads + 255) / 256), dim3(256), 0, st, static_cast<const int*>(offsets),
              static_cast<const int*>(tile_expert), tile_rows, rows, experts, num_tiles, work, max_items, 0);
   g_launches.fetch_add(1, std::memory_order_relaxed);
@@ -1022,9 +1026,9 @@ int run_grouped_token_major(const void* a, const void* sfa, const void* b_stack,
   if (int rc = make_sf_stack_map(&maps.sfq, sfb_stack, N, p.sf_cols, experts, sfb_stride, L::SFQ_BLOCKS)) return rc;
   if (int rc = make_output_map(&maps.d, out, rows, N, N)) return rc;
   auto* work = static_cast<GroupWork*>(workspace);
-  if (cudaMemsetAsync(work, 0, 16, st) != cudaSuccess) return FRT_E_LAUNCH;
   const int num_tiles = tile_rows > 0 ? rows / tile_rows : 0;
   const int plan_threads = offsets ? experts : num_tiles;
+  if (plan_threads > 256 && cudaMemsetAsync(work, 0, 16, st) != cudaSuccess) return FRT_E_LAUNCH;   // (else the plan's one CTA does it)
   launch_pdl(group_plan_kernel, dim3((plan_threads + 255) / 256), dim3(256), 0, st, static_cast<const int*>(offsets),
              static_cast<const int*>(tile_expert), tile_rows, rows, experts, num_tiles, work, p.max_items, 1);
   g_launches.fetch_add(1, std::memory_order_relaxed);
