@@ -80,6 +80,8 @@ struct GemmParams {
   int group_m;              // raster: tiles walk GROUP_M p-tiles before the next q-tile
   const float* alpha_stack; // grouped: per-expert alpha
   int max_items;            // grouped: capacity of the work list (items beyond it were dropped by the plan)
+  const int* inline_offsets;  // grouped, weight-major: expert offsets [num_experts + 1] when every CTA plans for itself
+  int num_experts;
   int splits;               // split-K cluster size (small-M form), 1 otherwise
   long long wait_limit;     // SM clocks a wait on an mbarrier may take before the CTA gives up
   int p_interleaved;        // P is stored in the interleaved GEMV layout [rows/8][K/64][8][32 B] (4-D tensor map)
@@ -813,10 +815,7 @@ int launch_gemm_splitk(const CUtensorMap& mp, const CUtensorMap& mq, GemmParams&
 // MMA takes that scale address only at even columns.
 // Rows of the window that starts at `start` when the expert's rows end at `hi`: what is left, rounded up to
 // 32, if that is at most 320; else 256.
-__device__ __forceinline__ int window_rows(int start, int hi) {
-  const int rem = hi - start;
-  return rem <= 320 ? (rem + 31) & ~31 : 256;
-}
+__device__ __forceinline__ int window_rows(int start, int hi) { return grouped_window_rows(start, hi); }
 
 __device__ __forceinline__ void emit_windows(GroupWork* work, int max_items, int lo, int hi, int expert) {
   // All windows of one expert take consecutive slots: their tiles then run at about the same
@@ -974,12 +973,18 @@ int run_grouped_impl(const void* a, const void* sfa, const void* b_stack, const 
   if (int rc = make_output_map(&maps.d, out, rows, N, N)) return rc;
   auto* work = static_cast<GroupWork*>(workspace);
   const int max_items = p.max_items;
-  const int num_tiles = tile_rows > 0 ? rows / tile_rows : 0;
-  const int plan_threads = offsets ? experts : num_tiles;
-  if (plan_threads > 256 && cudaMemsetAsync(work, 0, 16, st) != cudaSuccess) return FRT_E_LAUNCH;   // (else the plan's one CTA does it)
-  launch_pdl(group_plan_kernel, dim3((plan_threads + 255) / 256), dim3(256), 0, st, static_cast<const int*>(offsets),
-             static_cast<const int*>(tile_expert), tile_rows, rows, experts, num_tiles, work, max_items, 0);
-  g_launches.fetch_add(1, std::memory_order_relaxed);
+  if (offsets != nullptr && experts <= L::PLAN_EXPERTS) {
+    // per-expert offsets, few enough experts: the GEMM's CTAs derive the window list themselves (one launch)
+    p.inline_offsets = static_cast<const int*>(offsets);
+    p.num_experts = experts;
+  } else {
+    const int num_tiles = tile_rows > 0 ? rows / tile_rows : 0;
+    const int plan_threads = offsets ? experts : num_tiles;
+    if (plan_threads > 256 && cudaMemsetAsync(work, 0, 16, st) != cudaSuccess) return FRT_E_LAUNCH;   // (else the plan's one CTA does it)
+    launch_pdl(group_plan_kernel, dim3((plan_threads + 255) / 256), dim3(256), 0, st, static_cast<const int*>(offsets),
+               static_cast<const int*>(tile_expert), tile_rows, rows, experts, num_tiles, work, max_items, 0);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+  }
   launch_pdl(kern, dim3(2 * (di.sms / 2)), dim3(320), L::TOTAL, st, maps, p, static_cast<const GroupWork*>(work));
   return launch_result();
 }

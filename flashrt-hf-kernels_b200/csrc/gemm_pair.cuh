@@ -72,6 +72,18 @@ __device__ __forceinline__ void decode_unit(int u, const GemmParams& p, int& pt,
   tile_coords(t, p, pt, qt);
 }
 
+// Weight-major windows of one expert's rows [lo, hi): the first starts on the 64-row boundary below lo, every
+// window but the last is 256 rows, and the last takes what is left when that is at most 320 rows.
+__host__ __device__ __forceinline__ int grouped_window_rows(int start, int hi) {
+  const int rem = hi - start;
+  return rem <= 320 ? (rem + 31) & ~31 : 256;
+}
+__host__ __device__ __forceinline__ int grouped_window_count(int lo, int hi) {
+  if (hi <= lo) return 0;
+  const int span = hi - (lo & ~63);
+  return span <= 320 ? 1 : 1 + (span - 320 + 255) / 256;
+}
+
 template <int BN, int STAGES, bool GROUPED = false, bool TM = false>
 struct PairLayout {
 
@@ -89,7 +101,11 @@ struct PairLayout {
   static constexpr int SBUFS = 2;
   static constexpr int STAGING_BYTES = 8 * SBUFS * 2048;
   static constexpr int ITEM_CACHE = GROUPED ? 96 : 0;    // this pair's first work items, copied to smem
-  static constexpr int TOTAL = STAGES * STAGE_BYTES + STAGING_BYTES + ITEM_CACHE * 32 + 1024 + 256;
+  // weight-major grouped form with per-expert offsets: every CTA builds the window list itself (prefix of the
+  // experts' window counts), so a call is one launch
+  static constexpr int PLAN_EXPERTS = 256;
+  static constexpr int PLAN_BYTES = (GROUPED && !TM) ? (PLAN_EXPERTS + 4) * 4 : 0;
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + STAGING_BYTES + ITEM_CACHE * 32 + PLAN_BYTES + 1024 + 256;
   static constexpr int SF_COLS = KT_PER_STAGE * (4 + SFQ_BLOCKS * 4);
   // accumulator placement: disjoint when they fit, else overlapping by OVERLAP columns
   static constexpr int ACC1 = (2 * BN + SF_COLS <= 512) ? BN : 512 - SF_COLS - BN;
@@ -146,7 +162,8 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* staging = smem + STAGES * L::STAGE_BYTES;
   GroupItem* item_cache = reinterpret_cast<GroupItem*>(staging + L::STAGING_BYTES);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + L::STAGING_BYTES + L::ITEM_CACHE * 32);
+  int* win_pre = reinterpret_cast<int*>(staging + L::STAGING_BYTES + L::ITEM_CACHE * 32);   // [experts + 1] windows before expert e
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + L::STAGING_BYTES + L::ITEM_CACHE * 32 + L::PLAN_BYTES);
   uint64_t* full = bars;                    // [STAGES] used in the leader: both CTAs' TMA bytes
   uint64_t* empty = bars + STAGES;          // [STAGES] in each CTA: multicast commit from the leader
   uint64_t* acc_full = bars + 2 * STAGES;   // [2] in each CTA: multicast commit from the leader
@@ -185,7 +202,58 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
     ptx::tmem_relinquish_pair();
   }
   pdl_wait();                 // everything above overlapped the previous kernel; global memory from here on
-  if (GROUPED_ANY) {
+  // item j of the inline plan: the expert whose windows contain j (binary search in the prefix), then the window
+  auto make_item = [&](int j) {
+    int e0 = 0, e1 = p.num_experts;               // win_pre[e0] <= j < win_pre[e1]
+    while (e1 - e0 > 1) {
+      const int mid = (e0 + e1) >> 1;
+      if (win_pre[mid] <= j) e0 = mid; else e1 = mid;
+    }
+    const int lo = max(0, min(p.inline_offsets[e0], p.Q)), hi = max(0, min(p.inline_offsets[e0 + 1], p.Q));
+    const int start = (lo & ~63) + 256 * (j - win_pre[e0]);
+    GroupItem it{};
+    it.q_row0 = start; it.n_tokens = grouped_window_rows(start, hi);
+    it.lo = max(lo, start); it.hi = min(hi, start + it.n_tokens);
+    it.expert = e0;
+    return it;
+  };
+  const bool inline_plan = GROUPED && p.inline_offsets != nullptr;
+  if (inline_plan) {
+    // windows per expert, then their exclusive prefix (one warp, consecutive experts per lane)
+    for (int e = threadIdx.x; e < p.num_experts; e += blockDim.x)
+      win_pre[e + 1] = grouped_window_count(max(0, min(p.inline_offsets[e], p.Q)), max(0, min(p.inline_offsets[e + 1], p.Q)));
+    if (threadIdx.x == 0) win_pre[0] = 0;
+    __syncthreads();
+    if (warp == 0) {
+      const int per = (p.num_experts + 31) / 32, first = lane * per;
+      int sum = 0;
+      for (int i = 0; i < per; ++i) sum += first + i < p.num_experts ? win_pre[first + i + 1] : 0;
+      int incl = sum;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+      }
+      int run = incl - sum;                        // windows before this lane's experts
+      for (int i = 0; i < per; ++i) {
+        if (first + i < p.num_experts) {
+          run += win_pre[first + i + 1];
+          win_pre[first + i + 1] = run;
+        }
+      }
+    }
+    __syncthreads();
+    int items = win_pre[p.num_experts];
+    if (items > p.max_items) {                     // offsets that claim more rows than exist: cut short, and say so
+      if (threadIdx.x == 0 && blockIdx.x == 0) atomicOr(&g_status_word, 0x200u);
+      items = p.max_items;
+    }
+    total_tiles = items * per_item;
+    for (int i = threadIdx.x; i < L::ITEM_CACHE; i += blockDim.x) {
+      const int t = pair_id + i * num_pairs;
+      if (t < total_tiles) item_cache[i] = make_item(t / per_item);
+    }
+  } else if (GROUPED_ANY) {
     total_tiles = min(work->count, p.max_items) * per_item;   // the plan never stores beyond max_items
     // tile i of this pair is global tile pair_id + i * num_pairs; its item is items[tile / per_item]
     for (int i = threadIdx.x; i < L::ITEM_CACHE; i += blockDim.x) {
@@ -193,6 +261,8 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
       if (t < total_tiles) item_cache[i] = work->items[t / per_item];
     }
   }
+  // an item beyond the cached ones (weight-major form)
+  auto far_item = [&](int t) { return inline_plan ? make_item(t / p.p_tiles) : work->items[t / p.p_tiles]; };
   ptx::tc_fence_before();
   __syncthreads();
   // both CTAs' barriers must be initialised before either signals the other
@@ -224,7 +294,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
           expert = item.expert;
           pt = 0;
         } else if (GROUPED) {
-          const GroupItem item = ti < L::ITEM_CACHE ? item_cache[ti] : work->items[t / p.p_tiles];
+          const GroupItem item = ti < L::ITEM_CACHE ? item_cache[ti] : far_item(t);
           pt = t % p.p_tiles;
           const int main_n = min(item.n_tokens, 256), extra_n = item.n_tokens - main_n;
           q_row = item.q_row0 + static_cast<int>(rank) * (main_n >> 1);
@@ -341,7 +411,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
         if (TM) {
           qoff = (static_cast<uint32_t>((t % per_item) * BN) & 127u) >> 5;
         } else if (GROUPED) {
-          const GroupItem item = tl < L::ITEM_CACHE ? item_cache[tl] : work->items[t / p.p_tiles];
+          const GroupItem item = tl < L::ITEM_CACHE ? item_cache[tl] : far_item(t);
           qoff = (static_cast<uint32_t>(item.q_row0) & 127u) >> 5;
           const int main_n = min(item.n_tokens, 256);
           idesc = ptx::idesc_nvf4(256, main_n);
@@ -432,7 +502,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
         tm_any = blk >= 0 && tm_row0 < item.hi && tm_row0 + 32 > item.lo;
         tm_all = blk >= 0 && tm_row0 >= item.lo && tm_row0 + 32 <= item.hi;
       } else if (GROUPED) {
-        item = tl < L::ITEM_CACHE ? item_cache[tl] : work->items[t / p.p_tiles];
+        item = tl < L::ITEM_CACHE ? item_cache[tl] : far_item(t);
         pt = t % p.p_tiles;
         alpha = p.alpha_stack[item.expert];
       } else if (SLICED) {
@@ -519,7 +589,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ PairMaps maps, const GemmParams p
         const int nch = item.n_tokens >> 5;
         int shared = 0;
         if (t + num_pairs < total_tiles) {
-          const int n_next = (tl + 1 < L::ITEM_CACHE ? item_cache[tl + 1] : work->items[(t + num_pairs) / p.p_tiles]).n_tokens;
+          const int n_next = (tl + 1 < L::ITEM_CACHE ? item_cache[tl + 1] : far_item(t + num_pairs)).n_tokens;
           shared = max(0, (item.n_tokens + n_next - L::ACC_COLS) >> 5);
         }
         const int my_n = (nch - half + 1) >> 1;                       // drain positions half, half + 2, ...
