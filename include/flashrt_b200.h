@@ -247,6 +247,9 @@ int frt_nvfp4_gemm_swiglu_nvfp4(const void* a_packed, const void* sfa, const voi
  * tile_expert pattern (16-row tiles of alternating experts included).  Offsets that overlap or
  * decrease describe more rows than exist; windows that do not fit are dropped, never written past
  * the buffer, and bit 0x200 of the status word (frt_device_status) reports it.
+ * (With expert_offsets and num_experts <= 256 the GEMM's CTAs derive the windows themselves and the call is
+ * one launch that does not touch `work`; the same limit on the number of windows applies.  Pass the buffer
+ * all the same: the tile_expert description and larger expert counts use it.)
  * replaces moe_blocktile_mma_sm120_bf16 / moe_m64_mma_sm120_bf16 / moe_m16_mma_sm120_bf16,
  *   grouped-moe-gemm/csrc/moe_blocktile_mma_sm120.cuh */
 int64_t frt_nvfp4_grouped_gemm_workspace_bytes(int rows, int num_experts);
