@@ -129,6 +129,23 @@ class NormQuant(nn.Module):
         return out
 
 
+class KernelNorm(nn.Module):
+    """A plain (or 1 + weight) RMSNorm over the last dimension as ONE kernel, for the norms that feed no NVFP4
+    projection: the per-head q / k norms of Qwen3-style attention.  Eager `transformers` runs such a norm as half
+    a dozen elementwise kernels with an fp32 intermediate."""
+
+    def __init__(self, weight: torch.Tensor, eps: float, one_plus_weight: bool = False):
+        super().__init__()
+        w = weight.detach().float()
+        self.register_buffer("weight", (1.0 + w if one_plus_weight else w).to(torch.bfloat16).contiguous(), persistent=False)
+        self.variance_epsilon = float(eps)
+
+    def forward(self, hidden_states: torch.Tensor) -> torch.Tensor:
+        shape = hidden_states.shape
+        x = hidden_states.to(torch.bfloat16).contiguous().view(-1, shape[-1])
+        return _norm.rms_norm_bf16(x, self.weight, self.variance_epsilon).view(shape)
+
+
 class FinalNorm(nn.Module):
     """The model's last norm: adds the pending residual of the last fused decoder layer in the norm kernel."""
 
@@ -315,6 +332,12 @@ def convert_decoder_model(model: nn.Module, *, fuse: bool = True, fuse_residual:
                 attn_src = nq.produced
             else:
                 mlp_src = nq.produced
+        for attr in ("q_norm", "k_norm"):             # per-head norms (Qwen3): one kernel each instead of eager arithmetic
+            n = getattr(attn, attr, None)
+            kind = _norm_semantics(n) if (fuse and n is not None and not skipped(n)) else None
+            if kind is not None and n.weight.numel() % 16 == 0:
+                setattr(attn, attr, KernelNorm(n.weight.data, getattr(n, "variance_epsilon", getattr(n, "eps", 1e-6)),
+                                               kind == "one_plus"))
         q, k, v, o = (getattr(attn, n, None) for n in ("q_proj", "k_proj", "v_proj", "o_proj"))
         qkv_ok = all(isinstance(l, nn.Linear) and not skipped(l) for l in (q, k, v))
         if (fuse and qkv_ok and len({l.bias is None for l in (q, k, v)}) == 1
