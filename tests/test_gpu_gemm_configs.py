@@ -261,3 +261,26 @@ def test_bounded_wait_runs_out_and_the_context_stays_usable():
     out = gemm(ap, sfa, bp, sfb, m, n, k)
     check(out, O.gemm_bf16(ap.cpu().numpy(), sf_linear(sfa, m, k), bp.cpu().numpy(), sf_linear(sfb, n, k)))
     assert device_status() == 0
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 4096, 4096), (3, 6144, 4096), (16, 4096, 12288), (64, 4096, 12288)])
+def test_split_k_results_are_bit_stable_over_repeated_launches(m, n, k):
+    """The cluster split-K forms (partials pushed to the owning CTA up to 16 token columns, pulled between two
+    cluster barriers above) add their partials in rank order: 100 back-to-back launches into a poisoned output give
+    the same bytes every time (a race in the exchange would not)."""
+    assert plan(m, n, k)[1] > 1
+    g = torch.Generator().manual_seed(m + n + k)
+    ap = torch.randint(0, 256, (m, k // 2), generator=g, dtype=torch.uint8).to(DEV)
+    bp = torch.randint(0, 256, (n, k // 2), generator=g, dtype=torch.uint8).to(DEV)
+    L = capi.lib()
+    sfa = torch.randint(32, 80, (int(L.frt_nvfp4_sf_swizzled_bytes(m, k)),), generator=g, dtype=torch.uint8).to(DEV)
+    sfb = torch.randint(32, 80, (int(L.frt_nvfp4_sf_swizzled_bytes(n, k)),), generator=g, dtype=torch.uint8).to(DEV)
+    ref = gemm(ap, sfa, bp, sfb, m, n, k).clone()
+    out = torch.empty_like(ref)
+    for it in range(100):
+        out.fill_(7.0)
+        gemm(ap, sfa, bp, sfb, m, n, k, out=out)
+        if it % 25 == 24:
+            torch.cuda.synchronize()
+            assert torch.equal(out, ref)
+    assert device_status() == 0
