@@ -305,7 +305,7 @@ norm_quant_kernel(const NormParams p) {
   pdl_wait();
   constexpr int CTA = TPR > 256 ? TPR : 256;
   constexpr int ROWS_PER_CTA = CTA / TPR;
-  constexpr int WPR = TPR / 32;                       // warps per row
+  constexpr int WPR = TPR >= 32 ? TPR / 32 : 1;       // warps per row (TPR = 8, 16: several rows per warp)
   __shared__ float warp_sums[CTA / 32];
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
@@ -360,8 +360,10 @@ norm_quant_kernel(const NormParams p) {
   }
 
   // ---- row reduction -------------------------------------------------------
+  // (rows of at most 8 / 16 blocks share a warp: the butterfly stays inside the row's aligned group of lanes;
+  // the offsets it skips would only add the zeros of lanes that own no block, so the sum is the same bits)
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) part = __fadd_rn(part, __shfl_xor_sync(0xffffffffu, part, o));
+  for (int o = TPR >= 32 ? 16 : TPR / 2; o > 0; o >>= 1) part = __fadd_rn(part, __shfl_xor_sync(0xffffffffu, part, o));
   float ssq = part;
   if (WPR > 1) {
     if (lane == 0) warp_sums[warp] = part;
@@ -718,7 +720,7 @@ int launch_norm(const NormParams& p, bool has_res, bool quant, cudaStream_t st) 
   // warps per SM hide the latency by themselves); for wider rows the CTA-wide barrier of a
   // 512/1024-thread CTA stalls the SM and the staged persistent form is 15-35 % faster.
   // FRT_OPT_NORM_FORM forces one form or the other (tests run every case on both).
-  const bool stream = p.out_fp8 == nullptr &&
+  const bool stream = p.out_fp8 == nullptr && TPR >= 32 &&       // (rows that share a warp: the one-CTA form only)
                       (g_opt_norm_form == 2 || (g_opt_norm_form != 1 && TPR > (quant ? 256 : 512)));
   if (!stream) {
     constexpr int CTA = TPR > 256 ? TPR : 256;
@@ -749,6 +751,8 @@ int launch_norm(const NormParams& p, bool has_res, bool quant, cudaStream_t st) 
 
 int dispatch_norm(NormParams& p, bool has_res, bool quant, cudaStream_t st) {
   const int nb = p.nb;
+  if (nb <= 8) return launch_norm<8>(p, has_res, quant, st);       // per-head norms (dim 128): four rows per warp
+  if (nb <= 16) return launch_norm<16>(p, has_res, quant, st);
   if (nb <= 32) return launch_norm<32>(p, has_res, quant, st);
   if (nb <= 64) return launch_norm<64>(p, has_res, quant, st);
   if (nb <= 128) return launch_norm<128>(p, has_res, quant, st);

@@ -140,7 +140,7 @@ def test_dequantize_exact():
     assert torch.equal(out.cpu().view(torch.int16), want.view(torch.int16))      # exact, signed zeros included
 
 
-CASES = [(1, 1024), (16, 128), (63, 2048), (128, 4096), (257, 4096), (33, 5120), (9, 8192), (5, 12288), (3, 16384)]
+CASES = [(1, 1024), (16, 128), (131, 128), (37, 256), (100, 64), (45, 192), (63, 2048), (128, 4096), (257, 4096), (33, 5120), (9, 8192), (5, 12288), (3, 16384)]
 
 # The norm kernels exist in two forms (one CTA per row group; persistent CTAs fed by bulk
 # copies); the library picks one by row width.  FRT_OPT_NORM_FORM (key 5) forces each form, so
