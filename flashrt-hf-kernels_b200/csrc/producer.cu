@@ -749,6 +749,48 @@ int launch_norm(const NormParams& p, bool has_res, bool quant, cudaStream_t st) 
                  : launch_norm_stream<TPR, false, true, kEncHw>(p, st);
 }
 
+// Per-head RMSNorm in place over the heads of a stacked projection output (the q and k heads of a fused q/k/v
+// GEMM): row (token, head) is head_dim contiguous elements at token * row_pitch + head * head_dim; heads
+// [0, heads_a) take weight_a, the next heads_b take weight_b.  Arithmetic and summation order of the plain
+// rms_norm path above (a thread per 16-element block, butterfly inside the row's LPR lanes), so each head equals
+// frt_rms_norm_bf16 of its contiguous copy bit for bit; one launch instead of two copies and two norms.
+template <int LPR>
+__global__ void __launch_bounds__(256)
+head_norm_kernel(uint4* __restrict__ x, int tokens, int pitch_blocks, int heads_a, int heads_b,
+                 const uint4* __restrict__ wa, const uint4* __restrict__ wb, float eps, float dim_f) {
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int ROWS = 256 / LPR;
+  const int heads = heads_a + heads_b;
+  const int64_t r = static_cast<int64_t>(blockIdx.x) * ROWS + threadIdx.x / LPR;
+  const int s = threadIdx.x % LPR;
+  const bool ok = r < static_cast<int64_t>(tokens) * heads;
+  const int token = ok ? static_cast<int>(r / heads) : 0, head = ok ? static_cast<int>(r % heads) : 0;
+  uint4* px = x + 2 * (static_cast<int64_t>(token) * pitch_blocks + head * LPR + s);
+  float v[16];
+  uint4 x0 = make_uint4(0, 0, 0, 0), x1 = x0;
+  if (ok) { x0 = px[0]; x1 = px[1]; }
+  unpack_bf16x8(x0, v);
+  unpack_bf16x8(x1, v + 8);
+  float part = 0.f;
+#pragma unroll
+  for (int j = 0; j < 16; ++j) part = __fadd_rn(part, __fmul_rn(v[j], v[j]));
+#pragma unroll
+  for (int o = LPR / 2; o > 0; o >>= 1) part = __fadd_rn(part, __shfl_xor_sync(0xffffffffu, part, o));
+  if (!ok) return;
+  const float rstd = __frsqrt_rn(__fadd_rn(__fdiv_rn(part, dim_f), eps));
+  const uint4* w = head < heads_a ? wa : wb;
+  float g[16];
+  unpack_bf16x8(__ldg(w + 2 * s), g);
+  unpack_bf16x8(__ldg(w + 2 * s + 1), g + 8);
+#pragma unroll
+  for (int j = 0; j < 16; ++j) v[j] = __fmul_rn(__fmul_rn(v[j], rstd), g[j]);
+  uint4 o0, o1;
+  pack16_bf16(v, o0, o1);
+  px[0] = o0;
+  px[1] = o1;
+}
+
 int dispatch_norm(NormParams& p, bool has_res, bool quant, cudaStream_t st) {
   const int nb = p.nb;
   if (nb <= 8) return launch_norm<8>(p, has_res, quant, st);       // per-head norms (dim 128): four rows per warp
@@ -964,6 +1006,32 @@ int frt_rms_norm_bf16(const void* x, const void* weight, void* out, int rows, in
   p.rows = rows; p.nb = dim / 16; p.sf_cols = (dim + 63) / 64;
   p.eps = eps; p.inv_global_scale = 1.0f; p.dim_f = static_cast<float>(dim);
   return dispatch_norm(p, false, false, as_stream(stream));
+}
+
+int frt_rms_norm_heads_bf16(void* x, int tokens, int row_pitch, int head_dim, int heads_a, const void* weight_a,
+                            int heads_b, const void* weight_b, float eps, void* stream) {
+  if (!x || !weight_a || (heads_b > 0 && !weight_b)) return FRT_E_NULL;
+  if (tokens <= 0 || heads_a <= 0 || heads_b < 0 || row_pitch <= 0 || row_pitch % 8 != 0 ||
+      static_cast<int64_t>(heads_a + heads_b) * head_dim > row_pitch)
+    return FRT_E_SHAPE;
+  if (head_dim != 64 && head_dim != 128 && head_dim != 256 && head_dim != 512) return FRT_E_UNSUPPORTED;
+  if (row_pitch % 16 != 0) return FRT_E_SHAPE;
+  if (!aligned(x, 16) || !aligned(weight_a, 16) || !aligned(weight_b, 16)) return FRT_E_ALIGN;
+  const int lpr = head_dim / 16;
+  const int64_t rows = static_cast<int64_t>(tokens) * (heads_a + heads_b);
+  const dim3 grid(static_cast<unsigned>((rows + 256 / lpr - 1) / (256 / lpr))), block(256);
+  auto xs = static_cast<uint4*>(x);
+  auto wa = static_cast<const uint4*>(weight_a);
+  auto wb = static_cast<const uint4*>(weight_b ? weight_b : weight_a);
+  const cudaStream_t st = as_stream(stream);
+  const float dim_f = static_cast<float>(head_dim);
+  switch (lpr) {
+    case 4: launch_pdl(head_norm_kernel<4>, grid, block, 0, st, xs, tokens, row_pitch / 16, heads_a, heads_b, wa, wb, eps, dim_f); break;
+    case 8: launch_pdl(head_norm_kernel<8>, grid, block, 0, st, xs, tokens, row_pitch / 16, heads_a, heads_b, wa, wb, eps, dim_f); break;
+    case 16: launch_pdl(head_norm_kernel<16>, grid, block, 0, st, xs, tokens, row_pitch / 16, heads_a, heads_b, wa, wb, eps, dim_f); break;
+    default: launch_pdl(head_norm_kernel<32>, grid, block, 0, st, xs, tokens, row_pitch / 16, heads_a, heads_b, wa, wb, eps, dim_f); break;
+  }
+  return launch_result();
 }
 
 int frt_layer_norm_bf16(const void* x, const void* weight, const void* bias, void* out, int rows, int dim, float eps,

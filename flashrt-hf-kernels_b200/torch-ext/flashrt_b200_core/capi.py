@@ -23,6 +23,7 @@ SIGNATURES = {
     "frt_nvfp4_quantize_mse": (_I, [_P, _I, _P, _P, _I, _I, _P]),
     "frt_nvfp4_dequantize_fp16": (_I, [_P, _P, _P, _I, _I, _P]),
     "frt_rms_norm_bf16": (_I, [_P, _P, _P, _I, _I, _F, _P]),
+    "frt_rms_norm_heads_bf16": (_I, [_P, _I, _I, _I, _I, _P, _I, _P, _F, _P]),
     "frt_residual_add_rms_norm_bf16": (_I, [_P, _P, _P, _P, _I, _I, _F, _P]),
     "frt_norm_quant_nvfp4": (_I, [_P, _P, _P, _F, _F, _P, _P, _P, _I, _I, _U, _P]),
     "frt_norm_quant_nvfp4_bcast": (_I, [_P, _P, _P, _F, _F, _P, _P, C.POINTER(_P), C.POINTER(_P), _I, _I, _I, _I, _U, _P,

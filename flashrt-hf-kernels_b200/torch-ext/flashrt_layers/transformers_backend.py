@@ -146,6 +146,41 @@ class KernelNorm(nn.Module):
         return _norm.rms_norm_bf16(x, self.weight, self.variance_epsilon).view(shape)
 
 
+class StackedHeadNorm(KernelNorm):
+    """q_norm / k_norm of an attention whose q, k and v come from one `StackedProjection`: when q_norm is called on
+    the q slice of the stacked output, ONE kernel normalises the q heads and the k heads in place in that buffer;
+    k_norm, called next on the k slice of the same buffer, returns it as it is.  Any other input (another tensor,
+    another order) takes the plain one-kernel norm of `KernelNorm`."""
+
+    def __init__(self, weight, eps, one_plus_weight, stacked, is_q: bool):
+        super().__init__(weight, eps, one_plus_weight)
+        self.__dict__["stacked"] = stacked                     # not a submodule: it lives at q_proj
+        self.is_q = is_q
+        self.__dict__["partner"] = None                        # the other norm of the pair
+
+    def forward(self, hidden_states: torch.Tensor) -> torch.Tensor:
+        st, other = self.stacked, self.partner
+        buf = st.last_out
+        head_dim = self.weight.numel()
+        if self.is_q:
+            st.__dict__["heads_normed"] = None
+            wq, wk = st.widths[0], st.widths[1]
+            if (buf is not None and other is not None and buf.is_contiguous() and hidden_states.shape[-1] == head_dim
+                    and hidden_states.data_ptr() == buf.data_ptr() and hidden_states.numel() == buf.numel() // buf.shape[-1] * wq
+                    and wq % head_dim == 0 and wk % head_dim == 0 and other.weight.numel() == head_dim
+                    and other.variance_epsilon == self.variance_epsilon and head_dim in (64, 128, 256, 512)):
+                _norm.rms_norm_heads_bf16_(buf.view(-1, buf.shape[-1]), self.weight, wq // head_dim, other.weight,
+                                           wk // head_dim, head_dim, self.variance_epsilon)
+                st.__dict__["heads_normed"] = buf
+                return hidden_states
+            return super().forward(hidden_states)
+        done = st.__dict__.get("heads_normed")
+        if done is not None and hidden_states.data_ptr() == done.data_ptr() + 2 * st.widths[0]:
+            st.__dict__["heads_normed"] = None
+            return hidden_states
+        return super().forward(hidden_states)
+
+
 class FinalNorm(nn.Module):
     """The model's last norm: adds the pending residual of the last fused decoder layer in the norm kernel."""
 
@@ -346,6 +381,12 @@ def convert_decoder_model(model: nn.Module, *, fuse: bool = True, fuse_residual:
             attn.k_proj = ProjectionSlice(attn.q_proj, 1)
             attn.v_proj = ProjectionSlice(attn.q_proj, 2)
             replaced += 3
+            qn, kn = getattr(attn, "q_norm", None), getattr(attn, "k_norm", None)
+            if type(qn) is KernelNorm and type(kn) is KernelNorm:    # one kernel for both head norms
+                sq = StackedHeadNorm(qn.weight, qn.variance_epsilon, False, attn.q_proj, True)
+                sk = StackedHeadNorm(kn.weight, kn.variance_epsilon, False, attn.q_proj, False)
+                sq.__dict__["partner"], sk.__dict__["partner"] = sk, sq
+                attn.q_norm, attn.k_norm = sq, sk
         else:
             for name, lin in (("q_proj", q), ("k_proj", k), ("v_proj", v)):
                 if isinstance(lin, nn.Linear) and not skipped(lin):

@@ -95,5 +95,20 @@ def residual_add_rms_norm_bf16(residual, x, weight, eps: float = 1e-6, out=None)
     return out
 
 
-__all__ = ["layer_norm_bf16", "residual_add_rms_norm_quant_fp8_static_bf16", "rms_norm_quant_fp8_static_bf16",
+@torch.library.register_fake(add_op_namespace_prefix("rms_norm_heads_bf16_"))
+def _rms_norm_heads_fake(x, weight_a, heads_a, weight_b, heads_b, head_dim, eps) -> None:
+    if x.dim() != 2 or (heads_a + heads_b) * head_dim > x.shape[1]:
+        raise RuntimeError("x must be (tokens, width) with room for the heads")
+    return None
+
+
+def rms_norm_heads_bf16_(x, weight_a, heads_a: int, weight_b=None, heads_b: int = 0, head_dim: int = 128,
+                         eps: float = 1e-6):
+    """Per-head RMSNorm in place over the leading heads of every row of `x` (tokens, width; unit inner stride): the q
+    and k heads of a stacked q/k/v projection output in one launch.  Extension of this build."""
+    ops.rms_norm_heads_bf16_(x, weight_a, int(heads_a), weight_b, int(heads_b), int(head_dim), float(eps))
+    return x
+
+
+__all__ = ["rms_norm_heads_bf16_", "layer_norm_bf16", "residual_add_rms_norm_quant_fp8_static_bf16", "rms_norm_quant_fp8_static_bf16",
            "rms_norm_bf16", "residual_add_rms_norm_bf16"]

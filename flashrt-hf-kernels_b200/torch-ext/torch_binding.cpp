@@ -312,6 +312,30 @@ void rms_norm_bf16(const Tensor& x, const Tensor& weight, double eps, Tensor& ou
   check_rc(frt_rms_norm_bf16(x.data_ptr(), weight.data_ptr(), out.data_ptr(), as_int(x.size(0), "rows"),
                              as_int(x.size(1), "dim"), static_cast<float>(eps), stream_of(x)), "rms_norm_bf16");
 }
+// x: bf16 [tokens, width], unit stride along width (a stacked q/k/v projection output); normalises heads
+// [0, heads_a + heads_b) of every row in place (extension of this build: no reference schema)
+void rms_norm_heads_bf16_(Tensor& x, const Tensor& weight_a, int64_t heads_a, const c10::optional<Tensor>& weight_b,
+                          int64_t heads_b, int64_t head_dim, double eps) {
+  check_dtype(x, torch::kBFloat16, "x", "torch.bfloat16");
+  check_dtype(weight_a, torch::kBFloat16, "weight_a", "torch.bfloat16");
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.stride(1) == 1, "x must be a CUDA (tokens, width) tensor with unit inner stride");
+  TORCH_CHECK(weight_a.is_contiguous() && weight_a.dim() == 1 && weight_a.size(0) == head_dim, "weight_a must have shape (head_dim,)");
+  TORCH_CHECK((heads_a + heads_b) * head_dim <= x.size(1), "the heads do not fit the row");
+  const void* wb = nullptr;
+  if (heads_b > 0) {
+    TORCH_CHECK(weight_b.has_value(), "weight_b is required when heads_b > 0");
+    check_dtype(*weight_b, torch::kBFloat16, "weight_b", "torch.bfloat16");
+    TORCH_CHECK(weight_b->is_contiguous() && weight_b->dim() == 1 && weight_b->size(0) == head_dim, "weight_b must have shape (head_dim,)");
+    check_same_device(x, *weight_b, "x", "weight_b");
+    wb = weight_b->data_ptr();
+  }
+  check_same_device(x, weight_a, "x", "weight_a");
+  c10::cuda::CUDAGuard guard(x.device());
+  check_rc(frt_rms_norm_heads_bf16(x.data_ptr(), as_int(x.size(0), "tokens"), as_int(x.stride(0), "row pitch"),
+                                   as_int(head_dim, "head_dim"), as_int(heads_a, "heads_a"), weight_a.data_ptr(),
+                                   as_int(heads_b, "heads_b"), wb, static_cast<float>(eps), stream_of(x)),
+           "rms_norm_heads_bf16_");
+}
 void layer_norm_bf16(const Tensor& x, const Tensor& weight, const Tensor& bias, double eps, Tensor& out) {
   check_norm_inputs(x, &weight, &out, "out");
   check_dtype(bias, torch::kBFloat16, "bias", "torch.bfloat16");
@@ -663,6 +687,8 @@ TORCH_LIBRARY_EXPAND(flashrt_residual_norm_quant_b200, ops) {
   ops.def("residual_add_rms_norm_bf16(Tensor! residual, Tensor x, Tensor weight, float eps, Tensor! out) -> ()");
   ops.impl("rms_norm_bf16", torch::kCUDA, &rms_norm_bf16);
   ops.impl("residual_add_rms_norm_bf16", torch::kCUDA, &residual_add_rms_norm_bf16);
+  ops.def("rms_norm_heads_bf16_(Tensor! x, Tensor weight_a, int heads_a, Tensor? weight_b, int heads_b, int head_dim, float eps) -> ()");
+  ops.impl("rms_norm_heads_bf16_", torch::kCUDA, &rms_norm_heads_bf16_);
   ops.def("layer_norm_bf16(Tensor x, Tensor weight, Tensor bias, float eps, Tensor! out) -> ()");
   ops.def("rms_norm_quant_fp8_static_bf16(Tensor x, Tensor weight, Tensor scale, float eps, Tensor! out) -> ()");
   ops.def("residual_add_rms_norm_quant_fp8_static_bf16(Tensor! residual, Tensor x, Tensor weight, Tensor scale, float eps, Tensor! out) -> ()");

@@ -84,6 +84,15 @@ int frt_nvfp4_dequantize_fp16(const void* packed, const void* sf_swizzled, void*
 int frt_rms_norm_bf16(const void* x, const void* weight, void* out,
                       int rows, int dim, float eps, void* stream);
 
+/* Per-head RMSNorm IN PLACE over the leading heads of a stacked projection output (the q and k heads of one
+ * q/k/v GEMM): head h of token t is head_dim contiguous elements at x + t * row_pitch + h * head_dim (elements);
+ * heads [0, heads_a) use weight_a [head_dim], the next heads_b use weight_b (NULL when heads_b == 0); what lies
+ * beyond them in the row (the v heads) is untouched.  head_dim in {64, 128, 256, 512}; row_pitch % 16 == 0.
+ * Each head equals frt_rms_norm_bf16 of its contiguous copy bit for bit.  The reference runs such norms through
+ * its kernelize RMSNorm layer, one launch per norm after a copy (demos/space/transformers-qwen3/flashrt_kernelize.py:19-40). */
+int frt_rms_norm_heads_bf16(void* x, int tokens, int row_pitch, int head_dim, int heads_a, const void* weight_a,
+                            int heads_b, const void* weight_b, float eps, void* stream);
+
 /* residual <- bf16(residual + x) in place; rstd from the fp32 sums; the
  * output pass uses the rounded bf16 residual.
  * replaces residual_add_rms_norm_bf16, flashrt-residual-norm-quant/csrc/residual_norm_quant.cuh:48 */

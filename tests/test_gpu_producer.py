@@ -390,3 +390,31 @@ def test_fp16_residual_norm_quant(rows, dim):
     res2 = r.to(DEV).clone()
     p2, s2 = fp4_fused_ops.residual_add_rms_norm_fp4_sfa_v2_fp16(res2, x.to(DEV))
     assert torch.equal(p2, packed) and torch.equal(res2, res)
+
+
+@pytest.mark.parametrize("tokens,heads_a,heads_b,head_dim,extra", [(37, 32, 8, 128, 1024), (5, 4, 0, 64, 0), (130, 3, 2, 256, 48),
+                                                                   (9, 2, 2, 512, 512)])
+def test_rms_norm_heads_in_place_equals_per_head_norm(tokens, heads_a, heads_b, head_dim, extra):
+    """frt_rms_norm_heads_bf16 (the q and k heads of a stacked q/k/v output, in place, one launch) against
+    frt_rms_norm_bf16 of each head group's contiguous copy: bit-equal; the columns after the heads stay untouched."""
+    width = (heads_a + heads_b) * head_dim + extra
+    x = randn_bf16((tokens, width), 5 + tokens).to(DEV)
+    wa, wb = randn_bf16((head_dim,), 6, 0.1, 1.0).to(DEV), randn_bf16((head_dim,), 7, 0.1, 1.0).to(DEV)
+    L = capi.lib()
+    want = x.clone()
+    for lo, n, w in ((0, heads_a, wa), (heads_a * head_dim, heads_b, wb)):
+        if n == 0:
+            continue
+        part = x[:, lo:lo + n * head_dim].reshape(tokens * n, head_dim).contiguous()
+        out = torch.empty_like(part)
+        capi.check(L.frt_rms_norm_bf16(P(part), P(w), P(out), tokens * n, head_dim, 1e-6, st()))
+        want[:, lo:lo + n * head_dim] = out.view(tokens, n * head_dim)
+    got = x.clone()
+    capi.check(L.frt_rms_norm_heads_bf16(P(got), tokens, width, head_dim, heads_a, P(wa), heads_b, P(wb) if heads_b else None,
+                                         1e-6, st()))
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)
+    # argument checks
+    assert L.frt_rms_norm_heads_bf16(P(got), tokens, width, 48, 1, P(wa), 0, None, 1e-6, st()) == -4
+    assert L.frt_rms_norm_heads_bf16(P(got), tokens, head_dim, head_dim, heads_a + 1, P(wa), heads_b, P(wb), 1e-6, st()) == -2
+    assert L.frt_rms_norm_heads_bf16(P(got), tokens, width, head_dim, heads_a, P(wa), 1, None, 1e-6, st()) == -1
